@@ -1,0 +1,191 @@
+/*
+ * tfcc_b200.h -- C ABI of the B200 (sm_100a) matmul kernel library for TFCC.
+ *
+ * Every entry point is `extern "C"`, never throws, never exits the process and
+ * returns an int status: 0 on success, a negative TFCCB200_E* code for an
+ * argument problem detected on the host, or a positive cudaError_t value for a
+ * CUDA runtime failure.  Device buffers are plain pointers; all matrices are
+ * contiguous row-major, exactly as TFCC tensors are
+ * (tfcc/core/framework/tfcc_tensor.h:26-56).  Strides between consecutive
+ * batch entries are counted in ELEMENTS and a stride of 0 broadcasts a single
+ * matrix over the batch, which is how the reference backends receive a rank-2
+ * operand next to a batched one
+ * (tfcc/mkl/interfaces/tfcc_mklblasinterface.cpp:127-151,
+ *  tfcc/cuda/interfaces/tfcc_cudablasinterface.cu:201-217).
+ *
+ * Launches are asynchronous on the given stream; nothing here synchronises
+ * unless the comment of the function says so.  The library keeps no mutable
+ * global state besides per-device caches of immutable facts (SM count, driver
+ * entry point for tensor-map encoding).
+ */
+#ifndef TFCC_B200_H_
+#define TFCC_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Exported from the shared library even when it is built with hidden default visibility. */
+#define TFCCB200_API __attribute__((visibility("default")))
+
+/* ---- status codes ------------------------------------------------------- */
+#define TFCCB200_OK 0
+#define TFCCB200_EINVAL -1      /* NULL pointer, zero extent, bad enum value          */
+#define TFCCB200_EALIGN -2      /* a forced kernel path needs an alignment not met     */
+#define TFCCB200_EWORKSPACE -3  /* workspace too small for the chosen kernel           */
+#define TFCCB200_EOVERFLOW -4   /* an element count does not fit the 32-bit TFCC Shape */
+#define TFCCB200_EUNSUPPORTED -5/* forced kernel path cannot run this problem          */
+#define TFCCB200_EDEVICE -6     /* a kernel gave up a bounded wait (see device_status) */
+
+/* ---- precision modes of the fp32 GEMM ----------------------------------- */
+/* FP32:  fp32 result.  Tensor-core tiles split every operand into a TF32 head
+ *        and a TF32 tail and issue three MMAs (head*head, head*tail,
+ *        tail*head); CUDA-core paths use fp32 FMA.  Normwise relative error
+ *        against an fp64 product stays below 1e-5.
+ * TF32:  one MMA per tile on the TF32 heads only (about 1e-3 relative).
+ * Both read and write fp32 buffers. */
+#define TFCCB200_PRECISION_FP32 0
+#define TFCCB200_PRECISION_TF32 1
+
+/* ---- kernel paths (for tests and benchmarks; AUTO is what TFCC uses) ----- */
+#define TFCCB200_PATH_AUTO 0
+#define TFCCB200_PATH_SIMT 1    /* CUDA-core tiled kernel, any shape / alignment          */
+#define TFCCB200_PATH_SKINNY 2  /* M <= 8 streaming kernel, HBM-bound                      */
+#define TFCCB200_PATH_UMMA 3    /* tcgen05 + TMEM + TMA, one CTA per tile                  */
+#define TFCCB200_PATH_UMMA2 4   /* tcgen05 cta_group::2, a pair of CTAs per 256-row tile    */
+
+/* Bits a kernel ORs into *device_status when it abandons a bounded wait.     */
+#define TFCCB200_DEV_TIMEOUT_TMA 0x1
+#define TFCCB200_DEV_TIMEOUT_MMA 0x2
+#define TFCCB200_DEV_TIMEOUT_CONVERT 0x4
+#define TFCCB200_DEV_TIMEOUT_EPILOGUE 0x8
+
+TFCCB200_API const char* tfccb200_strerror(int status);
+
+/* Library version as major*10000 + minor*100 + patch. */
+TFCCB200_API int tfccb200_version(void);
+
+/*
+ * C[b] = A[b] . B[b] (+ bias), fp32, b in [0, batch).
+ *   A: [M,K], B: [K,N], C: [M,N], bias: [N] or NULL.
+ * Replaces CUDABlasInterface<float>::matmul(a,b) and matmul(a,b,c)
+ * (tfcc/cuda/interfaces/tfcc_cudablasinterface.cu:201-248, :251-303) and the
+ * oneDNN calls of MKLBlasInterface<float>
+ * (tfcc/mkl/interfaces/tfcc_mklblasinterface.cpp:41-67, :87-118).  The bias is
+ * added in the epilogue, so C is written once instead of being pre-filled and
+ * accumulated into.
+ *
+ * workspace / workspace_bytes: scratch in device memory of at least
+ * tfccb200_sgemm_workspace() bytes (may be NULL when that returns 0).
+ * device_status: optional int in device memory; kernels OR a TFCCB200_DEV_*
+ * bit into it if a bounded wait runs out.  May be NULL.
+ */
+TFCCB200_API int tfccb200_sgemm(void* stream, const float* A, unsigned strideA, const float* B,
+                   unsigned strideB, float* C, unsigned strideC, const float* bias, unsigned M,
+                   unsigned N, unsigned K, unsigned batch, int precision_mode, void* workspace,
+                   size_t workspace_bytes, int* device_status);
+
+/* Same, with the kernel path forced (TFCCB200_PATH_*).  Used by the parity
+ * tests to exercise every kernel on every shape it accepts. */
+TFCCB200_API int tfccb200_sgemm_ex(void* stream, const float* A, unsigned strideA, const float* B,
+                      unsigned strideB, float* C, unsigned strideC, const float* bias, unsigned M,
+                      unsigned N, unsigned K, unsigned batch, int precision_mode, int path,
+                      void* workspace, size_t workspace_bytes, int* device_status);
+
+/* Scratch bytes tfccb200_sgemm needs for this problem on the current device. */
+TFCCB200_API size_t tfccb200_sgemm_workspace(unsigned M, unsigned N, unsigned K, unsigned batch,
+                                int precision_mode);
+
+/* Which TFCCB200_PATH_* tfccb200_sgemm would take (pointers assumed 16-byte
+ * aligned, as TFCC's allocators guarantee). */
+TFCCB200_API int tfccb200_sgemm_path(unsigned M, unsigned N, unsigned K, unsigned batch, unsigned strideA,
+                        unsigned strideB, int precision_mode);
+
+/*
+ * Quantized matmul, u8 x s8 -> s32 with the zero-point correction fused into
+ * the epilogue:
+ *   C[b][i][j] = sum_k A[b][i][k]*B[b][k][j]
+ *              + offA*offB*K + rsA[b][i]*offB + rsB[b][j]*offA      (int32, wraps)
+ * which equals sum_k (A+offA)(B+offB) when rsA / rsB are the row sums of A and
+ * column sums of B.  Replaces the two queued tasks of
+ * tfcc::mkl::quantization::matmul -- _mkl_create_offset_matrix followed by the
+ * accumulating AVX2 GEMM (tfcc/mkl/operations/tfcc_mklquantization.cpp:33-69,
+ * :176-201) -- and its N==1 fast path (:151-174).
+ * strideRsA / strideRsB are 0 when the sums are shared by the whole batch.
+ */
+TFCCB200_API int tfccb200_qgemm_u8s8s32(void* stream, const uint8_t* A, unsigned strideA, const int32_t* rsA,
+                           unsigned strideRsA, int32_t offA, const int8_t* B, unsigned strideB,
+                           const int32_t* rsB, unsigned strideRsB, int32_t offB, int32_t* C,
+                           unsigned strideC, unsigned M, unsigned N, unsigned K, unsigned batch,
+                           int* device_status);
+
+TFCCB200_API int tfccb200_qgemm_u8s8s32_ex(void* stream, const uint8_t* A, unsigned strideA,
+                              const int32_t* rsA, unsigned strideRsA, int32_t offA,
+                              const int8_t* B, unsigned strideB, const int32_t* rsB,
+                              unsigned strideRsB, int32_t offB, int32_t* C, unsigned strideC,
+                              unsigned M, unsigned N, unsigned K, unsigned batch, int path,
+                              int* device_status);
+
+/*
+ * Host-side scalar math of the quantized matmul: zero-point offsets and the
+ * float range of the int32 result, from the (min,max) float ranges of the
+ * operands.  Restates get_quantized_scale_info<uint8_t/int8_t> minus
+ * numeric_limits::lowest() and get_quantization_range_for_multiplication
+ * (tfcc/core/utils/tfcc_quantizationutils.h:23-56,
+ *  tfcc/mkl/operations/tfcc_mklquantization.cpp:181-193).
+ */
+TFCCB200_API int tfccb200_quantized_matmul_params(float minA, float maxA, float minB, float maxB,
+                                     int32_t* offA, int32_t* offB, float* minC, float* maxC);
+
+/*
+ * dst = sum of src over its last dimension (row_flag != 0, dst is
+ * [batch,rows]) or over its second-to-last dimension (row_flag == 0, dst is
+ * [batch,cols]); src is [batch,rows,cols].  int32 accumulation.  Replaces
+ * tfcc::mkl::quantization::reduce_sum<T>
+ * (tfcc/mkl/operations/tfcc_mklquantization.cpp:205-318).
+ */
+TFCCB200_API int tfccb200_reduce_sum_u8(void* stream, const uint8_t* src, unsigned batch, unsigned rows,
+                           unsigned cols, int row_flag, int32_t* dst);
+TFCCB200_API int tfccb200_reduce_sum_s8(void* stream, const int8_t* src, unsigned batch, unsigned rows,
+                           unsigned cols, int row_flag, int32_t* dst);
+TFCCB200_API int tfccb200_reduce_sum_s16(void* stream, const int16_t* src, unsigned batch, unsigned rows,
+                            unsigned cols, int row_flag, int32_t* dst);
+
+/*
+ * dst[m][g*ns + j] = src[g][m][j] for g < G, m < M, j < ns (fp32, ns % 4 == 0).
+ * Turns the rank-major result of an all-gather of column shards of C into the
+ * row-major [M, G*ns] matrix.  No counterpart in the reference, which has no
+ * multi-device operator; used by the N-split multi-GPU shim.
+ */
+TFCCB200_API int tfccb200_interleave_panels_f32(void* stream, const float* src, float* dst,
+                                                unsigned M, unsigned ns, unsigned G);
+
+/*
+ * Host-buffer forms: the caller passes HOST pointers; the call stages the
+ * operands in device memory, runs the device entry point above on `stream`,
+ * copies the result back and synchronises the stream before returning.  This
+ * is the data::set -> matmul -> data::get round trip of a TFCC user
+ * (tfcc/cuda/interfaces/tfcc_cudadatainterface.cu:62-90) in one call.
+ * Device staging buffers come from the stream-ordered CUDA allocator.
+ */
+TFCCB200_API int tfccb200_sgemm_host(void* stream, const float* hA, unsigned strideA, const float* hB,
+                        unsigned strideB, float* hC, unsigned strideC, const float* hbias,
+                        unsigned M, unsigned N, unsigned K, unsigned batch, int precision_mode);
+
+TFCCB200_API int tfccb200_qgemm_u8s8s32_host(void* stream, const uint8_t* hA, unsigned strideA,
+                                const int8_t* hB, unsigned strideB, float minA, float maxA,
+                                float minB, float maxB, int32_t* hC, unsigned strideC,
+                                float* minC, float* maxC, unsigned M, unsigned N, unsigned K,
+                                unsigned batch);
+
+/* Number of kernels this library has launched in the calling process since it
+ * was loaded (monotonic; for benchmarks that must report their launch count). */
+TFCCB200_API unsigned long long tfccb200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TFCC_B200_H_ */

@@ -1,0 +1,334 @@
+"""TEST INFRASTRUCTURE -- CPU oracle of the TFCC matmul hot path.
+
+Only tests, the smoke check and the benchmark's CPU-baseline leg may import this
+module; the product never does.
+
+What it restates, and from where (paths relative to the reference tree):
+
+* ``blas_matmul``        shape rules of ``tfcc::blas::matmul``
+                         (tfcc/core/operations/tfcc_blas.cpp:26-96) and the batch /
+                         broadcast strides of ``MKLBlasInterface<float>::matmul``
+                         (tfcc/mkl/interfaces/tfcc_mklblasinterface.cpp:127-186).  The
+                         arithmetic itself is a third-party dependency that is not in
+                         the reference tree -- oneDNN v1.8.1 ``dnnl::matmul``
+                         (pinned in build.sh:19-23) -- so the oracle computes the
+                         mathematically exact product in float64 and, as the stand-in
+                         for "the reference's fp32 result", numpy's float32 GEMM.
+* ``is_similar``         the reference's comparison predicate
+                         (tfcc/core/utils/tfcc_debugutils.cpp:102-127).
+* ``quantized_*``        scale / offset math (tfcc/core/utils/tfcc_quantizationutils.h),
+                         quantize / dequantize
+                         (tfcc/mkl/kernel/tfcc_mklquantizationkernel.hpp:21-46),
+                         ``reduce_sum`` and the quantized ``matmul``
+                         (tfcc/mkl/operations/tfcc_mklquantization.cpp), in numpy
+                         (int64, wrapped to int32) and through the C port / the
+                         reference's own compiled AVX2 kernel when built.
+
+Parity pin: fp32 -- pinned to the reference's own tolerance only (its tests compare
+with ``is_similar`` against numpy, tfcc/test/blas.cpp:34-61); int8 -- pinned exactly
+by the reference's known-answer tests (tfcc/test/quantization.cpp:105-218) and by
+the reference kernel compiled from its sources into ``oracle/_ref``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+PORT_LIB = HERE / "liboracle_port.so"
+REF_LIB = HERE / "_ref" / "libtfcc_ref_qmatmul.so"
+_REF_COLMAJOR = "_ZN4tfcc28_MKLQuantizationMatmulAVX25623quantizedMatmulColMajorEjPKajPKhjjjjPij"
+_REF_N1 = "_ZN4tfcc28_MKLQuantizationMatmulAVX25617quantizedMatmulN1EPKhPKiiPKaiijjPi"
+
+
+class OracleError(ValueError):
+    """Argument rejected by the restated reference checks (InvalidArgumentError)."""
+
+
+# --------------------------------------------------------------------------- build / load
+def build(ref_root: str | None = None) -> None:
+    """Compile the C port, and the reference kernel when the reference tree is present."""
+    subprocess.run(["make", "-s", "-C", str(HERE), "port"], check=True)
+    ref_root = ref_root or os.environ.get("TFCC_REF_ROOT", "/root/reference")
+    if Path(ref_root, "tfcc/mkl/kernel/tfcc_mklquantizationmatmul.avx256.cpp").exists():
+        subprocess.run(["make", "-s", "-C", str(HERE), "ref", f"TFCC_REF_ROOT={ref_root}"],
+                       check=True)
+
+
+_port = None
+_ref = None
+
+
+def port_lib():
+    global _port
+    if _port is None:
+        if not PORT_LIB.exists():
+            build()
+        _port = C.CDLL(str(PORT_LIB))
+    return _port
+
+
+def ref_lib():
+    """The reference's compiled int8 kernel, or None when it was not built."""
+    global _ref
+    if _ref is None and REF_LIB.exists():
+        _ref = C.CDLL(str(REF_LIB))
+    return _ref
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+# --------------------------------------------------------------------------- fp32 matmul
+def matmul_result_shape(sa, sb, sc=None):
+    """Result shape, or OracleError, per tfcc_blas.cpp:27-45 (and :61-82 with a bias)."""
+    sa, sb = tuple(sa), tuple(sb)
+    if len(sa) < 2 or len(sb) < 2:
+        raise OracleError("matmul require tensors with two or more dimensions")
+    if len(sa) != len(sb) and len(sa) != 2 and len(sb) != 2:
+        raise OracleError("shape invalid")
+    if sa[-1] != sb[-2]:
+        raise OracleError("shape invalid")
+    if sc is not None and (len(sc) != 1 or sc[0] != sb[-1]):
+        raise OracleError("shape invalid")
+    if len(sa) == len(sb) and sa[:-2] != sb[:-2]:
+        raise OracleError("shape invalid")
+    lead = sa[:-2] if len(sa) >= len(sb) else sb[:-2]
+    return tuple(lead) + (sa[-2], sb[-1])
+
+
+def blas_matmul(a, b, c=None, dtype=np.float64):
+    """``a . b (+ c)`` with the reference's batching.  ``dtype=float64`` gives the exact
+    product of the float32 inputs rounded nowhere (ground truth); ``dtype=float32`` gives a
+    float32 BLAS product, the stand-in for the reference's own fp32 output."""
+    a = np.asarray(a)
+    b = np.asarray(b)
+    shape = matmul_result_shape(a.shape, b.shape, None if c is None else np.asarray(c).shape)
+    if a.size == 0 or b.size == 0:
+        return np.zeros(shape, dtype=dtype)
+    m, k, n = a.shape[-2], a.shape[-1], b.shape[-1]
+    batch = int(np.prod(shape[:-2])) if len(shape) > 2 else 1
+    a3 = a.reshape(-1, m, k).astype(dtype, copy=False)
+    b3 = b.reshape(-1, k, n).astype(dtype, copy=False)
+    out = np.empty((batch, m, n), dtype=dtype)
+    for i in range(batch):  # stride 0 for a rank-2 operand next to a batched one
+        ai = a3[i if a3.shape[0] > 1 else 0]
+        bi = b3[i if b3.shape[0] > 1 else 0]
+        np.matmul(ai, bi, out=out[i])
+    if c is not None:
+        out += np.asarray(c).astype(dtype, copy=False)
+    return out.reshape(shape)
+
+
+def is_similar(a, b) -> bool:
+    """tfcc::is_similar: integers exact; floats |a-b| < 1e-3*|a+b| or |a-b| < 1e-5."""
+    a = np.asarray(a)
+    b = np.asarray(b)
+    if a.shape != b.shape:
+        return False
+    if np.issubdtype(a.dtype, np.integer) and np.issubdtype(b.dtype, np.integer):
+        return bool(np.array_equal(a.astype(np.int64), b.astype(np.int64)))
+    a = a.astype(np.float64)
+    b = b.astype(np.float64)
+    d = np.abs(a - b)
+    return bool(np.all((d < 1e-3 * np.abs(a + b)) | (d < 1e-5)))
+
+
+def normwise_rel_error(x, truth) -> float:
+    truth = np.asarray(truth, dtype=np.float64)
+    x = np.asarray(x, dtype=np.float64)
+    den = np.linalg.norm(truth.ravel())
+    return float(np.linalg.norm((x - truth).ravel()) / den) if den > 0 else float(
+        np.linalg.norm((x - truth).ravel()))
+
+
+# --------------------------------------------------------------------------- quantization
+_LIMITS = {np.uint8: (0, 255), np.int8: (-128, 127), np.uint16: (0, 65535),
+           np.int16: (-32768, 32767), np.int32: (-2**31, 2**31 - 1)}
+
+
+def _c_round(x: float) -> int:
+    """C ``round``: half away from zero."""
+    import math
+    return int(math.floor(abs(x) + 0.5)) * (1 if x >= 0 else -1)
+
+
+def quantized_scale_info(min_value, max_value, bits=8):
+    """get_quantized_scale_info<T> (tfcc_quantizationutils.h:45-56)."""
+    min_value = float(np.float32(min_value))
+    max_value = float(np.float32(max_value))
+    step_cnt = 1 << bits
+    range_adjust = step_cnt / (step_cnt - 1.0)
+    rng = float(np.float32(max_value) - np.float32(min_value)) * range_adjust
+    range_scale = step_cnt / rng
+    return range_scale, _c_round(min_value * range_scale)
+
+
+def matmul_params(min_a, max_a, min_b, max_b):
+    """(offA, offB, minC, maxC) as tfcc_mklquantization.cpp:181-193 computes them."""
+    _, oa = quantized_scale_info(min_a, max_a)
+    _, ob = quantized_scale_info(min_b, max_b)
+    oa -= 0
+    ob -= -128
+    f = np.float32
+    a_level = (f(max_a) - f(min_a)) / f(255)
+    b_level = (f(max_b) - f(min_b)) / f(255)
+    c_level = f(a_level * b_level)
+    return int(oa), int(ob), float(f(c_level * f(-2**31))), float(f(c_level * f(2**31 - 1)))
+
+
+def quantize(a, dtype):
+    """MKLQuantizationInterface<T>::quantize(a): (q, min, max)
+    (tfcc/mkl/interfaces/tfcc_mklquantizationinterface.cpp:47-69,
+     kernel/tfcc_mklquantizationkernel.hpp:23-33)."""
+    a = np.asarray(a, dtype=np.float32)
+    lo, hi = _LIMITS[dtype]
+    mn, mx = float(a.min()), float(a.max())
+    if mn == mx:
+        return np.full(a.shape, lo, dtype=dtype), mn, mx
+    scale, offset = quantized_scale_info(mn, mx, bits=np.dtype(dtype).itemsize * 8)
+    x = a.astype(np.float64) * scale
+    r = np.sign(x) * np.floor(np.abs(x) + 0.5)  # C round()
+    q = r.astype(np.int64) - offset + lo
+    return np.clip(q, lo, hi).astype(dtype), mn, mx
+
+
+def dequantize(a, min_value, max_value):
+    """kernel/tfcc_mklquantizationkernel.hpp:35-45 with get_dequantized_scale_info
+    (tfcc_quantizationutils.h:58-70)."""
+    a = np.asarray(a)
+    lo, _ = _LIMITS[a.dtype.type]
+    bits = a.dtype.itemsize * 8
+    step_cnt = float(2 ** bits)
+    range_adjust = step_cnt / (step_cnt - 1.0)
+    rng = float(np.float32(max_value) - np.float32(min_value)) * range_adjust
+    scale = rng / step_cnt
+    return (float(np.float32(min_value)) + (a.astype(np.float64) - lo) * scale).astype(np.float32)
+
+
+def reduce_sum(a, row: bool):
+    """tfcc::mkl::quantization::reduce_sum (tfcc_mklquantization.cpp:284-318)."""
+    a = np.asarray(a)
+    if a.size == 0 or a.ndim < 2:
+        raise OracleError("invalid input tensor a")
+    return a.astype(np.int64).sum(axis=-1 if row else -2).astype(np.int32)
+
+
+def _check_qmatmul(a, rs_a, b, rs_b):
+    if a.size == 0 or a.ndim < 2:
+        raise OracleError("invalid input tensor a")
+    if rs_a.size == 0:
+        raise OracleError("invalid tensor reduceSumA")
+    if b.size == 0 or b.ndim < 2:
+        raise OracleError("invalid input tensor b")
+    if rs_b.size == 0:
+        raise OracleError("invalid tensor reduceSumB")
+    if a.shape[-1] != b.shape[-2]:
+        raise OracleError("tensor a and b don't match")
+    if a.ndim != b.ndim and a.ndim != 2 and b.ndim != 2:
+        raise OracleError("tensor a and b don't match")
+    if a.shape[-2] != rs_a.shape[-1]:
+        raise OracleError("tensor a and reduceSumA don't match")
+    if b.shape[-1] != rs_b.shape[-1]:
+        raise OracleError("tensor b and reduceSumB don't match")
+    if a.ndim == b.ndim and a.shape[:-2] != b.shape[:-2]:
+        raise OracleError("tensor a and b don't match")
+
+
+def _fold(a, rs_a, b, rs_b):
+    """Shapes, strides and the single-B batch fold of tfcc_mklquantization.cpp:120-145."""
+    lead = a.shape[:-2] if a.ndim >= b.ndim else b.shape[:-2]
+    m, k, n = a.shape[-2], a.shape[-1], b.shape[-1]
+    shape = tuple(lead) + (m, n)
+    batch = int(np.prod(lead)) if lead else 1
+    srs_a = 0 if rs_a.ndim == 1 else m
+    srs_b = 0 if rs_b.ndim == 1 else n
+    sa = 0 if a.ndim == 2 else m * k
+    sb = 0 if b.ndim == 2 else k * n
+    if b.size == k * n:
+        m *= batch
+        srs_a *= batch
+        sa *= batch
+        batch = 1
+    return shape, batch, m, n, k, sa, sb, srs_a, srs_b
+
+
+def quantized_matmul(a, rs_a, min_a, max_a, b, rs_b, min_b, max_b, impl="numpy"):
+    """tfcc::mkl::quantization::matmul -> (C int32, minC, maxC).
+
+    impl: "numpy" (int64 einsum wrapped to int32), "port" (the C restatement) or "ref"
+    (offset matrix from the C port, accumulation by the reference's compiled kernel called
+    with the reference's own argument order, tfcc_mklquantization.cpp:199-201).
+    """
+    a = np.ascontiguousarray(a, dtype=np.uint8)
+    b = np.ascontiguousarray(b, dtype=np.int8)
+    rs_a = np.ascontiguousarray(rs_a, dtype=np.int32)
+    rs_b = np.ascontiguousarray(rs_b, dtype=np.int32)
+    _check_qmatmul(a, rs_a, b, rs_b)
+    off_a, off_b, min_c, max_c = matmul_params(min_a, max_a, min_b, max_b)
+    shape, batch, m, n, k, sa, sb, srs_a, srs_b = _fold(a, rs_a, b, rs_b)
+    if impl == "numpy":
+        a3 = a.reshape(-1, a.shape[-2], k).astype(np.int64)
+        b3 = b.reshape(-1, k, n).astype(np.int64)
+        nb = max(a3.shape[0], b3.shape[0])
+        ra = np.broadcast_to(rs_a.reshape(-1, a.shape[-2]).astype(np.int64), (a3.shape[0] if rs_a.ndim > 1 else 1, a.shape[-2]))
+        rb = rs_b.reshape(-1, n).astype(np.int64)
+        out = np.empty((nb, a.shape[-2], n), dtype=np.int64)
+        for i in range(nb):
+            ai = a3[i if a3.shape[0] > 1 else 0]
+            bi = b3[i if b3.shape[0] > 1 else 0]
+            rai = ra[i if ra.shape[0] > 1 else 0]
+            rbi = rb[i if rb.shape[0] > 1 else 0]
+            out[i] = ai @ bi + off_a * off_b * k + rai[:, None] * off_b + rbi[None, :] * off_a
+        c = (out & 0xFFFFFFFF).astype(np.uint32).view(np.int32).reshape(shape)
+        return c, min_c, max_c
+    lib = port_lib()
+    c = np.zeros(shape, dtype=np.int32)
+    u, i32 = C.c_uint, C.c_int32
+    if impl == "port":
+        lib.oracle_qmatmul(u(batch), _p(a), u(sa), _p(rs_a), u(srs_a), i32(off_a), _p(b), u(sb),
+                           _p(rs_b), u(srs_b), i32(off_b), u(m), u(n), u(k), _p(c))
+        return c, min_c, max_c
+    if impl == "ref":
+        ref = ref_lib()
+        if ref is None:
+            raise RuntimeError("oracle/_ref is not built")
+        if n == 1 and batch == 1:
+            getattr(ref, _REF_N1)(_p(a), _p(rs_a), i32(off_a), _p(b), i32(int(rs_b.ravel()[0])),
+                                  i32(off_b), u(m), u(k), _p(c))
+            return c, min_c, max_c
+        lib.oracle_create_offset_matrix(u(batch), _p(rs_a), u(m), u(srs_a), _p(rs_b), u(n),
+                                        u(srs_b), i32(off_a), i32(off_b), i32(k), _p(c), u(m * n))
+        getattr(ref, _REF_COLMAJOR)(u(batch), _p(b), u(sb), _p(a), u(sa), u(n), u(m), u(k), _p(c),
+                                    u(m * n))
+        return c, min_c, max_c
+    raise ValueError(impl)
+
+
+def quantized_dense(a, b, impl="numpy"):
+    """quantize -> reduce_sum -> matmul -> dequantize on float inputs: the helper of the
+    reference's known-answer tests (tfcc/test/quantization.cpp:105-121)."""
+    qa, min_a, max_a = quantize(a, np.uint8)
+    qb, min_b, max_b = quantize(b, np.int8)
+    ra = reduce_sum(qa, True)
+    rb = reduce_sum(qb, False)
+    qc, min_c, max_c = quantized_matmul(qa, ra, min_a, max_a, qb, rb, min_b, max_b, impl=impl)
+    return dequantize(qc, min_c, max_c)
+
+
+def sgemm_f64acc_c(a, b, bias=None):
+    """The C port's double-accumulating fp32 GEMM on rank-2 operands (float32 result)."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    m, k = a.shape
+    n = b.shape[1]
+    c = np.empty((m, n), dtype=np.float32)
+    bp = _p(np.ascontiguousarray(bias, dtype=np.float32)) if bias is not None else None
+    port_lib().oracle_sgemm_f64acc(C.c_uint(1), _p(a), C.c_uint(0), _p(b), C.c_uint(0), bp,
+                                   C.c_uint(m), C.c_uint(n), C.c_uint(k), _p(c), None)
+    return c

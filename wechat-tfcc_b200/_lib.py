@@ -1,0 +1,92 @@
+"""ctypes binding of libtfcc_b200.so.  Loading fails loudly: no fallback exists."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+from . import exceptions
+
+_HERE = Path(__file__).resolve().parent
+
+
+def library_path() -> Path:
+    return _HERE / "libtfcc_b200.so"
+
+
+class _Lib:
+    """Lazy handle: the library is opened on first use so that importing the
+    package on a machine without the build does not fail until an op is called."""
+
+    def __init__(self):
+        self._dll = None
+
+    def _load(self):
+        path = library_path()
+        if not path.exists():
+            raise ImportError(
+                f"{path} is missing: build it with `python {_HERE / 'build.py'}`; "
+                "this package has no CPU or eager fallback")
+        dll = C.CDLL(str(path))
+        vp, u, i, sz = C.c_void_p, C.c_uint, C.c_int, C.c_size_t
+        i32, f = C.c_int32, C.c_float
+        sig = {
+            "tfccb200_strerror": (C.c_char_p, [i]),
+            "tfccb200_version": (i, []),
+            "tfccb200_launch_count": (C.c_ulonglong, []),
+            "tfccb200_sgemm": (i, [vp, vp, u, vp, u, vp, u, vp, u, u, u, u, i, vp, sz, vp]),
+            "tfccb200_sgemm_ex": (i, [vp, vp, u, vp, u, vp, u, vp, u, u, u, u, i, i, vp, sz, vp]),
+            "tfccb200_sgemm_workspace": (sz, [u, u, u, u, i]),
+            "tfccb200_sgemm_path": (i, [u, u, u, u, u, u, i]),
+            "tfccb200_qgemm_u8s8s32": (i, [vp, vp, u, vp, u, i32, vp, u, vp, u, i32, vp, u, u, u, u, u, vp]),
+            "tfccb200_qgemm_u8s8s32_ex": (i, [vp, vp, u, vp, u, i32, vp, u, vp, u, i32, vp, u, u, u, u, u, i, vp]),
+            "tfccb200_quantized_matmul_params": (i, [f, f, f, f, C.POINTER(i32), C.POINTER(i32),
+                                                     C.POINTER(f), C.POINTER(f)]),
+            "tfccb200_reduce_sum_u8": (i, [vp, vp, u, u, u, i, vp]),
+            "tfccb200_reduce_sum_s8": (i, [vp, vp, u, u, u, i, vp]),
+            "tfccb200_reduce_sum_s16": (i, [vp, vp, u, u, u, i, vp]),
+            "tfccb200_interleave_panels_f32": (i, [vp, vp, vp, u, u, u]),
+            "tfccb200_sgemm_host": (i, [vp, vp, u, vp, u, vp, u, vp, u, u, u, u, i]),
+            "tfccb200_qgemm_u8s8s32_host": (i, [vp, vp, u, vp, u, f, f, f, f, vp, u,
+                                                C.POINTER(f), C.POINTER(f), u, u, u, u]),
+        }
+        for name, (res, args) in sig.items():
+            fn = getattr(dll, name)
+            fn.restype = res
+            fn.argtypes = args
+        self._dll = dll
+
+    def __getattr__(self, name):
+        if self._dll is None:
+            self._load()
+        return getattr(self._dll, name)
+
+
+lib = _Lib()
+
+EXPORTED_SYMBOLS = (
+    "tfccb200_strerror", "tfccb200_version", "tfccb200_launch_count", "tfccb200_sgemm",
+    "tfccb200_sgemm_ex", "tfccb200_sgemm_workspace", "tfccb200_sgemm_path",
+    "tfccb200_qgemm_u8s8s32", "tfccb200_qgemm_u8s8s32_ex", "tfccb200_quantized_matmul_params",
+    "tfccb200_reduce_sum_u8", "tfccb200_reduce_sum_s8", "tfccb200_reduce_sum_s16",
+    "tfccb200_interleave_panels_f32", "tfccb200_sgemm_host", "tfccb200_qgemm_u8s8s32_host",
+)
+
+PATHS = {"auto": 0, "simt": 1, "skinny": 2, "umma": 3, "umma2": 4}
+PRECISIONS = {"fp32": 0, "tf32": 1}
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(lib.tfccb200_launch_count())
+
+
+def check(status: int) -> None:
+    """Turn a C-ABI status into the matching exception."""
+    if status == 0:
+        return
+    msg = lib.tfccb200_strerror(status).decode()
+    if status in (-1, -2, -4, -5):
+        raise exceptions.InvalidArgumentError(f"tfcc_b200 status {status}: {msg}")
+    if status == -3:
+        raise exceptions.ResourceExhaustedError(f"tfcc_b200 status {status}: {msg}")
+    raise exceptions.RuntimeError(status, msg)

@@ -1,0 +1,400 @@
+// extern "C" surface of libtfcc_b200: argument checks, kernel-path choice and
+// the host-buffer convenience forms.  Nothing here throws.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <limits>
+#include <mutex>
+
+#include "internal.h"
+
+namespace tfccb200 {
+
+namespace {
+std::atomic<unsigned long long> g_launches{0};
+constexpr int kMaxDevices = 64;
+DeviceInfo g_info[kMaxDevices];
+std::once_flag g_info_once[kMaxDevices];
+cudaError_t g_info_err[kMaxDevices];
+}  // namespace
+
+void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+const DeviceInfo* current_device_info(cudaError_t* err) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    *err = (e != cudaSuccess) ? e : cudaErrorInvalidDevice;
+    return nullptr;
+  }
+  std::call_once(g_info_once[dev], [dev] {
+    cudaDeviceProp prop;
+    g_info_err[dev] = cudaGetDeviceProperties(&prop, dev);
+    if (g_info_err[dev] == cudaSuccess) {
+      g_info[dev].sm_count = prop.multiProcessorCount;
+      g_info[dev].cc_major = prop.major;
+      g_info[dev].cc_minor = prop.minor;
+      g_info[dev].l2_bytes = static_cast<size_t>(prop.l2CacheSize);
+    }
+  });
+  if (g_info_err[dev] != cudaSuccess) {
+    *err = g_info_err[dev];
+    return nullptr;
+  }
+  return &g_info[dev];
+}
+
+namespace {
+
+// A rank-2 B next to a batched, densely packed A is one tall GEMM: the batch
+// folds into M (the reference CUDA backend does the same before cublasGemmEx,
+// tfcc/cuda/interfaces/tfcc_cudablasinterface.cu:224-236).
+template <class Args>
+void fold_batch(Args& a) {
+  if (a.batch > 1 && a.strideB == 0 && a.strideA == a.M * a.K && a.strideC == a.M * a.N &&
+      static_cast<unsigned long long>(a.M) * a.batch <= 0xffffffffull) {
+    a.M *= a.batch;
+    a.batch = 1;
+  }
+}
+
+bool shape_overflows(unsigned M, unsigned N, unsigned K, unsigned batch) {
+  // TFCC's Shape keeps the element count of a tensor in 32 bits
+  // (tfcc/core/framework/tfcc_shape.h:24-81).
+  const unsigned long long lim = 0xffffffffull;
+  return static_cast<unsigned long long>(M) * K > lim ||
+         static_cast<unsigned long long>(K) * N > lim ||
+         static_cast<unsigned long long>(M) * N * batch > lim;
+}
+
+int pick_sgemm_path(const SgemmArgs& a) {
+  if (a.M <= 8 && skinny_sgemm_supported(a) &&
+      static_cast<unsigned long long>(a.K) * a.N >= (1ull << 16))
+    return TFCCB200_PATH_SKINNY;
+  const unsigned long long macs = static_cast<unsigned long long>(a.M) * a.N * a.K * a.batch;
+  if (umma_sgemm_supported(a) && macs >= (1ull << 22) && a.K >= 32 && a.N >= 64) {
+    // CTA pairs pay off once there are enough 256-row tiles to fill the machine.
+    return TFCCB200_PATH_UMMA;
+  }
+  return TFCCB200_PATH_SIMT;
+}
+
+int run_sgemm(SgemmArgs a, int path) {
+  if (!a.A || !a.B || !a.C) return TFCCB200_EINVAL;
+  if (a.M == 0 || a.N == 0 || a.K == 0 || a.batch == 0) return TFCCB200_EINVAL;
+  if (a.precision != TFCCB200_PRECISION_FP32 && a.precision != TFCCB200_PRECISION_TF32)
+    return TFCCB200_EINVAL;
+  if (shape_overflows(a.M, a.N, a.K, a.batch)) return TFCCB200_EOVERFLOW;
+  if (a.batch == 1) a.strideA = a.strideB = 0, a.strideC = a.M * a.N;
+  fold_batch(a);
+  if (path == TFCCB200_PATH_AUTO) path = pick_sgemm_path(a);
+  switch (path) {
+    case TFCCB200_PATH_SIMT: return simt_sgemm(a);
+    case TFCCB200_PATH_SKINNY: return skinny_sgemm(a);
+    case TFCCB200_PATH_UMMA: return umma_sgemm(a, false);
+    case TFCCB200_PATH_UMMA2: return umma_sgemm(a, true);
+    default: return TFCCB200_EINVAL;
+  }
+}
+
+int pick_qgemm_path(const QgemmArgs& a) {
+  const unsigned long long macs = static_cast<unsigned long long>(a.M) * a.N * a.K * a.batch;
+  if (umma_qgemm_supported(a) && macs >= (1ull << 22) && a.K >= 128 && a.N >= 128)
+    return TFCCB200_PATH_UMMA;
+  return TFCCB200_PATH_SIMT;
+}
+
+int run_qgemm(QgemmArgs a, int path) {
+  if (!a.A || !a.B || !a.C || !a.rsA || !a.rsB) return TFCCB200_EINVAL;
+  if (a.M == 0 || a.N == 0 || a.K == 0 || a.batch == 0) return TFCCB200_EINVAL;
+  if (shape_overflows(a.M, a.N, a.K, a.batch)) return TFCCB200_EOVERFLOW;
+  if (a.batch == 1) a.strideA = a.strideB = 0, a.strideC = a.M * a.N;
+  // Same fold as the reference: a single B matrix turns the batch into rows
+  // (tfcc/mkl/operations/tfcc_mklquantization.cpp:140-145).
+  if (a.batch > 1 && a.strideB == 0 && a.strideA == a.M * a.K && a.strideC == a.M * a.N &&
+      a.strideRsB == 0 && (a.strideRsA == a.M) &&
+      static_cast<unsigned long long>(a.M) * a.batch <= 0xffffffffull) {
+    a.M *= a.batch;
+    a.batch = 1;
+  }
+  if (path == TFCCB200_PATH_AUTO) path = pick_qgemm_path(a);
+  switch (path) {
+    case TFCCB200_PATH_SIMT: return simt_qgemm(a);
+    case TFCCB200_PATH_UMMA: return umma_qgemm(a, false);
+    case TFCCB200_PATH_UMMA2: return umma_qgemm(a, true);
+    default: return TFCCB200_EINVAL;
+  }
+}
+
+template <class T>
+int reduce_sum_checked(void* stream, const T* src, unsigned batch, unsigned rows, unsigned cols,
+                       int row_flag, int32_t* dst) {
+  if (!src || !dst || batch == 0 || rows == 0 || cols == 0) return TFCCB200_EINVAL;
+  if (static_cast<unsigned long long>(batch) * rows * cols > 0xffffffffull)
+    return TFCCB200_EOVERFLOW;
+  return reduce_sum<T>(static_cast<cudaStream_t>(stream), src, batch, rows, cols, row_flag, dst);
+}
+
+// get_quantized_scale_info<T> of the reference for 8-bit T: scale = 256 /
+// ((max - min) * 256/255) in double, offset = round(min * scale).
+int64_t quantized_offset_8bit(float minv, float maxv) {
+  const double step_cnt = 256.0;
+  const double range_adjust = step_cnt / (step_cnt - 1.0);
+  const double range = (static_cast<double>(maxv - minv)) * range_adjust;
+  const double range_scale = step_cnt / range;
+  return static_cast<int64_t>(std::round(minv * range_scale));
+}
+
+struct DeviceBuffer {
+  void* p = nullptr;
+  cudaStream_t s;
+  explicit DeviceBuffer(cudaStream_t st) : s(st) {}
+  cudaError_t alloc(size_t bytes) { return cudaMallocAsync(&p, bytes ? bytes : 16, s); }
+  ~DeviceBuffer() {
+    if (p) cudaFreeAsync(p, s);
+  }
+};
+
+}  // namespace
+}  // namespace tfccb200
+
+using namespace tfccb200;
+
+extern "C" {
+
+const char* tfccb200_strerror(int status) {
+  switch (status) {
+    case TFCCB200_OK: return "ok";
+    case TFCCB200_EINVAL: return "invalid argument";
+    case TFCCB200_EALIGN: return "operand alignment not supported by the requested kernel path";
+    case TFCCB200_EWORKSPACE: return "workspace missing, misaligned or too small";
+    case TFCCB200_EOVERFLOW: return "element count exceeds the 32-bit shape limit";
+    case TFCCB200_EUNSUPPORTED: return "requested kernel path cannot run this problem";
+    case TFCCB200_EDEVICE: return "a kernel abandoned a bounded wait";
+    default:
+      if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+      return "unknown status";
+  }
+}
+
+int tfccb200_version(void) { return 100; }
+
+unsigned long long tfccb200_launch_count(void) {
+  return g_launches.load(std::memory_order_relaxed);
+}
+
+int tfccb200_sgemm_ex(void* stream, const float* A, unsigned strideA, const float* B,
+                      unsigned strideB, float* C, unsigned strideC, const float* bias, unsigned M,
+                      unsigned N, unsigned K, unsigned batch, int precision_mode, int path,
+                      void* workspace, size_t workspace_bytes, int* device_status) {
+  SgemmArgs a;
+  a.stream = static_cast<cudaStream_t>(stream);
+  a.A = A; a.B = B; a.C = C; a.bias = bias;
+  a.strideA = strideA; a.strideB = strideB; a.strideC = strideC;
+  a.M = M; a.N = N; a.K = K; a.batch = batch;
+  a.precision = precision_mode;
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  a.status = device_status;
+  return run_sgemm(a, path);
+}
+
+int tfccb200_sgemm(void* stream, const float* A, unsigned strideA, const float* B,
+                   unsigned strideB, float* C, unsigned strideC, const float* bias, unsigned M,
+                   unsigned N, unsigned K, unsigned batch, int precision_mode, void* workspace,
+                   size_t workspace_bytes, int* device_status) {
+  return tfccb200_sgemm_ex(stream, A, strideA, B, strideB, C, strideC, bias, M, N, K, batch,
+                           precision_mode, TFCCB200_PATH_AUTO, workspace, workspace_bytes,
+                           device_status);
+}
+
+size_t tfccb200_sgemm_workspace(unsigned M, unsigned N, unsigned K, unsigned batch,
+                                int precision_mode) {
+  (void)precision_mode;
+  if (M == 0 || N == 0 || K == 0 || batch == 0) return 0;
+  cudaError_t e;
+  const DeviceInfo* di = current_device_info(&e);
+  const int sms = di ? di->sm_count : 148;
+  // Only the M <= 8 streaming kernel uses scratch (its per-slice partial sums).
+  // The bound covers both the batched and the batch-folded reading of the problem.
+  size_t need = 0;
+  if (M <= 8) need = skinny_sgemm_workspace(M, N, K, batch, sms);
+  if (static_cast<unsigned long long>(M) * batch <= 8) {
+    const size_t folded = skinny_sgemm_workspace(M * batch, N, K, 1, sms);
+    if (folded > need) need = folded;
+  }
+  return need;
+}
+
+int tfccb200_sgemm_path(unsigned M, unsigned N, unsigned K, unsigned batch, unsigned strideA,
+                        unsigned strideB, int precision_mode) {
+  SgemmArgs a = {};
+  a.A = a.B = reinterpret_cast<const float*>(16);
+  a.C = reinterpret_cast<float*>(16);
+  a.strideA = strideA; a.strideB = strideB; a.strideC = M * N;
+  a.M = M; a.N = N; a.K = K; a.batch = batch;
+  a.precision = precision_mode;
+  if (M == 0 || N == 0 || K == 0 || batch == 0) return TFCCB200_EINVAL;
+  if (a.batch == 1) a.strideA = a.strideB = 0;
+  fold_batch(a);
+  return pick_sgemm_path(a);
+}
+
+int tfccb200_qgemm_u8s8s32_ex(void* stream, const uint8_t* A, unsigned strideA,
+                              const int32_t* rsA, unsigned strideRsA, int32_t offA,
+                              const int8_t* B, unsigned strideB, const int32_t* rsB,
+                              unsigned strideRsB, int32_t offB, int32_t* C, unsigned strideC,
+                              unsigned M, unsigned N, unsigned K, unsigned batch, int path,
+                              int* device_status) {
+  QgemmArgs a;
+  a.stream = static_cast<cudaStream_t>(stream);
+  a.A = A; a.B = B; a.C = C; a.rsA = rsA; a.rsB = rsB;
+  a.strideA = strideA; a.strideB = strideB; a.strideC = strideC;
+  a.strideRsA = strideRsA; a.strideRsB = strideRsB;
+  a.offA = offA; a.offB = offB;
+  a.M = M; a.N = N; a.K = K; a.batch = batch;
+  a.status = device_status;
+  return run_qgemm(a, path);
+}
+
+int tfccb200_qgemm_u8s8s32(void* stream, const uint8_t* A, unsigned strideA, const int32_t* rsA,
+                           unsigned strideRsA, int32_t offA, const int8_t* B, unsigned strideB,
+                           const int32_t* rsB, unsigned strideRsB, int32_t offB, int32_t* C,
+                           unsigned strideC, unsigned M, unsigned N, unsigned K, unsigned batch,
+                           int* device_status) {
+  return tfccb200_qgemm_u8s8s32_ex(stream, A, strideA, rsA, strideRsA, offA, B, strideB, rsB,
+                                   strideRsB, offB, C, strideC, M, N, K, batch,
+                                   TFCCB200_PATH_AUTO, device_status);
+}
+
+int tfccb200_quantized_matmul_params(float minA, float maxA, float minB, float maxB,
+                                     int32_t* offA, int32_t* offB, float* minC, float* maxC) {
+  if (!offA || !offB || !minC || !maxC) return TFCCB200_EINVAL;
+  int64_t oa = quantized_offset_8bit(minA, maxA);
+  int64_t ob = quantized_offset_8bit(minB, maxB);
+  oa -= static_cast<int64_t>(std::numeric_limits<uint8_t>::lowest());
+  ob -= static_cast<int64_t>(std::numeric_limits<int8_t>::lowest());
+  *offA = static_cast<int32_t>(oa);
+  *offB = static_cast<int32_t>(ob);
+  // One quantization level of each operand, in float as the reference computes it.
+  const float a_level = (maxA - minA) / 255;
+  const float b_level = (maxB - minB) / 255;
+  const float c_level = a_level * b_level;
+  *minC = c_level * static_cast<int64_t>(std::numeric_limits<int32_t>::lowest());
+  *maxC = c_level * static_cast<int64_t>(std::numeric_limits<int32_t>::max());
+  return TFCCB200_OK;
+}
+
+int tfccb200_reduce_sum_u8(void* stream, const uint8_t* src, unsigned batch, unsigned rows,
+                           unsigned cols, int row_flag, int32_t* dst) {
+  return reduce_sum_checked<uint8_t>(stream, src, batch, rows, cols, row_flag, dst);
+}
+int tfccb200_reduce_sum_s8(void* stream, const int8_t* src, unsigned batch, unsigned rows,
+                           unsigned cols, int row_flag, int32_t* dst) {
+  return reduce_sum_checked<int8_t>(stream, src, batch, rows, cols, row_flag, dst);
+}
+int tfccb200_reduce_sum_s16(void* stream, const int16_t* src, unsigned batch, unsigned rows,
+                            unsigned cols, int row_flag, int32_t* dst) {
+  return reduce_sum_checked<int16_t>(stream, src, batch, rows, cols, row_flag, dst);
+}
+
+int tfccb200_interleave_panels_f32(void* stream, const float* src, float* dst, unsigned M,
+                                   unsigned ns, unsigned G) {
+  if (!src || !dst || M == 0 || ns == 0 || G == 0) return TFCCB200_EINVAL;
+  return interleave_panels_f32(static_cast<cudaStream_t>(stream), src, dst, M, ns, G);
+}
+
+int tfccb200_sgemm_host(void* stream, const float* hA, unsigned strideA, const float* hB,
+                        unsigned strideB, float* hC, unsigned strideC, const float* hbias,
+                        unsigned M, unsigned N, unsigned K, unsigned batch, int precision_mode) {
+  if (!hA || !hB || !hC || M == 0 || N == 0 || K == 0 || batch == 0) return TFCCB200_EINVAL;
+  if (shape_overflows(M, N, K, batch)) return TFCCB200_EOVERFLOW;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (batch == 1) strideA = strideB = 0, strideC = M * N;
+  const size_t nA = strideA ? static_cast<size_t>(strideA) * (batch - 1) + size_t(M) * K
+                            : size_t(M) * K;
+  const size_t nB = strideB ? static_cast<size_t>(strideB) * (batch - 1) + size_t(K) * N
+                            : size_t(K) * N;
+  const size_t nC = static_cast<size_t>(strideC) * (batch - 1) + size_t(M) * N;
+  const size_t ws = tfccb200_sgemm_workspace(M, N, K, batch, precision_mode);
+  DeviceBuffer dA(s), dB(s), dC(s), dBias(s), dW(s), dS(s);
+  cudaError_t e;
+  if ((e = dA.alloc(nA * 4)) != cudaSuccess) return e;
+  if ((e = dB.alloc(nB * 4)) != cudaSuccess) return e;
+  if ((e = dC.alloc(nC * 4)) != cudaSuccess) return e;
+  if ((e = dW.alloc(ws)) != cudaSuccess) return e;
+  if ((e = dS.alloc(sizeof(int))) != cudaSuccess) return e;
+  if (hbias && (e = dBias.alloc(size_t(N) * 4)) != cudaSuccess) return e;
+  if ((e = cudaMemsetAsync(dS.p, 0, sizeof(int), s)) != cudaSuccess) return e;
+  if ((e = cudaMemcpyAsync(dA.p, hA, nA * 4, cudaMemcpyHostToDevice, s)) != cudaSuccess) return e;
+  if ((e = cudaMemcpyAsync(dB.p, hB, nB * 4, cudaMemcpyHostToDevice, s)) != cudaSuccess) return e;
+  if (hbias &&
+      (e = cudaMemcpyAsync(dBias.p, hbias, size_t(N) * 4, cudaMemcpyHostToDevice, s)) !=
+          cudaSuccess)
+    return e;
+  int st = tfccb200_sgemm(s, static_cast<float*>(dA.p), strideA, static_cast<float*>(dB.p),
+                          strideB, static_cast<float*>(dC.p), strideC,
+                          hbias ? static_cast<float*>(dBias.p) : nullptr, M, N, K, batch,
+                          precision_mode, dW.p, ws, static_cast<int*>(dS.p));
+  if (st != TFCCB200_OK) return st;
+  int dev_status = 0;
+  if ((e = cudaMemcpyAsync(hC, dC.p, nC * 4, cudaMemcpyDeviceToHost, s)) != cudaSuccess) return e;
+  if ((e = cudaMemcpyAsync(&dev_status, dS.p, sizeof(int), cudaMemcpyDeviceToHost, s)) !=
+      cudaSuccess)
+    return e;
+  if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return e;
+  return dev_status ? TFCCB200_EDEVICE : TFCCB200_OK;
+}
+
+int tfccb200_qgemm_u8s8s32_host(void* stream, const uint8_t* hA, unsigned strideA,
+                                const int8_t* hB, unsigned strideB, float minA, float maxA,
+                                float minB, float maxB, int32_t* hC, unsigned strideC,
+                                float* minC, float* maxC, unsigned M, unsigned N, unsigned K,
+                                unsigned batch) {
+  if (!hA || !hB || !hC || !minC || !maxC || M == 0 || N == 0 || K == 0 || batch == 0)
+    return TFCCB200_EINVAL;
+  if (shape_overflows(M, N, K, batch)) return TFCCB200_EOVERFLOW;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (batch == 1) strideA = strideB = 0, strideC = M * N;
+  int32_t offA, offB;
+  int st = tfccb200_quantized_matmul_params(minA, maxA, minB, maxB, &offA, &offB, minC, maxC);
+  if (st != TFCCB200_OK) return st;
+  const unsigned batchA = strideA ? batch : 1, batchB = strideB ? batch : 1;
+  const size_t nA = size_t(batchA) * M * K, nB = size_t(batchB) * K * N;
+  const size_t nC = static_cast<size_t>(strideC) * (batch - 1) + size_t(M) * N;
+  if ((strideA && strideA != M * K) || (strideB && strideB != K * N)) return TFCCB200_EINVAL;
+  DeviceBuffer dA(s), dB(s), dC(s), dRa(s), dRb(s), dS(s);
+  cudaError_t e;
+  if ((e = dA.alloc(nA)) != cudaSuccess) return e;
+  if ((e = dB.alloc(nB)) != cudaSuccess) return e;
+  if ((e = dC.alloc(nC * 4)) != cudaSuccess) return e;
+  if ((e = dRa.alloc(size_t(batchA) * M * 4)) != cudaSuccess) return e;
+  if ((e = dRb.alloc(size_t(batchB) * N * 4)) != cudaSuccess) return e;
+  if ((e = dS.alloc(sizeof(int))) != cudaSuccess) return e;
+  if ((e = cudaMemsetAsync(dS.p, 0, sizeof(int), s)) != cudaSuccess) return e;
+  if ((e = cudaMemcpyAsync(dA.p, hA, nA, cudaMemcpyHostToDevice, s)) != cudaSuccess) return e;
+  if ((e = cudaMemcpyAsync(dB.p, hB, nB, cudaMemcpyHostToDevice, s)) != cudaSuccess) return e;
+  // reduce_sum(a, row) and reduce_sum(b, column), then the matmul: the
+  // sequence of tfcc/test/quantization.cpp:105-121.
+  st = tfccb200_reduce_sum_u8(s, static_cast<uint8_t*>(dA.p), batchA, M, K, 1,
+                              static_cast<int32_t*>(dRa.p));
+  if (st != TFCCB200_OK) return st;
+  st = tfccb200_reduce_sum_s8(s, static_cast<int8_t*>(dB.p), batchB, K, N, 0,
+                              static_cast<int32_t*>(dRb.p));
+  if (st != TFCCB200_OK) return st;
+  st = tfccb200_qgemm_u8s8s32(s, static_cast<uint8_t*>(dA.p), strideA,
+                              static_cast<int32_t*>(dRa.p), strideA ? M : 0, offA,
+                              static_cast<int8_t*>(dB.p), strideB, static_cast<int32_t*>(dRb.p),
+                              strideB ? N : 0, offB, static_cast<int32_t*>(dC.p), strideC, M, N, K,
+                              batch, static_cast<int*>(dS.p));
+  if (st != TFCCB200_OK) return st;
+  int dev_status = 0;
+  if ((e = cudaMemcpyAsync(hC, dC.p, nC * 4, cudaMemcpyDeviceToHost, s)) != cudaSuccess) return e;
+  if ((e = cudaMemcpyAsync(&dev_status, dS.p, sizeof(int), cudaMemcpyDeviceToHost, s)) !=
+      cudaSuccess)
+    return e;
+  if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return e;
+  return dev_status ? TFCCB200_EDEVICE : TFCCB200_OK;
+}
+
+}  // extern "C"

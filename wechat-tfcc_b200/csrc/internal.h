@@ -1,0 +1,72 @@
+// Internal declarations shared by the translation units of libtfcc_b200.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/tfcc_b200.h"
+
+namespace tfccb200 {
+
+// Immutable facts about one CUDA device, looked up once.
+struct DeviceInfo {
+  int sm_count;
+  int cc_major, cc_minor;
+  size_t l2_bytes;
+};
+// Info for the current device; nullptr when the runtime reports an error (*err is set).
+const DeviceInfo* current_device_info(cudaError_t* err);
+
+void count_launch(unsigned n = 1);
+
+// Default bound of every device-side wait (nanoseconds).
+constexpr unsigned long long kDefaultTimeoutNs = 2000000000ull;
+
+struct SgemmArgs {
+  cudaStream_t stream;
+  const float* A;
+  const float* B;
+  float* C;
+  const float* bias;
+  unsigned strideA, strideB, strideC;
+  unsigned M, N, K, batch;
+  int precision;
+  void* workspace;
+  size_t workspace_bytes;
+  int* status;
+};
+
+struct QgemmArgs {
+  cudaStream_t stream;
+  const uint8_t* A;
+  const int8_t* B;
+  int32_t* C;
+  const int32_t* rsA;
+  const int32_t* rsB;
+  unsigned strideA, strideB, strideC, strideRsA, strideRsB;
+  int32_t offA, offB;
+  unsigned M, N, K, batch;
+  int* status;
+};
+
+// ---- tcgen05 paths (umma_launch.cu) ----
+// pair == true runs cta_group::2 (a CTA pair per 256-row tile).
+bool umma_sgemm_supported(const SgemmArgs& a);
+int umma_sgemm(const SgemmArgs& a, bool pair);
+bool umma_qgemm_supported(const QgemmArgs& a);
+int umma_qgemm(const QgemmArgs& a, bool pair);
+
+// ---- CUDA-core paths (simt_kernels.cu) ----
+int simt_sgemm(const SgemmArgs& a);
+bool skinny_sgemm_supported(const SgemmArgs& a);
+size_t skinny_sgemm_workspace(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count);
+int skinny_sgemm(const SgemmArgs& a);
+int simt_qgemm(const QgemmArgs& a);
+int interleave_panels_f32(cudaStream_t stream, const float* src, float* out, unsigned M,
+                          unsigned ns, unsigned G);
+template <class T>
+int reduce_sum(cudaStream_t stream, const T* src, unsigned batch, unsigned rows, unsigned cols,
+               int row_flag, int32_t* dst);
+
+}  // namespace tfccb200

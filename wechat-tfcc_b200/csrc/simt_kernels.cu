@@ -1,0 +1,431 @@
+// CUDA-core kernels: the any-shape fp32 and int8 GEMMs that take whatever the
+// tensor-core path cannot (unaligned pitches, tiny problems), the streaming
+// kernel for M <= 8, and the integer row / column sums of the quantized path.
+#include <cuda_runtime.h>
+
+#include "internal.h"
+
+namespace tfccb200 {
+
+namespace {
+
+// --------------------------------------------------------------------------
+// Any-shape tiled GEMM: 64x64 tile, 16-deep k-slab, 256 threads, 4x4 outputs
+// per thread.  Scalar guarded loads, so no alignment or divisibility demands.
+// fp32 accumulates with FMA in k order; int8 accumulates exactly in int32.
+// --------------------------------------------------------------------------
+template <class TA, class TB, class TAcc>
+struct Widen;
+template <>
+struct Widen<float, float, float> {
+  static __device__ __forceinline__ float a(float v) { return v; }
+  static __device__ __forceinline__ float b(float v) { return v; }
+};
+template <>
+struct Widen<uint8_t, int8_t, int32_t> {
+  static __device__ __forceinline__ int32_t a(uint8_t v) { return static_cast<int32_t>(v); }
+  static __device__ __forceinline__ int32_t b(int8_t v) { return static_cast<int32_t>(v); }
+};
+
+struct SimtEpilogue {
+  const float* bias;        // fp32
+  const int32_t* rsA;       // int8
+  const int32_t* rsB;
+  unsigned strideRsA, strideRsB;
+  int32_t offA, offB, kterm;
+};
+
+template <class TA, class TB, class TAcc>
+__global__ void __launch_bounds__(256)
+simt_gemm_kernel(const TA* __restrict__ A, const TB* __restrict__ B, TAcc* __restrict__ C,
+                 unsigned M, unsigned N, unsigned K, unsigned long long strideA,
+                 unsigned long long strideB, unsigned long long strideC, SimtEpilogue ep) {
+  constexpr int TM = 64, TN = 64, TK = 16;
+  __shared__ TAcc As[TK][TM + 4];
+  __shared__ TAcc Bs[TK][TN + 4];
+  using W = Widen<TA, TB, TAcc>;
+
+  const unsigned b = blockIdx.z;
+  A += strideA * b;
+  B += strideB * b;
+  C += strideC * b;
+  const unsigned m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+  const unsigned tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+
+  TAcc acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0;
+
+  for (unsigned k0 = 0; k0 < K; k0 += TK) {
+    // A slab: 64 rows x 16 k, read along k (contiguous), stored k-major
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      unsigned idx = threadIdx.x + i * 256;
+      unsigned r = idx >> 4, kk = idx & 15;
+      unsigned gr = m0 + r, gk = k0 + kk;
+      As[kk][r] = (gr < M && gk < K) ? W::a(A[static_cast<size_t>(gr) * K + gk]) : TAcc(0);
+    }
+    // B slab: 16 k x 64 columns, read along n (contiguous)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      unsigned idx = threadIdx.x + i * 256;
+      unsigned kk = idx >> 6, c = idx & 63;
+      unsigned gk = k0 + kk, gc = n0 + c;
+      Bs[kk][c] = (gk < K && gc < N) ? W::b(B[static_cast<size_t>(gk) * N + gc]) : TAcc(0);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      TAcc av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bv[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += av[i] * bv[j];
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    unsigned r = m0 + ty * 4 + i;
+    if (r >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      unsigned c = n0 + tx * 4 + j;
+      if (c >= N) continue;
+      TAcc v = acc[i][j];
+      if constexpr (sizeof(TA) == 4) {
+        if (ep.bias) v += ep.bias[c];
+      } else {
+        v += ep.kterm + ep.rsA[static_cast<size_t>(ep.strideRsA) * b + r] * ep.offB +
+             ep.rsB[static_cast<size_t>(ep.strideRsB) * b + c] * ep.offA;
+      }
+      C[static_cast<size_t>(r) * N + c] = v;
+    }
+  }
+}
+
+// --------------------------------------------------------------------------
+// M <= 8 streaming kernel.  y[m,n] = sum_k x[m,k] W[k,n] with W row-major, so
+// the contiguous direction of the big operand is n: a thread owns 4 adjacent
+// columns (one 128-bit load per row of W), a warp 128 columns, a CTA 1024
+// columns = 4 KB of every row it visits.  K is cut into slices so that the
+// grid fills every SM several times; a slice's partial sums go to scratch and
+// a second tiny kernel adds the slices in a fixed order (deterministic).
+// The x slice sits in shared memory as [k][MP] so one broadcast 128-bit read
+// yields four rows' multipliers.
+// --------------------------------------------------------------------------
+constexpr int kSkinnyThreads = 256;
+constexpr int kSkinnyCols = kSkinnyThreads * 4;
+constexpr int kSkinnyMaxSlice = 512;  // rows of W per CTA (bounds the x slice in smem)
+
+template <int MP>
+__global__ void __launch_bounds__(kSkinnyThreads)
+skinny_partial_kernel(const float* __restrict__ X, const float* __restrict__ W,
+                      float* __restrict__ part, unsigned M, unsigned N, unsigned K,
+                      unsigned slice_rows, unsigned long long strideX, unsigned long long strideW,
+                      unsigned kslices) {
+  __shared__ __align__(16) float xs[kSkinnyMaxSlice * MP];
+  const unsigned b = blockIdx.z;
+  X += strideX * b;
+  W += strideW * b;
+  const unsigned k_begin = blockIdx.y * slice_rows;
+  const unsigned k_end = min(K, k_begin + slice_rows);
+  const unsigned rows = k_end > k_begin ? k_end - k_begin : 0;
+
+  for (unsigned i = threadIdx.x; i < rows * MP; i += kSkinnyThreads) {
+    unsigned kk = i / MP, m = i % MP;
+    xs[i] = (m < M) ? X[static_cast<size_t>(m) * K + k_begin + kk] : 0.f;
+  }
+  __syncthreads();
+
+  const unsigned col = blockIdx.x * kSkinnyCols + threadIdx.x * 4;
+  float acc[MP][4];
+#pragma unroll
+  for (int m = 0; m < MP; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+
+  if (col < N) {  // N % 4 == 0 on this path
+    const float4* wp = reinterpret_cast<const float4*>(W + static_cast<size_t>(k_begin) * N + col);
+    const size_t pitch = N / 4;
+    constexpr int U = 8;
+    unsigned kk = 0;
+    for (; kk + U <= rows; kk += U) {
+      float4 w[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) w[u] = __ldcs(wp + (kk + u) * pitch);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+          const float xv = xs[(kk + u) * MP + m];
+          acc[m][0] = fmaf(xv, w[u].x, acc[m][0]);
+          acc[m][1] = fmaf(xv, w[u].y, acc[m][1]);
+          acc[m][2] = fmaf(xv, w[u].z, acc[m][2]);
+          acc[m][3] = fmaf(xv, w[u].w, acc[m][3]);
+        }
+      }
+    }
+    for (; kk < rows; ++kk) {
+      const float4 w = __ldcs(wp + kk * pitch);
+#pragma unroll
+      for (int m = 0; m < MP; ++m) {
+        const float xv = xs[kk * MP + m];
+        acc[m][0] = fmaf(xv, w.x, acc[m][0]);
+        acc[m][1] = fmaf(xv, w.y, acc[m][1]);
+        acc[m][2] = fmaf(xv, w.z, acc[m][2]);
+        acc[m][3] = fmaf(xv, w.w, acc[m][3]);
+      }
+    }
+    // part: [batch][kslices][M][N]
+    float* pp = part + ((static_cast<size_t>(b) * kslices + blockIdx.y) * M) * N + col;
+#pragma unroll
+    for (int m = 0; m < MP; ++m)
+      if (m < static_cast<int>(M))
+        *reinterpret_cast<float4*>(pp + static_cast<size_t>(m) * N) =
+            make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+skinny_reduce_kernel(const float* __restrict__ part, const float* __restrict__ bias,
+                     float* __restrict__ Y, unsigned MN, unsigned N, unsigned kslices,
+                     unsigned long long strideY) {
+  const unsigned b = blockIdx.y;
+  const unsigned i = (blockIdx.x * 256 + threadIdx.x) * 4;
+  if (i >= MN) return;
+  const float* pp = part + static_cast<size_t>(b) * kslices * MN + i;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (unsigned k = 0; k < kslices; ++k) {
+    const float4 v = *reinterpret_cast<const float4*>(pp + static_cast<size_t>(k) * MN);
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
+  if (bias) {
+    const float4 bv = *reinterpret_cast<const float4*>(bias + (i % N));
+    s.x += bv.x; s.y += bv.y; s.z += bv.z; s.w += bv.w;
+  }
+  *reinterpret_cast<float4*>(Y + strideY * b + i) = s;
+}
+
+// K slices: enough CTAs for ~4 per SM, slice length capped by the x buffer.
+void skinny_plan(unsigned N, unsigned K, unsigned batch, int sm_count, unsigned* kslices,
+                 unsigned* slice_rows) {
+  const unsigned col_blocks = (N + kSkinnyCols - 1) / kSkinnyCols;
+  const unsigned long long want = 4ull * sm_count;
+  unsigned long long ks = (want + static_cast<unsigned long long>(col_blocks) * batch - 1) /
+                          (static_cast<unsigned long long>(col_blocks) * batch);
+  if (ks < 1) ks = 1;
+  if (ks > K) ks = K;
+  unsigned rows = static_cast<unsigned>((K + ks - 1) / ks);
+  if (rows > kSkinnyMaxSlice) rows = kSkinnyMaxSlice;
+  if (rows < 8 && K >= 8) rows = 8;
+  *slice_rows = rows;
+  *kslices = (K + rows - 1) / rows;
+}
+
+// --------------------------------------------------------------------------
+// Integer sums for the zero-point correction.
+// --------------------------------------------------------------------------
+template <class T>
+__global__ void __launch_bounds__(256)
+reduce_rows_kernel(const T* __restrict__ src, unsigned total_rows, unsigned cols,
+                   int32_t* __restrict__ dst) {
+  // one warp per row
+  const unsigned row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const unsigned lane = threadIdx.x & 31;
+  if (row >= total_rows) return;
+  const T* p = src + static_cast<size_t>(row) * cols;
+  int32_t s = 0;
+  constexpr unsigned V = 16 / sizeof(T);
+  if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0 && cols % V == 0) {
+    const uint4* p4 = reinterpret_cast<const uint4*>(p);
+    for (unsigned i = lane; i < cols / V; i += 32) {
+      const uint4 v = __ldg(p4 + i);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (unsigned j = 0; j < V; ++j) s += static_cast<int32_t>(e[j]);
+    }
+  } else {
+    for (unsigned i = lane; i < cols; i += 32) s += static_cast<int32_t>(p[i]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) dst[row] = s;
+}
+
+// dst must be zero on entry: row slabs are combined with integer atomics,
+// which is exact and order-independent.
+template <class T>
+__global__ void __launch_bounds__(256)
+reduce_cols_kernel(const T* __restrict__ src, unsigned rows, unsigned cols, unsigned slab,
+                   int32_t* __restrict__ dst) {
+  const unsigned b = blockIdx.z;
+  const unsigned c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= cols) return;
+  const unsigned r0 = blockIdx.y * slab;
+  const unsigned r1 = min(rows, r0 + slab);
+  const T* p = src + static_cast<size_t>(b) * rows * cols + c;
+  int32_t s = 0;
+  for (unsigned r = r0; r < r1; ++r) s += static_cast<int32_t>(p[static_cast<size_t>(r) * cols]);
+  atomicAdd(dst + static_cast<size_t>(b) * cols + c, s);
+}
+
+// out[m][g*ns + j] = src[g][m][j], 128 bits per thread.
+__global__ void __launch_bounds__(256)
+interleave_panels_kernel(const float4* __restrict__ src, float4* __restrict__ out, unsigned M,
+                         unsigned ns4, unsigned G) {
+  const unsigned long long total = static_cast<unsigned long long>(G) * M * ns4;
+  for (unsigned long long i = blockIdx.x * 256ull + threadIdx.x; i < total;
+       i += static_cast<unsigned long long>(gridDim.x) * 256ull) {
+    const unsigned j = static_cast<unsigned>(i % ns4);
+    const unsigned long long r = i / ns4;
+    const unsigned g = static_cast<unsigned>(r % G);
+    const unsigned long long m = r / G;
+    out[i] = __ldcs(src + (static_cast<unsigned long long>(g) * M + m) * ns4 + j);
+  }
+}
+
+inline cudaError_t launch_status() { return cudaGetLastError(); }
+
+}  // namespace
+
+int simt_sgemm(const SgemmArgs& a) {
+  dim3 grid((a.N + 63) / 64, (a.M + 63) / 64, a.batch);
+  if (grid.y > 65535 || grid.z > 65535) return TFCCB200_EOVERFLOW;
+  SimtEpilogue ep = {};
+  ep.bias = a.bias;
+  simt_gemm_kernel<float, float, float><<<grid, 256, 0, a.stream>>>(
+      a.A, a.B, a.C, a.M, a.N, a.K, a.strideA, a.strideB, a.strideC, ep);
+  cudaError_t e = launch_status();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  count_launch();
+  return TFCCB200_OK;
+}
+
+int simt_qgemm(const QgemmArgs& a) {
+  dim3 grid((a.N + 63) / 64, (a.M + 63) / 64, a.batch);
+  if (grid.y > 65535 || grid.z > 65535) return TFCCB200_EOVERFLOW;
+  SimtEpilogue ep = {};
+  ep.rsA = a.rsA; ep.rsB = a.rsB;
+  ep.strideRsA = a.strideRsA; ep.strideRsB = a.strideRsB;
+  ep.offA = a.offA; ep.offB = a.offB;
+  ep.kterm = static_cast<int32_t>(static_cast<uint32_t>(a.offA) * static_cast<uint32_t>(a.offB) *
+                                  a.K);
+  simt_gemm_kernel<uint8_t, int8_t, int32_t><<<grid, 256, 0, a.stream>>>(
+      a.A, a.B, a.C, a.M, a.N, a.K, a.strideA, a.strideB, a.strideC, ep);
+  cudaError_t e = launch_status();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  count_launch();
+  return TFCCB200_OK;
+}
+
+bool skinny_sgemm_supported(const SgemmArgs& a) {
+  if (a.M > 8 || a.N % 4 != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(a.B) & 15u) || (reinterpret_cast<uintptr_t>(a.C) & 15u))
+    return false;
+  if (a.bias && (reinterpret_cast<uintptr_t>(a.bias) & 15u)) return false;
+  if (a.batch > 1 && (a.strideB % 4 != 0 || a.strideC % 4 != 0)) return false;
+  if (a.batch > 65535) return false;
+  return true;
+}
+
+size_t skinny_sgemm_workspace(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count) {
+  unsigned ks, rows;
+  skinny_plan(N, K, batch, sm_count, &ks, &rows);
+  return static_cast<size_t>(batch) * ks * M * N * sizeof(float);
+}
+
+int skinny_sgemm(const SgemmArgs& a) {
+  cudaError_t ce;
+  const DeviceInfo* di = current_device_info(&ce);
+  if (!di) return static_cast<int>(ce);
+  if (!skinny_sgemm_supported(a)) return TFCCB200_EUNSUPPORTED;
+  unsigned ks, rows;
+  skinny_plan(a.N, a.K, a.batch, di->sm_count, &ks, &rows);
+  const size_t need = static_cast<size_t>(a.batch) * ks * a.M * a.N * sizeof(float);
+  if (a.workspace_bytes < need || !a.workspace ||
+      (reinterpret_cast<uintptr_t>(a.workspace) & 15u))
+    return TFCCB200_EWORKSPACE;
+  float* part = static_cast<float*>(a.workspace);
+  dim3 grid((a.N + kSkinnyCols - 1) / kSkinnyCols, ks, a.batch);
+  if (grid.y > 65535) return TFCCB200_EOVERFLOW;
+#define TFCCB200_SKINNY(MP)                                                                  \
+  skinny_partial_kernel<MP><<<grid, kSkinnyThreads, 0, a.stream>>>(                          \
+      a.A, a.B, part, a.M, a.N, a.K, rows, a.strideA, a.strideB, ks)
+  if (a.M == 1) TFCCB200_SKINNY(1);
+  else if (a.M == 2) TFCCB200_SKINNY(2);
+  else if (a.M <= 4) TFCCB200_SKINNY(4);
+  else TFCCB200_SKINNY(8);
+#undef TFCCB200_SKINNY
+  cudaError_t e = launch_status();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const unsigned MN = a.M * a.N;
+  dim3 rgrid((MN / 4 + 255) / 256, a.batch);
+  skinny_reduce_kernel<<<rgrid, 256, 0, a.stream>>>(part, a.bias, a.C, MN, a.N, ks, a.strideC);
+  e = launch_status();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  count_launch(2);
+  return TFCCB200_OK;
+}
+
+int interleave_panels_f32(cudaStream_t stream, const float* src, float* out, unsigned M,
+                          unsigned ns, unsigned G) {
+  if (ns % 4 != 0 || (reinterpret_cast<uintptr_t>(src) & 15u) ||
+      (reinterpret_cast<uintptr_t>(out) & 15u))
+    return TFCCB200_EALIGN;
+  cudaError_t ce;
+  const DeviceInfo* di = current_device_info(&ce);
+  if (!di) return static_cast<int>(ce);
+  const unsigned long long total = static_cast<unsigned long long>(G) * M * (ns / 4);
+  unsigned long long blocks = (total + 255) / 256;
+  const unsigned long long cap = 16ull * di->sm_count;
+  if (blocks > cap) blocks = cap;
+  interleave_panels_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(out), M, ns / 4, G);
+  cudaError_t e = launch_status();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  count_launch();
+  return TFCCB200_OK;
+}
+
+template <class T>
+int reduce_sum(cudaStream_t stream, const T* src, unsigned batch, unsigned rows, unsigned cols,
+               int row_flag, int32_t* dst) {
+  if (row_flag) {
+    const unsigned long long total = static_cast<unsigned long long>(batch) * rows;
+    if (total > 0xffffffffull) return TFCCB200_EOVERFLOW;
+    const unsigned blocks = static_cast<unsigned>((total + 7) / 8);
+    reduce_rows_kernel<T><<<blocks, 256, 0, stream>>>(src, static_cast<unsigned>(total), cols, dst);
+    cudaError_t e = launch_status();
+    if (e != cudaSuccess) return static_cast<int>(e);
+    count_launch();
+    return TFCCB200_OK;
+  }
+  if (batch > 65535) return TFCCB200_EOVERFLOW;
+  cudaError_t e =
+      cudaMemsetAsync(dst, 0, static_cast<size_t>(batch) * cols * sizeof(int32_t), stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  // row slabs sized so that the grid has a few thousand CTAs at most
+  unsigned slab = 64;
+  while ((rows + slab - 1) / slab > 4096) slab *= 2;
+  dim3 grid((cols + 255) / 256, (rows + slab - 1) / slab, batch);
+  reduce_cols_kernel<T><<<grid, 256, 0, stream>>>(src, rows, cols, slab, dst);
+  e = launch_status();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  count_launch();
+  return TFCCB200_OK;
+}
+
+template int reduce_sum<uint8_t>(cudaStream_t, const uint8_t*, unsigned, unsigned, unsigned, int,
+                                 int32_t*);
+template int reduce_sum<int8_t>(cudaStream_t, const int8_t*, unsigned, unsigned, unsigned, int,
+                                int32_t*);
+template int reduce_sum<int16_t>(cudaStream_t, const int16_t*, unsigned, unsigned, unsigned, int,
+                                 int32_t*);
+
+}  // namespace tfccb200

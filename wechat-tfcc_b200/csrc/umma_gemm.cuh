@@ -1,0 +1,449 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   C[b] = A[b] . B[b]       A: [M,K] row-major (K-major operand)
+//                            B: [K,N] row-major (MN-major operand, no transpose pass)
+//
+// Two element kinds share the kernel:
+//   * TF32 on fp32 data.  With kSplit the fp32 product is rebuilt from three
+//     MMAs per k-step: every raw fp32 tile that TMA brings in is split in
+//     shared memory into a TF32 head (top 19 bits, truncation) and a TF32 tail
+//     (x - head, rounded to TF32); head*head + head*tail + tail*head is
+//     accumulated in fp32 in tensor memory.  HBM traffic stays that of one
+//     fp32 GEMM.
+//   * I8: u8 x s8 -> s32, exact, with the zero-point correction applied while
+//     the accumulator leaves tensor memory.
+//
+// Work layout per CTA (kCtaGroup == 1) or per CTA pair (kCtaGroup == 2):
+//   tile        128*kCtaGroup rows x BN columns, accumulator in TMEM, two
+//               accumulator buffers so the epilogue of tile i overlaps the
+//               mainloop of tile i+1
+//   k-block     128 bytes of K per A row (32 fp32 / 128 int8) = 4 MMA k-steps
+//   stage       A: 128 rows x 128 B, 128B-swizzled (K-major canonical layout)
+//               B: (BN_local*elem/128) boxes of [k-block rows x 128 B], MN-major
+//                  canonical layout: 128B swizzle of 16-byte units for int8, of
+//                  32-byte units for fp32 (the TMA mode SWIZZLE_128B_ATOM_32B)
+//               (+ a second copy of both for the TF32 tails when kSplit)
+// Warps: 0 = TMA producer, 1 = MMA issuer and TMEM owner, 2..5 = epilogue
+// (one TMEM lane quarter each), 6.. = converters (kSplit only).
+//
+// Every wait on an mbarrier is bounded: after `timeout_ns` the waiter raises a
+// CTA-wide abort flag, ORs a bit into *status and carries on without the data,
+// so the kernel always runs to its end, frees its tensor memory and returns.
+#pragma once
+
+#include "../../include/tfcc_b200.h"
+#include "ptx.cuh"
+
+namespace tfccb200 {
+
+struct UmmaGemmParams {
+  void* C;                 // float* (TF32) or int32_t* (I8)
+  const float* bias;       // [N] or nullptr (TF32 only)
+  const int32_t* rsA;      // I8: row sums of A, [batch?][M]
+  const int32_t* rsB;      // I8: column sums of B, [batch?][N]
+  int32_t offA, offB;      // I8 zero-point offsets
+  int32_t kterm;           // I8: offA*offB*K (wrapped)
+  unsigned strideRsA, strideRsB;
+  unsigned M, N, K, batch;
+  unsigned long long strideC;  // elements between batch entries of C
+  unsigned a_batched, b_batched;  // 0: operand shared by the whole batch
+  unsigned tiles_m, tiles_n;      // tile grid of one batch entry
+  unsigned write_head;     // kSplit: 1 = store the truncated head back (independent of how
+                           // the tensor core narrows fp32), 0 = feed the raw fp32 as head
+  int* status;             // device int or nullptr
+  unsigned long long timeout_ns;
+};
+
+template <ptx::MmaKind kKind, bool kSplit, int kCtaGroup, int BN, int kStages>
+struct UmmaGemmConfig {
+  static constexpr int kElemBytes = (kKind == ptx::MmaKind::TF32) ? 4 : 1;
+  static constexpr int kBM = 128;                      // rows per CTA
+  static constexpr int kTileM = kBM * kCtaGroup;       // rows per MMA
+  static constexpr int kBK = 128 / kElemBytes;         // elements of K per k-block
+  static constexpr int kUmmaK = 32 / kElemBytes;       // elements of K per MMA
+  static constexpr int kKSteps = 4;
+  static constexpr int kBNLocal = BN / kCtaGroup;      // B columns staged by one CTA
+  static constexpr int kBChunks = kBNLocal * kElemBytes / 128;  // 128-byte-wide boxes of B
+  static constexpr int kABytes = kBM * 128;
+  static constexpr int kBChunkBytes = kBK * 128;
+  static constexpr int kBBytes = kBChunks * kBChunkBytes;
+  static constexpr int kRawBytes = kABytes + kBBytes;
+  static constexpr int kStageBytes = kRawBytes * (kSplit ? 2 : 1);
+  static constexpr int kBKStepBytes = kUmmaK * 128;    // B advance per MMA k-step
+  // MN-major B: 8-bit data uses the plain 128-byte swizzle (atoms of 8 k-rows, 1024 B apart);
+  // 32-bit data must use the 128-byte swizzle with 32-byte units (atoms of 4 k-rows, 512 B).
+  static constexpr uint32_t kBLayout =
+      (kKind == ptx::MmaKind::TF32) ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+  static constexpr uint32_t kBSbo = (kKind == ptx::MmaKind::TF32) ? 512 : 1024;
+  static constexpr int kNumConvertWarps = kSplit ? 8 : 0;
+  static constexpr int kNumEpilogueWarps = 4;
+  static constexpr int kThreads = 32 * (2 + kNumEpilogueWarps + kNumConvertWarps);
+  static constexpr int kTmemCols = (2 * BN <= 32) ? 32 : 2 * BN;  // power of two by construction
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // +align slack
+  static constexpr uint32_t kIdesc =
+      (kKind == ptx::MmaKind::TF32)
+          ? ptx::make_idesc(1u, 2u, 2u, 0u, 1u, static_cast<uint32_t>(kTileM), BN)
+          : ptx::make_idesc(2u, 0u, 1u, 0u, 1u, static_cast<uint32_t>(kTileM), BN);
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "MMA N out of range");
+  static_assert((BN & (BN - 1)) == 0, "BN must be a power of two (TMEM allocation)");
+  static_assert(kBNLocal * kElemBytes % 128 == 0, "B tile must be whole 128-byte boxes");
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
+};
+
+struct UmmaCtl {
+  volatile uint32_t* abort_flag;  // shared
+  int* status;                    // global or nullptr
+  unsigned long long timeout_ns;
+};
+
+template <bool kClusterAcquire>
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, int bit,
+                                             const UmmaCtl& ctl) {
+  auto probe = [&]() {
+    if constexpr (kClusterAcquire) return ptx::mbar_try_wait_cluster(bar, parity);
+    else return ptx::mbar_try_wait(bar, parity);
+  };
+  if (probe()) return true;
+  if (*ctl.abort_flag) return false;
+  uint64_t start = 0;
+  uint32_t spins = 0;
+  while (true) {
+    if (probe()) return true;
+    if ((++spins & 0xFF) == 0) {
+      if (*ctl.abort_flag) return false;
+      uint64_t now = ptx::globaltimer_ns();
+      if (start == 0) {
+        start = now;
+      } else if (now - start > ctl.timeout_ns) {
+        *ctl.abort_flag = 1;
+        if (ctl.status) atomicOr(ctl.status, bit);
+        return false;
+      }
+    }
+  }
+}
+
+// Tile order: groups of 8 tile-rows are walked column by column so that CTAs
+// running at the same time share B panels and a small set of A panels in L2.
+__device__ __forceinline__ void tile_coords(unsigned t, unsigned tiles_m, unsigned tiles_n,
+                                            unsigned& b, unsigned& tm, unsigned& tn) {
+  const unsigned per_batch = tiles_m * tiles_n;
+  b = t / per_batch;
+  unsigned r = t - b * per_batch;
+  constexpr unsigned G = 8;
+  unsigned group = r / (G * tiles_n);
+  unsigned first_m = group * G;
+  unsigned gsz = min(tiles_m - first_m, G);
+  unsigned in_group = r - group * G * tiles_n;
+  tm = first_m + in_group % gsz;
+  tn = in_group / gsz;
+}
+
+template <ptx::MmaKind kKind, bool kSplit, int kCtaGroup, int BN, int kStages>
+__global__ void __launch_bounds__(UmmaGemmConfig<kKind, kSplit, kCtaGroup, BN, kStages>::kThreads,
+                                  1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
+                 const UmmaGemmParams p) {
+  using Cfg = UmmaGemmConfig<kKind, kSplit, kCtaGroup, BN, kStages>;
+  extern __shared__ uint8_t smem_raw[];
+
+  // ---- carve shared memory (stage buffers need 1024-byte alignment for the swizzle) ----
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes;
+  uint8_t* bar_gen = smem_gen + kStages * Cfg::kStageBytes;
+  // barrier slots (8 bytes each)
+  auto full_raw = [&](int s) { return bar_base + 8u * s; };                 // TMA -> converter / MMA
+  auto full_cvt = [&](int s) { return bar_base + 8u * (kStages + s); };     // converter -> MMA
+  auto empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };  // MMA -> TMA
+  auto tmem_full = [&](int a) { return bar_base + 8u * (3 * kStages + a); };
+  auto tmem_empty = [&](int a) { return bar_base + 8u * (3 * kStages + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (3 * kStages + 4);
+  volatile uint32_t* tmem_slot_gen =
+      reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (3 * kStages + 4));
+  volatile uint32_t* abort_flag =
+      reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (3 * kStages + 4) + 4);
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (kCtaGroup == 2) ? ptx::cluster_ctarank() : 0u;
+  const bool is_leader = (cta_rank == 0);
+  const unsigned num_groups = gridDim.x / kCtaGroup;        // CTAs (or pairs) walking the tiles
+  const unsigned group_id = blockIdx.x / kCtaGroup;
+  const unsigned total_tiles = p.batch * p.tiles_m * p.tiles_n;
+  const unsigned num_kb = (p.K + Cfg::kBK - 1) / Cfg::kBK;
+
+  UmmaCtl ctl{abort_flag, p.status, p.timeout_ns};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_raw(s), 1);
+      ptx::mbar_init(full_cvt(s), kSplit ? Cfg::kNumConvertWarps * kCtaGroup : 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tmem_full(a), 1);
+      ptx::mbar_init(tmem_empty(a), Cfg::kNumEpilogueWarps * kCtaGroup);
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tmapA);
+    ptx::prefetch_tensormap(&tmapB);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<kCtaGroup>(tmem_slot, Cfg::kTmemCols);
+    ptx::tmem_relinquish<kCtaGroup>();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (kCtaGroup == 2) {  // peer barriers must exist before anyone signals them
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  // =========================== TMA producer ===========================
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (unsigned t = group_id; t < total_tiles; t += num_groups) {
+        unsigned b, tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, b, tm, tn);
+        const int m0 = static_cast<int>(tm * Cfg::kTileM + cta_rank * Cfg::kBM);
+        const int n0 = static_cast<int>(tn * BN + cta_rank * Cfg::kBNLocal);
+        const int ba = p.a_batched ? static_cast<int>(b) : 0;
+        const int bb = p.b_batched ? static_cast<int>(b) : 0;
+        for (unsigned kb = 0; kb < num_kb; ++kb) {
+          bounded_wait<false>(empty_bar(s), ph ^ 1u, TFCCB200_DEV_TIMEOUT_TMA, ctl);
+          const uint32_t stage = smem_base + s * Cfg::kStageBytes;
+          const int k0 = static_cast<int>(kb * Cfg::kBK);
+          if constexpr (kCtaGroup == 2 && !kSplit) {
+            // Both CTAs' bytes are counted on the leader's barrier; the MMA
+            // issuer in the leader is the only consumer.
+            const uint32_t bar = full_raw(s) & 0xFEFFFFFFu;
+            if (is_leader) ptx::mbar_expect_tx(full_raw(s), 2u * Cfg::kRawBytes);
+            ptx::tma_load_3d_pair(stage, &tmapA, bar, k0, m0, ba);
+#pragma unroll
+            for (int c = 0; c < Cfg::kBChunks; ++c)
+              ptx::tma_load_3d_pair(stage + Cfg::kABytes + c * Cfg::kBChunkBytes, &tmapB, bar,
+                                    n0 + c * (128 / Cfg::kElemBytes), k0, bb);
+          } else {
+            ptx::mbar_expect_tx(full_raw(s), Cfg::kRawBytes);
+            ptx::tma_load_3d(stage, &tmapA, full_raw(s), k0, m0, ba);
+#pragma unroll
+            for (int c = 0; c < Cfg::kBChunks; ++c)
+              ptx::tma_load_3d(stage + Cfg::kABytes + c * Cfg::kBChunkBytes, &tmapB, full_raw(s),
+                               n0 + c * (128 / Cfg::kElemBytes), k0, bb);
+          }
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  }
+  // =========================== MMA issuer ===========================
+  else if (warp == 1) {
+    if (lane == 0 && is_leader) {
+      int s = 0;
+      uint32_t ph = 0;
+      unsigned it = 0;
+      const uint16_t pair_mask = 0x3;
+      for (unsigned t = group_id; t < total_tiles; t += num_groups, ++it) {
+        const unsigned acc = it & 1u;
+        const uint32_t acc_ph = (it >> 1) & 1u;
+        bounded_wait<(kCtaGroup == 2)>(tmem_empty(acc), acc_ph ^ 1u, TFCCB200_DEV_TIMEOUT_MMA,
+                                       ctl);
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (unsigned kb = 0; kb < num_kb; ++kb) {
+          if constexpr (kSplit) {
+            bounded_wait<(kCtaGroup == 2)>(full_cvt(s), ph, TFCCB200_DEV_TIMEOUT_MMA, ctl);
+          } else {
+            bounded_wait<false>(full_raw(s), ph, TFCCB200_DEV_TIMEOUT_MMA, ctl);
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_hi = smem_base + s * Cfg::kStageBytes;
+          const uint32_t b_hi = a_hi + Cfg::kABytes;
+          const uint32_t a_lo = a_hi + Cfg::kRawBytes;
+          const uint32_t b_lo = b_hi + Cfg::kRawBytes;
+#pragma unroll
+          for (int ks = 0; ks < Cfg::kKSteps; ++ks) {
+            const uint64_t da_hi = ptx::smem_desc(a_hi + ks * 32, 16, 1024, ptx::kLayoutSw128);
+            const uint64_t db_hi = ptx::smem_desc(b_hi + ks * Cfg::kBKStepBytes,
+                                                  Cfg::kBChunkBytes, Cfg::kBSbo, Cfg::kBLayout);
+            const uint32_t accum = (kb > 0 || ks > 0) ? 1u : 0u;
+            if constexpr (kSplit) {
+              const uint64_t da_lo = ptx::smem_desc(a_lo + ks * 32, 16, 1024, ptx::kLayoutSw128);
+              const uint64_t db_lo = ptx::smem_desc(b_lo + ks * Cfg::kBKStepBytes,
+                                                    Cfg::kBChunkBytes, Cfg::kBSbo, Cfg::kBLayout);
+              ptx::umma<kKind, kCtaGroup>(d_tmem, da_lo, db_hi, Cfg::kIdesc, accum);
+              ptx::umma<kKind, kCtaGroup>(d_tmem, da_hi, db_lo, Cfg::kIdesc, 1u);
+              ptx::umma<kKind, kCtaGroup>(d_tmem, da_hi, db_hi, Cfg::kIdesc, 1u);
+            } else {
+              ptx::umma<kKind, kCtaGroup>(d_tmem, da_hi, db_hi, Cfg::kIdesc, accum);
+            }
+          }
+          ptx::umma_commit<kCtaGroup>(empty_bar(s), pair_mask);  // stage reusable when MMAs retire
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+        ptx::umma_commit<kCtaGroup>(tmem_full(acc), pair_mask);  // accumulator complete
+      }
+    }
+  }
+  // =========================== epilogue ===========================
+  else if (warp < 2 + Cfg::kNumEpilogueWarps) {
+    const uint32_t q = warp & 3u;  // TMEM lane quarter this warp may read
+    unsigned it = 0;
+    const uint32_t leader_tmem_empty0 =
+        (kCtaGroup == 2) ? ptx::mapa(tmem_empty(0), 0) : tmem_empty(0);
+    for (unsigned t = group_id; t < total_tiles; t += num_groups, ++it) {
+      unsigned b, tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, b, tm, tn);
+      const unsigned acc = it & 1u;
+      const uint32_t acc_ph = (it >> 1) & 1u;
+      bounded_wait<false>(tmem_full(acc), acc_ph, TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
+      ptx::tc_fence_after_sync();
+      const unsigned row = tm * Cfg::kTileM + cta_rank * Cfg::kBM + q * 32 + lane;
+      const unsigned col0 = tn * BN;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
+      if constexpr (kKind == ptx::MmaKind::TF32) {
+        float* crow = static_cast<float*>(p.C) + p.strideC * b +
+                      static_cast<unsigned long long>(row) * p.N + col0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (col0 + c * 32 >= p.N) break;  // warp-uniform
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(taddr + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const unsigned col = col0 + c * 32 + j;
+              if (col < p.N) {  // N % 4 == 0 on this path: a float4 is all in or all out
+                float4 v;
+                v.x = __uint_as_float(r[j + 0]);
+                v.y = __uint_as_float(r[j + 1]);
+                v.z = __uint_as_float(r[j + 2]);
+                v.w = __uint_as_float(r[j + 3]);
+                if (p.bias) {
+                  const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+                  v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+                }
+                *reinterpret_cast<float4*>(crow + c * 32 + j) = v;
+              }
+            }
+          }
+        }
+      } else {
+        int32_t* crow = static_cast<int32_t*>(p.C) + p.strideC * b +
+                        static_cast<unsigned long long>(row) * p.N + col0;
+        const int32_t* rsB = p.rsB + static_cast<size_t>(p.strideRsB) * b;
+        int32_t row_term = p.kterm;
+        if (row_ok) row_term += p.rsA[static_cast<size_t>(p.strideRsA) * b + row] * p.offB;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (col0 + c * 32 >= p.N) break;
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(taddr + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const unsigned col = col0 + c * 32 + j;
+              if (col < p.N) {  // N % 16 == 0 on this path
+                const int4 sb = __ldg(reinterpret_cast<const int4*>(rsB + col));
+                int4 v;
+                v.x = static_cast<int32_t>(r[j + 0]) + row_term + sb.x * p.offA;
+                v.y = static_cast<int32_t>(r[j + 1]) + row_term + sb.y * p.offA;
+                v.z = static_cast<int32_t>(r[j + 2]) + row_term + sb.z * p.offA;
+                v.w = static_cast<int32_t>(r[j + 3]) + row_term + sb.w * p.offA;
+                *reinterpret_cast<int4*>(crow + c * 32 + j) = v;
+              }
+            }
+          }
+        }
+      }
+      // accumulator buffer may be overwritten by the MMA of tile it+2
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (kCtaGroup == 2) ptx::mbar_arrive_cluster(leader_tmem_empty0 + 8u * acc);
+        else ptx::mbar_arrive(tmem_empty(acc));
+      }
+    }
+  }
+  // =========================== converters (kSplit) ===========================
+  else {
+    if constexpr (kSplit) {
+      const unsigned cthread = threadIdx.x - 32 * (2 + Cfg::kNumEpilogueWarps);
+      constexpr unsigned kCThreads = 32 * Cfg::kNumConvertWarps;
+      constexpr unsigned kVecs = Cfg::kRawBytes / 16;
+      static_assert(kVecs % kCThreads == 0, "converter loop must divide evenly");
+      const uint32_t leader_full_cvt0 = (kCtaGroup == 2) ? ptx::mapa(full_cvt(0), 0) : full_cvt(0);
+      int s = 0;
+      uint32_t ph = 0;
+      for (unsigned t = group_id; t < total_tiles; t += num_groups) {
+        for (unsigned kb = 0; kb < num_kb; ++kb) {
+          bounded_wait<false>(full_raw(s), ph, TFCCB200_DEV_TIMEOUT_CONVERT, ctl);
+          float4* raw = reinterpret_cast<float4*>(smem_gen + s * Cfg::kStageBytes);
+          float4* tail = reinterpret_cast<float4*>(smem_gen + s * Cfg::kStageBytes + Cfg::kRawBytes);
+          constexpr int kIter = kVecs / kCThreads;
+          constexpr int kUnroll = (kIter % 4 == 0) ? 4 : (kIter % 2 == 0 ? 2 : 1);
+#pragma unroll 1
+          for (int i0 = 0; i0 < kIter; i0 += kUnroll) {
+            float4 x[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) x[u] = raw[cthread + (i0 + u) * kCThreads];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+              float4 h, l;
+              h.x = __uint_as_float(__float_as_uint(x[u].x) & 0xFFFFE000u);
+              h.y = __uint_as_float(__float_as_uint(x[u].y) & 0xFFFFE000u);
+              h.z = __uint_as_float(__float_as_uint(x[u].z) & 0xFFFFE000u);
+              h.w = __uint_as_float(__float_as_uint(x[u].w) & 0xFFFFE000u);
+              uint32_t lx, ly, lz, lw;
+              asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lx) : "f"(x[u].x - h.x));
+              asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(ly) : "f"(x[u].y - h.y));
+              asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lz) : "f"(x[u].z - h.z));
+              asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lw) : "f"(x[u].w - h.w));
+              l.x = __uint_as_float(lx); l.y = __uint_as_float(ly);
+              l.z = __uint_as_float(lz); l.w = __uint_as_float(lw);
+              tail[cthread + (i0 + u) * kCThreads] = l;
+              if (p.write_head) raw[cthread + (i0 + u) * kCThreads] = h;
+            }
+          }
+          ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to tcgen05.mma
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kCtaGroup == 2) ptx::mbar_arrive_cluster(leader_full_cvt0 + 8u * s);
+            else ptx::mbar_arrive(full_cvt(s));
+          }
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  }
+
+  // ---- teardown: nobody leaves while a peer may still signal it; TMEM goes back ----
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait was abandoned: loads and MMAs may still be in flight.  Give them a
+    // bounded moment to land before shared and tensor memory are released.
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  if constexpr (kCtaGroup == 2) {
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc<kCtaGroup>(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+}  // namespace tfccb200

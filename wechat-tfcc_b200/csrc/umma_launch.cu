@@ -1,0 +1,248 @@
+// Host side of the tcgen05 GEMMs: tensor-map encoding, tile-shape choice and
+// launch (plain launch for one CTA per tile, cluster launch for CTA pairs).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "internal.h"
+#include "umma_gemm.cuh"
+
+namespace tfccb200 {
+
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                              const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled is a driver entry point; it is fetched through the
+// runtime so the library links against cudart only.
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeFn>(p);
+    }
+  });
+  return fn;
+}
+
+// 3-D map over a batch of row-major matrices: dim0 = contiguous elements of a
+// row, dim1 = rows, dim2 = batch entries.  The box is 128 bytes wide with the
+// 128-byte swizzle; out-of-range elements read as zero, which is what makes
+// ragged M, N and K tails free.
+bool make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base,
+               uint64_t row_elems, uint64_t rows, uint64_t batch, uint64_t batch_stride_elems,
+               uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {row_elems, rows, batch};
+  uint64_t bstride = batch_stride_elems ? batch_stride_elems : row_elems * rows;
+  cuuint64_t strides[2] = {row_elems * elem_bytes, bstride * elem_bytes};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / elem_bytes), box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <ptx::MmaKind kKind, bool kSplit, int kCtaGroup, int BN, int kStages>
+int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, UmmaGemmParams p,
+           int sm_count) {
+  using Cfg = UmmaGemmConfig<kKind, kSplit, kCtaGroup, BN, kStages>;
+  auto kernel = umma_gemm_kernel<kKind, kSplit, kCtaGroup, BN, kStages>;
+  // The opt-in shared-memory size is a per-device attribute of the function.
+  static std::atomic<unsigned long long> configured{0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (!(configured.load(std::memory_order_acquire) & bit)) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured.fetch_or(bit, std::memory_order_release);
+  }
+  p.tiles_m = (p.M + Cfg::kTileM - 1) / Cfg::kTileM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  const unsigned long long total =
+      static_cast<unsigned long long>(p.tiles_m) * p.tiles_n * p.batch;
+  if (total == 0 || total > 0x7fffffffull) return TFCCB200_EOVERFLOW;
+  unsigned groups = static_cast<unsigned>(sm_count / kCtaGroup);
+  if (total < groups) groups = static_cast<unsigned>(total);
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(groups * kCtaGroup, 1, 1);
+  cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCtaGroup;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  count_launch();
+  return TFCCB200_OK;
+}
+
+// Widest tile that still gives every SM (or SM pair) a tile; small problems
+// fall to narrower tiles so more SMs take part.
+int pick_bn(unsigned M, unsigned N, unsigned batch, int tile_m, int groups) {
+  const unsigned long long tm = (M + tile_m - 1) / tile_m;
+  for (int bn : {256, 128}) {
+    unsigned long long tiles = tm * ((N + bn - 1) / bn) * batch;
+    if (tiles >= static_cast<unsigned long long>(groups) && N >= static_cast<unsigned>(bn))
+      return bn;
+  }
+  if (N > 128 && tm * ((N + 127) / 128) * batch >= static_cast<unsigned long long>(groups) / 2)
+    return 128;
+  return 64;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+bool umma_sgemm_supported(const SgemmArgs& a) {
+  // TMA wants 16-byte aligned bases and row pitches; the epilogue stores float4.
+  if (a.K % 4 != 0 || a.N % 4 != 0) return false;
+  if (!aligned16(a.A) || !aligned16(a.B) || !aligned16(a.C)) return false;
+  if (a.bias && !aligned16(a.bias)) return false;
+  if (a.batch > 1) {
+    if (a.strideA % 4 != 0 || a.strideB % 4 != 0 || a.strideC % 4 != 0) return false;
+    // A non-zero batch stride must be the dense one: the tensor map describes
+    // whole matrices laid end to end.
+    if (a.strideA && a.strideA < a.M * a.K) return false;
+    if (a.strideB && a.strideB < a.K * a.N) return false;
+  }
+  return true;
+}
+
+int umma_sgemm(const SgemmArgs& a, bool pair) {
+  cudaError_t ce;
+  const DeviceInfo* di = current_device_info(&ce);
+  if (!di) return static_cast<int>(ce);
+  if (di->cc_major != 10) return TFCCB200_EUNSUPPORTED;
+  if (!umma_sgemm_supported(a)) return TFCCB200_EALIGN;
+
+  const bool a_batched = a.batch > 1 && a.strideA != 0;
+  const bool b_batched = a.batch > 1 && a.strideB != 0;
+  const int tile_m = pair ? 256 : 128;
+  const int groups = pair ? di->sm_count / 2 : di->sm_count;
+  const int bn = pick_bn(a.M, a.N, a.batch, tile_m, groups);
+  const int bn_local = pair ? bn / 2 : bn;
+
+  CUtensorMap ta, tb;
+  if (!make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.A, a.K, a.M, a_batched ? a.batch : 1,
+                 a.strideA, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+    return TFCCB200_EINVAL;
+  // B is the MN-major operand: 32-bit data needs the 32-byte-unit flavour of the swizzle.
+  if (!make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.B, a.N, a.K, b_batched ? a.batch : 1,
+                 a.strideB, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+    return TFCCB200_EINVAL;
+  (void)bn_local;
+
+  UmmaGemmParams p = {};
+  p.C = a.C;
+  p.bias = a.bias;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
+  p.strideC = a.strideC;
+  p.a_batched = a_batched; p.b_batched = b_batched;
+  p.write_head = 1;
+  p.status = a.status;
+  p.timeout_ns = kDefaultTimeoutNs;
+
+  constexpr auto T = ptx::MmaKind::TF32;
+  const bool split = a.precision == TFCCB200_PRECISION_FP32;
+  const int sms = di->sm_count;
+  if (split) {
+    if (!pair) {
+      if (bn == 256) return launch<T, true, 1, 256, 2>(a.stream, ta, tb, p, sms);
+      if (bn == 128) return launch<T, true, 1, 128, 3>(a.stream, ta, tb, p, sms);
+      return launch<T, true, 1, 64, 4>(a.stream, ta, tb, p, sms);
+    }
+    if (bn == 256) return launch<T, true, 2, 256, 3>(a.stream, ta, tb, p, sms);
+    if (bn == 128) return launch<T, true, 2, 128, 4>(a.stream, ta, tb, p, sms);
+    return launch<T, true, 2, 64, 5>(a.stream, ta, tb, p, sms);
+  }
+  if (!pair) {
+    if (bn == 256) return launch<T, false, 1, 256, 4>(a.stream, ta, tb, p, sms);
+    if (bn == 128) return launch<T, false, 1, 128, 6>(a.stream, ta, tb, p, sms);
+    return launch<T, false, 1, 64, 8>(a.stream, ta, tb, p, sms);
+  }
+  if (bn == 256) return launch<T, false, 2, 256, 6>(a.stream, ta, tb, p, sms);
+  if (bn == 128) return launch<T, false, 2, 128, 8>(a.stream, ta, tb, p, sms);
+  return launch<T, false, 2, 64, 8>(a.stream, ta, tb, p, sms);
+}
+
+bool umma_qgemm_supported(const QgemmArgs& a) {
+  if (a.K % 16 != 0 || a.N % 16 != 0) return false;
+  if (!aligned16(a.A) || !aligned16(a.B) || !aligned16(a.C) || !aligned16(a.rsB)) return false;
+  if (a.batch > 1) {
+    if (a.strideA % 16 != 0 || a.strideB % 16 != 0 || a.strideC % 4 != 0 ||
+        a.strideRsB % 4 != 0)
+      return false;
+    if (a.strideA && a.strideA < a.M * a.K) return false;
+    if (a.strideB && a.strideB < a.K * a.N) return false;
+  }
+  return true;
+}
+
+int umma_qgemm(const QgemmArgs& a, bool pair) {
+  cudaError_t ce;
+  const DeviceInfo* di = current_device_info(&ce);
+  if (!di) return static_cast<int>(ce);
+  if (di->cc_major != 10) return TFCCB200_EUNSUPPORTED;
+  if (!umma_qgemm_supported(a)) return TFCCB200_EALIGN;
+
+  const bool a_batched = a.batch > 1 && a.strideA != 0;
+  const bool b_batched = a.batch > 1 && a.strideB != 0;
+  const int tile_m = pair ? 256 : 128;
+  const int groups = pair ? di->sm_count / 2 : di->sm_count;
+  int bn = pick_bn(a.M, a.N, a.batch, tile_m, groups);
+  if (pair && bn < 256) bn = 256;  // a pair stages BN/2 int8 columns per CTA: 128 bytes minimum
+  if (!pair && bn < 128) bn = 128;
+
+  CUtensorMap ta, tb;
+  if (!make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.A, a.K, a.M, a_batched ? a.batch : 1,
+                 a.strideA, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+    return TFCCB200_EINVAL;
+  if (!make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.B, a.N, a.K, b_batched ? a.batch : 1,
+                 a.strideB, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+    return TFCCB200_EINVAL;
+
+  UmmaGemmParams p = {};
+  p.C = a.C;
+  p.rsA = a.rsA; p.rsB = a.rsB;
+  p.offA = a.offA; p.offB = a.offB;
+  p.kterm = static_cast<int32_t>(static_cast<uint32_t>(a.offA) * static_cast<uint32_t>(a.offB) *
+                                 a.K);
+  p.strideRsA = a.strideRsA; p.strideRsB = a.strideRsB;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
+  p.strideC = a.strideC;
+  p.a_batched = a_batched; p.b_batched = b_batched;
+  p.status = a.status;
+  p.timeout_ns = kDefaultTimeoutNs;
+
+  constexpr auto I = ptx::MmaKind::I8;
+  const int sms = di->sm_count;
+  if (!pair) {
+    if (bn == 256) return launch<I, false, 1, 256, 4>(a.stream, ta, tb, p, sms);
+    return launch<I, false, 1, 128, 6>(a.stream, ta, tb, p, sms);
+  }
+  return launch<I, false, 2, 256, 6>(a.stream, ta, tb, p, sms);
+}
+
+}  // namespace tfccb200
