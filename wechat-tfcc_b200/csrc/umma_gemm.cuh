@@ -23,8 +23,18 @@
 //                  canonical layout: 128B swizzle of 16-byte units for int8, of
 //                  32-byte units for fp32 (the TMA mode SWIZZLE_128B_ATOM_32B)
 //               (+ a second copy of both for the TF32 tails when kSplit)
-// Warps: 0 = TMA producer, 1 = MMA issuer and TMEM owner, 2..5 = epilogue
-// (one TMEM lane quarter each), 6.. = converters (kSplit only).
+// Warps without kSplit: 0 = TMA producer, 1 = MMA issuer and TMEM owner,
+// 2..5 = epilogue (one TMEM lane quarter each).
+//
+// With kSplit the tensor core's fp32 accumulator is not trusted over a long K:
+// it narrows every partial sum without round-to-nearest, which biases the
+// result by an amount that grows linearly with K (measured 7e-9 * K normwise).
+// So K is cut into chunks of `kb_per_chunk` k-blocks; each chunk is accumulated
+// in one of the two TMEM buffers starting from zero, and eight epilogue warps
+// add the finished chunk into fp32 registers with round-to-nearest adds while
+// the MMA issuer fills the other buffer.  The register budget is rebalanced
+// with setmaxnreg: warpgroup 0 = {TMA, MMA, 2 idle warps}, warpgroups 1-2 =
+// epilogue (hold a 128 x BN fp32 running sum), warpgroup 3 = converters.
 //
 // Every wait on an mbarrier is bounded: after `timeout_ns` the waiter raises a
 // CTA-wide abort flag, ORs a bit into *status and carries on without the data,
@@ -50,6 +60,8 @@ struct UmmaGemmParams {
   unsigned tiles_m, tiles_n;      // tile grid of one batch entry
   unsigned write_head;     // kSplit: 1 = store the truncated head back (independent of how
                            // the tensor core narrows fp32), 0 = feed the raw fp32 as head
+  unsigned kb_per_chunk;   // kSplit: k-blocks accumulated inside tensor memory before the
+                           // partial sum is promoted to registers (>= 1)
   int* status;             // device int or nullptr
   unsigned long long timeout_ns;
 };
@@ -75,9 +87,14 @@ struct UmmaGemmConfig {
   static constexpr uint32_t kBLayout =
       (kKind == ptx::MmaKind::TF32) ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
   static constexpr uint32_t kBSbo = (kKind == ptx::MmaKind::TF32) ? 512 : 1024;
-  static constexpr int kNumConvertWarps = kSplit ? 8 : 0;
-  static constexpr int kNumEpilogueWarps = 4;
-  static constexpr int kThreads = 32 * (2 + kNumEpilogueWarps + kNumConvertWarps);
+  static constexpr int kNumConvertWarps = kSplit ? 4 : 0;
+  static constexpr int kNumEpilogueWarps = kSplit ? 8 : 4;
+  static constexpr int kFirstEpilogueWarp = kSplit ? 4 : 2;  // kSplit: warps 2,3 idle (warpgroup fill)
+  static constexpr int kFirstConvertWarp = kFirstEpilogueWarp + kNumEpilogueWarps;
+  static constexpr int kThreads = 32 * (kFirstConvertWarp + kNumConvertWarps);
+  static constexpr int kEpiCols = kSplit ? BN / 2 : BN;  // accumulator columns owned by one thread
+  // setmaxnreg targets (kSplit): 128*40 + 256*200 + 128*56 = 63488 <= 65536 registers
+  static constexpr int kRegsControl = 40, kRegsEpilogue = 200, kRegsConvert = 56;
   static constexpr int kTmemCols = (2 * BN <= 32) ? 32 : 2 * BN;  // power of two by construction
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // +align slack
@@ -89,6 +106,9 @@ struct UmmaGemmConfig {
   static_assert((BN & (BN - 1)) == 0, "BN must be a power of two (TMEM allocation)");
   static_assert(kBNLocal * kElemBytes % 128 == 0, "B tile must be whole 128-byte boxes");
   static_assert(kSmemBytes <= 232448, "shared memory budget");
+  static_assert(!kSplit || kEpiCols % 16 == 0, "epilogue reads 16 columns at a time");
+  static_assert(!kSplit || (kFirstEpilogueWarp == 4 && kFirstConvertWarp == 12 && kThreads == 512),
+                "setmaxnreg assumes warpgroups {control, epilogue, epilogue, convert}");
 };
 
 struct UmmaCtl {
@@ -204,6 +224,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_gen;
 
+  // number of k-blocks per accumulator hand-off: the whole K unless partial sums are promoted
+  const unsigned kb_per_chunk = kSplit ? max(1u, p.kb_per_chunk) : max(1u, num_kb);
+
+  // Roles are split by warpgroup first, so that (kSplit) each warpgroup executes exactly
+  // one setmaxnreg at the top of the code it alone runs.
+  if (warp < Cfg::kFirstEpilogueWarp) {
+  if constexpr (kSplit) ptx::setmaxnreg_dec<Cfg::kRegsControl>();
   // =========================== TMA producer ===========================
   if (warp == 0) {
     if (lane == 0) {
@@ -248,137 +275,191 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     if (lane == 0 && is_leader) {
       int s = 0;
       uint32_t ph = 0;
-      unsigned it = 0;
+      unsigned it = 0;  // accumulator hand-offs so far (tiles, or chunks when kSplit)
       const uint16_t pair_mask = 0x3;
-      for (unsigned t = group_id; t < total_tiles; t += num_groups, ++it) {
-        const unsigned acc = it & 1u;
-        const uint32_t acc_ph = (it >> 1) & 1u;
-        bounded_wait<(kCtaGroup == 2)>(tmem_empty(acc), acc_ph ^ 1u, TFCCB200_DEV_TIMEOUT_MMA,
-                                       ctl);
-        ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (unsigned kb = 0; kb < num_kb; ++kb) {
-          if constexpr (kSplit) {
-            bounded_wait<(kCtaGroup == 2)>(full_cvt(s), ph, TFCCB200_DEV_TIMEOUT_MMA, ctl);
-          } else {
-            bounded_wait<false>(full_raw(s), ph, TFCCB200_DEV_TIMEOUT_MMA, ctl);
-          }
+      for (unsigned t = group_id; t < total_tiles; t += num_groups) {
+        for (unsigned kb0 = 0; kb0 < num_kb; kb0 += kb_per_chunk, ++it) {
+          const unsigned acc = it & 1u;
+          const uint32_t acc_ph = (it >> 1) & 1u;
+          bounded_wait<(kCtaGroup == 2)>(tmem_empty(acc), acc_ph ^ 1u, TFCCB200_DEV_TIMEOUT_MMA,
+                                         ctl);
           ptx::tc_fence_after_sync();
-          const uint32_t a_hi = smem_base + s * Cfg::kStageBytes;
-          const uint32_t b_hi = a_hi + Cfg::kABytes;
-          const uint32_t a_lo = a_hi + Cfg::kRawBytes;
-          const uint32_t b_lo = b_hi + Cfg::kRawBytes;
-#pragma unroll
-          for (int ks = 0; ks < Cfg::kKSteps; ++ks) {
-            const uint64_t da_hi = ptx::smem_desc(a_hi + ks * 32, 16, 1024, ptx::kLayoutSw128);
-            const uint64_t db_hi = ptx::smem_desc(b_hi + ks * Cfg::kBKStepBytes,
-                                                  Cfg::kBChunkBytes, Cfg::kBSbo, Cfg::kBLayout);
-            const uint32_t accum = (kb > 0 || ks > 0) ? 1u : 0u;
+          const uint32_t d_tmem = tmem_base + acc * BN;
+          const unsigned kb_end = min(num_kb, kb0 + kb_per_chunk);
+          for (unsigned kb = kb0; kb < kb_end; ++kb) {
             if constexpr (kSplit) {
-              const uint64_t da_lo = ptx::smem_desc(a_lo + ks * 32, 16, 1024, ptx::kLayoutSw128);
-              const uint64_t db_lo = ptx::smem_desc(b_lo + ks * Cfg::kBKStepBytes,
-                                                    Cfg::kBChunkBytes, Cfg::kBSbo, Cfg::kBLayout);
-              ptx::umma<kKind, kCtaGroup>(d_tmem, da_lo, db_hi, Cfg::kIdesc, accum);
-              ptx::umma<kKind, kCtaGroup>(d_tmem, da_hi, db_lo, Cfg::kIdesc, 1u);
-              ptx::umma<kKind, kCtaGroup>(d_tmem, da_hi, db_hi, Cfg::kIdesc, 1u);
+              bounded_wait<(kCtaGroup == 2)>(full_cvt(s), ph, TFCCB200_DEV_TIMEOUT_MMA, ctl);
             } else {
-              ptx::umma<kKind, kCtaGroup>(d_tmem, da_hi, db_hi, Cfg::kIdesc, accum);
+              bounded_wait<false>(full_raw(s), ph, TFCCB200_DEV_TIMEOUT_MMA, ctl);
             }
+            ptx::tc_fence_after_sync();
+            const uint32_t a_hi = smem_base + s * Cfg::kStageBytes;
+            const uint32_t b_hi = a_hi + Cfg::kABytes;
+            const uint32_t a_lo = a_hi + Cfg::kRawBytes;
+            const uint32_t b_lo = b_hi + Cfg::kRawBytes;
+#pragma unroll
+            for (int ks = 0; ks < Cfg::kKSteps; ++ks) {
+              const uint64_t da_hi = ptx::smem_desc(a_hi + ks * 32, 16, 1024, ptx::kLayoutSw128);
+              const uint64_t db_hi = ptx::smem_desc(b_hi + ks * Cfg::kBKStepBytes,
+                                                    Cfg::kBChunkBytes, Cfg::kBSbo, Cfg::kBLayout);
+              const uint32_t accum = (kb > kb0 || ks > 0) ? 1u : 0u;
+              if constexpr (kSplit) {
+                const uint64_t da_lo = ptx::smem_desc(a_lo + ks * 32, 16, 1024, ptx::kLayoutSw128);
+                const uint64_t db_lo = ptx::smem_desc(b_lo + ks * Cfg::kBKStepBytes,
+                                                      Cfg::kBChunkBytes, Cfg::kBSbo, Cfg::kBLayout);
+                ptx::umma<kKind, kCtaGroup>(d_tmem, da_lo, db_hi, Cfg::kIdesc, accum);
+                ptx::umma<kKind, kCtaGroup>(d_tmem, da_hi, db_lo, Cfg::kIdesc, 1u);
+                ptx::umma<kKind, kCtaGroup>(d_tmem, da_hi, db_hi, Cfg::kIdesc, 1u);
+              } else {
+                ptx::umma<kKind, kCtaGroup>(d_tmem, da_hi, db_hi, Cfg::kIdesc, accum);
+              }
+            }
+            ptx::umma_commit<kCtaGroup>(empty_bar(s), pair_mask);  // stage free when MMAs retire
+            if (++s == kStages) { s = 0; ph ^= 1u; }
           }
-          ptx::umma_commit<kCtaGroup>(empty_bar(s), pair_mask);  // stage reusable when MMAs retire
-          if (++s == kStages) { s = 0; ph ^= 1u; }
+          ptx::umma_commit<kCtaGroup>(tmem_full(acc), pair_mask);  // this accumulator is complete
         }
-        ptx::umma_commit<kCtaGroup>(tmem_full(acc), pair_mask);  // accumulator complete
       }
     }
   }
+  // (kSplit: warps 2 and 3 only fill the control warpgroup)
+  }
   // =========================== epilogue ===========================
-  else if (warp < 2 + Cfg::kNumEpilogueWarps) {
+  else if (warp < Cfg::kFirstConvertWarp) {
+    if constexpr (kSplit) ptx::setmaxnreg_inc<Cfg::kRegsEpilogue>();
     const uint32_t q = warp & 3u;  // TMEM lane quarter this warp may read
+    // kSplit: warps 4..7 own the left half of the columns, 8..11 the right half
+    const uint32_t col_half = kSplit ? (warp - Cfg::kFirstEpilogueWarp) >> 2 : 0u;
     unsigned it = 0;
     const uint32_t leader_tmem_empty0 =
         (kCtaGroup == 2) ? ptx::mapa(tmem_empty(0), 0) : tmem_empty(0);
-    for (unsigned t = group_id; t < total_tiles; t += num_groups, ++it) {
-      unsigned b, tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, b, tm, tn);
-      const unsigned acc = it & 1u;
-      const uint32_t acc_ph = (it >> 1) & 1u;
-      bounded_wait<false>(tmem_full(acc), acc_ph, TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
-      ptx::tc_fence_after_sync();
-      const unsigned row = tm * Cfg::kTileM + cta_rank * Cfg::kBM + q * 32 + lane;
-      const unsigned col0 = tn * BN;
-      const bool row_ok = row < p.M;
-      const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
-      if constexpr (kKind == ptx::MmaKind::TF32) {
-        float* crow = static_cast<float*>(p.C) + p.strideC * b +
-                      static_cast<unsigned long long>(row) * p.N + col0;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          if (col0 + c * 32 >= p.N) break;  // warp-uniform
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(taddr + c * 32, r);
-          ptx::tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const unsigned col = col0 + c * 32 + j;
-              if (col < p.N) {  // N % 4 == 0 on this path: a float4 is all in or all out
-                float4 v;
-                v.x = __uint_as_float(r[j + 0]);
-                v.y = __uint_as_float(r[j + 1]);
-                v.z = __uint_as_float(r[j + 2]);
-                v.w = __uint_as_float(r[j + 3]);
-                if (p.bias) {
-                  const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
-                  v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
-                }
-                *reinterpret_cast<float4*>(crow + c * 32 + j) = v;
-              }
-            }
-          }
-        }
-      } else {
-        int32_t* crow = static_cast<int32_t*>(p.C) + p.strideC * b +
-                        static_cast<unsigned long long>(row) * p.N + col0;
-        const int32_t* rsB = p.rsB + static_cast<size_t>(p.strideRsB) * b;
-        int32_t row_term = p.kterm;
-        if (row_ok) row_term += p.rsA[static_cast<size_t>(p.strideRsA) * b + row] * p.offB;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          if (col0 + c * 32 >= p.N) break;
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(taddr + c * 32, r);
-          ptx::tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const unsigned col = col0 + c * 32 + j;
-              if (col < p.N) {  // N % 16 == 0 on this path
-                const int4 sb = __ldg(reinterpret_cast<const int4*>(rsB + col));
-                int4 v;
-                v.x = static_cast<int32_t>(r[j + 0]) + row_term + sb.x * p.offA;
-                v.y = static_cast<int32_t>(r[j + 1]) + row_term + sb.y * p.offA;
-                v.z = static_cast<int32_t>(r[j + 2]) + row_term + sb.z * p.offA;
-                v.w = static_cast<int32_t>(r[j + 3]) + row_term + sb.w * p.offA;
-                *reinterpret_cast<int4*>(crow + c * 32 + j) = v;
-              }
-            }
-          }
-        }
-      }
-      // accumulator buffer may be overwritten by the MMA of tile it+2
+    auto release_acc = [&](unsigned acc) {
+      // the accumulator buffer may now be overwritten by the MMA issuer
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
         if constexpr (kCtaGroup == 2) ptx::mbar_arrive_cluster(leader_tmem_empty0 + 8u * acc);
         else ptx::mbar_arrive(tmem_empty(acc));
       }
+    };
+    for (unsigned t = group_id; t < total_tiles; t += num_groups) {
+      unsigned b, tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, b, tm, tn);
+      const unsigned row = tm * Cfg::kTileM + cta_rank * Cfg::kBM + q * 32 + lane;
+      const unsigned col0 = tn * BN + col_half * Cfg::kEpiCols;
+      const bool row_ok = row < p.M;
+      const uint32_t lane_addr = tmem_base + ((q * 32u) << 16) + col_half * Cfg::kEpiCols;
+
+      if constexpr (kSplit) {
+        // ---- promote every chunk's partial sum into registers (round-to-nearest adds) ----
+        float sum[Cfg::kEpiCols];
+#pragma unroll
+        for (int j = 0; j < Cfg::kEpiCols; ++j) sum[j] = 0.f;
+        for (unsigned kb0 = 0; kb0 < num_kb; kb0 += kb_per_chunk, ++it) {
+          const unsigned acc = it & 1u;
+          const uint32_t acc_ph = (it >> 1) & 1u;
+          bounded_wait<false>(tmem_full(acc), acc_ph, TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
+          ptx::tc_fence_after_sync();
+          const uint32_t taddr = lane_addr + acc * BN;
+#pragma unroll
+          for (int c = 0; c < Cfg::kEpiCols / 16; ++c) {
+            uint32_t r[16];
+            ptx::tmem_ld_32x16(taddr + c * 16, r);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sum[c * 16 + j] += __uint_as_float(r[j]);
+          }
+          release_acc(acc);
+        }
+        if (row_ok) {
+          float* crow = static_cast<float*>(p.C) + p.strideC * b +
+                        static_cast<unsigned long long>(row) * p.N + col0;
+#pragma unroll
+          for (int j = 0; j < Cfg::kEpiCols; j += 4) {
+            const unsigned col = col0 + j;
+            if (col < p.N) {  // N % 4 == 0 on this path: a float4 is all in or all out
+              float4 v = make_float4(sum[j], sum[j + 1], sum[j + 2], sum[j + 3]);
+              if (p.bias) {
+                const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+              }
+              *reinterpret_cast<float4*>(crow + j) = v;
+            }
+          }
+        }
+      } else {
+        const unsigned acc = it & 1u;
+        const uint32_t acc_ph = (it >> 1) & 1u;
+        ++it;
+        bounded_wait<false>(tmem_full(acc), acc_ph, TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
+        ptx::tc_fence_after_sync();
+        const uint32_t taddr = lane_addr + acc * BN;
+        if constexpr (kKind == ptx::MmaKind::TF32) {
+          float* crow = static_cast<float*>(p.C) + p.strideC * b +
+                        static_cast<unsigned long long>(row) * p.N + col0;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            if (col0 + c * 32 >= p.N) break;  // warp-uniform
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(taddr + c * 32, r);
+            ptx::tmem_ld_wait();
+            if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                const unsigned col = col0 + c * 32 + j;
+                if (col < p.N) {
+                  float4 v;
+                  v.x = __uint_as_float(r[j + 0]);
+                  v.y = __uint_as_float(r[j + 1]);
+                  v.z = __uint_as_float(r[j + 2]);
+                  v.w = __uint_as_float(r[j + 3]);
+                  if (p.bias) {
+                    const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+                    v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+                  }
+                  *reinterpret_cast<float4*>(crow + c * 32 + j) = v;
+                }
+              }
+            }
+          }
+        } else {
+          int32_t* crow = static_cast<int32_t*>(p.C) + p.strideC * b +
+                          static_cast<unsigned long long>(row) * p.N + col0;
+          const int32_t* rsB = p.rsB + static_cast<size_t>(p.strideRsB) * b;
+          int32_t row_term = p.kterm;
+          if (row_ok) row_term += p.rsA[static_cast<size_t>(p.strideRsA) * b + row] * p.offB;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            if (col0 + c * 32 >= p.N) break;
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(taddr + c * 32, r);
+            ptx::tmem_ld_wait();
+            if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                const unsigned col = col0 + c * 32 + j;
+                if (col < p.N) {  // N % 16 == 0 on this path
+                  const int4 sb = __ldg(reinterpret_cast<const int4*>(rsB + col));
+                  int4 v;
+                  v.x = static_cast<int32_t>(r[j + 0]) + row_term + sb.x * p.offA;
+                  v.y = static_cast<int32_t>(r[j + 1]) + row_term + sb.y * p.offA;
+                  v.z = static_cast<int32_t>(r[j + 2]) + row_term + sb.z * p.offA;
+                  v.w = static_cast<int32_t>(r[j + 3]) + row_term + sb.w * p.offA;
+                  *reinterpret_cast<int4*>(crow + c * 32 + j) = v;
+                }
+              }
+            }
+          }
+        }
+        release_acc(acc);
+      }
     }
   }
   // =========================== converters (kSplit) ===========================
   else {
     if constexpr (kSplit) {
-      const unsigned cthread = threadIdx.x - 32 * (2 + Cfg::kNumEpilogueWarps);
+      ptx::setmaxnreg_dec<Cfg::kRegsConvert>();
+      const unsigned cthread = threadIdx.x - 32 * Cfg::kFirstConvertWarp;
       constexpr unsigned kCThreads = 32 * Cfg::kNumConvertWarps;
       constexpr unsigned kVecs = Cfg::kRawBytes / 16;
       static_assert(kVecs % kCThreads == 0, "converter loop must divide evenly");

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 #include "internal.h"
@@ -111,6 +112,11 @@ int pick_bn(unsigned M, unsigned N, unsigned batch, int tile_m, int groups) {
   return 64;
 }
 
+int env_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  return (v && *v) ? std::atoi(v) : fallback;
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
@@ -160,7 +166,16 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
   p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
   p.strideC = a.strideC;
   p.a_batched = a_batched; p.b_batched = b_batched;
-  p.write_head = 1;
+  // Tuning knobs, read once.  TFCCB200_WRITE_HEAD=1 makes the converters store the
+  // truncated TF32 head back over the raw tile; by default the raw fp32 tile is the
+  // head operand, because the tensor core ignores the 13 low mantissa bits itself
+  // (both settings give bit-identical products; the default saves shared-memory
+  // stores).  TFCCB200_KB_PER_CHUNK = k-blocks (32 elements of K each) a
+  // tensor-memory accumulator sums before its partial is promoted to registers.
+  static const int env_write_head = env_int("TFCCB200_WRITE_HEAD", 0);
+  static const int env_kb_per_chunk = env_int("TFCCB200_KB_PER_CHUNK", 4);
+  p.write_head = env_write_head ? 1 : 0;
+  p.kb_per_chunk = env_kb_per_chunk > 0 ? env_kb_per_chunk : 4;
   p.status = a.status;
   p.timeout_ns = kDefaultTimeoutNs;
 
