@@ -1,0 +1,459 @@
+"""Benchmark of the TFCC matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extra]
+
+Headline workload (one "step"): the fp32 GEMM A[8192,8192] . B[8192,8192] through
+``blas.matmul`` (3xTF32 on tcgen05 tensor cores).  With N > 1 ranks B is column-sharded,
+every rank multiplies its shard and one NCCL all-gather plus a local interleave leaves the
+full row-major C on every rank (strong scaling: the job is the same GEMM at every N).
+
+One JSON line is printed by rank 0.  ``value`` is TFLOP/s (2*M*N*K per step) with operands
+resident in HBM; ``e2e`` is the same metric through the host-buffer C-ABI call, uploads
+and download inside the timed region; ``roofline`` describes the tcgen05 kernel;
+``cpu_baseline`` is the CPU oracle (numpy sgemm, all host threads) timed on a bounded
+row panel of the same GEMM; ``extra`` holds the other configurations of the path
+(attention-shaped batches, int8, M<=8 streaming) measured with an L2 flush between
+launches.  ``--impl reference`` times only the CPU implementation.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+from __graft_entry__ import load_oracle, load_package  # noqa: E402
+
+M = N = K = 8192   # --size overrides this for profiler captures; the headline is 8192
+FLOP_PER_STEP = 2.0 * M * N * K
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one umma_gemm_kernel launch, from the ncu
+# capture summarised in profiles/ (captured at 4096^3 and scaled by the tiles processed,
+# traffic per tile being constant for this kernel).  None until a capture exists.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                     "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                parts = [x.strip() for x in out.stdout.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        mx = max((int(s[1]) for s in self.samples if s[1].isdigit()), default=None)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": reasons,
+                "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def blas_threads() -> int:
+    """Threads numpy's BLAS really uses (falls back to the visible core count)."""
+    try:
+        from threadpoolctl import threadpool_info
+        n = [p.get("num_threads", 0) for p in threadpool_info() if p.get("user_api") == "blas"]
+        if n:
+            return int(max(n))
+    except Exception:
+        pass
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+def cpu_sgemm_panel(seconds_target: float = 12.0):
+    """The oracle's fp32 GEMM (numpy sgemm, every host thread) on a bounded sample of the
+    8192^3 problem: a row panel sized for about `seconds_target` of CPU work, or the whole
+    GEMM repeated when one pass is shorter than that.  Returns (TFLOP/s, threads, text)."""
+    orc = load_oracle()
+    rng = np.random.default_rng(4)
+    b = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    rows = 64
+    a = rng.uniform(-1, 1, (rows, K)).astype(np.float32)
+    orc.blas_matmul(a, b, dtype=np.float32)  # warm the BLAS threads
+    t0 = time.perf_counter()
+    orc.blas_matmul(a, b, dtype=np.float32)
+    dt = time.perf_counter() - t0
+    rate = 2.0 * rows * N * K / dt
+    rows = int(min(M, max(64, (seconds_target * rate) / (2.0 * N * K) // 64 * 64)))
+    a = rng.uniform(-1, 1, (rows, K)).astype(np.float32)
+    orc.blas_matmul(a, b, dtype=np.float32)
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        orc.blas_matmul(a, b, dtype=np.float32)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds_target * 0.8 or reps >= 50:
+            break
+    return (2.0 * rows * N * K * reps / dt / 1e12, blas_threads(),
+            f"rows 0..{rows} of the {M}^3 GEMM x {reps} passes ({dt:.2f} s)")
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    sample = ""
+    cores = 1
+    for i in range(args.warmup + args.steps):
+        v, cores, sample = cpu_sgemm_panel(seconds_target=max(0.5, 60.0 / (args.warmup + args.steps)))
+        if i >= args.warmup:
+            vals.append(v)
+    value = float(np.mean(vals))
+    line = {
+        "impl": "reference", "metric": f"fp32 matmul TFLOP/s ({M}^3)", "value": value,
+        "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": FLOP_PER_STEP / (value * 1e12) * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"cfg5-large: fp32 A[{M},{K}] x B[{K},{N}], U(-1,1), seed 4",
+                   "note": "CPU arm: oneDNN v1.8.1 (the reference's fp32 backend) is not in the "
+                           "reference tree and cannot be built; the oracle's numpy sgemm stands in"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def flush_l2(torch, scratch):
+    scratch.add_(1)  # read+write a buffer larger than L2
+
+
+def time_launches(torch, fn, iters, flush=None):
+    """Average device time of `fn` over `iters` launches, each bracketed by events, with an
+    optional L2 flush before every launch (not timed)."""
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(iters)]
+    for a, b in evs:
+        if flush is not None:
+            flush()
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) for a, b in evs)
+    return float(np.mean(ts)), float(ts[len(ts) // 2])
+
+
+def extra_measurements(torch, pkg, dev, peaks):
+    """Other configurations of the path, single GPU, L2 flushed between launches."""
+    lib = pkg.lib
+    sess = pkg.session.get_session(dev)
+    rng = np.random.default_rng(5)
+    scratch = torch.zeros(96 * 1024 * 1024, dtype=torch.float32, device=dev)  # 384 MB > L2
+    fl = lambda: flush_l2(torch, scratch)
+    out = {}
+    to = lambda x: torch.from_numpy(x).to(dev)
+
+    def sgemm_case(name, a, b, bias=None, iters=30, precision="fp32"):
+        ta, tb = to(a), to(b)
+        tbias = to(bias) if bias is not None else None
+        fn = lambda: pkg.blas.matmul(ta, tb, tbias, precision=precision)
+        for _ in range(3):
+            fn()
+        mean_ms, med_ms = time_launches(torch, fn, iters, fl)
+        m, k, n = a.shape[-2], a.shape[-1], b.shape[-1]
+        batch = max(int(np.prod(a.shape[:-2])), int(np.prod(b.shape[:-2])), 1)
+        flop = 2.0 * m * n * k * batch
+        nbytes = 4.0 * (a.size + b.size + batch * m * n)
+        out[name] = {"us": med_ms * 1e3, "tflops": flop / (med_ms * 1e-3) / 1e12,
+                     "gbs": nbytes / (med_ms * 1e-3) / 1e9,
+                     "hbm_frac": nbytes / (med_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+
+    # cfg1
+    sgemm_case("cfg1_32x512x2048", rng.uniform(-1, 1, (32, 512)).astype(np.float32),
+               rng.normal(0, 0.02, (512, 2048)).astype(np.float32))
+    # cfg2: attention-shaped batches
+    q = rng.normal(0, 1, (96, 128, 64)).astype(np.float32)
+    kt = rng.normal(0, 1, (96, 64, 128)).astype(np.float32)
+    pm = rng.uniform(0, 1, (96, 128, 128)).astype(np.float32)
+    v = rng.normal(0, 1, (96, 128, 64)).astype(np.float32)
+    sgemm_case("cfg2_qk_96x128x64x128", q, kt)
+    sgemm_case("cfg2_pv_96x128x128x64", pm, v)
+    # cfg4-shaped dense layers (batch folded into rows)
+    x = rng.normal(0, 1, (8, 128, 768)).astype(np.float32)
+    sgemm_case("cfg4_ffn1_1024x768x3072", x, rng.normal(0, 0.02, (768, 3072)).astype(np.float32),
+               bias=np.zeros(3072, np.float32))
+    # cfg5 skinny sweep
+    w = rng.normal(0, 0.02, (4096, 16384)).astype(np.float32)
+    for m in (1, 4, 8):
+        sgemm_case(f"cfg5_gemv_M{m}", rng.normal(0, 1, (m, 4096)).astype(np.float32), w, iters=40)
+    del w
+    # TF32 single pass on the headline shape (what one MMA per product reaches)
+    a8 = torch.empty((M, K), dtype=torch.float32, device=dev).uniform_(-1, 1)
+    b8 = torch.empty((K, N), dtype=torch.float32, device=dev).uniform_(-1, 1)
+    fn = lambda: pkg.blas.matmul(a8, b8, precision="tf32")
+    for _ in range(2):
+        fn()
+    _, med = time_launches(torch, fn, 5)
+    out["tf32_single_pass_8192"] = {"us": med * 1e3, "tflops": FLOP_PER_STEP / (med * 1e-3) / 1e12}
+    del a8, b8
+
+    # cfg3 int8 (M=256) and the compute-bound int8 point (M=4096)
+    for m in (256, 4096):
+        qa = to(rng.integers(0, 256, (m, 4096), dtype=np.uint8))
+        qb = to(rng.integers(-127, 128, (4096, 4096), dtype=np.int8))
+        ra = pkg.quantization.reduce_sum(qa, True)
+        rb = pkg.quantization.reduce_sum(qb, False)
+        c = torch.empty((m, 4096), dtype=torch.int32, device=dev)
+        stream = sess.stream_ptr
+
+        def fn():
+            st = lib.tfccb200_qgemm_u8s8s32(stream, qa.data_ptr(), 0, ra.data_ptr(), 0, -128,
+                                            qb.data_ptr(), 0, rb.data_ptr(), 0, 0, c.data_ptr(),
+                                            m * 4096, m, 4096, 4096, 1, sess.status_ptr)
+            assert st == 0, st
+        for _ in range(3):
+            fn()
+        _, med = time_launches(torch, fn, 30, fl)
+        ops = 2.0 * m * 4096 * 4096
+        nbytes = m * 4096 + 4096 * 4096 + 4 * m * 4096 + 4 * m + 4 * 4096
+        out[f"cfg3_int8_M{m}"] = {"us": med * 1e3, "tops": ops / (med * 1e-3) / 1e12,
+                                  "gbs": nbytes / (med * 1e-3) / 1e9,
+                                  "hbm_frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        if m == 256:
+            f1 = lambda: pkg.quantization.reduce_sum(qa, True)
+            f2 = lambda: pkg.quantization.reduce_sum(qb, False)
+            for f, nm, nb in ((f1, "reduce_sum_rows_256x4096", m * 4096),
+                              (f2, "reduce_sum_cols_4096x4096", 4096 * 4096)):
+                for _ in range(3):
+                    f()
+                _, med = time_launches(torch, f, 20, fl)
+                out[nm] = {"us": med * 1e3, "gbs": nb / (med * 1e-3) / 1e9}
+    sess.sync()
+    return out
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    pkg = load_package()
+    peaks = measured_peaks()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert N % world == 0
+    ns = N // world
+
+    # ---- synthetic operands (seed 4, U(-1,1)); every rank holds A and its column shard of B
+    g = torch.Generator(device=dev)
+    g.manual_seed(4)
+    a = torch.empty((M, K), dtype=torch.float32, device=dev).uniform_(-1, 1, generator=g)
+    b_full = torch.empty((K, N), dtype=torch.float32, device=dev).uniform_(-1, 1, generator=g)
+    b = b_full[:, rank * ns:(rank + 1) * ns].contiguous() if world > 1 else b_full
+    if world > 1:
+        del b_full
+    staging = torch.empty((world, M, ns), dtype=torch.float32, device=dev) if world > 1 else None
+    c_out = torch.empty((M, N), dtype=torch.float32, device=dev) if world > 1 else None
+    sess = pkg.session.get_session(dev)
+
+    def step():
+        if world == 1:
+            return pkg.blas.matmul(a, b)
+        return pkg.parallel.nsplit_matmul(a, b, staging=staging, out=c_out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    launches0 = pkg.launch_count()
+    with sampler:
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+    launches = pkg.launch_count() - launches0
+    ms_total = e0.elapsed_time(e1)
+    sess.sync()
+
+    # device time of the GEMM launch alone for the roofline: at one GPU that is the step
+    # itself; with shards, a train of local products between two events
+    if world == 1:
+        kern_mean_ms = ms_total / args.steps
+    else:
+        reps = max(3, min(args.steps, 20))
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record()
+        for _ in range(reps):
+            pkg.blas.matmul(a, b)
+        k1.record()
+        torch.cuda.synchronize()
+        kern_mean_ms = k0.elapsed_time(k1) / reps
+
+    # ---- end to end: host buffers in, host buffer out, through the C-ABI host entry point
+    e2e_steps = max(1, min(args.steps, 3))
+    ha = torch.empty((M, K), dtype=torch.float32).pin_memory()
+    hb = torch.empty((K, ns), dtype=torch.float32).pin_memory()
+    hc = torch.empty((M, ns), dtype=torch.float32).pin_memory()
+    ha.copy_(a.cpu())
+    hb.copy_(b.cpu())
+    h_full = torch.empty((M, N), dtype=torch.float32).pin_memory() if world > 1 else None
+
+    def e2e_step():
+        if world == 1:
+            st = pkg.lib.tfccb200_sgemm_host(sess.stream_ptr, ha.data_ptr(), 0, hb.data_ptr(), 0,
+                                             hc.data_ptr(), M * ns, None, M, ns, K, 1, 0)
+            assert st == 0, st
+        else:
+            da = ha.to(dev, non_blocking=True)
+            db = hb.to(dev, non_blocking=True)
+            full = pkg.parallel.nsplit_matmul(da, db, staging=staging, out=c_out)
+            h_full.copy_(full, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    h2d = 4 * (M * K + K * ns)
+    d2h = 4 * (M * N if world > 1 else M * ns)
+
+    # ---- max over ranks
+    t = torch.tensor([ms_total, e2e_s * 1e3, float(launches)], dtype=torch.float64, device=dev)
+    if world > 1:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        ms_total, e2e_ms, launches = float(tmax[0]), float(tmax[1]), int(tsum[2])
+    else:
+        e2e_ms = float(t[1])
+
+    if rank == 0:
+        ms_per_step = ms_total / args.steps
+        value = FLOP_PER_STEP / (ms_per_step * 1e-3) / 1e12
+        e2e_value = FLOP_PER_STEP / (e2e_ms / e2e_steps * 1e-3) / 1e12
+        kern_flop = FLOP_PER_STEP / world
+        achieved = kern_flop / (kern_mean_ms * 1e-3) / 1e12
+        tensor_peak = peaks["bf16_tflops"] / 2.0 / 3.0
+        line = {
+            "metric": f"fp32 matmul TFLOP/s ({M}^3)", "value": value, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, fp32 accumulation)",
+            "data": "synthetic",
+            "config": {
+                "workload": f"cfg5-large: fp32 A[{M},{K}] x B[{K},{N}], U(-1,1), seed 4",
+                "parallelism": "single GPU" if world == 1 else
+                               f"N-split x{world}: B column shards, NCCL all-gather of C + interleave",
+                "l2": "operands (256 MiB each) exceed the 126 MB L2; no flush between steps",
+                "timing": "CUDA events on the launching stream, max over ranks"},
+            "roofline": {
+                "bound": "tensor", "kernel": "umma_gemm_kernel<TF32, split, cta_group::2, BN=256>",
+                "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
+                "frac": achieved / tensor_peak,
+                "peak_basis": f"{peaks['source']} bf16 {peaks['bf16_tflops']} TFLOP/s / 2 "
+                              "(TF32 runs at half the bf16 rate) / 3 (MMAs per fp32 product)",
+                "executed_tf32_tflops": 3.0 * achieved,
+                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "algorithmic_bytes": 4 * (M * K + K * ns + M * ns)},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": launches,
+            "clocks": sampler.summary(),
+        }
+        if world == 1:
+            if not args.no_cpu:
+                v, cores, sample = cpu_sgemm_panel()
+                line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cores,
+                                        "kind": "port", "sample": sample}
+            if not args.no_extra:
+                line["extra"] = extra_measurements(torch, pkg, dev, peaks)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the secondary configurations (headline line only)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--size", type=int, default=8192,
+                    help="edge of the square GEMM (profiler captures use a smaller one)")
+    args = ap.parse_args()
+    global M, N, K, FLOP_PER_STEP
+    M = N = K = args.size
+    FLOP_PER_STEP = 2.0 * M * N * K
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,185 @@
+"""fp32 matmul parity on the GPU, through the package's operator (which calls the C ABI).
+
+Tolerances.  FP32 mode: normwise relative error against the float64 product <= 1e-5 (the
+stated target), and the reference's own predicate ``is_similar`` (|a-b| < 1e-3|a+b| or
+< 1e-5, tfcc/core/utils/tfcc_debugutils.cpp:102-127) against the reference generator's
+expectation.  TF32 mode (opt-in): normwise <= 2e-3.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_cases
+
+pytestmark = pytest.mark.gpu
+TOL_FP32 = 1e-5
+TOL_TF32 = 2e-3
+
+
+def dev_of():
+    return torch.device("cuda:0")
+
+
+def run(pkg, a, b, c=None, **kw):
+    d = dev_of()
+    t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to(d)
+    out = pkg.blas.matmul(t(a), t(b), t(c) if c is not None else None, **kw)
+    pkg.session.get_session(d).sync()
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("key,prefix", [("blas_matmul", "blas/matmul"),
+                                        ("blas_matmulwithblas", "blas/matmulwithblas")])
+def test_reference_generator_cases(pkg, orc, golden, key, prefix):
+    """BlasTest.matmul / matmul_with_blas (tfcc/test/blas.cpp:34-61): all four batch layouts,
+    m,n,k in [1,100), values U(-1,1)."""
+    for i, case in golden_cases(golden[key], prefix):
+        got = run(pkg, case["a"], case["b"], case.get("c"))
+        assert got.shape == case["expect"].shape, i
+        assert orc.is_similar(got, case["expect"]), i
+        truth = orc.blas_matmul(case["a"], case["b"], case.get("c"))
+        assert orc.normwise_rel_error(got, truth) < TOL_FP32, i
+
+
+@pytest.mark.parametrize("path", ["simt", "umma", "umma2", "auto"])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 32), (300, 516, 132), (129, 260, 36), (1, 64, 64),
+                                   (257, 1028, 1000), (1024, 768, 768)])
+def test_paths_agree_with_float64_product(pkg, orc, path, m, n, k):
+    rng = np.random.default_rng(m * 7 + n * 3 + k)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.normal(0, 0.5, (k, n)).astype(np.float32)
+    c = rng.normal(0, 1, n).astype(np.float32)
+    truth = orc.blas_matmul(a, b, c)
+    got = run(pkg, a, b, c, path=path)
+    assert orc.normwise_rel_error(got, truth) < TOL_FP32
+
+
+@pytest.mark.parametrize("path", ["umma", "umma2", "simt"])
+def test_batched_layouts(pkg, orc, path):
+    rng = np.random.default_rng(5)
+    shapes = [((6, 128, 64), (6, 64, 128)),       # equal ranks
+              ((3, 2, 40, 64), (3, 2, 64, 72)),   # rank 4
+              ((5, 70, 96), (96, 132)),           # rank-2 B shared (folds into rows)
+              ((50, 96), (4, 96, 68))]            # rank-2 A shared
+    for sa, sb in shapes:
+        a = rng.uniform(-1, 1, sa).astype(np.float32)
+        b = rng.uniform(-1, 1, sb).astype(np.float32)
+        got = run(pkg, a, b, path=path)
+        truth = orc.blas_matmul(a, b)
+        assert got.shape == truth.shape
+        assert orc.normwise_rel_error(got, truth) < TOL_FP32, (sa, sb)
+
+
+def test_tensor_core_path_rejects_unaligned_pitch(pkg):
+    rng = np.random.default_rng(1)
+    a = rng.uniform(-1, 1, (64, 33)).astype(np.float32)
+    b = rng.uniform(-1, 1, (33, 64)).astype(np.float32)
+    with pytest.raises(pkg.exceptions.InvalidArgumentError):
+        run(pkg, a, b, path="umma")
+
+
+def test_config1_single_matmul(pkg, orc):
+    rng = np.random.default_rng(0)
+    a = rng.uniform(-1, 1, (32, 512)).astype(np.float32)
+    b = rng.normal(0, 0.02, (512, 2048)).astype(np.float32)
+    got = run(pkg, a, b)
+    assert orc.normwise_rel_error(got, orc.blas_matmul(a, b)) < TOL_FP32
+    assert orc.is_similar(got, orc.blas_matmul(a, b, dtype=np.float32))
+
+
+def test_config2_attention_batches(pkg, orc):
+    rng = np.random.default_rng(1)
+    q, k, v = (rng.normal(0, 1, (96, 128, 64)).astype(np.float32) for _ in range(3))
+    kt = np.ascontiguousarray(k.transpose(0, 2, 1))
+    s_truth = orc.blas_matmul(q, kt)
+    s = run(pkg, q, kt)
+    assert orc.normwise_rel_error(s, s_truth) < TOL_FP32
+    # row softmax of S/8 in fp32 from the oracle's S, so both sides multiply the same P
+    z = (s_truth.astype(np.float32) / np.float32(8.0))
+    z = np.exp(z - z.max(axis=-1, keepdims=True))
+    p = (z / z.sum(axis=-1, keepdims=True)).astype(np.float32)
+    o = run(pkg, p, v)
+    assert orc.normwise_rel_error(o, orc.blas_matmul(p, v)) < TOL_FP32
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 8])
+def test_skinny_decode_shapes(pkg, orc, m):
+    rng = np.random.default_rng(50 + m)
+    w = rng.normal(0, 0.02, (4096, 16384)).astype(np.float32)
+    x = rng.normal(0, 1, (m, 4096)).astype(np.float32)
+    bias = rng.normal(0, 1, 16384).astype(np.float32)
+    truth = orc.blas_matmul(x, w, bias)
+    for path in ("skinny", "auto"):
+        got = run(pkg, x, w, bias, path=path)
+        assert orc.normwise_rel_error(got, truth) < TOL_FP32
+
+
+def test_skinny_ragged_and_batched(pkg, orc):
+    rng = np.random.default_rng(9)
+    x = rng.normal(0, 1, (3, 5, 333)).astype(np.float32)
+    w = rng.normal(0, 1, (3, 333, 1100)).astype(np.float32)
+    got = run(pkg, x, w, path="skinny")
+    assert orc.normwise_rel_error(got, orc.blas_matmul(x, w)) < TOL_FP32
+
+
+def test_tf32_mode_has_its_own_tolerance(pkg, orc):
+    rng = np.random.default_rng(2)
+    a = rng.uniform(-1, 1, (512, 1024)).astype(np.float32)
+    b = rng.uniform(-1, 1, (1024, 512)).astype(np.float32)
+    truth = orc.blas_matmul(a, b)
+    for path in ("umma", "umma2"):
+        err = orc.normwise_rel_error(run(pkg, a, b, path=path, precision="tf32"), truth)
+        assert 1e-5 < err < TOL_TF32   # really a single TF32 pass, and within its bound
+
+
+def test_large_gemm_sampled_rows_and_linearity(pkg, orc):
+    """4096 x 8192 x 8192 on the CTA-pair path: sampled rows against float64, bit-for-bit
+    repeatability, and exact scaling by a power of two (a property that holds at any size)."""
+    d = dev_of()
+    g = torch.Generator(device=d)
+    g.manual_seed(4)
+    a = torch.empty((4096, 8192), dtype=torch.float32, device=d).uniform_(-1, 1, generator=g)
+    b = torch.empty((8192, 8192), dtype=torch.float32, device=d).uniform_(-1, 1, generator=g)
+    c1 = pkg.blas.matmul(a, b)
+    c2 = pkg.blas.matmul(a, b)
+    c4 = pkg.blas.matmul(a * 4.0, b)
+    pkg.session.get_session(d).sync()
+    assert torch.equal(c1, c2)
+    assert torch.equal(c4, c1 * 4.0)
+    rows = np.sort(np.random.default_rng(0).choice(4096, 64, replace=False))
+    truth = a[rows].double().cpu().numpy() @ b.double().cpu().numpy()
+    assert orc.normwise_rel_error(c1[rows].cpu().numpy(), truth) < TOL_FP32
+
+
+def test_empty_operand_returns_result_shape(pkg):
+    d = dev_of()
+    out = pkg.blas.matmul(torch.zeros((0, 5), device=d), torch.zeros((5, 7), device=d))
+    assert tuple(out.shape) == (0, 7)
+
+
+def test_host_buffer_entry_point(pkg, orc):
+    rng = np.random.default_rng(12)
+    a = rng.uniform(-1, 1, (3, 200, 260)).astype(np.float32)
+    b = rng.uniform(-1, 1, (260, 516)).astype(np.float32)
+    c = rng.uniform(-1, 1, 516).astype(np.float32)
+    got = pkg.blas.matmul_host(a, b, c)
+    assert orc.normwise_rel_error(got, orc.blas_matmul(a, b, c)) < TOL_FP32
+    x = rng.normal(0, 1, (2, 1024)).astype(np.float32)
+    w = rng.normal(0, 1, (1024, 2048)).astype(np.float32)
+    assert orc.normwise_rel_error(pkg.blas.matmul_host(x, w), orc.blas_matmul(x, w)) < TOL_FP32
+
+
+def test_head_truncation_setting_does_not_change_bits(pkg):
+    """The library feeds raw fp32 tiles as the TF32 head operand.  That is only right if the
+    tensor core ignores the 13 low mantissa bits; masking them explicitly on the host must
+    then give the same single-pass product bit for bit."""
+    d = dev_of()
+    g = torch.Generator(device=d)
+    g.manual_seed(9)
+    a = torch.empty((256, 512), dtype=torch.float32, device=d).uniform_(-1, 1, generator=g)
+    b = torch.empty((512, 256), dtype=torch.float32, device=d).uniform_(-1, 1, generator=g)
+    mask = lambda t: (t.view(torch.int32) & -8192).view(torch.float32)
+    c_raw = pkg.blas.matmul(a, b, precision="tf32", path="umma")
+    c_msk = pkg.blas.matmul(mask(a), mask(b), precision="tf32", path="umma")
+    pkg.session.get_session(d).sync()
+    assert torch.equal(c_raw, c_msk)
