@@ -406,7 +406,7 @@ def run_ours(args):
                 "workload": f"cfg5-large: fp32 A[{M},{K}] x B[{K},{N}], U(-1,1), seed 4",
                 "parallelism": "single GPU" if world == 1 else
                                f"N-split x{world}: B column shards, NCCL all-gather of C + interleave",
-                "l2": "operands (256 MiB each) exceed the 126 MB L2; no flush between steps",
+                "l2": f"operands ({4 * M * K >> 20} MiB each) exceed the 126 MB L2; no flush between steps",
                 "timing": "CUDA events on the launching stream, max over ranks"},
             "roofline": {
                 "bound": "tensor", "kernel": "umma_gemm_kernel<TF32, split, cta_group::2, BN=256>",
