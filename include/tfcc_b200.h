@@ -39,6 +39,7 @@ extern "C" {
 #define TFCCB200_EOVERFLOW -4   /* an element count does not fit the 32-bit TFCC Shape */
 #define TFCCB200_EUNSUPPORTED -5/* forced kernel path cannot run this problem          */
 #define TFCCB200_EDEVICE -6     /* a kernel gave up a bounded wait (see device_status) */
+#define TFCCB200_ESTATICLIMIT -7 /* tfccb200_sgemm_skinny_static: built-in scratch too small  */
 
 /* ---- precision modes of the fp32 GEMM ----------------------------------- */
 /* FP32:  fp32 result.  Tensor-core tiles split every operand into a TF32 head
@@ -153,6 +154,36 @@ TFCCB200_API int tfccb200_reduce_sum_s8(void* stream, const int8_t* src, unsigne
                            unsigned cols, int row_flag, int32_t* dst);
 TFCCB200_API int tfccb200_reduce_sum_s16(void* stream, const int16_t* src, unsigned batch, unsigned rows,
                             unsigned cols, int row_flag, int32_t* dst);
+
+/*
+ * C = A . B (+ bias) for M <= 8, single matrices, fp32 -- the decode / GEMV shape -- for
+ * callers that have no device memory to lend.  This entry point has no counterpart in the
+ * reference.
+ *
+ * Who needs it: an embedder that hands all of HBM to its own arena at start-up and runs with
+ * device allocation switched off afterwards, or a serving thread on which cudaMalloc is banned
+ * because it stalls every stream of the device.  Such a caller cannot allocate the workspace
+ * that tfccb200_sgemm wants for this shape and cannot let the library allocate it either.
+ * Here the per-slice partial sums go to a 20 MiB array that is part of the library's device
+ * image, so the call allocates nothing: no cudaMalloc, no cudaFree, no pool.
+ *
+ * Limits and rules:
+ *  - the problem's scratch need (what tfccb200_sgemm_workspace(M,N,K,1,..) reports) must fit
+ *    tfccb200_sgemm_skinny_static_capacity() bytes, else TFCCB200_ESTATICLIMIT; M = 8,
+ *    K = 4096, N = 16384 fits.  N % 4 == 0 and 16-byte aligned B, C, bias are required as for
+ *    the workspace form (TFCCB200_EUNSUPPORTED otherwise);
+ *  - the first call on each device looks up the array's device address (a one-time host-side
+ *    set-up); make that first call before starting any stream capture;
+ *  - the array is shared by every call on the device and is never cleared -- no call reads
+ *    what it has not written itself -- so calls must not overlap on the GPU: issue them on
+ *    one stream, or order the streams yourself.  Overlapping calls race on the array;
+ *  - every process that loads the library holds the 20 MiB on each GPU it uses, until exit.
+ * The result is bit-identical to tfccb200_sgemm on the same problem.
+ */
+TFCCB200_API int tfccb200_sgemm_skinny_static(void* stream, const float* A, const float* B,
+                                              float* C, const float* bias, unsigned M,
+                                              unsigned N, unsigned K);
+TFCCB200_API size_t tfccb200_sgemm_skinny_static_capacity(void);
 
 /*
  * dst[m][g*ns + j] = src[g][m][j] for g < G, m < M, j < ns (fp32, ns % 4 == 0).

@@ -44,6 +44,8 @@ class _Lib:
             "tfccb200_reduce_sum_u8": (i, [vp, vp, u, u, u, i, vp]),
             "tfccb200_reduce_sum_s8": (i, [vp, vp, u, u, u, i, vp]),
             "tfccb200_reduce_sum_s16": (i, [vp, vp, u, u, u, i, vp]),
+            "tfccb200_sgemm_skinny_static": (i, [vp, vp, vp, vp, vp, u, u, u]),
+            "tfccb200_sgemm_skinny_static_capacity": (sz, []),
             "tfccb200_interleave_panels_f32": (i, [vp, vp, vp, u, u, u]),
             "tfccb200_sgemm_host": (i, [vp, vp, u, vp, u, vp, u, vp, u, u, u, u, i]),
             "tfccb200_qgemm_u8s8s32_host": (i, [vp, vp, u, vp, u, f, f, f, f, vp, u,
@@ -68,6 +70,7 @@ EXPORTED_SYMBOLS = (
     "tfccb200_sgemm_ex", "tfccb200_sgemm_workspace", "tfccb200_sgemm_path",
     "tfccb200_qgemm_u8s8s32", "tfccb200_qgemm_u8s8s32_ex", "tfccb200_quantized_matmul_params",
     "tfccb200_reduce_sum_u8", "tfccb200_reduce_sum_s8", "tfccb200_reduce_sum_s16",
+    "tfccb200_sgemm_skinny_static", "tfccb200_sgemm_skinny_static_capacity",
     "tfccb200_interleave_panels_f32", "tfccb200_sgemm_host", "tfccb200_qgemm_u8s8s32_host",
 )
 
@@ -85,7 +88,7 @@ def check(status: int) -> None:
     if status == 0:
         return
     msg = lib.tfccb200_strerror(status).decode()
-    if status in (-1, -2, -4, -5):
+    if status in (-1, -2, -4, -5, -7):
         raise exceptions.InvalidArgumentError(f"tfcc_b200 status {status}: {msg}")
     if status == -3:
         raise exceptions.ResourceExhaustedError(f"tfcc_b200 status {status}: {msg}")

@@ -178,6 +178,8 @@ const char* tfccb200_strerror(int status) {
     case TFCCB200_EOVERFLOW: return "element count exceeds the 32-bit shape limit";
     case TFCCB200_EUNSUPPORTED: return "requested kernel path cannot run this problem";
     case TFCCB200_EDEVICE: return "a kernel abandoned a bounded wait";
+    case TFCCB200_ESTATICLIMIT:
+      return "problem needs more scratch than the library's built-in 20 MiB array holds";
     default:
       if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
       return "unknown status";
@@ -303,6 +305,16 @@ int tfccb200_reduce_sum_s16(void* stream, const int16_t* src, unsigned batch, un
                             unsigned cols, int row_flag, int32_t* dst) {
   return reduce_sum_checked<int16_t>(stream, src, batch, rows, cols, row_flag, dst);
 }
+
+int tfccb200_sgemm_skinny_static(void* stream, const float* A, const float* B, float* C,
+                                 const float* bias, unsigned M, unsigned N, unsigned K) {
+  if (!A || !B || !C || M == 0 || N == 0 || K == 0) return TFCCB200_EINVAL;
+  if (M > 8) return TFCCB200_EUNSUPPORTED;
+  if (static_cast<unsigned long long>(K) * N > 0xffffffffull) return TFCCB200_EOVERFLOW;
+  return skinny_sgemm_static(static_cast<cudaStream_t>(stream), A, B, C, bias, M, N, K);
+}
+
+size_t tfccb200_sgemm_skinny_static_capacity(void) { return skinny_sgemm_static_capacity(); }
 
 int tfccb200_interleave_panels_f32(void* stream, const float* src, float* dst, unsigned M,
                                    unsigned ns, unsigned G) {

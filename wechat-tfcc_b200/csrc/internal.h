@@ -62,6 +62,9 @@ int simt_sgemm(const SgemmArgs& a);
 bool skinny_sgemm_supported(const SgemmArgs& a);
 size_t skinny_sgemm_workspace(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count);
 int skinny_sgemm(const SgemmArgs& a);
+int skinny_sgemm_static(cudaStream_t stream, const float* A, const float* B, float* C,
+                        const float* bias, unsigned M, unsigned N, unsigned K);
+size_t skinny_sgemm_static_capacity();
 int simt_qgemm(const QgemmArgs& a);
 int interleave_panels_f32(cudaStream_t stream, const float* src, float* out, unsigned M,
                           unsigned ns, unsigned G);

@@ -3,6 +3,8 @@
 // kernel for M <= 8, and the integer row / column sums of the quantized path.
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "internal.h"
 
 namespace tfccb200 {
@@ -392,6 +394,63 @@ int interleave_panels_f32(cudaStream_t stream, const float* src, float* out, uns
   count_launch();
   return TFCCB200_OK;
 }
+
+// --------------------------------------------------------------------------
+// The M <= 8 kernel for callers that cannot give it scratch memory.
+//
+// Its per-slice partial sums live in a fixed array inside this library's device image
+// instead of caller-provided workspace.  Every GPU that loads the library carries the
+// array (20 MiB) until the process exits.  All calls on a device share it and it keeps
+// whatever the previous call left there; that is harmless because every element a call
+// reads was written by the same call first (nothing has to start at zero), but two calls
+// that run on the GPU at the same time -- different streams, or different host threads --
+// would overwrite each other's partial sums.
+// --------------------------------------------------------------------------
+constexpr size_t kStaticScratchFloats = size_t(5) << 20;  // 5 Mi floats = 20 MiB
+static __device__ __align__(256) float g_skinny_static_scratch[kStaticScratchFloats];
+
+int skinny_sgemm_static(cudaStream_t stream, const float* A, const float* B, float* C,
+                        const float* bias, unsigned M, unsigned N, unsigned K) {
+  cudaError_t ce;
+  const DeviceInfo* di = current_device_info(&ce);
+  if (!di) return static_cast<int>(ce);
+  int dev = 0;
+  if ((ce = cudaGetDevice(&dev)) != cudaSuccess) return static_cast<int>(ce);
+  if (dev < 0 || dev >= 64) return TFCCB200_EUNSUPPORTED;
+
+  // In host code the array's name is only a handle; the address the kernels need is looked
+  // up once per device, with that device current, and remembered.
+  static std::mutex mu;
+  static float* device_address[64] = {};
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!device_address[dev]) {
+      void* p = nullptr;
+      ce = cudaGetSymbolAddress(&p, g_skinny_static_scratch);
+      if (ce != cudaSuccess) return static_cast<int>(ce);
+      device_address[dev] = static_cast<float*>(p);
+    }
+    scratch = device_address[dev];
+  }
+
+  SgemmArgs a = {};
+  a.stream = stream;
+  a.A = A; a.B = B; a.C = C; a.bias = bias;
+  a.strideA = a.strideB = 0;
+  a.strideC = M * N;
+  a.M = M; a.N = N; a.K = K; a.batch = 1;
+  a.precision = TFCCB200_PRECISION_FP32;
+  a.workspace = scratch;
+  a.workspace_bytes = kStaticScratchFloats * sizeof(float);
+  a.status = nullptr;
+  if (!skinny_sgemm_supported(a)) return TFCCB200_EUNSUPPORTED;
+  if (skinny_sgemm_workspace(M, N, K, 1, di->sm_count) > a.workspace_bytes)
+    return TFCCB200_ESTATICLIMIT;
+  return skinny_sgemm(a);
+}
+
+size_t skinny_sgemm_static_capacity() { return kStaticScratchFloats * sizeof(float); }
 
 template <class T>
 int reduce_sum(cudaStream_t stream, const T* src, unsigned batch, unsigned rows, unsigned cols,
