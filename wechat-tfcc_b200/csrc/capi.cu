@@ -74,11 +74,11 @@ int pick_sgemm_path(const SgemmArgs& a) {
     return TFCCB200_PATH_SKINNY;
   const unsigned long long macs = static_cast<unsigned long long>(a.M) * a.N * a.K * a.batch;
   if (umma_sgemm_supported(a) && macs >= (1ull << 22) && a.K >= 32 && a.N >= 64) {
-    // CTA pairs (256-row tiles, half the B traffic per SM) pay off once there are
-    // enough of them to give every pair of SMs a few tiles.
-    const unsigned long long tiles256 =
-        static_cast<unsigned long long>((a.M + 255) / 256) * ((a.N + 255) / 256) * a.batch;
-    return tiles256 >= 148 ? TFCCB200_PATH_UMMA2 : TFCCB200_PATH_UMMA;
+    cudaError_t e;
+    const DeviceInfo* di = current_device_info(&e);
+    const int sms = di ? di->sm_count : 148;
+    return umma_plan(a.M, a.N, a.batch, sms, false, -1).pair ? TFCCB200_PATH_UMMA2
+                                                             : TFCCB200_PATH_UMMA;
   }
   return TFCCB200_PATH_SIMT;
 }
@@ -104,9 +104,11 @@ int run_sgemm(SgemmArgs a, int path) {
 int pick_qgemm_path(const QgemmArgs& a) {
   const unsigned long long macs = static_cast<unsigned long long>(a.M) * a.N * a.K * a.batch;
   if (umma_qgemm_supported(a) && macs >= (1ull << 22) && a.K >= 128 && a.N >= 128) {
-    const unsigned long long tiles256 =
-        static_cast<unsigned long long>((a.M + 255) / 256) * ((a.N + 255) / 256) * a.batch;
-    return tiles256 >= 148 ? TFCCB200_PATH_UMMA2 : TFCCB200_PATH_UMMA;
+    cudaError_t e;
+    const DeviceInfo* di = current_device_info(&e);
+    const int sms = di ? di->sm_count : 148;
+    return umma_plan(a.M, a.N, a.batch, sms, true, -1).pair ? TFCCB200_PATH_UMMA2
+                                                            : TFCCB200_PATH_UMMA;
   }
   return TFCCB200_PATH_SIMT;
 }

@@ -52,6 +52,14 @@ struct QgemmArgs {
 
 // ---- tcgen05 paths (umma_launch.cu) ----
 // pair == true runs cta_group::2 (a CTA pair per 256-row tile).
+// Tile shape for a problem: CTA pairs or single CTAs, and the tile width.
+// force_pair: -1 = choose, 0 = single CTAs, 1 = pairs.
+struct UmmaPlan {
+  bool pair;
+  int bn;
+};
+UmmaPlan umma_plan(unsigned M, unsigned N, unsigned batch, int sm_count, bool int8,
+                   int force_pair);
 bool umma_sgemm_supported(const SgemmArgs& a);
 int umma_sgemm(const SgemmArgs& a, bool pair);
 bool umma_qgemm_supported(const QgemmArgs& a);

@@ -127,8 +127,37 @@ constexpr int kSkinnyThreads = 256;
 constexpr int kSkinnyCols = kSkinnyThreads * 4;
 constexpr int kSkinnyMaxSlice = 512;  // rows of W per CTA (bounds the x slice in smem)
 
+// acc[m] (4 columns as two packed pairs) += x[m] * w, with the packed fp32x2 FMA of sm_100.
 template <int MP>
-__global__ void __launch_bounds__(kSkinnyThreads)
+__device__ __forceinline__ void skinny_row_fma(float2 (&acc)[MP][2], const float* __restrict__ xrow,
+                                               const float4& w) {
+  float xv[MP];
+  if constexpr (MP % 4 == 0) {
+#pragma unroll
+    for (int q = 0; q < MP / 4; ++q) {
+      const float4 t = reinterpret_cast<const float4*>(xrow)[q];  // broadcast 128-bit read
+      xv[4 * q + 0] = t.x; xv[4 * q + 1] = t.y; xv[4 * q + 2] = t.z; xv[4 * q + 3] = t.w;
+    }
+  } else if constexpr (MP == 2) {
+    const float2 t = *reinterpret_cast<const float2*>(xrow);
+    xv[0] = t.x; xv[1] = t.y;
+  } else {
+    xv[0] = xrow[0];
+  }
+  const float2 wlo = make_float2(w.x, w.y), whi = make_float2(w.z, w.w);
+#pragma unroll
+  for (int m = 0; m < MP; ++m) {
+    const float2 xx = make_float2(xv[m], xv[m]);
+    acc[m][0] = __ffma2_rn(xx, wlo, acc[m][0]);
+    acc[m][1] = __ffma2_rn(xx, whi, acc[m][1]);
+  }
+}
+
+// CTAs of the kernel that fit one SM (register-bound); the grid is planned as one full wave.
+constexpr int skinny_resident(int mp) { return mp == 1 ? 3 : 2; }
+
+template <int MP>
+__global__ void __launch_bounds__(kSkinnyThreads, skinny_resident(MP))
 skinny_partial_kernel(const float* __restrict__ X, const float* __restrict__ W,
                       float* __restrict__ part, unsigned M, unsigned N, unsigned K,
                       unsigned slice_rows, unsigned long long strideX, unsigned long long strideW,
@@ -140,6 +169,19 @@ skinny_partial_kernel(const float* __restrict__ X, const float* __restrict__ W,
   const unsigned k_begin = blockIdx.y * slice_rows;
   const unsigned k_end = min(K, k_begin + slice_rows);
   const unsigned rows = k_end > k_begin ? k_end - k_begin : 0;
+  const unsigned col = blockIdx.x * kSkinnyCols + threadIdx.x * 4;
+  const bool active = col < N;  // N % 4 == 0 on this path
+  const float4* wp =
+      reinterpret_cast<const float4*>(W + static_cast<size_t>(k_begin) * N + (active ? col : 0));
+  const size_t pitch = N / 4;
+  constexpr int U = 8;
+
+  // first batch of weight rows is requested before the x slice is staged
+  float4 w[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+    w[u] = (active && static_cast<unsigned>(u) < rows) ? __ldcs(wp + u * pitch)
+                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
 
   for (unsigned i = threadIdx.x; i < rows * MP; i += kSkinnyThreads) {
     unsigned kk = i / MP, m = i % MP;
@@ -147,64 +189,63 @@ skinny_partial_kernel(const float* __restrict__ X, const float* __restrict__ W,
   }
   __syncthreads();
 
-  const unsigned col = blockIdx.x * kSkinnyCols + threadIdx.x * 4;
-  float acc[MP][4];
+  float2 acc[MP][2];
 #pragma unroll
-  for (int m = 0; m < MP; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+  for (int m = 0; m < MP; ++m) acc[m][0] = acc[m][1] = make_float2(0.f, 0.f);
 
-  if (col < N) {  // N % 4 == 0 on this path
-    const float4* wp = reinterpret_cast<const float4*>(W + static_cast<size_t>(k_begin) * N + col);
-    const size_t pitch = N / 4;
-    constexpr int U = 8;
-    unsigned kk = 0;
-    for (; kk + U <= rows; kk += U) {
-      float4 w[U];
+  // software-pipelined: the next batch of U rows is in flight while this one is multiplied;
+  // rows past the slice load nothing and multiply by zero weights
+  for (unsigned kk = 0; kk < rows; kk += U) {
+    float4 wn[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) w[u] = __ldcs(wp + (kk + u) * pitch);
+    for (int u = 0; u < U; ++u)
+      wn[u] = (active && kk + U + u < rows) ? __ldcs(wp + (kk + U + u) * pitch)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
+    for (int u = 0; u < U; ++u)
+      if (kk + u < rows) skinny_row_fma<MP>(acc, xs + (kk + u) * MP, w[u]);
 #pragma unroll
-        for (int m = 0; m < MP; ++m) {
-          const float xv = xs[(kk + u) * MP + m];
-          acc[m][0] = fmaf(xv, w[u].x, acc[m][0]);
-          acc[m][1] = fmaf(xv, w[u].y, acc[m][1]);
-          acc[m][2] = fmaf(xv, w[u].z, acc[m][2]);
-          acc[m][3] = fmaf(xv, w[u].w, acc[m][3]);
-        }
-      }
-    }
-    for (; kk < rows; ++kk) {
-      const float4 w = __ldcs(wp + kk * pitch);
-#pragma unroll
-      for (int m = 0; m < MP; ++m) {
-        const float xv = xs[kk * MP + m];
-        acc[m][0] = fmaf(xv, w.x, acc[m][0]);
-        acc[m][1] = fmaf(xv, w.y, acc[m][1]);
-        acc[m][2] = fmaf(xv, w.z, acc[m][2]);
-        acc[m][3] = fmaf(xv, w.w, acc[m][3]);
-      }
-    }
+    for (int u = 0; u < U; ++u) w[u] = wn[u];
+  }
+
+  // let the dependent reduce kernel begin launching; it still waits for this grid's stores
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (active) {
     // part: [batch][kslices][M][N]
     float* pp = part + ((static_cast<size_t>(b) * kslices + blockIdx.y) * M) * N + col;
 #pragma unroll
     for (int m = 0; m < MP; ++m)
       if (m < static_cast<int>(M))
         *reinterpret_cast<float4*>(pp + static_cast<size_t>(m) * N) =
-            make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
+            make_float4(acc[m][0].x, acc[m][0].y, acc[m][1].x, acc[m][1].y);
   }
 }
 
-__global__ void __launch_bounds__(256)
+// Adds the K slices in a fixed order (slice 0 first), then the bias.  Launched with
+// programmatic stream serialisation: it may start while the partial kernel drains, and
+// waits for that kernel's memory to be visible before it reads the partial sums.
+__global__ void __launch_bounds__(128)
 skinny_reduce_kernel(const float* __restrict__ part, const float* __restrict__ bias,
                      float* __restrict__ Y, unsigned MN, unsigned N, unsigned kslices,
                      unsigned long long strideY) {
   const unsigned b = blockIdx.y;
-  const unsigned i = (blockIdx.x * 256 + threadIdx.x) * 4;
+  const unsigned i = (blockIdx.x * 128 + threadIdx.x) * 4;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (i >= MN) return;
   const float* pp = part + static_cast<size_t>(b) * kslices * MN + i;
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (unsigned k = 0; k < kslices; ++k) {
-    const float4 v = *reinterpret_cast<const float4*>(pp + static_cast<size_t>(k) * MN);
+  constexpr unsigned U = 8;
+  unsigned k = 0;
+  for (; k + U <= kslices; k += U) {  // U independent loads in flight, summed in slice order
+    float4 v[U];
+#pragma unroll
+    for (unsigned u = 0; u < U; ++u)
+      v[u] = __ldcg(reinterpret_cast<const float4*>(pp + static_cast<size_t>(k + u) * MN));
+#pragma unroll
+    for (unsigned u = 0; u < U; ++u) { s.x += v[u].x; s.y += v[u].y; s.z += v[u].z; s.w += v[u].w; }
+  }
+  for (; k < kslices; ++k) {
+    const float4 v = __ldcg(reinterpret_cast<const float4*>(pp + static_cast<size_t>(k) * MN));
     s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
   }
   if (bias) {
@@ -214,18 +255,19 @@ skinny_reduce_kernel(const float* __restrict__ part, const float* __restrict__ b
   *reinterpret_cast<float4*>(Y + strideY * b + i) = s;
 }
 
-// K slices: enough CTAs for ~4 per SM, slice length capped by the x buffer.
-void skinny_plan(unsigned N, unsigned K, unsigned batch, int sm_count, unsigned* kslices,
-                 unsigned* slice_rows) {
+// K slices: as many CTAs as are resident at once (one wave), slice length capped by the x
+// buffer and rounded to whole batches of 8 rows.
+void skinny_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count,
+                 unsigned* kslices, unsigned* slice_rows) {
   const unsigned col_blocks = (N + kSkinnyCols - 1) / kSkinnyCols;
-  const unsigned long long want = 4ull * sm_count;
-  unsigned long long ks = (want + static_cast<unsigned long long>(col_blocks) * batch - 1) /
-                          (static_cast<unsigned long long>(col_blocks) * batch);
+  const int mp = M == 1 ? 1 : (M == 2 ? 2 : (M <= 4 ? 4 : 8));
+  const unsigned long long want = static_cast<unsigned long long>(skinny_resident(mp)) * sm_count;
+  unsigned long long ks = want / (static_cast<unsigned long long>(col_blocks) * batch);
   if (ks < 1) ks = 1;
   if (ks > K) ks = K;
   unsigned rows = static_cast<unsigned>((K + ks - 1) / ks);
+  rows = (rows + 7) / 8 * 8;  // whole batches of 8 rows, no ragged tail inside a slice
   if (rows > kSkinnyMaxSlice) rows = kSkinnyMaxSlice;
-  if (rows < 8 && K >= 8) rows = 8;
   *slice_rows = rows;
   *kslices = (K + rows - 1) / rows;
 }
@@ -261,7 +303,48 @@ reduce_rows_kernel(const T* __restrict__ src, unsigned total_rows, unsigned cols
 }
 
 // dst must be zero on entry: row slabs are combined with integer atomics,
-// which is exact and order-independent.
+// which is exact and order-independent.  A thread owns the V = 4/sizeof(T) adjacent columns
+// of one 32-bit word and walks its slab of rows with 8 loads in flight.
+template <class T>
+__global__ void __launch_bounds__(256)
+reduce_cols_vec_kernel(const T* __restrict__ src, unsigned rows, unsigned cols, unsigned slab,
+                       int32_t* __restrict__ dst) {
+  constexpr unsigned V = 4 / sizeof(T);
+  const unsigned b = blockIdx.z;
+  const unsigned c = (blockIdx.x * 256 + threadIdx.x) * V;
+  if (c >= cols) return;
+  const unsigned r0 = blockIdx.y * slab;
+  const unsigned r1 = min(rows, r0 + slab);
+  const size_t pitch = cols / V;  // in 32-bit words
+  const uint32_t* p = reinterpret_cast<const uint32_t*>(src + static_cast<size_t>(b) * rows * cols) + c / V;
+  int32_t s[V];
+#pragma unroll
+  for (unsigned v = 0; v < V; ++v) s[v] = 0;
+  constexpr unsigned U = 8;
+  unsigned r = r0;
+  for (; r + U <= r1; r += U) {
+    uint32_t w[U];
+#pragma unroll
+    for (unsigned u = 0; u < U; ++u) w[u] = __ldcs(p + (r + u) * pitch);
+#pragma unroll
+    for (unsigned u = 0; u < U; ++u) {
+      const T* e = reinterpret_cast<const T*>(&w[u]);
+#pragma unroll
+      for (unsigned v = 0; v < V; ++v) s[v] += static_cast<int32_t>(e[v]);
+    }
+  }
+  for (; r < r1; ++r) {
+    const uint32_t w = __ldcs(p + r * pitch);
+    const T* e = reinterpret_cast<const T*>(&w);
+#pragma unroll
+    for (unsigned v = 0; v < V; ++v) s[v] += static_cast<int32_t>(e[v]);
+  }
+  int32_t* d = dst + static_cast<size_t>(b) * cols + c;
+#pragma unroll
+  for (unsigned v = 0; v < V; ++v) atomicAdd(d + v, s[v]);
+}
+
+// Any alignment: one column per thread.
 template <class T>
 __global__ void __launch_bounds__(256)
 reduce_cols_kernel(const T* __restrict__ src, unsigned rows, unsigned cols, unsigned slab,
@@ -338,7 +421,7 @@ bool skinny_sgemm_supported(const SgemmArgs& a) {
 
 size_t skinny_sgemm_workspace(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count) {
   unsigned ks, rows;
-  skinny_plan(N, K, batch, sm_count, &ks, &rows);
+  skinny_plan(M, N, K, batch, sm_count, &ks, &rows);
   return static_cast<size_t>(batch) * ks * M * N * sizeof(float);
 }
 
@@ -348,7 +431,7 @@ int skinny_sgemm(const SgemmArgs& a) {
   if (!di) return static_cast<int>(ce);
   if (!skinny_sgemm_supported(a)) return TFCCB200_EUNSUPPORTED;
   unsigned ks, rows;
-  skinny_plan(a.N, a.K, a.batch, di->sm_count, &ks, &rows);
+  skinny_plan(a.M, a.N, a.K, a.batch, di->sm_count, &ks, &rows);
   const size_t need = static_cast<size_t>(a.batch) * ks * a.M * a.N * sizeof(float);
   if (a.workspace_bytes < need || !a.workspace ||
       (reinterpret_cast<uintptr_t>(a.workspace) & 15u))
@@ -367,9 +450,21 @@ int skinny_sgemm(const SgemmArgs& a) {
   cudaError_t e = launch_status();
   if (e != cudaSuccess) return static_cast<int>(e);
   const unsigned MN = a.M * a.N;
-  dim3 rgrid((MN / 4 + 255) / 256, a.batch);
-  skinny_reduce_kernel<<<rgrid, 256, 0, a.stream>>>(part, a.bias, a.C, MN, a.N, ks, a.strideC);
-  e = launch_status();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((MN / 4 + 127) / 128, a.batch, 1);
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.stream = a.stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const float* part_c = part;
+  const float* bias_c = a.bias;
+  float* out_c = a.C;
+  unsigned n_c = a.N;
+  unsigned long long stride_c = a.strideC;
+  e = cudaLaunchKernelEx(&cfg, skinny_reduce_kernel, part_c, bias_c, out_c, MN, n_c, ks, stride_c);
   if (e != cudaSuccess) return static_cast<int>(e);
   count_launch(2);
   return TFCCB200_OK;
@@ -472,8 +567,16 @@ int reduce_sum(cudaStream_t stream, const T* src, unsigned batch, unsigned rows,
   // row slabs sized so that the grid has a few thousand CTAs at most
   unsigned slab = 64;
   while ((rows + slab - 1) / slab > 4096) slab *= 2;
-  dim3 grid((cols + 255) / 256, (rows + slab - 1) / slab, batch);
-  reduce_cols_kernel<T><<<grid, 256, 0, stream>>>(src, rows, cols, slab, dst);
+  constexpr unsigned V = 4 / sizeof(T);
+  const bool vec = cols % V == 0 && (reinterpret_cast<uintptr_t>(src) & 3u) == 0 &&
+                   (static_cast<unsigned long long>(rows) * cols) % V == 0;
+  if (vec) {
+    dim3 grid((cols / V + 255) / 256, (rows + slab - 1) / slab, batch);
+    reduce_cols_vec_kernel<T><<<grid, 256, 0, stream>>>(src, rows, cols, slab, dst);
+  } else {
+    dim3 grid((cols + 255) / 256, (rows + slab - 1) / slab, batch);
+    reduce_cols_kernel<T><<<grid, 256, 0, stream>>>(src, rows, cols, slab, dst);
+  }
   e = launch_status();
   if (e != cudaSuccess) return static_cast<int>(e);
   count_launch();

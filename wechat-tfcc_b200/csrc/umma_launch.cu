@@ -98,18 +98,16 @@ int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, Um
   return TFCCB200_OK;
 }
 
-// Widest tile that still gives every SM (or SM pair) a tile; small problems
-// fall to narrower tiles so more SMs take part.
-int pick_bn(unsigned M, unsigned N, unsigned batch, int tile_m, int groups) {
-  const unsigned long long tm = (M + tile_m - 1) / tile_m;
-  for (int bn : {256, 128}) {
-    unsigned long long tiles = tm * ((N + bn - 1) / bn) * batch;
-    if (tiles >= static_cast<unsigned long long>(groups) && N >= static_cast<unsigned>(bn))
-      return bn;
-  }
-  if (N > 128 && tm * ((N + 127) / 128) * batch >= static_cast<unsigned long long>(groups) / 2)
-    return 128;
-  return 64;
+// Tile choice.  A tile row-block costs time proportional to its width BN, with a penalty
+// for narrow tiles (their A operand is re-read from shared memory more often per flop) and
+// a bonus for CTA pairs (each CTA stages only half of B); the grid runs in waves of `groups`
+// tiles.  The cheapest (waves x width x penalty) wins.
+double tile_cost(unsigned M, unsigned N, unsigned batch, int tile_m, int bn, int groups,
+                 double penalty) {
+  const unsigned long long tiles =
+      static_cast<unsigned long long>((M + tile_m - 1) / tile_m) * ((N + bn - 1) / bn) * batch;
+  const unsigned long long waves = (tiles + groups - 1) / groups;
+  return static_cast<double>(waves) * bn * penalty;
 }
 
 int env_int(const char* name, int fallback) {
@@ -120,6 +118,36 @@ int env_int(const char* name, int fallback) {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
+
+UmmaPlan umma_plan(unsigned M, unsigned N, unsigned batch, int sm_count, bool int8,
+                   int force_pair) {
+  UmmaPlan best = {false, 0};
+  double best_cost = 0;
+  for (int pair = 0; pair <= 1; ++pair) {
+    if (force_pair >= 0 && pair != force_pair) continue;
+    const int tile_m = pair ? 256 : 128;
+    const int groups = pair ? sm_count / 2 : sm_count;
+    if (groups < 1) continue;
+    if (pair && M <= 128 && force_pair < 0) continue;  // a second CTA would only hold padding
+    for (int bn : {256, 128, 64}) {
+      // int8 stages BN (or BN/2 per CTA of a pair) one-byte columns: 128 bytes at least
+      if (int8 && (pair ? bn < 256 : bn < 128)) continue;
+      if (bn > 64 && static_cast<unsigned>(bn) >= 2 * N) continue;  // mostly padding
+      const double penalty = (bn == 256 ? 1.0 : bn == 128 ? 1.25 : 1.6) * (pair ? 0.85 : 1.0);
+      const double c = tile_cost(M, N, batch, tile_m, bn, groups, penalty);
+      if (best.bn == 0 || c < best_cost) {
+        best_cost = c;
+        best.pair = pair != 0;
+        best.bn = bn;
+      }
+    }
+  }
+  if (best.bn == 0) {  // nothing admissible (e.g. int8 with tiny N): widest legal tile
+    best.pair = force_pair == 1;
+    best.bn = int8 ? (best.pair ? 256 : 128) : 64;
+  }
+  return best;
+}
 
 bool umma_sgemm_supported(const SgemmArgs& a) {
   // TMA wants 16-byte aligned bases and row pitches; the epilogue stores float4.
@@ -145,10 +173,7 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
 
   const bool a_batched = a.batch > 1 && a.strideA != 0;
   const bool b_batched = a.batch > 1 && a.strideB != 0;
-  const int tile_m = pair ? 256 : 128;
-  const int groups = pair ? di->sm_count / 2 : di->sm_count;
-  const int bn = pick_bn(a.M, a.N, a.batch, tile_m, groups);
-  const int bn_local = pair ? bn / 2 : bn;
+  const int bn = umma_plan(a.M, a.N, a.batch, di->sm_count, false, pair ? 1 : 0).bn;
 
   CUtensorMap ta, tb;
   if (!make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.A, a.K, a.M, a_batched ? a.batch : 1,
@@ -158,7 +183,6 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
   if (!make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.B, a.N, a.K, b_batched ? a.batch : 1,
                  a.strideB, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
     return TFCCB200_EINVAL;
-  (void)bn_local;
 
   UmmaGemmParams p = {};
   p.C = a.C;
@@ -224,11 +248,7 @@ int umma_qgemm(const QgemmArgs& a, bool pair) {
 
   const bool a_batched = a.batch > 1 && a.strideA != 0;
   const bool b_batched = a.batch > 1 && a.strideB != 0;
-  const int tile_m = pair ? 256 : 128;
-  const int groups = pair ? di->sm_count / 2 : di->sm_count;
-  int bn = pick_bn(a.M, a.N, a.batch, tile_m, groups);
-  if (pair && bn < 256) bn = 256;  // a pair stages BN/2 int8 columns per CTA: 128 bytes minimum
-  if (!pair && bn < 128) bn = 128;
+  const int bn = umma_plan(a.M, a.N, a.batch, di->sm_count, true, pair ? 1 : 0).bn;
 
   CUtensorMap ta, tb;
   if (!make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.A, a.K, a.M, a_batched ? a.batch : 1,

@@ -1,0 +1,462 @@
+#include "tfcc_b200.h"
+
+#include <algorithm>
+#include <utility>
+
+#include "tfcc_b200.h"
+#include "../../include/tfcc_b200.h"
+
+namespace tfcc {
+
+namespace {
+
+inline void check_cuda(cudaError_t e) {
+  if (e != cudaSuccess) throw B200RuntimeError(static_cast<int>(e));
+}
+
+inline void check_status(int st) {
+  if (st == TFCCB200_OK) return;
+  if (st == TFCCB200_EINVAL || st == TFCCB200_EALIGN || st == TFCCB200_EOVERFLOW ||
+      st == TFCCB200_EUNSUPPORTED)
+    throw InvalidArgumentError(tfccb200_strerror(st));
+  if (st == TFCCB200_EWORKSPACE) throw ResourceExhaustedError();
+  throw B200RuntimeError(st);
+}
+
+B200Session* current_session() {
+  B200Session* s = dynamic_cast<B200Session*>(Session::getThreadDefault());
+  if (s == nullptr) throw RuntimeError("the thread default session is not a B200 session");
+  return s;
+}
+
+B200Device* current_device() {
+  B200Device* d = dynamic_cast<B200Device*>(Device::getThreadDefault());
+  if (d == nullptr) throw RuntimeError("the thread default device is not a B200 device");
+  return d;
+}
+
+template <class T>
+std::shared_ptr<ConstantManager<T>> make_constant_manager(
+    const std::function<void*(size_t)>& realMalloc, const std::function<void(void*)>& realFree) {
+  auto m = std::make_shared<ConstantManager<T>>();
+  m->getAllocator().setRealMalloc(realMalloc);
+  m->getAllocator().setRealFree(realFree);
+  return m;
+}
+
+// Shapes, strides and batch count exactly as the reference backends derive them
+// (tfcc/mkl/interfaces/tfcc_mklblasinterface.cpp:127-151).
+struct MatmulGeometry {
+  unsigned m, n, k, strideA, strideB, strideC, batch;
+  std::vector<unsigned> resultShape;
+};
+
+template <class TA, class TB>
+MatmulGeometry matmul_geometry(const Tensor<TA>& a, const Tensor<TB>& b) {
+  MatmulGeometry g;
+  g.m = a.shape(a.shape().size() - 2);
+  g.n = b.shape(b.shape().size() - 1);
+  g.k = a.shape(a.shape().size() - 1);
+  g.strideA = g.m * g.k;
+  g.strideB = g.n * g.k;
+  g.strideC = g.m * g.n;
+  if (a.shape().size() != b.shape().size()) {
+    g.strideA = a.shape().size() == 2 ? 0 : g.strideA;
+    g.strideB = b.shape().size() == 2 ? 0 : g.strideB;
+  }
+  g.resultShape = a.shape().size() > b.shape().size() ? a.shape().toVector() : b.shape().toVector();
+  g.resultShape[g.resultShape.size() - 2] = g.m;
+  g.resultShape[g.resultShape.size() - 1] = g.n;
+  unsigned long long area = 1;
+  for (unsigned d : g.resultShape) area *= d;
+  g.batch = static_cast<unsigned>(area / (static_cast<unsigned long long>(g.m) * g.n));
+  return g;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- exception
+B200RuntimeError::B200RuntimeError(int status) : _status(status) {
+  _reason = std::string("tfcc_b200 [") + std::to_string(status) + "] " + tfccb200_strerror(status);
+}
+
+const char* B200RuntimeError::reason() const noexcept { return _reason.c_str(); }
+
+// ---------------------------------------------------------------- device
+unsigned B200Device::getDeviceCount() {
+  int n = 0;
+  check_cuda(cudaGetDeviceCount(&n));
+  return static_cast<unsigned>(n);
+}
+
+B200Device::B200Device(unsigned deviceID)
+    : B200Device(deviceID, std::unique_ptr<Allocator>(new FlexAllocator())) {
+  size_t freeBytes = 0, totalBytes = 0;
+  check_cuda(cudaSetDevice(_cudaDevice));
+  check_cuda(cudaMemGetInfo(&freeBytes, &totalBytes));
+  FlexAllocator* alloc = dynamic_cast<FlexAllocator*>(_allocator.get());
+  if (alloc) alloc->setLimit(totalBytes * 9 / 10);
+}
+
+B200Device::B200Device(unsigned deviceID, std::unique_ptr<Allocator> allocator)
+    : Device(deviceID & 0x00ffffff, std::move(allocator)),
+      _cudaDevice(static_cast<int>(deviceID & 0x00ffffff)),
+      _tf32(false) {
+  const int dev = _cudaDevice;
+  std::function<void*(size_t)> realMalloc = [dev](size_t len) -> void* {
+    void* p = nullptr;
+    if (cudaSetDevice(dev) != cudaSuccess) return nullptr;
+    if (cudaMalloc(&p, len) != cudaSuccess) return nullptr;
+    return p;
+  };
+  std::function<void(void*)> realFree = [](void* p) {
+    cudaError_t e = cudaFree(p);
+    if (e != cudaSuccess && e != cudaErrorCudartUnloading) throw B200RuntimeError(static_cast<int>(e));
+  };
+  _allocator->setRealMalloc(realMalloc);
+  _allocator->setRealFree(realFree);
+
+  _floatConstantManager = make_constant_manager<float>(realMalloc, realFree);
+  _doubleConstantManager = make_constant_manager<double>(realMalloc, realFree);
+  _int8ConstantManager = make_constant_manager<int8_t>(realMalloc, realFree);
+  _uint8ConstantManager = make_constant_manager<uint8_t>(realMalloc, realFree);
+  _int16ConstantManager = make_constant_manager<int16_t>(realMalloc, realFree);
+  _uint16ConstantManager = make_constant_manager<uint16_t>(realMalloc, realFree);
+  _int32ConstantManager = make_constant_manager<int32_t>(realMalloc, realFree);
+  _uint32ConstantManager = make_constant_manager<uint32_t>(realMalloc, realFree);
+  _int64ConstantManager = make_constant_manager<int64_t>(realMalloc, realFree);
+  _uint64ConstantManager = make_constant_manager<uint64_t>(realMalloc, realFree);
+
+  _floatInterface = get_b200_interface(float(), *this);
+  _doubleInterface = get_b200_interface(double(), *this);
+  _int8Interface = get_b200_interface(int8_t(), *this);
+  _uint8Interface = get_b200_interface(uint8_t(), *this);
+  _int16Interface = get_b200_interface(int16_t(), *this);
+  _uint16Interface = get_b200_interface(uint16_t(), *this);
+  _int32Interface = get_b200_interface(int32_t(), *this);
+  _uint32Interface = get_b200_interface(uint32_t(), *this);
+  _int64Interface = get_b200_interface(int64_t(), *this);
+  _uint64Interface = get_b200_interface(uint64_t(), *this);
+}
+
+B200Device::~B200Device() {}
+
+void B200Device::attach() { check_cuda(cudaSetDevice(_cudaDevice)); }
+
+int B200Device::precisionMode() const {
+  return _tf32 ? TFCCB200_PRECISION_TF32 : TFCCB200_PRECISION_FP32;
+}
+
+// ---------------------------------------------------------------- session
+B200Session::B200Session(B200Device& device)
+    : B200Session(device, std::unique_ptr<Allocator>(new FlexAllocator())) {
+  size_t freeBytes = 0, totalBytes = 0;
+  check_cuda(cudaMemGetInfo(&freeBytes, &totalBytes));
+  FlexAllocator* alloc = dynamic_cast<FlexAllocator*>(_allocator.get());
+  if (alloc) alloc->setLimit(totalBytes * 6 / 10);
+}
+
+B200Session::B200Session(B200Device& device, std::unique_ptr<Allocator> allocator)
+    : Session(std::move(allocator)),
+      _device(device),
+      _stream(nullptr),
+      _status(nullptr),
+      _scratch(nullptr),
+      _scratchBytes(0),
+      _destroying(false) {
+  _device.attach();
+  check_cuda(cudaStreamCreateWithFlags(&_stream, cudaStreamNonBlocking));
+  _allocator->setRealMalloc([this](size_t len) { return this->_device.malloc(len); });
+  _allocator->setRealFree([this](void* p) {
+    this->sync();
+    this->_device.free(p);
+  });
+  _status = static_cast<int*>(_device.malloc(sizeof(int)));
+  if (_status == nullptr) throw ResourceExhaustedError();
+  check_cuda(cudaMemsetAsync(_status, 0, sizeof(int), _stream));
+}
+
+B200Session::~B200Session() {
+  _destroying = true;
+  preRelease();
+  cudaStreamSynchronize(_stream);
+  if (_scratch) _allocator->free(_scratch);
+  _device.free(_status);
+  cudaStreamDestroy(_stream);
+}
+
+void B200Session::sync() const {
+  cudaError_t e = cudaStreamSynchronize(_stream);
+  if (e != cudaSuccess) {
+    if (e == cudaErrorCudartUnloading && _destroying) return;
+    throw B200RuntimeError(static_cast<int>(e));
+  }
+  if (_destroying) return;
+  // Device-side give-ups (bounded waits that ran out) surface here, like any asynchronous fault.
+  int st = 0;
+  check_cuda(cudaMemcpy(&st, _status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (st != 0) {
+    cudaMemset(_status, 0, sizeof(int));
+    throw B200RuntimeError(TFCCB200_EDEVICE);
+  }
+}
+
+Device& B200Session::getDevice() { return _device; }
+const Device& B200Session::getDevice() const { return _device; }
+
+void* B200Session::scratch(size_t bytes) {
+  if (bytes <= _scratchBytes) return _scratch;
+  if (_scratch) _allocator->free(_scratch);  // the allocator syncs before memory really goes back
+  _scratch = nullptr;
+  _scratchBytes = 0;
+  void* p = _allocator->malloc(bytes);
+  if (p == nullptr) throw ResourceExhaustedError();
+  _scratch = p;
+  _scratchBytes = bytes;
+  return p;
+}
+
+// ---------------------------------------------------------------- blas
+template <class T>
+Variable<T> B200BlasInterface<T>::matmul(const Tensor<T>&, const Tensor<T>&) {
+  throw NotImplementedError();  // float only, as the MKL backend (tfcc_mklblasinterface.cpp:35-39)
+}
+
+template <class T>
+Variable<T> B200BlasInterface<T>::matmul(const Tensor<T>&, const Tensor<T>&, const Tensor<T>&) {
+  throw NotImplementedError();
+}
+
+static Variable<float> b200_matmul(const Tensor<float>& a, const Tensor<float>& b,
+                                   const float* bias) {
+  MatmulGeometry g = matmul_geometry(a, b);
+  Variable<float> result(Shape(g.resultShape));
+  B200Session* session = current_session();
+  const int mode = current_device()->precisionMode();
+  const size_t ws = tfccb200_sgemm_workspace(g.m, g.n, g.k, g.batch, mode);
+  void* scratch = ws ? session->scratch(ws) : nullptr;
+  check_status(tfccb200_sgemm(session->stream(), a.data(), g.strideA, b.data(), g.strideB,
+                              result.data(), g.strideC, bias, g.m, g.n, g.k, g.batch, mode,
+                              scratch, ws, session->deviceStatus()));
+  return result;
+}
+
+template <>
+Variable<float> B200BlasInterface<float>::matmul(const Tensor<float>& a, const Tensor<float>& b) {
+  return b200_matmul(a, b, nullptr);
+}
+
+template <>
+Variable<float> B200BlasInterface<float>::matmul(const Tensor<float>& a, const Tensor<float>& b,
+                                                 const Tensor<float>& c) {
+  return b200_matmul(a, b, c.data());
+}
+
+// ---------------------------------------------------------------- data
+template <class T>
+void B200DataInterface<T>::set(T* dst, const T* data, size_t len) {
+  B200Session* session = current_session();
+  check_cuda(cudaMemcpyAsync(dst, data, len * sizeof(T), cudaMemcpyHostToDevice, session->stream()));
+  check_cuda(cudaStreamSynchronize(session->stream()));  // the host buffer may go away
+}
+
+template <class T>
+void B200DataInterface<T>::set(Variable<T>& a, const T* data) {
+  set(a.data(), data, a.size());
+}
+
+template <class T>
+void B200DataInterface<T>::set(Variable<T>& a, std::vector<T>&& data) {
+  set(a.data(), data.data(), a.size());
+}
+
+template <class T>
+void B200DataInterface<T>::get(const Tensor<T>& a, T* data) {
+  a.sync();
+  check_cuda(cudaMemcpy(data, a.data(), a.size() * sizeof(T), cudaMemcpyDeviceToHost));
+}
+
+template <class T>
+void B200DataInterface<T>::zeros(Variable<T>& a) {
+  check_cuda(cudaMemsetAsync(a.data(), 0, a.size() * sizeof(T), current_session()->stream()));
+}
+
+template <class T>
+Variable<T> B200DataInterface<T>::copy(const Tensor<T>& a) {
+  Variable<T> result(a.shape());
+  check_cuda(cudaMemcpyAsync(result.data(), a.data(), a.size() * sizeof(T),
+                             cudaMemcpyDeviceToDevice, current_session()->stream()));
+  return result;
+}
+
+// ---------------------------------------------------------------- registration
+template <class T>
+Interface<T> get_b200_interface(T, B200Device&) {
+  Interface<T> interface;
+  interface.setBlasInterface(std::unique_ptr<BlasInterface<T>>(new B200BlasInterface<T>()));
+  interface.setDataInterface(std::unique_ptr<DataInterface<T>>(new B200DataInterface<T>()));
+  return interface;
+}
+
+#define TFCC_B200_INSTANTIATE(type)                                   \
+  template class B200BlasInterface<type>;                             \
+  template class B200DataInterface<type>;                             \
+  template Interface<type> get_b200_interface(type, B200Device& device);
+TFCC_B200_INSTANTIATE(float)
+TFCC_B200_INSTANTIATE(double)
+TFCC_B200_INSTANTIATE(int8_t)
+TFCC_B200_INSTANTIATE(uint8_t)
+TFCC_B200_INSTANTIATE(int16_t)
+TFCC_B200_INSTANTIATE(uint16_t)
+TFCC_B200_INSTANTIATE(int32_t)
+TFCC_B200_INSTANTIATE(uint32_t)
+TFCC_B200_INSTANTIATE(int64_t)
+TFCC_B200_INSTANTIATE(uint64_t)
+#undef TFCC_B200_INSTANTIATE
+
+static Initializer& b200_initializer() {
+  static Initializer initializer(
+      B200Device::getDeviceCount(),
+      [](size_t i) { return std::shared_ptr<Device>(new B200Device(static_cast<unsigned>(i))); },
+      [](Device& device) {
+        return std::shared_ptr<Session>(new B200Session(*dynamic_cast<B200Device*>(&device)));
+      });
+  return initializer;
+}
+
+static InitializerGuard& b200_initializer_guard() {
+  thread_local InitializerGuard guard;
+  return guard;
+}
+
+void initialize_b200() {
+  if (Device::getThreadDefault() == nullptr || Session::getThreadDefault() == nullptr) {
+    InitializerGuard& guard = b200_initializer_guard();
+    guard = b200_initializer().allocate();
+    Device::setThreadDefault(&guard.getDevice());
+    Session::setThreadDefault(&guard.getSession());
+  }
+  Device::getThreadDefault()->attach();
+}
+
+void initialize_b200(unsigned deviceID) {
+  if (Device::getThreadDefault() == nullptr || Session::getThreadDefault() == nullptr) {
+    InitializerGuard& guard = b200_initializer_guard();
+    guard = b200_initializer().allocate(deviceID);
+    Device::setThreadDefault(&guard.getDevice());
+    Session::setThreadDefault(&guard.getSession());
+  }
+  Device::getThreadDefault()->attach();
+}
+
+// ---------------------------------------------------------------- quantization
+namespace b200 {
+namespace quantization {
+
+// Argument checks and messages of tfcc::mkl::quantization::matmul
+// (tfcc/mkl/operations/tfcc_mklquantization.cpp:75-118); the min/max scalars are read back
+// to the host (one small synchronous copy each) to derive the zero-point offsets.
+std::tuple<Variable<int32_t>, Variable<float>, Variable<float>> matmul(
+    const Tensor<uint8_t>& a, const Tensor<int32_t>& reduceSumA, const Tensor<float>& minA,
+    const Tensor<float>& maxA, const Tensor<int8_t>& b, const Tensor<int32_t>& reduceSumB,
+    const Tensor<float>& minB, const Tensor<float>& maxB) {
+  if (a.size() == 0 || a.shape().size() < 2) throw InvalidArgumentError("invalid input tensor a");
+  if (reduceSumA.size() == 0) throw InvalidArgumentError("invalid tensor reduceSumA");
+  if (minA.size() != 1 || minA.shape().size() != 1) throw InvalidArgumentError("invalid tensor minA");
+  if (maxA.size() != 1 || maxA.shape().size() != 1) throw InvalidArgumentError("invalid tensor maxA");
+  if (b.size() == 0 || b.shape().size() < 2) throw InvalidArgumentError("invalid input tensor b");
+  if (reduceSumB.size() == 0) throw InvalidArgumentError("invalid tensor reduceSumB");
+  if (minB.size() != 1 || minB.shape().size() != 1) throw InvalidArgumentError("invalid tensor minB");
+  if (maxB.size() != 1 || maxB.shape().size() != 1) throw InvalidArgumentError("invalid tensor maxB");
+  if (a.shape(a.shape().size() - 1) != b.shape(b.shape().size() - 2))
+    throw InvalidArgumentError("tensor a and b don't match");
+  if (a.shape().size() != b.shape().size() && a.shape().size() != 2 && b.shape().size() != 2)
+    throw InvalidArgumentError("tensor a and b don't match");
+  if (a.shape(a.shape().size() - 2) != reduceSumA.shape(reduceSumA.shape().size() - 1))
+    throw InvalidArgumentError("tensor a and reduceSumA don't match");
+  if (b.shape(b.shape().size() - 1) != reduceSumB.shape(reduceSumB.shape().size() - 1))
+    throw InvalidArgumentError("tensor b and reduceSumB don't match");
+  if (a.shape().size() == b.shape().size()) {
+    for (size_t i = 0; i + 2 < a.shape().size(); ++i)
+      if (a.shape(i) != b.shape(i)) throw InvalidArgumentError("tensor a and b don't match");
+  }
+
+  MatmulGeometry g = matmul_geometry(a, b);
+  const unsigned strideRsA = reduceSumA.shape().size() == 1 ? 0 : g.m;
+  const unsigned strideRsB = reduceSumB.shape().size() == 1 ? 0 : g.n;
+  // rank-2 operands are shared over the batch even when both ranks are equal to 2
+  const unsigned strideA = a.shape().size() == 2 ? 0 : g.m * g.k;
+  const unsigned strideB = b.shape().size() == 2 ? 0 : g.k * g.n;
+
+  Variable<int32_t> result(Shape(g.resultShape));
+  Variable<float> minResult({1}), maxResult({1});
+  B200Session* session = current_session();
+
+  float h[4];
+  const Tensor<float>* scalars[4] = {&minA, &maxA, &minB, &maxB};
+  for (int i = 0; i < 4; ++i) {
+    scalars[i]->sync();
+    check_cuda(cudaMemcpy(&h[i], scalars[i]->data(), sizeof(float), cudaMemcpyDeviceToHost));
+  }
+  int32_t offA = 0, offB = 0;
+  float hostMinC = 0.f, hostMaxC = 0.f;
+  check_status(tfccb200_quantized_matmul_params(h[0], h[1], h[2], h[3], &offA, &offB, &hostMinC,
+                                                &hostMaxC));
+  check_status(tfccb200_qgemm_u8s8s32(session->stream(), a.data(), strideA, reduceSumA.data(),
+                                      strideRsA, offA, b.data(), strideB, reduceSumB.data(),
+                                      strideRsB, offB, result.data(), g.m * g.n, g.m, g.n, g.k,
+                                      g.batch, session->deviceStatus()));
+  check_cuda(cudaMemcpyAsync(minResult.data(), &hostMinC, sizeof(float), cudaMemcpyHostToDevice,
+                             session->stream()));
+  check_cuda(cudaMemcpyAsync(maxResult.data(), &hostMaxC, sizeof(float), cudaMemcpyHostToDevice,
+                             session->stream()));
+  check_cuda(cudaStreamSynchronize(session->stream()));  // the two host floats leave scope
+  return std::make_tuple(std::move(result), std::move(minResult), std::move(maxResult));
+}
+
+template <class T>
+struct ReduceEntry;
+template <>
+struct ReduceEntry<int8_t> {
+  static int call(void* s, const int8_t* p, unsigned b, unsigned r, unsigned c, int f, int32_t* d) {
+    return tfccb200_reduce_sum_s8(s, p, b, r, c, f, d);
+  }
+};
+template <>
+struct ReduceEntry<uint8_t> {
+  static int call(void* s, const uint8_t* p, unsigned b, unsigned r, unsigned c, int f, int32_t* d) {
+    return tfccb200_reduce_sum_u8(s, p, b, r, c, f, d);
+  }
+};
+template <>
+struct ReduceEntry<int16_t> {
+  static int call(void* s, const int16_t* p, unsigned b, unsigned r, unsigned c, int f, int32_t* d) {
+    return tfccb200_reduce_sum_s16(s, p, b, r, c, f, d);
+  }
+};
+
+// tfcc::mkl::quantization::reduce_sum (tfcc_mklquantization.cpp:284-318).
+template <class T>
+Variable<int32_t> reduce_sum(const Tensor<T>& a, bool row) {
+  if (a.size() == 0 || a.shape().size() < 2) throw InvalidArgumentError("invalid input tensor a");
+  std::vector<unsigned> newS = a.shape().toVector();
+  newS.pop_back();
+  newS.pop_back();
+  const unsigned r = a.shape(a.shape().size() - 2);
+  const unsigned c = a.shape(a.shape().size() - 1);
+  const unsigned batch = a.size() / r / c;
+  newS.push_back(row ? r : c);
+  Variable<int32_t> result(Shape(std::move(newS)));
+  check_status(ReduceEntry<T>::call(current_session()->stream(), a.data(), batch, r, c, row ? 1 : 0,
+                                    result.data()));
+  return result;
+}
+
+template Variable<int32_t> reduce_sum(const Tensor<int8_t>& a, bool row);
+template Variable<int32_t> reduce_sum(const Tensor<uint8_t>& a, bool row);
+template Variable<int32_t> reduce_sum(const Tensor<int16_t>& a, bool row);
+
+}  // namespace quantization
+}  // namespace b200
+
+}  // namespace tfcc

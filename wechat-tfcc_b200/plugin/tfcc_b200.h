@@ -1,0 +1,132 @@
+// tfcc/b200 -- a TFCC backend for B200 that provides the matmul hot path.
+//
+// Written against the reference's own headers (include path: <reference>/tfcc/core) and
+// meant to sit beside tfcc/cuda and tfcc/mkl.  It supplies
+//   * B200Device / B200Session       the pattern of CUDADevice / CUDASession
+//                                    (tfcc/cuda/framework/tfcc_cudadevice.cpp:36-108,
+//                                     tfcc/cuda/framework/tfcc_cudasession.cpp:27-90)
+//   * B200BlasInterface<T>           BlasInterface<T>::matmul x2
+//                                    (tfcc/core/interfaces/tfcc_blasinterface.h:41,55)
+//   * B200DataInterface<T>           set / get / zeros / copy, so data::set, data::get and
+//                                    Constant upload work (tfcc/core/interfaces/tfcc_datainterface.h)
+//   * tfcc::b200::quantization       matmul and reduce_sum with the signatures of
+//                                    tfcc/mkl/operations/tfcc_mklquantization.h:39-51
+// and forwards all arithmetic to libtfcc_b200 (include/tfcc_b200.h).  Nothing else of the
+// eighteen interface families is provided: other operators keep throwing NotImplementedError
+// as the core's defaults do.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <memory>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "tfcc.h"
+#include "interfaces/tfcc_blasinterface.h"
+#include "interfaces/tfcc_datainterface.h"
+#include "interfaces/tfcc_interface.h"
+#include "utils/tfcc_initializer.h"
+
+namespace tfcc {
+
+// Failure reported by the kernel library or the CUDA runtime (cf. CUDARuntimeError,
+// tfcc/cuda/exceptions/tfcc_cudaruntimeerror.h).
+class B200RuntimeError : public Exception {
+  int _status;
+  std::string _reason;
+
+ public:
+  explicit B200RuntimeError(int status);
+  const char* reason() const noexcept override;
+  int status() const { return _status; }
+};
+
+class B200Device : public Device {
+  int _cudaDevice;
+  bool _tf32;
+
+ public:
+  explicit B200Device(unsigned deviceID);
+  B200Device(unsigned deviceID, std::unique_ptr<Allocator> allocator);
+  ~B200Device();
+
+  void attach() override;
+
+  // Opt-in single-pass TF32 products (about 1e-3 relative); the default is fp32 results
+  // within 1e-5.  Mirrors CUDADevice::enableTensorCore (tfcc/cuda/framework/tfcc_cudadevice.h:39-41).
+  void enableTF32() { _tf32 = true; }
+  void disableTF32() { _tf32 = false; }
+  bool isTF32Enabled() const { return _tf32; }
+  int precisionMode() const;
+  int cudaDevice() const { return _cudaDevice; }
+
+  static unsigned getDeviceCount();
+};
+
+class B200Session : public Session {
+  B200Device& _device;
+  cudaStream_t _stream;
+  int* _status;       // device word the kernels OR give-up bits into
+  void* _scratch;     // grown on demand, reused across calls
+  size_t _scratchBytes;
+  bool _destroying;
+
+ public:
+  explicit B200Session(B200Device& device);
+  B200Session(B200Device& device, std::unique_ptr<Allocator> allocator);
+  ~B200Session();
+
+  void sync() const override;
+  Device& getDevice() override;
+  const Device& getDevice() const override;
+
+  cudaStream_t stream() const { return _stream; }
+  int* deviceStatus() const { return _status; }
+  // Scratch of at least `bytes` from the session allocator (valid until the next request).
+  void* scratch(size_t bytes);
+};
+
+template <class T>
+class B200BlasInterface : public BlasInterface<T> {
+ public:
+  Variable<T> matmul(const Tensor<T>& a, const Tensor<T>& b) override;
+  Variable<T> matmul(const Tensor<T>& a, const Tensor<T>& b, const Tensor<T>& c) override;
+};
+
+template <class T>
+class B200DataInterface : public DataInterface<T> {
+ public:
+  void set(T* dst, const T* data, size_t len) override;
+  void set(Variable<T>& a, const T* data) override;
+  void set(Variable<T>& a, std::vector<T>&& data) override;
+  void get(const Tensor<T>& a, T* data) override;
+  void zeros(Variable<T>& a) override;
+  Variable<T> copy(const Tensor<T>& a) override;
+};
+
+template <class T>
+Interface<T> get_b200_interface(T, B200Device& device);
+
+// Binds the calling thread to the least used B200 device and a fresh session on it
+// (cf. initialize_cuda, tfcc/cuda/utils/tfcc_cudautils.cpp:23-50).
+void initialize_b200();
+void initialize_b200(unsigned deviceID);
+
+namespace b200 {
+namespace quantization {
+
+std::tuple<Variable<int32_t>, Variable<float>, Variable<float>> matmul(
+    const Tensor<uint8_t>& a, const Tensor<int32_t>& reduceSumA, const Tensor<float>& minA,
+    const Tensor<float>& maxA, const Tensor<int8_t>& b, const Tensor<int32_t>& reduceSumB,
+    const Tensor<float>& minB, const Tensor<float>& maxB);
+
+template <class T>
+Variable<int32_t> reduce_sum(const Tensor<T>& a, bool row);
+
+}  // namespace quantization
+}  // namespace b200
+
+}  // namespace tfcc
