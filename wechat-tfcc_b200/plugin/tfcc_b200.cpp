@@ -178,9 +178,11 @@ B200Session::B200Session(B200Device& device, std::unique_ptr<Allocator> allocato
 
 B200Session::~B200Session() {
   _destroying = true;
-  preRelease();
   cudaStreamSynchronize(_stream);
+  // the session allocator refuses to be destroyed while any of its blocks is still out
   if (_scratch) _allocator->free(_scratch);
+  _scratch = nullptr;
+  preRelease();
   _device.free(_status);
   cudaStreamDestroy(_stream);
 }
