@@ -187,6 +187,37 @@ def time_launches(torch, fn, iters, flush=None):
     return float(np.mean(ts)), float(ts[len(ts) // 2])
 
 
+def time_graph_train(torch, calls, replays=5):
+    """Device time per launch of a train of calls captured in one CUDA graph.
+
+    `calls` is a list of zero-argument functions, each launching one operator on its own
+    operands; together the operand sets exceed twice the L2 size, so no launch finds its
+    inputs cached by the previous one.  Replaying the graph removes host launch cost, which
+    is how a latency-bound operator sequence is deployed.  Returns (mean us per call, best)."""
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for c in calls:   # warm-up outside capture (lazy module load, allocator growth)
+            c()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for c in calls:
+                c()
+        graph.replay()
+        stream.synchronize()
+        ts = []
+        for _ in range(replays):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3 / len(calls))
+    torch.cuda.current_stream().wait_stream(stream)
+    return float(np.mean(ts)), float(min(ts))
+
+
 def extra_measurements(torch, pkg, dev, peaks):
     """Other configurations of the path, single GPU, L2 flushed between launches."""
     lib = pkg.lib
@@ -197,7 +228,12 @@ def extra_measurements(torch, pkg, dev, peaks):
     out = {}
     to = lambda x: torch.from_numpy(x).to(dev)
 
+    l2_bytes = 126 * 1024 * 1024
+
     def sgemm_case(name, a, b, bias=None, iters=30, precision="fp32"):
+        """Two timings of one configuration: `us` = one launch after an L2 flush, CUDA events
+        around that launch (includes the launch gap an isolated call pays); `train_us` = mean
+        per launch of a CUDA-graph train over rotating operand sets larger than 2x L2."""
         ta, tb = to(a), to(b)
         tbias = to(bias) if bias is not None else None
         fn = lambda: pkg.blas.matmul(ta, tb, tbias, precision=precision)
@@ -208,9 +244,17 @@ def extra_measurements(torch, pkg, dev, peaks):
         batch = max(int(np.prod(a.shape[:-2])), int(np.prod(b.shape[:-2])), 1)
         flop = 2.0 * m * n * k * batch
         nbytes = 4.0 * (a.size + b.size + batch * m * n)
-        out[name] = {"us": med_ms * 1e3, "tflops": flop / (med_ms * 1e-3) / 1e12,
-                     "gbs": nbytes / (med_ms * 1e-3) / 1e9,
-                     "hbm_frac": nbytes / (med_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        sets = max(2, int(2 * l2_bytes // nbytes) + 1)
+        ops = [(ta.clone(), tb.clone()) for _ in range(sets)]
+        calls = [(lambda x=x, y=y: pkg.blas.matmul(x, y, tbias, precision=precision))
+                 for x, y in ops]
+        calls = calls * max(1, 16 // len(calls))
+        train_us, _ = time_graph_train(torch, calls)
+        out[name] = {"us": med_ms * 1e3, "train_us": train_us, "operand_sets": sets,
+                     "tflops": flop / (train_us * 1e-6) / 1e12,
+                     "gbs": nbytes / (train_us * 1e-6) / 1e9,
+                     "hbm_frac": nbytes / (train_us * 1e-6) / 1e9 / peaks["hbm_gbs"]}
+        del ops, calls
 
     # cfg1
     sgemm_case("cfg1_32x512x2048", rng.uniform(-1, 1, (32, 512)).astype(np.float32),
@@ -243,27 +287,36 @@ def extra_measurements(torch, pkg, dev, peaks):
 
     # cfg3 int8 (M=256) and the compute-bound int8 point (M=4096)
     for m in (256, 4096):
-        qa = to(rng.integers(0, 256, (m, 4096), dtype=np.uint8))
-        qb = to(rng.integers(-127, 128, (4096, 4096), dtype=np.int8))
-        ra = pkg.quantization.reduce_sum(qa, True)
-        rb = pkg.quantization.reduce_sum(qb, False)
-        c = torch.empty((m, 4096), dtype=torch.int32, device=dev)
-        stream = sess.stream_ptr
-
-        def fn():
-            st = lib.tfccb200_qgemm_u8s8s32(stream, qa.data_ptr(), 0, ra.data_ptr(), 0, -128,
-                                            qb.data_ptr(), 0, rb.data_ptr(), 0, 0, c.data_ptr(),
-                                            m * 4096, m, 4096, 4096, 1, sess.status_ptr)
-            assert st == 0, st
-        for _ in range(3):
-            fn()
-        _, med = time_launches(torch, fn, 30, fl)
-        ops = 2.0 * m * 4096 * 4096
         nbytes = m * 4096 + 4096 * 4096 + 4 * m * 4096 + 4 * m + 4 * 4096
-        out[f"cfg3_int8_M{m}"] = {"us": med * 1e3, "tops": ops / (med * 1e-3) / 1e12,
-                                  "gbs": nbytes / (med * 1e-3) / 1e9,
-                                  "hbm_frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        sets = max(2, int(2 * l2_bytes // nbytes) + 1)
+        ops = []
+        for _ in range(sets):
+            qa = to(rng.integers(0, 256, (m, 4096), dtype=np.uint8))
+            qb = to(rng.integers(-127, 128, (4096, 4096), dtype=np.int8))
+            ops.append((qa, qb, pkg.quantization.reduce_sum(qa, True),
+                        pkg.quantization.reduce_sum(qb, False),
+                        torch.empty((m, 4096), dtype=torch.int32, device=dev)))
+
+        def make(qa, qb, ra, rb, c):
+            def fn():
+                st = lib.tfccb200_qgemm_u8s8s32(
+                    torch.cuda.current_stream().cuda_stream, qa.data_ptr(), 0, ra.data_ptr(), 0,
+                    -128, qb.data_ptr(), 0, rb.data_ptr(), 0, 0, c.data_ptr(), m * 4096, m, 4096,
+                    4096, 1, sess.status_ptr)
+                assert st == 0, st
+            return fn
+        calls = [make(*o) for o in ops]
+        for c in calls[:2]:
+            c()
+        _, med = time_launches(torch, calls[0], 30, fl)
+        train_us, _ = time_graph_train(torch, calls * max(1, 16 // len(calls)))
+        ops_count = 2.0 * m * 4096 * 4096
+        out[f"cfg3_int8_M{m}"] = {"us": med * 1e3, "train_us": train_us, "operand_sets": sets,
+                                  "tops": ops_count / (train_us * 1e-6) / 1e12,
+                                  "gbs": nbytes / (train_us * 1e-6) / 1e9,
+                                  "hbm_frac": nbytes / (train_us * 1e-6) / 1e9 / peaks["hbm_gbs"]}
         if m == 256:
+            qa, qb = ops[0][0], ops[0][1]
             f1 = lambda: pkg.quantization.reduce_sum(qa, True)
             f2 = lambda: pkg.quantization.reduce_sum(qb, False)
             for f, nm, nb in ((f1, "reduce_sum_rows_256x4096", m * 4096),
@@ -272,6 +325,7 @@ def extra_measurements(torch, pkg, dev, peaks):
                     f()
                 _, med = time_launches(torch, f, 20, fl)
                 out[nm] = {"us": med * 1e3, "gbs": nb / (med * 1e-3) / 1e9}
+        del ops, calls
     sess.sync()
     return out
 
@@ -302,13 +356,33 @@ def run_ours(args):
     b = b_full[:, rank * ns:(rank + 1) * ns].contiguous() if world > 1 else b_full
     if world > 1:
         del b_full
-    staging = torch.empty((world, M, ns), dtype=torch.float32, device=dev) if world > 1 else None
-    c_out = torch.empty((M, N), dtype=torch.float32, device=dev) if world > 1 else None
+    staging = c_out = fused = None
+    mode = "single GPU"
+    if world > 1:
+        if args.gather == "fused":
+            try:
+                fused = pkg.parallel.FusedNSplit(M, N, dev)
+                mode = (f"N-split x{world}: B column shards; C tiles pushed to every rank from the "
+                        f"GEMM epilogue over NVLink ({fused.how}) + barrier")
+            except Exception as exc:  # peer mapping unavailable: NCCL gather of our local product
+                print(f"[bench] fused N-split unavailable ({exc!r}); using NCCL all-gather",
+                      file=sys.stderr)
+                fused = None
+        ok = torch.tensor([1.0 if fused is not None else 0.0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok.item()) == 0.0:
+            fused = None
+        if fused is None:
+            staging = torch.empty((world, M, ns), dtype=torch.float32, device=dev)
+            c_out = torch.empty((M, N), dtype=torch.float32, device=dev)
+            mode = f"N-split x{world}: B column shards, NCCL all-gather of C + interleave kernel"
     sess = pkg.session.get_session(dev)
 
     def step():
         if world == 1:
             return pkg.blas.matmul(a, b)
+        if fused is not None:
+            return fused.matmul(a, b)
         return pkg.parallel.nsplit_matmul(a, b, staging=staging, out=c_out)
 
     def barrier():
@@ -319,6 +393,22 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    if world > 1 and args.check:
+        # the assembled C must equal the product computed locally against the matching
+        # shard of B, bit for bit (N-split does not touch the K order)
+        full = step()
+        barrier()
+        bad = 0
+        for r in range(world):
+            g2 = torch.Generator(device=dev)
+            g2.manual_seed(4)
+            torch.empty((M, K), dtype=torch.float32, device=dev).uniform_(-1, 1, generator=g2)
+            bf = torch.empty((K, N), dtype=torch.float32, device=dev).uniform_(-1, 1, generator=g2)
+            ref = pkg.blas.matmul(a, bf[:, r * ns:(r + 1) * ns].contiguous())
+            bad += int((ref != full[:, r * ns:(r + 1) * ns]).sum().item())
+            del bf, ref
+        print(f"[bench] rank {rank}: N-split check, mismatching elements = {bad}", file=sys.stderr)
+        barrier()
     sampler = ClockSampler(local_rank)
     launches0 = pkg.launch_count()
     with sampler:
@@ -364,7 +454,10 @@ def run_ours(args):
         else:
             da = ha.to(dev, non_blocking=True)
             db = hb.to(dev, non_blocking=True)
-            full = pkg.parallel.nsplit_matmul(da, db, staging=staging, out=c_out)
+            if fused is not None:
+                full = fused.matmul(da, db)
+            else:
+                full = pkg.parallel.nsplit_matmul(da, db, staging=staging, out=c_out)
             h_full.copy_(full, non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
@@ -404,8 +497,7 @@ def run_ours(args):
             "data": "synthetic",
             "config": {
                 "workload": f"cfg5-large: fp32 A[{M},{K}] x B[{K},{N}], U(-1,1), seed 4",
-                "parallelism": "single GPU" if world == 1 else
-                               f"N-split x{world}: B column shards, NCCL all-gather of C + interleave",
+                "parallelism": mode,
                 "l2": f"operands ({4 * M * K >> 20} MiB each) exceed the 126 MB L2; no flush between steps",
                 "timing": "CUDA events on the launching stream, max over ranks"},
             "roofline": {
@@ -443,6 +535,10 @@ def main():
     ap.add_argument("--no-extra", action="store_true",
                     help="skip the secondary configurations (headline line only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--gather", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: push C tiles to peers from the GEMM epilogue, or NCCL all-gather")
+    ap.add_argument("--check", action="store_true",
+                    help="N > 1: verify the assembled C against the single-GPU product")
     ap.add_argument("--size", type=int, default=8192,
                     help="edge of the square GEMM (profiler captures use a smaller one)")
     args = ap.parse_args()

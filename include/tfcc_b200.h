@@ -186,6 +186,25 @@ TFCCB200_API int tfccb200_sgemm_skinny_static(void* stream, const float* A, cons
 TFCCB200_API size_t tfccb200_sgemm_skinny_static_capacity(void);
 
 /*
+ * N-split GEMM with the all-gather fused into the epilogue.  Rank `rank` of `num_ranks`
+ * GPUs holds A [M,K] and the column shard B_shard [K, N_shard] of B; it computes
+ * A . B_shard (+ bias_shard) on the tensor-core path and stores the tile results directly
+ * into columns [rank*N_shard, (rank+1)*N_shard) of EVERY rank's row-major
+ * C [M, num_ranks*N_shard]: C_ranks is a HOST array of num_ranks device pointers, entry r
+ * being rank r's C mapped into this process (peer access / symmetric memory).  Remote rows
+ * are written with ordinary 128-byte-line stores over NVLink while the remaining tiles are
+ * still being multiplied; no TMA or multicast instruction touches peer memory.  When the
+ * kernel has finished on every rank (the caller runs a cross-rank barrier after it), each
+ * rank holds the complete C.  Needs K % 4 == 0, N_shard % 4 == 0, 16-byte aligned bases.
+ * No counterpart in the reference, which has no multi-device operator.
+ */
+TFCCB200_API int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shard,
+                                            float* const* C_ranks, unsigned num_ranks,
+                                            unsigned rank, const float* bias_shard, unsigned M,
+                                            unsigned N_shard, unsigned K, int precision_mode,
+                                            int* device_status);
+
+/*
  * dst[m][g*ns + j] = src[g][m][j] for g < G, m < M, j < ns (fp32, ns % 4 == 0).
  * Turns the rank-major result of an all-gather of column shards of C into the
  * row-major [M, G*ns] matrix.  No counterpart in the reference, which has no

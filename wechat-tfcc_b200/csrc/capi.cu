@@ -198,7 +198,7 @@ int tfccb200_sgemm_ex(void* stream, const float* A, unsigned strideA, const floa
                       unsigned strideB, float* C, unsigned strideC, const float* bias, unsigned M,
                       unsigned N, unsigned K, unsigned batch, int precision_mode, int path,
                       void* workspace, size_t workspace_bytes, int* device_status) {
-  SgemmArgs a;
+  SgemmArgs a = {};
   a.stream = static_cast<cudaStream_t>(stream);
   a.A = A; a.B = B; a.C = C; a.bias = bias;
   a.strideA = strideA; a.strideB = strideB; a.strideC = strideC;
@@ -306,6 +306,40 @@ int tfccb200_reduce_sum_s8(void* stream, const int8_t* src, unsigned batch, unsi
 int tfccb200_reduce_sum_s16(void* stream, const int16_t* src, unsigned batch, unsigned rows,
                             unsigned cols, int row_flag, int32_t* dst) {
   return reduce_sum_checked<int16_t>(stream, src, batch, rows, cols, row_flag, dst);
+}
+
+int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shard,
+                               float* const* C_ranks, unsigned num_ranks, unsigned rank,
+                               const float* bias_shard, unsigned M, unsigned N_shard, unsigned K,
+                               int precision_mode, int* device_status) {
+  if (!A || !B_shard || !C_ranks || num_ranks == 0 || num_ranks > 8 || rank >= num_ranks)
+    return TFCCB200_EINVAL;
+  if (M == 0 || N_shard == 0 || K == 0) return TFCCB200_EINVAL;
+  if (precision_mode != TFCCB200_PRECISION_FP32 && precision_mode != TFCCB200_PRECISION_TF32)
+    return TFCCB200_EINVAL;
+  const unsigned long long n_total = static_cast<unsigned long long>(N_shard) * num_ranks;
+  if (n_total > 0xffffffffull || shape_overflows(M, static_cast<unsigned>(n_total), K, 1))
+    return TFCCB200_EOVERFLOW;
+  SgemmArgs a = {};
+  a.stream = static_cast<cudaStream_t>(stream);
+  a.A = A; a.B = B_shard; a.bias = bias_shard;
+  a.M = M; a.N = N_shard; a.K = K; a.batch = 1;
+  a.strideC = 0;
+  a.precision = precision_mode;
+  a.status = device_status;
+  a.num_dst = num_ranks;
+  for (unsigned d = 0; d < num_ranks; ++d) {
+    if (!C_ranks[d] || (reinterpret_cast<uintptr_t>(C_ranks[d]) & 15u)) return TFCCB200_EALIGN;
+    a.dst[d] = C_ranks[d];
+  }
+  a.C = C_ranks[rank];
+  a.ldc = n_total;
+  a.col_offset = rank * N_shard;
+  if (!umma_sgemm_supported(a)) return TFCCB200_EALIGN;  // N_shard % 4, K % 4, 16-byte bases
+  cudaError_t e;
+  const DeviceInfo* di = current_device_info(&e);
+  if (!di) return static_cast<int>(e);
+  return umma_sgemm(a, umma_plan(M, N_shard, 1, di->sm_count, false, -1).pair);
 }
 
 int tfccb200_sgemm_skinny_static(void* stream, const float* A, const float* B, float* C,

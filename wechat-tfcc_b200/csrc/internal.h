@@ -35,6 +35,12 @@ struct SgemmArgs {
   void* workspace;
   size_t workspace_bytes;
   int* status;
+  // Tensor-core path only: store the result into `num_dst` matrices of row pitch `ldc`
+  // starting at column `col_offset` (num_dst == 0: the plain case, C with pitch N).
+  float* dst[8];
+  unsigned num_dst;
+  unsigned long long ldc;
+  unsigned col_offset;
 };
 
 struct QgemmArgs {

@@ -46,8 +46,17 @@
 
 namespace tfccb200 {
 
+constexpr int kMaxDestinations = 8;
+
 struct UmmaGemmParams {
-  void* C;                 // float* (TF32) or int32_t* (I8)
+  // Result destinations: the same tile is stored into each of them (one in the plain case;
+  // one per GPU when column shards of C are pushed straight into every peer's full matrix).
+  // float* (TF32) or int32_t* (I8); element (b, i, j) goes to
+  // dst[d] + b*strideC + i*ldc + col_offset + j.
+  void* dst[kMaxDestinations];
+  unsigned num_dst;
+  unsigned long long ldc;  // row pitch of the destinations, in elements
+  unsigned col_offset;     // first destination column of this problem's column 0
   const float* bias;       // [N] or nullptr (TF32 only)
   const int32_t* rsA;      // I8: row sums of A, [batch?][M]
   const int32_t* rsB;      // I8: column sums of B, [batch?][N]
@@ -93,11 +102,16 @@ struct UmmaGemmConfig {
   static constexpr int kFirstConvertWarp = kFirstEpilogueWarp + kNumEpilogueWarps;
   static constexpr int kThreads = 32 * (kFirstConvertWarp + kNumConvertWarps);
   static constexpr int kEpiCols = kSplit ? BN / 2 : BN;  // accumulator columns owned by one thread
-  // setmaxnreg targets (kSplit): 128*40 + 256*200 + 128*56 = 63488 <= 65536 registers
-  static constexpr int kRegsControl = 40, kRegsEpilogue = 200, kRegsConvert = 56;
+  // setmaxnreg targets (kSplit): 128*40 + 256*208 + 128*48 = 64512 <= 65536 registers
+  static constexpr int kRegsControl = 40, kRegsEpilogue = 208, kRegsConvert = 48;
   static constexpr int kTmemCols = (2 * BN <= 32) ? 32 : 2 * BN;  // power of two by construction
-  static constexpr int kBarrierBytes = 1024;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // +align slack
+  // Each epilogue warp transposes 32x32 blocks through 4 KB of shared memory so that its
+  // global stores cover whole 128-byte lines (and peers' memory is written in full lines).
+  static constexpr int kEpiStageBytes = 4096;
+  static constexpr int kEpiStagingBytes = kNumEpilogueWarps * kEpiStageBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + kEpiStagingBytes + kBarrierBytes + 1024;  // +align slack
   static constexpr uint32_t kIdesc =
       (kKind == ptx::MmaKind::TF32)
           ? ptx::make_idesc(1u, 2u, 2u, 0u, 1u, static_cast<uint32_t>(kTileM), BN)
@@ -144,6 +158,47 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, int 
   }
 }
 
+// ---- epilogue: 32x32 block of 32-bit results, one row per lane -> coalesced line stores ----
+// Chunk q (4 values) of the lane's row goes to 16-byte slot q ^ (row & 7) of that row: both
+// the row-wise writes and the transposed reads below are then free of bank conflicts.
+__device__ __forceinline__ void epi_stage_chunk(uint32_t* stage, uint32_t lane, int q, uint4 v) {
+  *reinterpret_cast<uint4*>(stage + lane * 32 + ((q ^ (lane & 7)) << 2)) = v;
+}
+
+// After all 8 chunks of every lane are staged: lane l takes column chunk l%8 of rows
+// i*4 + l/8, adds the per-column term, and stores to every destination.  A warp instruction
+// writes 4 rows x 128 contiguous bytes.
+template <bool kIsFloat>
+__device__ __forceinline__ void epi_flush_block(uint32_t* stage, uint32_t lane, unsigned row0,
+                                                unsigned col_blk, const UmmaGemmParams& p,
+                                                unsigned long long batch_off, uint4 col_term) {
+  __syncwarp();
+  const unsigned cq = lane & 7u;
+  const unsigned col = col_blk + cq * 4;
+  const bool col_ok = col < p.N;  // N is a multiple of 4 on this path: a chunk is all in or out
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const unsigned r = i * 4 + (lane >> 3);
+    uint4 v = *reinterpret_cast<const uint4*>(stage + r * 32 + ((cq ^ (r & 7u)) << 2));
+    if constexpr (kIsFloat) {
+      v.x = __float_as_uint(__uint_as_float(v.x) + __uint_as_float(col_term.x));
+      v.y = __float_as_uint(__uint_as_float(v.y) + __uint_as_float(col_term.y));
+      v.z = __float_as_uint(__uint_as_float(v.z) + __uint_as_float(col_term.z));
+      v.w = __float_as_uint(__uint_as_float(v.w) + __uint_as_float(col_term.w));
+    } else {
+      v.x += col_term.x; v.y += col_term.y; v.z += col_term.z; v.w += col_term.w;
+    }
+    const unsigned grow = row0 + r;
+    if (grow < p.M && col_ok) {
+      const unsigned long long off =
+          batch_off + static_cast<unsigned long long>(grow) * p.ldc + p.col_offset + col;
+      for (unsigned d = 0; d < p.num_dst; ++d)
+        *reinterpret_cast<uint4*>(static_cast<uint32_t*>(p.dst[d]) + off) = v;
+    }
+  }
+  __syncwarp();
+}
+
 // Tile order: groups of 8 tile-rows are walked column by column so that CTAs
 // running at the same time share B panels and a small set of A panels in L2.
 __device__ __forceinline__ void tile_coords(unsigned t, unsigned tiles_m, unsigned tiles_n,
@@ -171,8 +226,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   // ---- carve shared memory (stage buffers need 1024-byte alignment for the swizzle) ----
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-  const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes;
-  uint8_t* bar_gen = smem_gen + kStages * Cfg::kStageBytes;
+  uint8_t* epi_stage_gen = smem_gen + kStages * Cfg::kStageBytes;
+  const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes + Cfg::kEpiStagingBytes;
+  uint8_t* bar_gen = smem_gen + kStages * Cfg::kStageBytes + Cfg::kEpiStagingBytes;
   // barrier slots (8 bytes each)
   auto full_raw = [&](int s) { return bar_base + 8u * s; };                 // TMA -> converter / MMA
   auto full_cvt = [&](int s) { return bar_base + 8u * (kStages + s); };     // converter -> MMA
@@ -345,10 +401,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     for (unsigned t = group_id; t < total_tiles; t += num_groups) {
       unsigned b, tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, b, tm, tn);
-      const unsigned row = tm * Cfg::kTileM + cta_rank * Cfg::kBM + q * 32 + lane;
+      const unsigned row0 = tm * Cfg::kTileM + cta_rank * Cfg::kBM + q * 32;  // lane 0's row
       const unsigned col0 = tn * BN + col_half * Cfg::kEpiCols;
-      const bool row_ok = row < p.M;
       const uint32_t lane_addr = tmem_base + ((q * 32u) << 16) + col_half * Cfg::kEpiCols;
+      const unsigned long long batch_off = p.strideC * b;
+      uint32_t* stage = reinterpret_cast<uint32_t*>(
+          epi_stage_gen + (warp - Cfg::kFirstEpilogueWarp) * Cfg::kEpiStageBytes);
+      auto bias_term = [&](unsigned col_blk) {
+        uint4 t = make_uint4(0u, 0u, 0u, 0u);  // +0.0f
+        const unsigned col = col_blk + (lane & 7u) * 4;
+        if (p.bias && col < p.N) t = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+        return t;
+      };
 
       if constexpr (kSplit) {
         // ---- promote every chunk's partial sum into registers (round-to-nearest adds) ----
@@ -371,21 +435,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           }
           release_acc(acc);
         }
-        if (row_ok) {
-          float* crow = static_cast<float*>(p.C) + p.strideC * b +
-                        static_cast<unsigned long long>(row) * p.N + col0;
 #pragma unroll
-          for (int j = 0; j < Cfg::kEpiCols; j += 4) {
-            const unsigned col = col0 + j;
-            if (col < p.N) {  // N % 4 == 0 on this path: a float4 is all in or all out
-              float4 v = make_float4(sum[j], sum[j + 1], sum[j + 2], sum[j + 3]);
-              if (p.bias) {
-                const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
-                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
-              }
-              *reinterpret_cast<float4*>(crow + j) = v;
-            }
-          }
+        for (int c = 0; c < Cfg::kEpiCols / 32; ++c) {
+          if (col0 + c * 32 >= p.N) break;  // warp-uniform
+#pragma unroll
+          for (int qq = 0; qq < 8; ++qq)
+            epi_stage_chunk(stage, lane, qq,
+                            make_uint4(__float_as_uint(sum[c * 32 + 4 * qq + 0]),
+                                       __float_as_uint(sum[c * 32 + 4 * qq + 1]),
+                                       __float_as_uint(sum[c * 32 + 4 * qq + 2]),
+                                       __float_as_uint(sum[c * 32 + 4 * qq + 3])));
+          epi_flush_block<true>(stage, lane, row0, col0 + c * 32, p, batch_off,
+                                bias_term(col0 + c * 32));
         }
       } else {
         const unsigned acc = it & 1u;
@@ -395,60 +456,46 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         ptx::tc_fence_after_sync();
         const uint32_t taddr = lane_addr + acc * BN;
         if constexpr (kKind == ptx::MmaKind::TF32) {
-          float* crow = static_cast<float*>(p.C) + p.strideC * b +
-                        static_cast<unsigned long long>(row) * p.N + col0;
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             if (col0 + c * 32 >= p.N) break;  // warp-uniform
             uint32_t r[32];
             ptx::tmem_ld_32x32(taddr + c * 32, r);
             ptx::tmem_ld_wait();
-            if (row_ok) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                const unsigned col = col0 + c * 32 + j;
-                if (col < p.N) {
-                  float4 v;
-                  v.x = __uint_as_float(r[j + 0]);
-                  v.y = __uint_as_float(r[j + 1]);
-                  v.z = __uint_as_float(r[j + 2]);
-                  v.w = __uint_as_float(r[j + 3]);
-                  if (p.bias) {
-                    const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
-                    v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
-                  }
-                  *reinterpret_cast<float4*>(crow + c * 32 + j) = v;
-                }
-              }
-            }
+            for (int qq = 0; qq < 8; ++qq)
+              epi_stage_chunk(stage, lane, qq,
+                              make_uint4(r[4 * qq], r[4 * qq + 1], r[4 * qq + 2], r[4 * qq + 3]));
+            epi_flush_block<true>(stage, lane, row0, col0 + c * 32, p, batch_off,
+                                  bias_term(col0 + c * 32));
           }
         } else {
-          int32_t* crow = static_cast<int32_t*>(p.C) + p.strideC * b +
-                          static_cast<unsigned long long>(row) * p.N + col0;
+          // zero-point correction: the row term joins before the transpose (this lane owns the
+          // row), the column term after it (the lane then owns four columns)
           const int32_t* rsB = p.rsB + static_cast<size_t>(p.strideRsB) * b;
-          int32_t row_term = p.kterm;
-          if (row_ok) row_term += p.rsA[static_cast<size_t>(p.strideRsA) * b + row] * p.offB;
+          uint32_t row_term = static_cast<uint32_t>(p.kterm);
+          if (row0 + lane < p.M)
+            row_term += static_cast<uint32_t>(p.rsA[static_cast<size_t>(p.strideRsA) * b + row0 + lane]) *
+                        static_cast<uint32_t>(p.offB);
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             if (col0 + c * 32 >= p.N) break;
             uint32_t r[32];
             ptx::tmem_ld_32x32(taddr + c * 32, r);
             ptx::tmem_ld_wait();
-            if (row_ok) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                const unsigned col = col0 + c * 32 + j;
-                if (col < p.N) {  // N % 16 == 0 on this path
-                  const int4 sb = __ldg(reinterpret_cast<const int4*>(rsB + col));
-                  int4 v;
-                  v.x = static_cast<int32_t>(r[j + 0]) + row_term + sb.x * p.offA;
-                  v.y = static_cast<int32_t>(r[j + 1]) + row_term + sb.y * p.offA;
-                  v.z = static_cast<int32_t>(r[j + 2]) + row_term + sb.z * p.offA;
-                  v.w = static_cast<int32_t>(r[j + 3]) + row_term + sb.w * p.offA;
-                  *reinterpret_cast<int4*>(crow + c * 32 + j) = v;
-                }
-              }
+            for (int qq = 0; qq < 8; ++qq)
+              epi_stage_chunk(stage, lane, qq,
+                              make_uint4(r[4 * qq] + row_term, r[4 * qq + 1] + row_term,
+                                         r[4 * qq + 2] + row_term, r[4 * qq + 3] + row_term));
+            uint4 ct = make_uint4(0u, 0u, 0u, 0u);
+            const unsigned col = col0 + c * 32 + (lane & 7u) * 4;
+            if (col < p.N) {  // N % 16 == 0 on this path
+              const uint4 sb = __ldg(reinterpret_cast<const uint4*>(rsB + col));
+              const uint32_t oa = static_cast<uint32_t>(p.offA);
+              ct = make_uint4(sb.x * oa, sb.y * oa, sb.z * oa, sb.w * oa);
             }
+            epi_flush_block<false>(stage, lane, row0, col0 + c * 32, p, batch_off, ct);
           }
         }
         release_acc(acc);

@@ -185,7 +185,12 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
     return TFCCB200_EINVAL;
 
   UmmaGemmParams p = {};
-  p.C = a.C;
+  p.num_dst = a.num_dst ? a.num_dst : 1;
+  if (p.num_dst > kMaxDestinations) return TFCCB200_EINVAL;
+  p.dst[0] = a.C;
+  for (unsigned d = 0; d < a.num_dst; ++d) p.dst[d] = a.dst[d];
+  p.ldc = a.ldc ? a.ldc : a.N;
+  p.col_offset = a.col_offset;
   p.bias = a.bias;
   p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
   p.strideC = a.strideC;
@@ -214,7 +219,7 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
     }
     if (bn == 256) return launch<T, true, 2, 256, 3>(a.stream, ta, tb, p, sms);
     if (bn == 128) return launch<T, true, 2, 128, 4>(a.stream, ta, tb, p, sms);
-    return launch<T, true, 2, 64, 5>(a.stream, ta, tb, p, sms);
+    return launch<T, true, 2, 64, 4>(a.stream, ta, tb, p, sms);
   }
   if (!pair) {
     if (bn == 256) return launch<T, false, 1, 256, 4>(a.stream, ta, tb, p, sms);
@@ -259,7 +264,10 @@ int umma_qgemm(const QgemmArgs& a, bool pair) {
     return TFCCB200_EINVAL;
 
   UmmaGemmParams p = {};
-  p.C = a.C;
+  p.num_dst = 1;
+  p.dst[0] = a.C;
+  p.ldc = a.N;
+  p.col_offset = 0;
   p.rsA = a.rsA; p.rsB = a.rsB;
   p.offA = a.offA; p.offB = a.offB;
   p.kterm = static_cast<int32_t>(static_cast<uint32_t>(a.offA) * static_cast<uint32_t>(a.offB) *

@@ -19,8 +19,10 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+import ctypes as C
+
 from . import blas, exceptions
-from ._lib import check, lib
+from ._lib import PRECISIONS, check, lib
 from .session import get_session
 
 
@@ -83,3 +85,83 @@ def nsplit_matmul(a, b_shard, bias_shard=None, *, group=None, matmul_fn=None,
     dist.all_gather_into_tensor(staging.view(-1), c_local.view(-1), group=group)
     interleave_fn(staging, out)
     return out
+
+
+class FusedNSplit:
+    """N-split matmul whose all-gather happens inside the GEMM epilogue.
+
+    Every rank owns a full row-major ``C [M, N]`` that its peers can address (symmetric
+    memory, or CUDA IPC handles when that is unavailable).  ``matmul`` runs the tensor-core
+    GEMM on this rank's column shard of B and stores each finished tile into the matching
+    columns of every rank's C with ordinary 128-byte-line stores over NVLink, overlapping the
+    transfer with the remaining tiles; a cross-rank barrier then closes the step.  The result
+    is valid on every rank until the next ``matmul`` on any rank starts writing again.
+    """
+
+    def __init__(self, m: int, n_total: int, device, group=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.device = torch.device(device)
+        if n_total % self.world != 0:
+            raise exceptions.InvalidArgumentError("N must divide evenly over the ranks")
+        self.m, self.n_total, self.ns = m, n_total, n_total // self.world
+        self.handle = None
+        self.how = None
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.c = symm_mem.empty((m, n_total), dtype=torch.float32, device=self.device)
+            self.handle = symm_mem.rendezvous(self.c, group=self.group)
+            ptrs = [int(p) for p in self.handle.buffer_ptrs]
+            self.how = "symmetric memory"
+        except Exception as exc:  # fall back to classic CUDA IPC handles
+            self.handle = None
+            self._symm_error = repr(exc)
+            self.c = torch.empty((m, n_total), dtype=torch.float32, device=self.device)
+            ptrs = self._exchange_ipc()
+            self.how = "CUDA IPC handles"
+        self._ptrs = (C.c_void_p * self.world)(*ptrs)
+        self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
+
+    def _exchange_ipc(self):
+        storage = self.c.untyped_storage()
+        handle = storage._share_cuda_()
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, (handle, self.c.storage_offset()), group=self.group)
+        self._peers = []
+        ptrs = []
+        for r, (h, off) in enumerate(gathered):
+            if r == self.rank:
+                ptrs.append(self.c.data_ptr())
+                continue
+            st = torch.UntypedStorage._new_shared_cuda(*h)
+            t = torch.empty(0, dtype=torch.float32, device=st.device).set_(
+                st, off, (self.m, self.n_total), (self.n_total, 1))
+            self._peers.append(t)  # keeps the mapping alive
+            ptrs.append(t.data_ptr())
+        return ptrs
+
+    def barrier(self):
+        """All ranks' kernels issued so far on the current streams have completed."""
+        if self.handle is not None and hasattr(self.handle, "barrier"):
+            self.handle.barrier(channel=0)
+        else:
+            dist.all_reduce(self._flag, group=self.group)
+
+    def matmul(self, a, b_shard, bias_shard=None, *, precision: str = "fp32"):
+        if a.dim() != 2 or b_shard.dim() != 2 or a.shape[1] != b_shard.shape[0]:
+            raise exceptions.InvalidArgumentError("shape invalid")
+        if a.shape[0] != self.m or b_shard.shape[1] != self.ns:
+            raise exceptions.InvalidArgumentError("operands do not match the planned C")
+        for t in (a, b_shard) + ((bias_shard,) if bias_shard is not None else ()):
+            if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
+                raise exceptions.InvalidArgumentError("operands must be contiguous float32 CUDA tensors")
+        sess = get_session(self.device)
+        with torch.cuda.device(self.device):
+            st = lib.tfccb200_sgemm_nsplit_push(
+                sess.stream_ptr, a.data_ptr(), b_shard.data_ptr(), self._ptrs, self.world, self.rank,
+                bias_shard.data_ptr() if bias_shard is not None else None, self.m, self.ns,
+                a.shape[1], PRECISIONS[precision], sess.status_ptr)
+        check(st)
+        self.barrier()
+        return self.c
