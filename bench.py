@@ -35,10 +35,10 @@ from __graft_entry__ import load_oracle, load_package  # noqa: E402
 M = N = K = 8192   # --size overrides this for profiler captures; the headline is 8192
 FLOP_PER_STEP = 2.0 * M * N * K
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one umma_gemm_kernel launch, from the ncu
-# capture summarised in profiles/ (captured at 4096^3 and scaled by the tiles processed,
-# traffic per tile being constant for this kernel).  None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one umma_gemm_kernel launch on the 8192^3
+# problem, from the ncu capture summarised in profiles/umma_gemm_tf32x3_pair_8192_traffic.md
+# (2,288,931,584 B read + 256,376,832 B written).  Only valid for the single-GPU headline size.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2545308416
 
 
 def measured_peaks():
@@ -218,6 +218,41 @@ def time_graph_train(torch, calls, replays=5):
     return float(np.mean(ts)), float(min(ts))
 
 
+def profile_case(torch, pkg, dev, name):
+    """Launch one configuration's kernel a few times and return: the small, self-ending
+    workload that `ncu -k <kernel> -c 1` captures (`--profile-case NAME`)."""
+    rng = np.random.default_rng(5)
+    to = lambda x: torch.from_numpy(x).to(dev)
+    sess = pkg.session.get_session(dev)
+    if name.startswith("gemv_M"):
+        m = int(name[len("gemv_M"):])
+        w = to(rng.normal(0, 0.02, (4096, 16384)).astype(np.float32))
+        x = to(rng.normal(0, 1, (m, 4096)).astype(np.float32))
+        fn = lambda: pkg.blas.matmul(x, w)
+    elif name.startswith("int8_M"):
+        m = int(name[len("int8_M"):])
+        qa = to(rng.integers(0, 256, (m, 4096), dtype=np.uint8))
+        qb = to(rng.integers(-127, 128, (4096, 4096), dtype=np.int8))
+        ra, rb = pkg.quantization.reduce_sum(qa, True), pkg.quantization.reduce_sum(qb, False)
+        f = lambda v: torch.tensor([v], dtype=torch.float32)
+        fn = lambda: pkg.quantization.matmul(qa, ra, f(-128.0), f(127.0), qb, rb, f(-128.0), f(127.0))
+    elif name == "attention_qk":
+        q = to(rng.normal(0, 1, (96, 128, 64)).astype(np.float32))
+        kt = to(rng.normal(0, 1, (96, 64, 128)).astype(np.float32))
+        fn = lambda: pkg.blas.matmul(q, kt)
+    elif name == "ffn1":
+        x = to(rng.normal(0, 1, (8, 128, 768)).astype(np.float32))
+        w = to(rng.normal(0, 0.02, (768, 3072)).astype(np.float32))
+        b = to(np.zeros(3072, np.float32))
+        fn = lambda: pkg.blas.matmul(x, w, b)
+    else:
+        raise SystemExit(f"unknown --profile-case {name}")
+    for _ in range(5):
+        fn()
+    sess.sync()
+    print(json.dumps({"profile_case": name, "launches": pkg.launch_count()}))
+
+
 def extra_measurements(torch, pkg, dev, peaks):
     """Other configurations of the path, single GPU, L2 flushed between launches."""
     lib = pkg.lib
@@ -343,6 +378,9 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    if args.profile_case:
+        profile_case(torch, pkg, dev, args.profile_case)
+        return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     assert N % world == 0
@@ -488,7 +526,11 @@ def run_ours(args):
         e2e_value = FLOP_PER_STEP / (e2e_ms / e2e_steps * 1e-3) / 1e12
         kern_flop = FLOP_PER_STEP / world
         achieved = kern_flop / (kern_mean_ms * 1e-3) / 1e12
-        tensor_peak = peaks["bf16_tflops"] / 2.0 / 3.0
+        # a kernel timed alone is judged against the burst figure, one timed inside a long
+        # region (power-capped clocks) against the sustained one
+        sustained = ms_total >= 250.0 and peaks.get("bf16_tflops_sustained")
+        bf16_peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
+        tensor_peak = bf16_peak / 2.0 / 3.0
         line = {
             "metric": f"fp32 matmul TFLOP/s ({M}^3)", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -504,10 +546,12 @@ def run_ours(args):
                 "bound": "tensor", "kernel": "umma_gemm_kernel<TF32, split, cta_group::2, BN=256>",
                 "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
                 "frac": achieved / tensor_peak,
-                "peak_basis": f"{peaks['source']} bf16 {peaks['bf16_tflops']} TFLOP/s / 2 "
-                              "(TF32 runs at half the bf16 rate) / 3 (MMAs per fp32 product)",
+                "peak_basis": f"of {peaks['source']}: bf16 {'sustained' if sustained else 'burst'} "
+                              f"{bf16_peak} TFLOP/s / 2 (TF32 runs at half the bf16 rate) / 3 "
+                              "(MMAs per fp32 product)",
+                "frac_of_burst_peak": achieved / (peaks["bf16_tflops"] / 6.0),
                 "executed_tf32_tflops": 3.0 * achieved,
-                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (world == 1 and M == 8192) else None,
                 "algorithmic_bytes": 4 * (M * K + K * ns + M * ns)},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps},
@@ -537,6 +581,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--gather", choices=["fused", "nccl"], default="fused",
                     help="N > 1: push C tiles to peers from the GEMM epilogue, or NCCL all-gather")
+    ap.add_argument("--profile-case", default="",
+                    help="run only one small configuration (gemv_M1, int8_M256, int8_M4096, "
+                         "attention_qk, ffn1) a few times and exit: the target of ncu captures")
     ap.add_argument("--check", action="store_true",
                     help="N > 1: verify the assembled C against the single-GPU product")
     ap.add_argument("--size", type=int, default=8192,

@@ -183,3 +183,35 @@ def test_head_truncation_setting_does_not_change_bits(pkg):
     c_msk = pkg.blas.matmul(mask(a), mask(b), precision="tf32", path="umma")
     pkg.session.get_session(d).sync()
     assert torch.equal(c_raw, c_msk)
+
+
+def test_nsplit_push_entry_point_on_one_gpu(pkg, orc):
+    """tfccb200_sgemm_nsplit_push with two 'ranks' played one after the other on one GPU: each
+    pushes its column shard of C into both full-size result matrices.  Checks the column
+    offsets, the row pitch and the multi-destination stores; the NVLink part needs two GPUs
+    and is exercised by `bench.py --gpus N --check`."""
+    import ctypes as C
+    d = dev_of()
+    rng = np.random.default_rng(77)
+    m, k, ns, g = 300, 260, 132, 2
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, g * ns)).astype(np.float32)
+    bias = rng.uniform(-1, 1, g * ns).astype(np.float32)
+    ta = torch.from_numpy(a).to(d)
+    outs = [torch.full((m, g * ns), float("nan"), dtype=torch.float32, device=d) for _ in range(g)]
+    ptrs = (C.c_void_p * g)(*[o.data_ptr() for o in outs])
+    stream = torch.cuda.current_stream(d).cuda_stream
+    for r in range(g):
+        tb = torch.from_numpy(np.ascontiguousarray(b[:, r * ns:(r + 1) * ns])).to(d)
+        tbias = torch.from_numpy(np.ascontiguousarray(bias[r * ns:(r + 1) * ns])).to(d)
+        st = pkg.lib.tfccb200_sgemm_nsplit_push(stream, ta.data_ptr(), tb.data_ptr(), ptrs, g, r,
+                                                tbias.data_ptr(), m, ns, k, 0, None)
+        assert st == 0, pkg.lib.tfccb200_strerror(st)
+        torch.cuda.synchronize()
+    truth = orc.blas_matmul(a, b, bias)
+    for o in outs:
+        assert orc.normwise_rel_error(o.cpu().numpy(), truth) < TOL_FP32
+    assert torch.equal(outs[0], outs[1])
+    # misaligned shard width is refused
+    assert pkg.lib.tfccb200_sgemm_nsplit_push(stream, ta.data_ptr(), ta.data_ptr(), ptrs, g, 0, None,
+                                              m, 130, k, 0, None) == -2

@@ -470,32 +470,40 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                                   bias_term(col0 + c * 32));
           }
         } else {
-          // zero-point correction: the row term joins before the transpose (this lane owns the
-          // row), the column term after it (the lane then owns four columns)
+          // zero-point correction.  The int8 mainloop already saturates shared-memory
+          // bandwidth (TMA fill + MMA operand reads), so this epilogue stays out of shared
+          // memory: every lane stores its own row's columns straight from registers.
           const int32_t* rsB = p.rsB + static_cast<size_t>(p.strideRsB) * b;
+          const unsigned row = row0 + lane;
+          const bool row_ok = row < p.M;
           uint32_t row_term = static_cast<uint32_t>(p.kterm);
-          if (row0 + lane < p.M)
-            row_term += static_cast<uint32_t>(p.rsA[static_cast<size_t>(p.strideRsA) * b + row0 + lane]) *
+          if (row_ok)
+            row_term += static_cast<uint32_t>(p.rsA[static_cast<size_t>(p.strideRsA) * b + row]) *
                         static_cast<uint32_t>(p.offB);
+          uint32_t* crow = static_cast<uint32_t*>(p.dst[0]) + batch_off +
+                           static_cast<unsigned long long>(row) * p.ldc + p.col_offset + col0;
+          const uint32_t oa = static_cast<uint32_t>(p.offA);
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             if (col0 + c * 32 >= p.N) break;
             uint32_t r[32];
             ptx::tmem_ld_32x32(taddr + c * 32, r);
             ptx::tmem_ld_wait();
+            if (row_ok) {
 #pragma unroll
-            for (int qq = 0; qq < 8; ++qq)
-              epi_stage_chunk(stage, lane, qq,
-                              make_uint4(r[4 * qq] + row_term, r[4 * qq + 1] + row_term,
-                                         r[4 * qq + 2] + row_term, r[4 * qq + 3] + row_term));
-            uint4 ct = make_uint4(0u, 0u, 0u, 0u);
-            const unsigned col = col0 + c * 32 + (lane & 7u) * 4;
-            if (col < p.N) {  // N % 16 == 0 on this path
-              const uint4 sb = __ldg(reinterpret_cast<const uint4*>(rsB + col));
-              const uint32_t oa = static_cast<uint32_t>(p.offA);
-              ct = make_uint4(sb.x * oa, sb.y * oa, sb.z * oa, sb.w * oa);
+              for (int j = 0; j < 32; j += 4) {
+                const unsigned col = col0 + c * 32 + j;
+                if (col < p.N) {  // N % 16 == 0 on this path
+                  const uint4 sb = __ldg(reinterpret_cast<const uint4*>(rsB + col));
+                  uint4 v;
+                  v.x = r[j + 0] + row_term + sb.x * oa;
+                  v.y = r[j + 1] + row_term + sb.y * oa;
+                  v.z = r[j + 2] + row_term + sb.z * oa;
+                  v.w = r[j + 3] + row_term + sb.w * oa;
+                  *reinterpret_cast<uint4*>(crow + c * 32 + j) = v;
+                }
+              }
             }
-            epi_flush_block<false>(stage, lane, row0, col0 + c * 32, p, batch_off, ct);
           }
         }
         release_acc(acc);
