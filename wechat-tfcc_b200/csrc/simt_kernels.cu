@@ -564,7 +564,8 @@ int reduce_sum(cudaStream_t stream, const T* src, unsigned batch, unsigned rows,
   cudaError_t e =
       cudaMemsetAsync(dst, 0, static_cast<size_t>(batch) * cols * sizeof(int32_t), stream);
   if (e != cudaSuccess) return static_cast<int>(e);
-  // row slabs sized so that the grid has a few thousand CTAs at most
+  // row slabs of 64: fewer slabs mean fewer atomics per column, which is what bounds this
+  // kernel; the grid stays within a few thousand CTAs
   unsigned slab = 64;
   while ((rows + slab - 1) / slab > 4096) slab *= 2;
   constexpr unsigned V = 4 / sizeof(T);
