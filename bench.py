@@ -52,7 +52,8 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples SM clock and throttle reasons of one GPU while a region runs: one
+    `nvidia-smi -lms 100` child process whose lines are collected by a reader thread."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -61,30 +62,38 @@ class ClockSampler:
     def __init__(self, index: int):
         self.index = index
         self.samples = []
-        self._stop = threading.Event()
+        self._proc = None
         self._thread = None
 
-    def _run(self):
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(
-                    ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                     "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
-                parts = [x.strip() for x in out.stdout.strip().split(",")]
-                if len(parts) >= 6:
-                    self.samples.append(parts)
-            except Exception:
-                pass
-            self._stop.wait(0.1)
+    def _read(self):
+        for line in self._proc.stdout:
+            parts = [x.strip() for x in line.strip().split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
 
     def __enter__(self):
-        self._thread = threading.Thread(target=self._run, daemon=True)
-        self._thread.start()
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self._thread = threading.Thread(target=self._read, daemon=True)
+            self._thread.start()
+            time.sleep(0.35)  # let the first samples arrive before the region starts
+            self.samples.clear()
+        except Exception:
+            self._proc = None
         return self
 
     def __exit__(self, *exc):
-        self._stop.set()
-        self._thread.join(timeout=6)
+        if self._proc is not None:
+            time.sleep(0.12)
+            self._proc.terminate()  # this exact child, by handle
+            try:
+                self._proc.wait(timeout=5)
+            except Exception:
+                self._proc.kill()
+            self._thread.join(timeout=5)
 
     def summary(self):
         if not self.samples:

@@ -279,3 +279,21 @@ def test_config4_encoder_stack_matmuls(pkg, orc):
     got = got.cpu().numpy()
     assert orc.normwise_rel_error(got, truth) < 1e-5
     assert orc.is_similar(got, truth.astype(np.float32))
+
+
+def test_host_buffer_entry_point_pipelined_large_product(pkg, orc):
+    """Large single products take the overlapped path of tfccb200_sgemm_host (B uploaded first,
+    A in 1024-row blocks while earlier blocks multiply and download); ragged last block."""
+    rng = np.random.default_rng(31)
+    m, k, n = 2348, 2048, 4096
+    a = torch.from_numpy(rng.uniform(-1, 1, (m, k)).astype(np.float32)).pin_memory().numpy()
+    b = torch.from_numpy(rng.uniform(-1, 1, (k, n)).astype(np.float32)).pin_memory().numpy()
+    bias = rng.uniform(-1, 1, n).astype(np.float32)
+    got = pkg.blas.matmul_host(a, b, bias)
+    rows = np.sort(rng.choice(m, 96, replace=False))
+    rows[-1] = m - 1
+    truth = a[rows].astype(np.float64) @ b.astype(np.float64) + bias
+    assert orc.normwise_rel_error(got[rows], truth) < TOL_FP32
+    # every row block was written: no element of the output kept its initial garbage pattern
+    dev = run(pkg, a, b, bias)
+    assert np.array_equal(got, dev)

@@ -4,8 +4,10 @@
 
 #include <atomic>
 #include <cmath>
+#include <cstdlib>
 #include <limits>
 #include <mutex>
+#include <vector>
 
 #include "internal.h"
 
@@ -152,6 +154,39 @@ int64_t quantized_offset_8bit(float minv, float maxv) {
   const double range = (static_cast<double>(maxv - minv)) * range_adjust;
   const double range_scale = step_cnt / range;
   return static_cast<int64_t>(std::round(minv * range_scale));
+}
+
+// Scoped helpers for the host-buffer entry points.
+struct ScopedStream {
+  cudaStream_t s = nullptr;
+  cudaError_t create() { return cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking); }
+  ~ScopedStream() {
+    if (s) cudaStreamDestroy(s);
+  }
+};
+struct ScopedEvent {
+  cudaEvent_t e = nullptr;
+  cudaError_t create() { return cudaEventCreateWithFlags(&e, cudaEventDisableTiming); }
+  ~ScopedEvent() {
+    if (e) cudaEventDestroy(e);
+  }
+};
+
+// The staging buffers of the host-buffer entry points come from the device's default
+// stream-ordered pool.  Its release threshold is raised once so that the pool keeps the
+// memory between calls instead of returning it to the driver at every synchronisation.
+void retain_pool_memory() {
+  static std::atomic<unsigned long long> done{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
+  const unsigned long long bit = 1ull << dev;
+  if (done.load(std::memory_order_acquire) & bit) return;
+  cudaMemPool_t pool;
+  if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+    unsigned long long threshold = ~0ull;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold);
+  }
+  done.fetch_or(bit, std::memory_order_release);
 }
 
 struct DeviceBuffer {
@@ -373,6 +408,78 @@ int tfccb200_sgemm_host(void* stream, const float* hA, unsigned strideA, const f
   const size_t ws = tfccb200_sgemm_workspace(M, N, K, batch, precision_mode);
   DeviceBuffer dA(s), dB(s), dC(s), dBias(s), dW(s), dS(s);
   cudaError_t e;
+
+  // One large product: the transfers dominate, so they are overlapped with the arithmetic.
+  // B goes up first; A then goes up in row blocks on a copy stream while the block before it
+  // is multiplied on the caller's stream and the block before that comes down on a third
+  // stream.  (Pinned host buffers are needed for the copies to really overlap.)
+  constexpr unsigned kRowBlock = 1024;
+  retain_pool_memory();
+  static const bool pipeline = [] {
+    const char* v = std::getenv("TFCCB200_HOST_PIPELINE");
+    return !(v && v[0] == '0');
+  }();
+  if (pipeline && batch == 1 && M >= 2 * kRowBlock &&
+      (nA + nB + nC) * 4 >= (size_t(64) << 20)) {
+    ScopedStream up, down;
+    ScopedEvent b_ready, c_done_all;
+    if ((e = up.create()) != cudaSuccess || (e = down.create()) != cudaSuccess) return e;
+    if ((e = b_ready.create()) != cudaSuccess || (e = c_done_all.create()) != cudaSuccess) return e;
+    if ((e = dA.alloc(nA * 4)) != cudaSuccess) return e;
+    if ((e = dB.alloc(nB * 4)) != cudaSuccess) return e;
+    if ((e = dC.alloc(nC * 4)) != cudaSuccess) return e;
+    if ((e = dS.alloc(sizeof(int))) != cudaSuccess) return e;
+    if (hbias && (e = dBias.alloc(size_t(N) * 4)) != cudaSuccess) return e;
+    if ((e = cudaMemsetAsync(dS.p, 0, sizeof(int), s)) != cudaSuccess) return e;
+    // the buffers come from the caller's stream: the side streams start after that point
+    ScopedEvent alloc_done;
+    if ((e = alloc_done.create()) != cudaSuccess) return e;
+    if ((e = cudaEventRecord(alloc_done.e, s)) != cudaSuccess) return e;
+    if ((e = cudaStreamWaitEvent(up.s, alloc_done.e, 0)) != cudaSuccess) return e;
+    if ((e = cudaStreamWaitEvent(down.s, alloc_done.e, 0)) != cudaSuccess) return e;
+    if (hbias && (e = cudaMemcpyAsync(dBias.p, hbias, size_t(N) * 4, cudaMemcpyHostToDevice,
+                                      up.s)) != cudaSuccess)
+      return e;
+    if ((e = cudaMemcpyAsync(dB.p, hB, nB * 4, cudaMemcpyHostToDevice, up.s)) != cudaSuccess)
+      return e;
+    if ((e = cudaEventRecord(b_ready.e, up.s)) != cudaSuccess) return e;
+    if ((e = cudaStreamWaitEvent(s, b_ready.e, 0)) != cudaSuccess) return e;
+    const unsigned blocks = (M + kRowBlock - 1) / kRowBlock;
+    std::vector<ScopedEvent> a_ready(blocks), c_ready(blocks);
+    for (unsigned i = 0; i < blocks; ++i) {
+      const unsigned r0 = i * kRowBlock;
+      const unsigned rows = (M - r0 < kRowBlock) ? M - r0 : kRowBlock;
+      float* dAi = static_cast<float*>(dA.p) + size_t(r0) * K;
+      float* dCi = static_cast<float*>(dC.p) + size_t(r0) * N;
+      if ((e = a_ready[i].create()) != cudaSuccess || (e = c_ready[i].create()) != cudaSuccess)
+        return e;
+      if ((e = cudaMemcpyAsync(dAi, hA + size_t(r0) * K, size_t(rows) * K * 4,
+                               cudaMemcpyHostToDevice, up.s)) != cudaSuccess)
+        return e;
+      if ((e = cudaEventRecord(a_ready[i].e, up.s)) != cudaSuccess) return e;
+      if ((e = cudaStreamWaitEvent(s, a_ready[i].e, 0)) != cudaSuccess) return e;
+      int st = tfccb200_sgemm(s, dAi, 0, static_cast<float*>(dB.p), 0, dCi, rows * N,
+                              hbias ? static_cast<float*>(dBias.p) : nullptr, rows, N, K, 1,
+                              precision_mode, nullptr, 0, static_cast<int*>(dS.p));
+      if (st == TFCCB200_EWORKSPACE) return st;  // cannot happen: row blocks have more than 8 rows
+      if (st != TFCCB200_OK) return st;
+      if ((e = cudaEventRecord(c_ready[i].e, s)) != cudaSuccess) return e;
+      if ((e = cudaStreamWaitEvent(down.s, c_ready[i].e, 0)) != cudaSuccess) return e;
+      if ((e = cudaMemcpyAsync(hC + size_t(r0) * N, dCi, size_t(rows) * N * 4,
+                               cudaMemcpyDeviceToHost, down.s)) != cudaSuccess)
+        return e;
+    }
+    int dev_status = 0;
+    if ((e = cudaMemcpyAsync(&dev_status, dS.p, sizeof(int), cudaMemcpyDeviceToHost, s)) !=
+        cudaSuccess)
+      return e;
+    // rejoin: the caller's stream (which frees the buffers) must follow both side streams
+    if ((e = cudaEventRecord(c_done_all.e, down.s)) != cudaSuccess) return e;
+    if ((e = cudaStreamWaitEvent(s, c_done_all.e, 0)) != cudaSuccess) return e;
+    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return e;
+    return dev_status ? TFCCB200_EDEVICE : TFCCB200_OK;
+  }
+
   if ((e = dA.alloc(nA * 4)) != cudaSuccess) return e;
   if ((e = dB.alloc(nB * 4)) != cudaSuccess) return e;
   if ((e = dC.alloc(nC * 4)) != cudaSuccess) return e;
