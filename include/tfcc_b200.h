@@ -155,6 +155,49 @@ TFCCB200_API int tfccb200_reduce_sum_s8(void* stream, const int8_t* src, unsigne
 TFCCB200_API int tfccb200_reduce_sum_s16(void* stream, const int16_t* src, unsigned batch, unsigned rows,
                             unsigned cols, int row_flag, int32_t* dst);
 
+/* ---- element types of the quantization entry points ------------------------ */
+#define TFCCB200_TYPE_S8 0
+#define TFCCB200_TYPE_U8 1
+#define TFCCB200_TYPE_S16 2
+#define TFCCB200_TYPE_U16 3
+#define TFCCB200_TYPE_S32 4
+#define TFCCB200_TYPE_U32 5
+
+/*
+ * minmax[0] = min(src), minmax[1] = max(src) over n floats; minmax is DEVICE memory (two
+ * floats, 8-byte aligned).  The range reduction of MKLQuantizationInterface<T>::quantize(a)
+ * (tfcc/mkl/interfaces/tfcc_mklquantizationinterface.cpp:47-57).
+ */
+TFCCB200_API int tfccb200_minmax_f32(void* stream, const float* src, size_t n, float* minmax);
+
+/*
+ * dst[i] = clamp(round(src[i] * scale) - offset + lowest(T)), scale and offset derived in
+ * double precision from the DEVICE scalars *min_value, *max_value; everything becomes
+ * lowest(T) when *min_value >= *max_value.  dst_type is a TFCCB200_TYPE_*.  Replaces
+ * MKLQuantizationInterface<T>::quantize (tfcc_mklquantizationinterface.cpp:150-240) and
+ * _MKLQuantizationKernel<T>::quantize (tfcc/mkl/kernel/tfcc_mklquantizationkernel.hpp:23-33).
+ */
+TFCCB200_API int tfccb200_quantize_f32(void* stream, const float* src, size_t n,
+                                       const float* min_value, const float* max_value, void* dst,
+                                       int dst_type);
+
+/*
+ * dst[i] = float(min + (src[i] - lowest(T)) * scale); *min_value when the range is empty.
+ * Replaces MKLQuantizationInterface<T>::dequantize (tfcc_mklquantizationinterface.cpp:284-333).
+ */
+TFCCB200_API int tfccb200_dequantize_f32(void* stream, const void* src, int src_type, size_t n,
+                                         const float* min_value, const float* max_value,
+                                         float* dst);
+
+/*
+ * Re-express quantized values of one type and range in another type and range.  Replaces
+ * _requantize_helper<TO,TI> (tfcc_mklquantizationinterface.cpp:71-147).
+ */
+TFCCB200_API int tfccb200_requantize(void* stream, const void* src, int src_type, size_t n,
+                                     const float* min_input, const float* max_input,
+                                     const float* min_output, const float* max_output, void* dst,
+                                     int dst_type);
+
 /*
  * C = A . B (+ bias) for M <= 8, single matrices, fp32 -- the decode / GEMV shape -- for
  * callers that have no device memory to lend.  This entry point has no counterpart in the

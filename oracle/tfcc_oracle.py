@@ -149,7 +149,7 @@ def normwise_rel_error(x, truth) -> float:
 
 # --------------------------------------------------------------------------- quantization
 _LIMITS = {np.uint8: (0, 255), np.int8: (-128, 127), np.uint16: (0, 65535),
-           np.int16: (-32768, 32767), np.int32: (-2**31, 2**31 - 1)}
+           np.int16: (-32768, 32767), np.int32: (-2**31, 2**31 - 1), np.uint32: (0, 2**32 - 1)}
 
 
 def _c_round(x: float) -> int:
@@ -182,26 +182,60 @@ def matmul_params(min_a, max_a, min_b, max_b):
     return int(oa), int(ob), float(f(c_level * f(-2**31))), float(f(c_level * f(2**31 - 1)))
 
 
-def quantize(a, dtype):
-    """MKLQuantizationInterface<T>::quantize(a): (q, min, max)
-    (tfcc/mkl/interfaces/tfcc_mklquantizationinterface.cpp:47-69,
+def _quantize_values(real, scale, offset, dtype):
+    """quantize_one over an array of doubles (tfcc_quantizationutils.h:72-79)."""
+    lo, hi = _LIMITS[dtype]
+    x = np.asarray(real, dtype=np.float64) * scale
+    r = np.sign(x) * np.floor(np.abs(x) + 0.5)  # C round()
+    q = r.astype(np.int64) - offset + lo
+    return np.clip(q, lo, hi).astype(dtype)
+
+
+def quantize(a, dtype, min_value=None, max_value=None):
+    """MKLQuantizationInterface<T>::quantize: with no range, (q, min, max) with the range
+    reduced from `a`; with a range, (q, min, max) for that range
+    (tfcc/mkl/interfaces/tfcc_mklquantizationinterface.cpp:47-69,150-240,
      kernel/tfcc_mklquantizationkernel.hpp:23-33)."""
     a = np.asarray(a, dtype=np.float32)
     lo, hi = _LIMITS[dtype]
-    mn, mx = float(a.min()), float(a.max())
-    if mn == mx:
+    if min_value is None:
+        mn, mx = float(a.min()), float(a.max())
+    else:
+        mn, mx = float(np.float32(min_value)), float(np.float32(max_value))
+    if mn >= mx:
         return np.full(a.shape, lo, dtype=dtype), mn, mx
     scale, offset = quantized_scale_info(mn, mx, bits=np.dtype(dtype).itemsize * 8)
-    x = a.astype(np.float64) * scale
-    r = np.sign(x) * np.floor(np.abs(x) + 0.5)  # C round()
-    q = r.astype(np.int64) - offset + lo
-    return np.clip(q, lo, hi).astype(dtype), mn, mx
+    return _quantize_values(a.astype(np.float64), scale, offset, dtype), mn, mx
+
+
+def requantize(a, min_in, max_in, min_out, max_out, dtype):
+    """_requantize_helper<TO,TI> (tfcc_mklquantizationinterface.cpp:71-147) with
+    _MKLRequantizationKernel (kernel/tfcc_mklquantizationkernel.hpp:48-64)."""
+    a = np.asarray(a)
+    lo_o, _ = _LIMITS[dtype]
+    f = lambda v: float(np.float32(v))
+    min_in, max_in, min_out, max_out = f(min_in), f(max_in), f(min_out), f(max_out)
+    if min_out >= max_out:
+        return np.full(a.shape, lo_o, dtype=dtype)
+    bits_i = a.dtype.itemsize * 8
+    step = float(2 ** bits_i)
+    rng = float(np.float32(max_in) - np.float32(min_in)) * (step / (step - 1.0))
+    in_scale = rng / step
+    out_scale, out_offset = quantized_scale_info(min_out, max_out, bits=np.dtype(dtype).itemsize * 8)
+    if min_in >= max_in:
+        return np.full(a.shape, _quantize_values(np.array([min_in]), out_scale, out_offset, dtype)[0],
+                       dtype=dtype)
+    lo_i, _ = _LIMITS[a.dtype.type]
+    real = min_in + (a.astype(np.float64) - lo_i) * in_scale
+    return _quantize_values(real, out_scale, out_offset, dtype)
 
 
 def dequantize(a, min_value, max_value):
     """kernel/tfcc_mklquantizationkernel.hpp:35-45 with get_dequantized_scale_info
     (tfcc_quantizationutils.h:58-70)."""
     a = np.asarray(a)
+    if float(np.float32(min_value)) >= float(np.float32(max_value)):
+        return np.full(a.shape, np.float32(min_value), dtype=np.float32)
     lo, _ = _LIMITS[a.dtype.type]
     bits = a.dtype.itemsize * 8
     step_cnt = float(2 ** bits)

@@ -44,6 +44,7 @@ def generate(ref: Path) -> None:
         ("testcase/blas/matmulwithblas.py", "MatmulWithBlas", "blas_matmulwithblas.npz"),
         ("testcase/quantization/mklquantizationmatmul.py", "MKLQuantizationMatmul",
          "quantization_mklquantizationmatmul.npz"),
+        ("testcase/quantization/quantize.py", "Quantize", "quantization_quantize.npz"),
     ]
     for i, (rel, cls, out) in enumerate(jobs):
         np.random.seed(SEED + i)
@@ -54,6 +55,8 @@ def generate(ref: Path) -> None:
             if key.endswith("/expect") and val.dtype == np.int64:
                 assert np.all(val == val.astype(np.int32)), "expectation does not fit int32"
                 val = val.astype(np.int32)
+            elif key.endswith("/a") and val.dtype == np.float32:
+                pass
             elif key.endswith("/a") and val.dtype == np.int64:
                 val = val.astype(np.uint8)
             elif key.endswith("/b") and val.dtype == np.int64:

@@ -1,0 +1,108 @@
+"""quantize / dequantize / requantize on the device against the oracle and the reference's
+vectors (QuantizationTest.quantize / dequantize / requantize, tfcc/test/quantization.cpp:40-102),
+and the whole quantized dense layer (quantize -> reduce_sum -> matmul -> dequantize) without
+leaving the GPU.  Integer outputs must match exactly; dequantized floats bit for bit too,
+since both sides evaluate the same double-precision expression."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_cases
+from test_oracle_golden import DEQUANT_EXPECT, DEQUANT_IN, REQUANT_EXPECT
+
+pytestmark = pytest.mark.gpu
+NP2T = {np.int8: torch.int8, np.uint8: torch.uint8, np.int16: torch.int16, np.uint16: torch.uint16,
+        np.int32: torch.int32, np.uint32: torch.uint32}
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def s1(v):
+    return torch.tensor([v], dtype=torch.float32, device=dev())
+
+
+def test_quantize_reference_generator_cases(pkg, orc, golden):
+    q = pkg.quantization
+    for i, case in golden_cases(golden["quantization_quantize"], "quantization/quantize"):
+        a = torch.from_numpy(case["a"]).to(dev())
+        q8, mn, mx = q.quantize(a, torch.int8)
+        u8, _, _ = q.quantize(a, torch.uint8)
+        assert np.array_equal(q8.cpu().numpy(), case["int8_a"]), i
+        assert np.array_equal(u8.cpu().numpy(), case["uint8_a"]), i
+        assert float(mn.item()) == float(case["a"].min()) and float(mx.item()) == float(case["a"].max())
+
+
+@pytest.mark.parametrize("np_t", [np.int8, np.uint8, np.int16, np.uint16, np.int32, np.uint32])
+def test_quantize_dequantize_all_types_match_oracle(pkg, orc, np_t):
+    rng = np.random.default_rng(int(np.dtype(np_t).itemsize) * 7 + 1)
+    a = rng.normal(0, 3, (37, 1021)).astype(np.float32)
+    ta = torch.from_numpy(a).to(dev())
+    got, mn, mx = pkg.quantization.quantize(ta, NP2T[np_t])
+    want, wmn, wmx = orc.quantize(a, np_t)
+    assert np.array_equal(got.cpu().numpy().view(np_t), want)
+    assert (float(mn.item()), float(mx.item())) == (wmn, wmx)
+    # explicit range narrower than the data: values clamp
+    got2 = pkg.quantization.quantize(ta, NP2T[np_t], s1(-1.25), s1(2.5))
+    assert np.array_equal(got2.cpu().numpy().view(np_t), orc.quantize(a, np_t, -1.25, 2.5)[0])
+    back = pkg.quantization.dequantize(got, mn, mx).cpu().numpy()
+    assert np.array_equal(back, orc.dequantize(want, wmn, wmx))
+
+
+def test_dequantize_requantize_known_answers(pkg, orc):
+    a = torch.from_numpy(DEQUANT_IN).to(dev())
+    got = pkg.quantization.dequantize(a, s1(-2.5), s1(3.4)).cpu().numpy()
+    assert orc.is_similar(got + np.float32(5.9), DEQUANT_EXPECT + np.float32(5.9))
+    assert np.array_equal(got, orc.dequantize(DEQUANT_IN, -2.5, 3.4))
+    r = pkg.quantization.requantize(a, s1(-2.5), s1(3.4), s1(-12.7), s1(24.5), torch.uint16)
+    assert np.array_equal(r.cpu().numpy().view(np.uint16), REQUANT_EXPECT)
+
+
+def test_requantize_type_pairs_and_degenerate_ranges(pkg, orc):
+    rng = np.random.default_rng(5)
+    q = pkg.quantization
+    for ti, to in ((np.int32, np.int8), (np.int32, np.uint8), (np.uint8, np.int16), (np.int16, np.uint32)):
+        info = np.iinfo(ti)
+        a = rng.integers(max(info.min, -2**31), min(info.max, 2**31 - 1), (64, 257)).astype(ti)
+        ta = torch.from_numpy(a).to(dev())
+        got = q.requantize(ta, s1(-7.5), s1(11.0), s1(-3.0), s1(4.5), NP2T[to]).cpu().numpy().view(to)
+        assert np.array_equal(got, orc.requantize(a, -7.5, 11.0, -3.0, 4.5, to)), (ti, to)
+    a8 = torch.from_numpy(DEQUANT_IN).to(dev())
+    assert np.all(q.quantize(torch.full((5, 5), 1.5, device=dev()), torch.int8)[0].cpu().numpy() == -128)
+    assert np.all(q.dequantize(a8, s1(2.0), s1(2.0)).cpu().numpy() == np.float32(2.0))
+    assert np.all(q.requantize(a8, s1(-1.0), s1(1.0), s1(3.0), s1(3.0), torch.int16).cpu().numpy() == -32768)
+    got = q.requantize(a8, s1(1.0), s1(1.0), s1(-3.0), s1(3.0), torch.int8).cpu().numpy()
+    assert np.array_equal(got, orc.requantize(DEQUANT_IN, 1.0, 1.0, -3.0, 3.0, np.int8))
+
+
+def test_quantized_dense_layer_on_device_known_answers(pkg, orc):
+    """mkl_quantized_matmul of the reference's tests, every step on the GPU: 5 / 11 / 17."""
+    q = pkg.quantization
+    v1 = np.array([1, 2, 3, 4, 5, 6, 1, 2, 3, 4, 5, 6], np.float32)
+    v2 = np.array([1, 2, 1, 2], np.float32)
+    for a, b in ((v1.reshape(2, 3, 2), v2.reshape(2, 2, 1)), (v1[:6].reshape(3, 2), v2.reshape(2, 2, 1)),
+                 (v1.reshape(2, 3, 2), v2[:2].reshape(2, 1))):
+        ta, tb = torch.from_numpy(a).to(dev()), torch.from_numpy(b).to(dev())
+        qa, amin, amax = q.quantize(ta, torch.uint8)
+        qb, bmin, bmax = q.quantize(tb, torch.int8)
+        ra, rb = q.reduce_sum(qa, True), q.reduce_sum(qb, False)
+        qc, cmin, cmax = q.matmul(qa, ra, amin, amax, qb, rb, bmin, bmax)
+        r = q.dequantize(qc, cmin, cmax).cpu().numpy()
+        assert [int(x) for x in r.ravel()] == [5, 11, 17, 5, 11, 17]
+        assert np.array_equal(r, orc.quantized_dense(a, b))
+
+
+def test_quantized_dense_layer_larger(pkg, orc):
+    rng = np.random.default_rng(8)
+    a = rng.normal(0, 1, (96, 768)).astype(np.float32)
+    w = rng.normal(0, 0.05, (768, 512)).astype(np.float32)
+    q = pkg.quantization
+    ta, tw = torch.from_numpy(a).to(dev()), torch.from_numpy(w).to(dev())
+    qa, amin, amax = q.quantize(ta, torch.uint8)
+    qw, wmin, wmax = q.quantize(tw, torch.int8)
+    qc, cmin, cmax = q.matmul(qa, q.reduce_sum(qa, True), amin, amax, qw, q.reduce_sum(qw, False), wmin, wmax)
+    got = q.dequantize(qc, cmin, cmax).cpu().numpy()
+    assert np.array_equal(got, orc.quantized_dense(a, w))
+    # and the quantized product tracks the float product to quantization accuracy
+    assert orc.normwise_rel_error(got, a.astype(np.float64) @ w.astype(np.float64)) < 2e-2

@@ -95,3 +95,31 @@ def test_matmul_shape_rules(orc):
             orc.matmul_result_shape(sa, sb)
     with pytest.raises(orc.OracleError):
         orc.matmul_result_shape((2, 3), (3, 4), (5,))
+
+
+# ---- quantize / dequantize / requantize (tfcc/test/quantization.cpp:40-102) ----
+DEQUANT_IN = np.array([23, -115, -128, 127, -20, -11], np.int8)
+DEQUANT_EXPECT = np.array([9.9372554e-01, -2.1992157e+00, -2.5000000e+00, 3.4000001e+00,
+                           -1.1765957e-03, 2.0705891e-01], np.float32)
+REQUANT_EXPECT = np.array([24125, 18500, 17970, 28364, 22372, 22739], np.uint16)
+
+
+def test_quantize_oracle_matches_reference_generator(orc, golden):
+    n = 0
+    for _, case in golden_cases(golden["quantization_quantize"], "quantization/quantize"):
+        q8, _, _ = orc.quantize(case["a"], np.int8)
+        u8, _, _ = orc.quantize(case["a"], np.uint8)
+        assert np.array_equal(q8, case["int8_a"]) and np.array_equal(u8, case["uint8_a"])
+        n += 1
+    assert n == 20
+
+
+def test_dequantize_and_requantize_known_answers(orc):
+    got = orc.dequantize(DEQUANT_IN, -2.5, 3.4)
+    # the reference compares after adding (max - min) to both sides, with is_similar
+    assert orc.is_similar(got + np.float32(5.9), DEQUANT_EXPECT + np.float32(5.9))
+    assert np.array_equal(orc.requantize(DEQUANT_IN, -2.5, 3.4, -12.7, 24.5, np.uint16), REQUANT_EXPECT)
+    # degenerate ranges
+    assert np.all(orc.quantize(np.full((3, 3), 1.5, np.float32), np.int8)[0] == -128)
+    assert np.all(orc.dequantize(DEQUANT_IN, 2.0, 2.0) == np.float32(2.0))
+    assert np.all(orc.requantize(DEQUANT_IN, -1.0, 1.0, 3.0, 3.0, np.int16) == -32768)

@@ -44,6 +44,10 @@ class _Lib:
             "tfccb200_reduce_sum_u8": (i, [vp, vp, u, u, u, i, vp]),
             "tfccb200_reduce_sum_s8": (i, [vp, vp, u, u, u, i, vp]),
             "tfccb200_reduce_sum_s16": (i, [vp, vp, u, u, u, i, vp]),
+            "tfccb200_minmax_f32": (i, [vp, vp, sz, vp]),
+            "tfccb200_quantize_f32": (i, [vp, vp, sz, vp, vp, vp, i]),
+            "tfccb200_dequantize_f32": (i, [vp, vp, i, sz, vp, vp, vp]),
+            "tfccb200_requantize": (i, [vp, vp, i, sz, vp, vp, vp, vp, vp, i]),
             "tfccb200_sgemm_nsplit_push": (i, [vp, vp, vp, C.POINTER(C.c_void_p), u, u, vp, u, u, u, i, vp]),
             "tfccb200_sgemm_skinny_static": (i, [vp, vp, vp, vp, vp, u, u, u]),
             "tfccb200_sgemm_skinny_static_capacity": (sz, []),
@@ -71,6 +75,7 @@ EXPORTED_SYMBOLS = (
     "tfccb200_sgemm_ex", "tfccb200_sgemm_workspace", "tfccb200_sgemm_path",
     "tfccb200_qgemm_u8s8s32", "tfccb200_qgemm_u8s8s32_ex", "tfccb200_quantized_matmul_params",
     "tfccb200_reduce_sum_u8", "tfccb200_reduce_sum_s8", "tfccb200_reduce_sum_s16",
+    "tfccb200_minmax_f32", "tfccb200_quantize_f32", "tfccb200_dequantize_f32", "tfccb200_requantize",
     "tfccb200_sgemm_nsplit_push", "tfccb200_sgemm_skinny_static",
     "tfccb200_sgemm_skinny_static_capacity",
     "tfccb200_interleave_panels_f32", "tfccb200_sgemm_host", "tfccb200_qgemm_u8s8s32_host",

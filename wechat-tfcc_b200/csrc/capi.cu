@@ -343,6 +343,34 @@ int tfccb200_reduce_sum_s16(void* stream, const int16_t* src, unsigned batch, un
   return reduce_sum_checked<int16_t>(stream, src, batch, rows, cols, row_flag, dst);
 }
 
+int tfccb200_minmax_f32(void* stream, const float* src, size_t n, float* minmax) {
+  if (!src || !minmax || n == 0) return TFCCB200_EINVAL;
+  return minmax_f32(static_cast<cudaStream_t>(stream), src, n, minmax);
+}
+
+int tfccb200_quantize_f32(void* stream, const float* src, size_t n, const float* min_value,
+                          const float* max_value, void* dst, int dst_type) {
+  if (!src || !min_value || !max_value || !dst || n == 0) return TFCCB200_EINVAL;
+  return quantize_f32(static_cast<cudaStream_t>(stream), src, n, min_value, max_value, dst,
+                      dst_type);
+}
+
+int tfccb200_dequantize_f32(void* stream, const void* src, int src_type, size_t n,
+                            const float* min_value, const float* max_value, float* dst) {
+  if (!src || !min_value || !max_value || !dst || n == 0) return TFCCB200_EINVAL;
+  return dequantize_f32(static_cast<cudaStream_t>(stream), src, src_type, n, min_value, max_value,
+                        dst);
+}
+
+int tfccb200_requantize(void* stream, const void* src, int src_type, size_t n,
+                        const float* min_input, const float* max_input, const float* min_output,
+                        const float* max_output, void* dst, int dst_type) {
+  if (!src || !min_input || !max_input || !min_output || !max_output || !dst || n == 0)
+    return TFCCB200_EINVAL;
+  return requantize(static_cast<cudaStream_t>(stream), src, src_type, n, min_input, max_input,
+                    min_output, max_output, dst, dst_type);
+}
+
 int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shard,
                                float* const* C_ranks, unsigned num_ranks, unsigned rank,
                                const float* bias_shard, unsigned M, unsigned N_shard, unsigned K,

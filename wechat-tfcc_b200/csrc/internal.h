@@ -86,4 +86,14 @@ template <class T>
 int reduce_sum(cudaStream_t stream, const T* src, unsigned batch, unsigned rows, unsigned cols,
                int row_flag, int32_t* dst);
 
+// ---- quantize / dequantize / requantize (quantize_kernels.cu) ----
+int minmax_f32(cudaStream_t stream, const float* src, size_t n, float* out);
+int quantize_f32(cudaStream_t stream, const float* src, size_t n, const float* pmin,
+                 const float* pmax, void* dst, int dst_type);
+int dequantize_f32(cudaStream_t stream, const void* src, int src_type, size_t n, const float* pmin,
+                   const float* pmax, float* dst);
+int requantize(cudaStream_t stream, const void* src, int src_type, size_t n, const float* pmin_in,
+               const float* pmax_in, const float* pmin_out, const float* pmax_out, void* dst,
+               int dst_type);
+
 }  // namespace tfccb200

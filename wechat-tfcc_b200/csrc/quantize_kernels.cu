@@ -1,0 +1,251 @@
+// quantize / dequantize / requantize on the device, with the reference's exact scalar math
+// (double precision, C round() = half away from zero, clamp to the integer type):
+//   get_quantized_scale_info / get_dequantized_scale_info / quantize_one
+//   (tfcc/core/utils/tfcc_quantizationutils.h:45-79) and the element loops of
+//   tfcc/mkl/kernel/tfcc_mklquantizationkernel.hpp:21-64.
+// The (min, max) ranges stay on the device: every thread derives scale and offset from the
+// two floats itself (IEEE double arithmetic gives the host's bits), so no host round trip or
+// synchronisation is needed between the range reduction and the conversion.
+#include <cuda_runtime.h>
+
+#include "internal.h"
+
+namespace tfccb200 {
+
+namespace {
+
+template <class T>
+struct Limits;
+template <> struct Limits<int8_t> { static constexpr long long lo = -128, hi = 127; };
+template <> struct Limits<uint8_t> { static constexpr long long lo = 0, hi = 255; };
+template <> struct Limits<int16_t> { static constexpr long long lo = -32768, hi = 32767; };
+template <> struct Limits<uint16_t> { static constexpr long long lo = 0, hi = 65535; };
+template <> struct Limits<int32_t> { static constexpr long long lo = -2147483648LL, hi = 2147483647LL; };
+template <> struct Limits<uint32_t> { static constexpr long long lo = 0, hi = 4294967295LL; };
+
+template <class T>
+__device__ __forceinline__ void quantized_scale_info(float min_value, float max_value,
+                                                     double* scale, long long* offset) {
+  const long long step_cnt = 1LL << (sizeof(T) * 8);
+  const double range_adjust = step_cnt / (step_cnt - 1.0);
+  const double range = (max_value - min_value) * range_adjust;  // float subtraction, as the reference
+  const double range_scale = step_cnt / range;
+  *scale = range_scale;
+  *offset = static_cast<long long>(round(__dmul_rn(static_cast<double>(min_value), range_scale)));
+}
+
+template <class T>
+__device__ __forceinline__ void dequantized_scale_info(float min_value, float max_value,
+                                                       double* scale, double* min_rounded) {
+  const long long step_cnt = 1LL << (sizeof(T) * 8);
+  const double range_adjust = step_cnt / (step_cnt - 1.0);
+  const double range = (max_value - min_value) * range_adjust;
+  *scale = range / step_cnt;
+  *min_rounded = min_value;
+}
+
+template <class T>
+__device__ __forceinline__ T quantize_value(double real, double scale, long long offset) {
+  long long q = static_cast<long long>(round(__dmul_rn(real, scale))) - offset;
+  q += Limits<T>::lo;
+  q = max(q, Limits<T>::lo);
+  q = min(q, Limits<T>::hi);
+  return static_cast<T>(q);
+}
+
+// ---- min / max of a float tensor -------------------------------------------------------
+// Floats are mapped to unsigned keys whose order is the floats' order, so that integer
+// atomics can combine the per-block results; out[0..1] hold keys between the init and the
+// decode kernels and floats afterwards.
+__device__ __forceinline__ unsigned float_key(float f) {
+  const unsigned u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(unsigned k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+__global__ void minmax_init_kernel(unsigned* out) {
+  out[0] = 0xffffffffu;  // larger than every key
+  out[1] = 0u;
+}
+
+__global__ void __launch_bounds__(256)
+minmax_reduce_kernel(const float* __restrict__ src, size_t n, unsigned* out) {
+  float lo = 3.402823466e+38f, hi = -3.402823466e+38f;  // std::numeric_limits<float>::max / lowest
+  for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull) {
+    const float v = src[i];
+    lo = fminf(lo, v);
+    hi = fmaxf(hi, v);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+  }
+  __shared__ float slo[8], shi[8];
+  if ((threadIdx.x & 31) == 0) {
+    slo[threadIdx.x >> 5] = lo;
+    shi[threadIdx.x >> 5] = hi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int w = 1; w < 8; ++w) {
+      lo = fminf(lo, slo[w]);
+      hi = fmaxf(hi, shi[w]);
+    }
+    atomicMin(out, float_key(lo));
+    atomicMax(out + 1, float_key(hi));
+  }
+}
+
+__global__ void minmax_decode_kernel(unsigned* out) {
+  const float lo = key_float(out[0]), hi = key_float(out[1]);
+  reinterpret_cast<float*>(out)[0] = lo;
+  reinterpret_cast<float*>(out)[1] = hi;
+}
+
+// ---- element kernels ---------------------------------------------------------------------
+template <class T>
+__global__ void __launch_bounds__(256)
+quantize_kernel(const float* __restrict__ src, size_t n, const float* __restrict__ pmin,
+                const float* __restrict__ pmax, T* __restrict__ dst) {
+  const float mn = *pmin, mx = *pmax;
+  const bool degenerate = mn >= mx;  // also the "all values equal" case of quantize(a)
+  double scale = 0;
+  long long offset = 0;
+  if (!degenerate) quantized_scale_info<T>(mn, mx, &scale, &offset);
+  for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull)
+    dst[i] = degenerate ? static_cast<T>(Limits<T>::lo)
+                        : quantize_value<T>(static_cast<double>(src[i]), scale, offset);
+}
+
+template <class T>
+__global__ void __launch_bounds__(256)
+dequantize_kernel(const T* __restrict__ src, size_t n, const float* __restrict__ pmin,
+                  const float* __restrict__ pmax, float* __restrict__ dst) {
+  const float mn = *pmin, mx = *pmax;
+  const bool degenerate = mn >= mx;
+  double scale = 0, min_rounded = 0;
+  if (!degenerate) dequantized_scale_info<T>(mn, mx, &scale, &min_rounded);
+  for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull) {
+    const double off = static_cast<double>(src[i]) - static_cast<double>(Limits<T>::lo);
+    // separate multiply and add, each rounded: the reference's expression is not fused
+    dst[i] = degenerate ? mn : static_cast<float>(__dadd_rn(min_rounded, __dmul_rn(off, scale)));
+  }
+}
+
+template <class TI, class TO>
+__global__ void __launch_bounds__(256)
+requantize_kernel(const TI* __restrict__ src, size_t n, const float* __restrict__ pmin_in,
+                  const float* __restrict__ pmax_in, const float* __restrict__ pmin_out,
+                  const float* __restrict__ pmax_out, TO* __restrict__ dst) {
+  const float min_in = *pmin_in, max_in = *pmax_in, min_out = *pmin_out, max_out = *pmax_out;
+  // the three cases of _requantize_helper (tfcc/mkl/interfaces/tfcc_mklquantizationinterface.cpp:114-140)
+  if (min_out >= max_out) {
+    for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull)
+      dst[i] = static_cast<TO>(Limits<TO>::lo);
+    return;
+  }
+  double in_scale, in_min, out_scale;
+  long long out_offset;
+  dequantized_scale_info<TI>(min_in, max_in, &in_scale, &in_min);
+  quantized_scale_info<TO>(min_out, max_out, &out_scale, &out_offset);
+  if (min_in >= max_in) {
+    const TO q = quantize_value<TO>(static_cast<double>(min_in), out_scale, out_offset);
+    for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull) dst[i] = q;
+    return;
+  }
+  for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull) {
+    const double off = static_cast<double>(src[i]) - static_cast<double>(Limits<TI>::lo);
+    dst[i] = quantize_value<TO>(__dadd_rn(in_min, __dmul_rn(off, in_scale)), out_scale, out_offset);
+  }
+}
+
+unsigned grid_for(size_t n, int sm_count) {
+  size_t blocks = (n + 255) / 256;
+  const size_t cap = static_cast<size_t>(sm_count) * 8;
+  if (blocks > cap) blocks = cap;
+  return static_cast<unsigned>(blocks ? blocks : 1);
+}
+
+template <class F>
+int dispatch_type(int type, F&& f) {
+  switch (type) {
+    case TFCCB200_TYPE_S8: return f(int8_t());
+    case TFCCB200_TYPE_U8: return f(uint8_t());
+    case TFCCB200_TYPE_S16: return f(int16_t());
+    case TFCCB200_TYPE_U16: return f(uint16_t());
+    case TFCCB200_TYPE_S32: return f(int32_t());
+    case TFCCB200_TYPE_U32: return f(uint32_t());
+    default: return TFCCB200_EINVAL;
+  }
+}
+
+int finish(unsigned launches) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  count_launch(launches);
+  return TFCCB200_OK;
+}
+
+}  // namespace
+
+int minmax_f32(cudaStream_t stream, const float* src, size_t n, float* out) {
+  cudaError_t ce;
+  const DeviceInfo* di = current_device_info(&ce);
+  if (!di) return static_cast<int>(ce);
+  unsigned* keys = reinterpret_cast<unsigned*>(out);
+  minmax_init_kernel<<<1, 1, 0, stream>>>(keys);
+  minmax_reduce_kernel<<<grid_for(n, di->sm_count), 256, 0, stream>>>(src, n, keys);
+  minmax_decode_kernel<<<1, 1, 0, stream>>>(keys);
+  return finish(3);
+}
+
+int quantize_f32(cudaStream_t stream, const float* src, size_t n, const float* pmin,
+                 const float* pmax, void* dst, int dst_type) {
+  cudaError_t ce;
+  const DeviceInfo* di = current_device_info(&ce);
+  if (!di) return static_cast<int>(ce);
+  const unsigned grid = grid_for(n, di->sm_count);
+  return dispatch_type(dst_type, [&](auto tag) {
+    using T = decltype(tag);
+    quantize_kernel<T><<<grid, 256, 0, stream>>>(src, n, pmin, pmax, static_cast<T*>(dst));
+    return finish(1);
+  });
+}
+
+int dequantize_f32(cudaStream_t stream, const void* src, int src_type, size_t n, const float* pmin,
+                   const float* pmax, float* dst) {
+  cudaError_t ce;
+  const DeviceInfo* di = current_device_info(&ce);
+  if (!di) return static_cast<int>(ce);
+  const unsigned grid = grid_for(n, di->sm_count);
+  return dispatch_type(src_type, [&](auto tag) {
+    using T = decltype(tag);
+    dequantize_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(src), n, pmin, pmax, dst);
+    return finish(1);
+  });
+}
+
+int requantize(cudaStream_t stream, const void* src, int src_type, size_t n, const float* pmin_in,
+               const float* pmax_in, const float* pmin_out, const float* pmax_out, void* dst,
+               int dst_type) {
+  cudaError_t ce;
+  const DeviceInfo* di = current_device_info(&ce);
+  if (!di) return static_cast<int>(ce);
+  const unsigned grid = grid_for(n, di->sm_count);
+  return dispatch_type(src_type, [&](auto in_tag) {
+    using TI = decltype(in_tag);
+    return dispatch_type(dst_type, [&](auto out_tag) {
+      using TO = decltype(out_tag);
+      requantize_kernel<TI, TO><<<grid, 256, 0, stream>>>(static_cast<const TI*>(src), n, pmin_in,
+                                                          pmax_in, pmin_out, pmax_out,
+                                                          static_cast<TO*>(dst));
+      return finish(1);
+    });
+  });
+}
+
+}  // namespace tfccb200

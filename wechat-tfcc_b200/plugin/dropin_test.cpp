@@ -160,6 +160,56 @@ int main() {
     int8_case(rng, 130, 72, 301, -3.f, 1.f, 0.25f, 4.f);
     int8_case(rng, 333, 1, 401, -4.f, -1.f, 0.5f, 3.f);
 
+    // QuantizationTest.mkl_matmul / 2 / 3 (tfcc/test/quantization.cpp:105-189): quantize ->
+    // reduce_sum -> matmul -> dequantize through the reference's operator layer, all on the
+    // device; the truncated results must be 5, 11, 17 twice
+    {
+      struct Layout { std::vector<unsigned> sa, sb; std::vector<float> a, b; };
+      const std::vector<float> six = {1, 2, 3, 4, 5, 6}, twelve = {1, 2, 3, 4, 5, 6, 1, 2, 3, 4, 5, 6};
+      const Layout layouts[3] = {{{2, 3, 2}, {2, 2, 1}, twelve, {1, 2, 1, 2}},
+                                 {{3, 2}, {2, 2, 1}, six, {1, 2, 1, 2}},
+                                 {{2, 3, 2}, {2, 1}, twelve, {1, 2}}};
+      for (const Layout& l : layouts) {
+        tfcc::Variable<float> v1{tfcc::Shape(l.sa)}, v2{tfcc::Shape(l.sb)};
+        tfcc::data::set(v1, l.a);
+        tfcc::data::set(v2, l.b);
+        tfcc::Variable<uint8_t> qa;
+        tfcc::Variable<int8_t> qb;
+        tfcc::Variable<float> minA, maxA, minB, maxB, minC, maxC;
+        std::tie(qa, minA, maxA) = tfcc::quantization::quantize<uint8_t>(v1);
+        std::tie(qb, minB, maxB) = tfcc::quantization::quantize<int8_t>(v2);
+        tfcc::Variable<int32_t> ra = tfcc::b200::quantization::reduce_sum(qa, true);
+        tfcc::Variable<int32_t> rb = tfcc::b200::quantization::reduce_sum(qb, false);
+        tfcc::Variable<int32_t> qc;
+        std::tie(qc, minC, maxC) = tfcc::b200::quantization::matmul(qa, ra, minA, maxA, qb, rb, minB, maxB);
+        std::vector<float> vr = tfcc::data::get(tfcc::quantization::dequantize(qc, minC, maxC));
+        const int want[6] = {5, 11, 17, 5, 11, 17};
+        bool ok = vr.size() == 6;
+        for (int i = 0; ok && i < 6; ++i) ok = static_cast<int>(vr[i]) == want[i];
+        expect(ok, "quantized dense layer known answers 5/11/17");
+      }
+      // QuantizationTest.dequantize / requantize (tfcc/test/quantization.cpp:60-102)
+      tfcc::Variable<int8_t> q({6});
+      tfcc::data::set(q, {23, -115, -128, 127, -20, -11});
+      tfcc::Variable<float> mn({1}), mx({1}), mno({1}), mxo({1});
+      tfcc::data::set(mn, {-2.5f});
+      tfcc::data::set(mx, {3.4f});
+      tfcc::data::set(mno, {-12.7f});
+      tfcc::data::set(mxo, {24.5f});
+      std::vector<float> dq = tfcc::data::get(tfcc::quantization::dequantize(q, mn, mx));
+      const float dq_want[6] = {9.9372554e-01f, -2.1992157e+00f, -2.5000000e+00f,
+                                3.4000001e+00f, -1.1765957e-03f, 2.0705891e-01f};
+      bool ok = dq.size() == 6;
+      for (int i = 0; ok && i < 6; ++i) ok = std::fabs(dq[i] - dq_want[i]) < 1e-5f;
+      expect(ok, "dequantize known answers");
+      std::vector<uint16_t> rq =
+          tfcc::data::get(tfcc::quantization::requantize<uint16_t>(q, mn, mx, mno, mxo));
+      const uint16_t rq_want[6] = {24125, 18500, 17970, 28364, 22372, 22739};
+      ok = rq.size() == 6;
+      for (int i = 0; ok && i < 6; ++i) ok = rq[i] == rq_want[i];
+      expect(ok, "requantize known answers");
+    }
+
     // error behaviour comes from the reference's operator layer, unchanged
     bool threw = false;
     try {

@@ -291,12 +291,131 @@ Variable<T> B200DataInterface<T>::copy(const Tensor<T>& a) {
   return result;
 }
 
+// ---------------------------------------------------------------- quantization interface
+namespace {
+
+template <class T> struct TypeId;
+template <> struct TypeId<int8_t> { static constexpr int value = TFCCB200_TYPE_S8; };
+template <> struct TypeId<uint8_t> { static constexpr int value = TFCCB200_TYPE_U8; };
+template <> struct TypeId<int16_t> { static constexpr int value = TFCCB200_TYPE_S16; };
+template <> struct TypeId<uint16_t> { static constexpr int value = TFCCB200_TYPE_U16; };
+template <> struct TypeId<int32_t> { static constexpr int value = TFCCB200_TYPE_S32; };
+template <> struct TypeId<uint32_t> { static constexpr int value = TFCCB200_TYPE_U32; };
+
+void check_range_tensor(const Tensor<float>& t, const char* message) {
+  if (t.size() != 1 || t.shape().size() != 1) throw InvalidArgumentError(message);
+}
+
+template <class TO, class TI>
+Variable<TO> b200_requantize(const Tensor<TI>& a, const Tensor<float>& minInput,
+                             const Tensor<float>& maxInput, const Tensor<float>& minOutput,
+                             const Tensor<float>& maxOutput) {
+  if (a.size() == 0) throw InvalidArgumentError("invalid tensor");
+  check_range_tensor(minInput, "invalid minInput");
+  check_range_tensor(maxInput, "invalid maxInput");
+  check_range_tensor(minOutput, "invalid minOutput");
+  check_range_tensor(maxOutput, "invalid maxOutput");
+  Variable<TO> result(a.shape());
+  check_status(tfccb200_requantize(current_session()->stream(), a.data(), TypeId<TI>::value,
+                                   a.size(), minInput.data(), maxInput.data(), minOutput.data(),
+                                   maxOutput.data(), result.data(), TypeId<TO>::value));
+  return result;
+}
+
+}  // namespace
+
+template <class T>
+std::tuple<Variable<T>, Variable<float>, Variable<float>> B200QuantizationInterface<T>::quantize(
+    const Tensor<float>& a) {
+  if (a.size() == 0) throw InvalidArgumentError("invalid tensor");
+  Variable<T> result(a.shape());
+  Variable<float> range({2});
+  B200Session* session = current_session();
+  check_status(tfccb200_minmax_f32(session->stream(), a.data(), a.size(), range.data()));
+  check_status(tfccb200_quantize_f32(session->stream(), a.data(), a.size(), range.data(),
+                                     range.data() + 1, result.data(), TypeId<T>::value));
+  Variable<float> minValue({1}), maxValue({1});
+  check_cuda(cudaMemcpyAsync(minValue.data(), range.data(), sizeof(float), cudaMemcpyDeviceToDevice,
+                             session->stream()));
+  check_cuda(cudaMemcpyAsync(maxValue.data(), range.data() + 1, sizeof(float),
+                             cudaMemcpyDeviceToDevice, session->stream()));
+  return std::make_tuple(std::move(result), std::move(minValue), std::move(maxValue));
+}
+
+template <class T>
+Variable<T> B200QuantizationInterface<T>::quantize(const Tensor<float>& a,
+                                                   const Tensor<float>& minValue,
+                                                   const Tensor<float>& maxValue) {
+  if (a.size() == 0) throw InvalidArgumentError("invalid tensor");
+  check_range_tensor(minValue, "invalid minValue");
+  check_range_tensor(maxValue, "invalid maxValue");
+  Variable<T> result(a.shape());
+  check_status(tfccb200_quantize_f32(current_session()->stream(), a.data(), a.size(),
+                                     minValue.data(), maxValue.data(), result.data(),
+                                     TypeId<T>::value));
+  return result;
+}
+
+#define TFCC_B200_REQUANTIZE(TI)                                                                 \
+  template <class T>                                                                             \
+  Variable<T> B200QuantizationInterface<T>::requantize(                                          \
+      const Tensor<TI>& a, const Tensor<float>& minInput, const Tensor<float>& maxInput,         \
+      const Tensor<float>& minOutput, const Tensor<float>& maxOutput) {                          \
+    return b200_requantize<T, TI>(a, minInput, maxInput, minOutput, maxOutput);                  \
+  }
+TFCC_B200_REQUANTIZE(int8_t)
+TFCC_B200_REQUANTIZE(uint8_t)
+TFCC_B200_REQUANTIZE(int16_t)
+TFCC_B200_REQUANTIZE(uint16_t)
+TFCC_B200_REQUANTIZE(int32_t)
+TFCC_B200_REQUANTIZE(uint32_t)
+#undef TFCC_B200_REQUANTIZE
+
+template <class T>
+Variable<float> B200QuantizationInterface<T>::dequantize(const Tensor<T>& a,
+                                                         const Tensor<float>& minValue,
+                                                         const Tensor<float>& maxValue) {
+  if (a.size() == 0) throw InvalidArgumentError("invalid tensor");
+  check_range_tensor(minValue, "invalid minValue");
+  check_range_tensor(maxValue, "invalid maxValue");
+  Variable<float> result(a.shape());
+  check_status(tfccb200_dequantize_f32(current_session()->stream(), a.data(), TypeId<T>::value,
+                                       a.size(), minValue.data(), maxValue.data(), result.data()));
+  return result;
+}
+
+template class B200QuantizationInterface<int8_t>;
+template class B200QuantizationInterface<uint8_t>;
+template class B200QuantizationInterface<int16_t>;
+template class B200QuantizationInterface<uint16_t>;
+template class B200QuantizationInterface<int32_t>;
+template class B200QuantizationInterface<uint32_t>;
+
 // ---------------------------------------------------------------- registration
+namespace {
+template <class T>
+void set_quantization_interface(Interface<T>&) {}  // only the six quantization types have one
+#define TFCC_B200_SET_QUANTIZATION(type)                                          \
+  template <>                                                                     \
+  void set_quantization_interface<type>(Interface<type> & interface) {            \
+    interface.setQuantizationInterface(                                           \
+        std::unique_ptr<QuantizationInterface<type>>(new B200QuantizationInterface<type>())); \
+  }
+TFCC_B200_SET_QUANTIZATION(int8_t)
+TFCC_B200_SET_QUANTIZATION(uint8_t)
+TFCC_B200_SET_QUANTIZATION(int16_t)
+TFCC_B200_SET_QUANTIZATION(uint16_t)
+TFCC_B200_SET_QUANTIZATION(int32_t)
+TFCC_B200_SET_QUANTIZATION(uint32_t)
+#undef TFCC_B200_SET_QUANTIZATION
+}  // namespace
+
 template <class T>
 Interface<T> get_b200_interface(T, B200Device&) {
   Interface<T> interface;
   interface.setBlasInterface(std::unique_ptr<BlasInterface<T>>(new B200BlasInterface<T>()));
   interface.setDataInterface(std::unique_ptr<DataInterface<T>>(new B200DataInterface<T>()));
+  set_quantization_interface<T>(interface);
   return interface;
 }
 

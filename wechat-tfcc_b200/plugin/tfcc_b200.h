@@ -28,6 +28,7 @@
 #include "interfaces/tfcc_blasinterface.h"
 #include "interfaces/tfcc_datainterface.h"
 #include "interfaces/tfcc_interface.h"
+#include "interfaces/tfcc_quantizationinterface.h"
 #include "utils/tfcc_initializer.h"
 
 namespace tfcc {
@@ -105,6 +106,38 @@ class B200DataInterface : public DataInterface<T> {
   void get(const Tensor<T>& a, T* data) override;
   void zeros(Variable<T>& a) override;
   Variable<T> copy(const Tensor<T>& a) override;
+};
+
+// quantize / requantize / dequantize on the device, ranges kept in device memory
+// (tfcc/core/interfaces/tfcc_quantizationinterface.h:39-138; semantics of
+// tfcc/mkl/interfaces/tfcc_mklquantizationinterface.cpp).  T is one of the six quantization
+// types (int8..uint32).
+template <class T>
+class B200QuantizationInterface : public QuantizationInterface<T> {
+ public:
+  std::tuple<Variable<T>, Variable<float>, Variable<float>> quantize(const Tensor<float>& a) override;
+  Variable<T> quantize(const Tensor<float>& a, const Tensor<float>& minValue,
+                       const Tensor<float>& maxValue) override;
+  Variable<T> requantize(const Tensor<int8_t>& a, const Tensor<float>& minInput,
+                         const Tensor<float>& maxInput, const Tensor<float>& minOutput,
+                         const Tensor<float>& maxOutput) override;
+  Variable<T> requantize(const Tensor<uint8_t>& a, const Tensor<float>& minInput,
+                         const Tensor<float>& maxInput, const Tensor<float>& minOutput,
+                         const Tensor<float>& maxOutput) override;
+  Variable<T> requantize(const Tensor<int16_t>& a, const Tensor<float>& minInput,
+                         const Tensor<float>& maxInput, const Tensor<float>& minOutput,
+                         const Tensor<float>& maxOutput) override;
+  Variable<T> requantize(const Tensor<uint16_t>& a, const Tensor<float>& minInput,
+                         const Tensor<float>& maxInput, const Tensor<float>& minOutput,
+                         const Tensor<float>& maxOutput) override;
+  Variable<T> requantize(const Tensor<int32_t>& a, const Tensor<float>& minInput,
+                         const Tensor<float>& maxInput, const Tensor<float>& minOutput,
+                         const Tensor<float>& maxOutput) override;
+  Variable<T> requantize(const Tensor<uint32_t>& a, const Tensor<float>& minInput,
+                         const Tensor<float>& maxInput, const Tensor<float>& minOutput,
+                         const Tensor<float>& maxOutput) override;
+  Variable<float> dequantize(const Tensor<T>& a, const Tensor<float>& minValue,
+                             const Tensor<float>& maxValue) override;
 };
 
 template <class T>

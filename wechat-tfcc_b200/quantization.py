@@ -19,6 +19,81 @@ _REDUCE = {torch.uint8: "tfccb200_reduce_sum_u8", torch.int8: "tfccb200_reduce_s
            torch.int16: "tfccb200_reduce_sum_s16"}
 
 
+_TYPE_IDS = {torch.int8: 0, torch.uint8: 1, torch.int16: 2, torch.uint16: 3, torch.int32: 4,
+             torch.uint32: 5}
+
+
+def _scalar(t, name, device):
+    """A (min or max) range tensor: one float32 element, rank 1, on the operand's device."""
+    if not isinstance(t, torch.Tensor) or t.numel() != 1 or t.dim() != 1:
+        raise exceptions.InvalidArgumentError(f"invalid {name}")
+    if t.dtype != torch.float32 or t.device != device or not t.is_contiguous():
+        raise exceptions.InvalidArgumentError(f"invalid {name}: expected float32 on {device}")
+    return t
+
+
+def quantize(a: torch.Tensor, dtype, min_value=None, max_value=None):
+    """``tfcc::quantization::quantize<T>``: with no range, ``(q, min, max)`` where the range is
+    reduced from ``a`` on the device; with ``min_value`` / ``max_value`` (one-element device
+    tensors), just ``q``.  No host synchronisation either way."""
+    if not isinstance(a, torch.Tensor) or a.numel() == 0:
+        raise exceptions.InvalidArgumentError("invalid tensor")
+    if dtype not in _TYPE_IDS:
+        raise exceptions.NotImplementedError(f"quantize is not implemented for {dtype}")
+    _dev(a, "a", torch.float32)
+    sess = get_session(a.device)
+    out = torch.empty(a.shape, dtype=dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        if min_value is None and max_value is None:
+            rng = torch.empty(2, dtype=torch.float32, device=a.device)
+            check(lib.tfccb200_minmax_f32(sess.stream_ptr, a.data_ptr(), a.numel(), rng.data_ptr()))
+            mn, mx = rng[0:1], rng[1:2]
+            check(lib.tfccb200_quantize_f32(sess.stream_ptr, a.data_ptr(), a.numel(), mn.data_ptr(),
+                                            mx.data_ptr(), out.data_ptr(), _TYPE_IDS[dtype]))
+            return out, mn, mx
+        mn = _scalar(min_value, "minValue", a.device)
+        mx = _scalar(max_value, "maxValue", a.device)
+        check(lib.tfccb200_quantize_f32(sess.stream_ptr, a.data_ptr(), a.numel(), mn.data_ptr(),
+                                        mx.data_ptr(), out.data_ptr(), _TYPE_IDS[dtype]))
+    return out
+
+
+def dequantize(a: torch.Tensor, min_value, max_value) -> torch.Tensor:
+    """``tfcc::quantization::dequantize``: float32 values of a quantized tensor."""
+    if not isinstance(a, torch.Tensor) or a.numel() == 0:
+        raise exceptions.InvalidArgumentError("invalid tensor")
+    if a.dtype not in _TYPE_IDS:
+        raise exceptions.NotImplementedError(f"dequantize is not implemented for {a.dtype}")
+    _dev(a, "a")
+    mn = _scalar(min_value, "minValue", a.device)
+    mx = _scalar(max_value, "maxValue", a.device)
+    out = torch.empty(a.shape, dtype=torch.float32, device=a.device)
+    sess = get_session(a.device)
+    with torch.cuda.device(a.device):
+        check(lib.tfccb200_dequantize_f32(sess.stream_ptr, a.data_ptr(), _TYPE_IDS[a.dtype],
+                                          a.numel(), mn.data_ptr(), mx.data_ptr(), out.data_ptr()))
+    return out
+
+
+def requantize(a: torch.Tensor, min_input, max_input, min_output, max_output, dtype) -> torch.Tensor:
+    """``tfcc::quantization::requantize<T>``: quantized ``a`` re-expressed in ``dtype`` over the
+    output range."""
+    if not isinstance(a, torch.Tensor) or a.numel() == 0:
+        raise exceptions.InvalidArgumentError("invalid tensor")
+    if a.dtype not in _TYPE_IDS or dtype not in _TYPE_IDS:
+        raise exceptions.NotImplementedError("requantize is implemented for 8/16/32-bit integers")
+    _dev(a, "a")
+    r = [_scalar(t, n, a.device) for t, n in ((min_input, "minInput"), (max_input, "maxInput"),
+                                              (min_output, "minOutput"), (max_output, "maxOutput"))]
+    out = torch.empty(a.shape, dtype=dtype, device=a.device)
+    sess = get_session(a.device)
+    with torch.cuda.device(a.device):
+        check(lib.tfccb200_requantize(sess.stream_ptr, a.data_ptr(), _TYPE_IDS[a.dtype], a.numel(),
+                                      r[0].data_ptr(), r[1].data_ptr(), r[2].data_ptr(),
+                                      r[3].data_ptr(), out.data_ptr(), _TYPE_IDS[dtype]))
+    return out
+
+
 def _dev(t, name, dtype=None):
     if not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous():
         raise exceptions.InvalidArgumentError(f"invalid tensor {name}")
