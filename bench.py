@@ -327,6 +327,13 @@ def extra_measurements(torch, pkg, dev, peaks):
         fn()
     _, med = time_launches(torch, fn, 5)
     out["tf32_single_pass_8192"] = {"us": med * 1e3, "tflops": FLOP_PER_STEP / (med * 1e-3) / 1e12}
+    # opt-in bfloat16 mode: two rounding pre-passes + the bf16 tensor-core kernel, all timed
+    fn = lambda: pkg.blas.matmul(a8, b8, precision="bf16")
+    for _ in range(2):
+        fn()
+    _, med = time_launches(torch, fn, 5)
+    out["bf16_mode_8192"] = {"us": med * 1e3, "tflops": FLOP_PER_STEP / (med * 1e-3) / 1e12,
+                             "frac_of_bf16_peak": FLOP_PER_STEP / (med * 1e-3) / 1e12 / peaks["bf16_tflops"]}
     del a8, b8
 
     # cfg3 int8 (M=256) and the compute-bound int8 point (M=4096)

@@ -47,9 +47,13 @@ extern "C" {
  *        tail*head); CUDA-core paths use fp32 FMA.  Normwise relative error
  *        against an fp64 product stays below 1e-5.
  * TF32:  one MMA per tile on the TF32 heads only (about 1e-3 relative).
- * Both read and write fp32 buffers. */
+ * BF16:  operands rounded to bfloat16 by a pre-pass into the caller's workspace, bfloat16
+ *        tensor-core products, fp32 accumulation (about 4e-3 relative).  Needs K % 8 == 0
+ *        and N % 8 == 0; other shapes are computed as FP32.
+ * All modes read and write fp32 buffers. */
 #define TFCCB200_PRECISION_FP32 0
 #define TFCCB200_PRECISION_TF32 1
+#define TFCCB200_PRECISION_BF16 2
 
 /* ---- kernel paths (for tests and benchmarks; AUTO is what TFCC uses) ----- */
 #define TFCCB200_PATH_AUTO 0

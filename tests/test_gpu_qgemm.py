@@ -80,6 +80,19 @@ def test_batched_layouts_bit_exact(pkg, orc):
             assert np.array_equal(got, want), (sa, sb, path)
 
 
+@pytest.mark.parametrize("m,n,k", [(100, 128, 8192), (256, 512, 4096), (130, 144, 1040)])
+def test_few_tiles_long_k_exact(pkg, orc, m, n, k):
+    """Few output tiles and a long K (up to 64 k-blocks through one accumulator)."""
+    rng = np.random.default_rng(m + k)
+    a = rng.integers(0, 256, (m, k), dtype=np.uint8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    want, _, _ = orc.quantized_matmul(a, orc.reduce_sum(a, True), -1.5, 2.0, b,
+                                      orc.reduce_sum(b, False), -0.7, 0.9, impl="port")
+    for path in ("umma", "umma2", "auto"):
+        got, _, _, _, _ = qrun(pkg, a, b, -1.5, 2.0, -0.7, 0.9, path=path)
+        assert np.array_equal(got, want), path
+
+
 def test_n_equals_one_fast_path_shape(pkg, orc):
     rng = np.random.default_rng(22)
     a = rng.integers(0, 256, (333, 401), dtype=np.uint8)

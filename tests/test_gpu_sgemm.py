@@ -132,6 +132,31 @@ def test_tf32_mode_has_its_own_tolerance(pkg, orc):
         assert 1e-5 < err < TOL_TF32   # really a single TF32 pass, and within its bound
 
 
+def test_bf16_mode_has_its_own_tolerance(pkg, orc):
+    """Opt-in bfloat16 products (operands rounded to bf16, fp32 accumulation): normwise error
+    against float64 below 1e-2, and equal to the float64 product of the bf16-rounded operands
+    to fp32 accuracy, which shows that rounding the inputs is the only loss."""
+    rng = np.random.default_rng(3)
+    a = rng.uniform(-1, 1, (384, 1024)).astype(np.float32)
+    b = rng.uniform(-1, 1, (1024, 640)).astype(np.float32)
+    bias = rng.uniform(-1, 1, 640).astype(np.float32)
+    truth = orc.blas_matmul(a, b, bias)
+    r16 = lambda x: torch.from_numpy(x).to(torch.bfloat16).to(torch.float32).numpy()
+    truth16 = orc.blas_matmul(r16(a), r16(b), bias)
+    for path in ("umma", "umma2", "auto"):
+        got = run(pkg, a, b, bias, path=path, precision="bf16")
+        err = orc.normwise_rel_error(got, truth)
+        assert 1e-4 < err < 1e-2, (path, err)
+        assert orc.normwise_rel_error(got, truth16) < 1e-5, path
+    # batched, and a pitch the bf16 tensor maps cannot take (falls back to fp32 accuracy)
+    a3 = rng.uniform(-1, 1, (3, 130, 72)).astype(np.float32)
+    b3 = rng.uniform(-1, 1, (3, 72, 136)).astype(np.float32)
+    assert orc.normwise_rel_error(run(pkg, a3, b3, precision="bf16"), orc.blas_matmul(a3, b3)) < 1e-2
+    a4 = rng.uniform(-1, 1, (64, 36)).astype(np.float32)
+    b4 = rng.uniform(-1, 1, (36, 68)).astype(np.float32)
+    assert orc.normwise_rel_error(run(pkg, a4, b4, precision="bf16"), orc.blas_matmul(a4, b4)) < 1e-5
+
+
 def test_large_gemm_sampled_rows_and_linearity(pkg, orc):
     """4096 x 8192 x 8192 on the CTA-pair path: sampled rows against float64, bit-for-bit
     repeatability, and exact scaling by a power of two (a property that holds at any size)."""

@@ -82,7 +82,7 @@ EXPORTED_SYMBOLS = (
 )
 
 PATHS = {"auto": 0, "simt": 1, "skinny": 2, "umma": 3, "umma2": 4}
-PRECISIONS = {"fp32": 0, "tf32": 1}
+PRECISIONS = {"fp32": 0, "tf32": 1, "bf16": 2}
 
 
 def launch_count() -> int:

@@ -2,6 +2,7 @@
 // the host-buffer convenience forms.  Nothing here throws.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstdlib>
@@ -79,7 +80,7 @@ int pick_sgemm_path(const SgemmArgs& a) {
     cudaError_t e;
     const DeviceInfo* di = current_device_info(&e);
     const int sms = di ? di->sm_count : 148;
-    return umma_plan(a.M, a.N, a.batch, sms, false, -1).pair ? TFCCB200_PATH_UMMA2
+    return umma_plan(a.M, a.N, a.batch, sms, a.precision == TFCCB200_PRECISION_BF16 ? 2 : 4, -1).pair ? TFCCB200_PATH_UMMA2
                                                              : TFCCB200_PATH_UMMA;
   }
   return TFCCB200_PATH_SIMT;
@@ -88,12 +89,18 @@ int pick_sgemm_path(const SgemmArgs& a) {
 int run_sgemm(SgemmArgs a, int path) {
   if (!a.A || !a.B || !a.C) return TFCCB200_EINVAL;
   if (a.M == 0 || a.N == 0 || a.K == 0 || a.batch == 0) return TFCCB200_EINVAL;
-  if (a.precision != TFCCB200_PRECISION_FP32 && a.precision != TFCCB200_PRECISION_TF32)
+  if (a.precision != TFCCB200_PRECISION_FP32 && a.precision != TFCCB200_PRECISION_TF32 &&
+      a.precision != TFCCB200_PRECISION_BF16)
     return TFCCB200_EINVAL;
   if (shape_overflows(a.M, a.N, a.K, a.batch)) return TFCCB200_EOVERFLOW;
   if (a.batch == 1) a.strideA = a.strideB = 0, a.strideC = a.M * a.N;
   fold_batch(a);
   if (path == TFCCB200_PATH_AUTO) path = pick_sgemm_path(a);
+  // The bfloat16 mode exists on the tensor-core paths only, for pitches that are multiples of
+  // 8 elements; anything else is computed in fp32, which is within every bfloat16 tolerance.
+  if (a.precision == TFCCB200_PRECISION_BF16 &&
+      ((path != TFCCB200_PATH_UMMA && path != TFCCB200_PATH_UMMA2) || a.K % 8 || a.N % 8))
+    a.precision = TFCCB200_PRECISION_FP32;
   switch (path) {
     case TFCCB200_PATH_SIMT: return simt_sgemm(a);
     case TFCCB200_PATH_SKINNY: return skinny_sgemm(a);
@@ -109,7 +116,7 @@ int pick_qgemm_path(const QgemmArgs& a) {
     cudaError_t e;
     const DeviceInfo* di = current_device_info(&e);
     const int sms = di ? di->sm_count : 148;
-    return umma_plan(a.M, a.N, a.batch, sms, true, -1).pair ? TFCCB200_PATH_UMMA2
+    return umma_plan(a.M, a.N, a.batch, sms, 1, -1).pair ? TFCCB200_PATH_UMMA2
                                                             : TFCCB200_PATH_UMMA;
   }
   return TFCCB200_PATH_SIMT;
@@ -263,7 +270,9 @@ size_t tfccb200_sgemm_workspace(unsigned M, unsigned N, unsigned K, unsigned bat
   // Only the M <= 8 streaming kernel uses scratch (its per-slice partial sums).
   // The bound covers both the batched and the batch-folded reading of the problem.
   size_t need = 0;
-  if (M <= 8) need = skinny_sgemm_workspace(M, N, K, batch, sms);
+  if (precision_mode == TFCCB200_PRECISION_BF16)  // dense upper bound: both operands batched
+    need = bf16_staging_bytes(M, N, K, batch, M * K, K * N);
+  if (M <= 8) need = std::max(need, skinny_sgemm_workspace(M, N, K, batch, sms));
   if (static_cast<unsigned long long>(M) * batch <= 8) {
     const size_t folded = skinny_sgemm_workspace(M * batch, N, K, 1, sms);
     if (folded > need) need = folded;
@@ -402,7 +411,7 @@ int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shar
   cudaError_t e;
   const DeviceInfo* di = current_device_info(&e);
   if (!di) return static_cast<int>(e);
-  return umma_sgemm(a, umma_plan(M, N_shard, 1, di->sm_count, false, -1).pair);
+  return umma_sgemm(a, umma_plan(M, N_shard, 1, di->sm_count, 4, -1).pair);
 }
 
 int tfccb200_sgemm_skinny_static(void* stream, const float* A, const float* B, float* C,

@@ -64,7 +64,7 @@ struct UmmaPlan {
   bool pair;
   int bn;
 };
-UmmaPlan umma_plan(unsigned M, unsigned N, unsigned batch, int sm_count, bool int8,
+UmmaPlan umma_plan(unsigned M, unsigned N, unsigned batch, int sm_count, int elem_bytes,
                    int force_pair);
 bool umma_sgemm_supported(const SgemmArgs& a);
 int umma_sgemm(const SgemmArgs& a, bool pair);
@@ -80,6 +80,10 @@ int skinny_sgemm_static(cudaStream_t stream, const float* A, const float* B, flo
                         const float* bias, unsigned M, unsigned N, unsigned K);
 size_t skinny_sgemm_static_capacity();
 int simt_qgemm(const QgemmArgs& a);
+int convert_f32_to_bf16(cudaStream_t stream, const float* src, void* dst, size_t n);
+// Scratch bytes of the bfloat16 mode: both operands rounded to bfloat16, each 256-byte aligned.
+size_t bf16_staging_bytes(unsigned M, unsigned N, unsigned K, unsigned batch, unsigned strideA,
+                          unsigned strideB);
 int interleave_panels_f32(cudaStream_t stream, const float* src, float* out, unsigned M,
                           unsigned ns, unsigned G);
 template <class T>

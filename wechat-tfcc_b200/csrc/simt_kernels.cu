@@ -1,6 +1,7 @@
 // CUDA-core kernels: the any-shape fp32 and int8 GEMMs that take whatever the
 // tensor-core path cannot (unaligned pitches, tiny problems), the streaming
 // kernel for M <= 8, and the integer row / column sums of the quantized path.
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <mutex>
@@ -375,6 +376,24 @@ interleave_panels_kernel(const float4* __restrict__ src, float4* __restrict__ ou
   }
 }
 
+// fp32 -> bfloat16 (round to nearest even), 8 elements per thread per step.
+__global__ void __launch_bounds__(256)
+convert_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
+  const size_t n8 = n / 8;
+  for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n8; i += gridDim.x * 256ull) {
+    const float4 a = __ldcs(reinterpret_cast<const float4*>(src) + 2 * i);
+    const float4 b = __ldcs(reinterpret_cast<const float4*>(src) + 2 * i + 1);
+    __nv_bfloat162 o[4];
+    o[0] = __floats2bfloat162_rn(a.x, a.y);
+    o[1] = __floats2bfloat162_rn(a.z, a.w);
+    o[2] = __floats2bfloat162_rn(b.x, b.y);
+    o[3] = __floats2bfloat162_rn(b.z, b.w);
+    reinterpret_cast<uint4*>(dst)[i] = *reinterpret_cast<const uint4*>(o);
+  }
+  for (size_t i = n8 * 8 + blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull)
+    dst[i] = __float2bfloat16_rn(src[i]);
+}
+
 inline cudaError_t launch_status() { return cudaGetLastError(); }
 
 }  // namespace
@@ -467,6 +486,22 @@ int skinny_sgemm(const SgemmArgs& a) {
   e = cudaLaunchKernelEx(&cfg, skinny_reduce_kernel, part_c, bias_c, out_c, MN, n_c, ks, stride_c);
   if (e != cudaSuccess) return static_cast<int>(e);
   count_launch(2);
+  return TFCCB200_OK;
+}
+
+int convert_f32_to_bf16(cudaStream_t stream, const float* src, void* dst, size_t n) {
+  cudaError_t ce;
+  const DeviceInfo* di = current_device_info(&ce);
+  if (!di) return static_cast<int>(ce);
+  size_t blocks = (n / 8 + 255) / 256;
+  const size_t cap = static_cast<size_t>(di->sm_count) * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks == 0) blocks = 1;
+  convert_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      src, static_cast<__nv_bfloat16*>(dst), n);
+  cudaError_t e = launch_status();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  count_launch();
   return TFCCB200_OK;
 }
 

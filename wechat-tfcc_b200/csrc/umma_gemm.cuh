@@ -12,6 +12,8 @@
 //     fp32 GEMM.
 //   * I8: u8 x s8 -> s32, exact, with the zero-point correction applied while
 //     the accumulator leaves tensor memory.
+//   * BF16 on operands that a pre-pass rounded from fp32 to bfloat16 (opt-in
+//     low-precision mode); fp32 accumulation and fp32 output.
 //
 // Work layout per CTA (kCtaGroup == 1) or per CTA pair (kCtaGroup == 2):
 //   tile        128*kCtaGroup rows x BN columns, accumulator in TMEM, two
@@ -77,7 +79,8 @@ struct UmmaGemmParams {
 
 template <ptx::MmaKind kKind, bool kSplit, int kCtaGroup, int BN, int kStages>
 struct UmmaGemmConfig {
-  static constexpr int kElemBytes = (kKind == ptx::MmaKind::TF32) ? 4 : 1;
+  static constexpr int kElemBytes =
+      (kKind == ptx::MmaKind::TF32) ? 4 : (kKind == ptx::MmaKind::BF16 ? 2 : 1);
   static constexpr int kBM = 128;                      // rows per CTA
   static constexpr int kTileM = kBM * kCtaGroup;       // rows per MMA
   static constexpr int kBK = 128 / kElemBytes;         // elements of K per k-block
@@ -115,7 +118,9 @@ struct UmmaGemmConfig {
   static constexpr uint32_t kIdesc =
       (kKind == ptx::MmaKind::TF32)
           ? ptx::make_idesc(1u, 2u, 2u, 0u, 1u, static_cast<uint32_t>(kTileM), BN)
-          : ptx::make_idesc(2u, 0u, 1u, 0u, 1u, static_cast<uint32_t>(kTileM), BN);
+          : (kKind == ptx::MmaKind::BF16)
+                ? ptx::make_idesc(1u, 1u, 1u, 0u, 1u, static_cast<uint32_t>(kTileM), BN)
+                : ptx::make_idesc(2u, 0u, 1u, 0u, 1u, static_cast<uint32_t>(kTileM), BN);
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "MMA N out of range");
   static_assert((BN & (BN - 1)) == 0, "BN must be a power of two (TMEM allocation)");
   static_assert(kBNLocal * kElemBytes % 128 == 0, "B tile must be whole 128-byte boxes");
@@ -455,7 +460,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         bounded_wait<false>(tmem_full(acc), acc_ph, TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
         ptx::tc_fence_after_sync();
         const uint32_t taddr = lane_addr + acc * BN;
-        if constexpr (kKind == ptx::MmaKind::TF32) {
+        if constexpr (kKind != ptx::MmaKind::I8) {
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             if (col0 + c * 32 >= p.N) break;  // warp-uniform

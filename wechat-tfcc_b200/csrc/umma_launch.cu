@@ -119,7 +119,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 }  // namespace
 
-UmmaPlan umma_plan(unsigned M, unsigned N, unsigned batch, int sm_count, bool int8,
+UmmaPlan umma_plan(unsigned M, unsigned N, unsigned batch, int sm_count, int elem_bytes,
                    int force_pair) {
   UmmaPlan best = {false, 0};
   double best_cost = 0;
@@ -130,8 +130,8 @@ UmmaPlan umma_plan(unsigned M, unsigned N, unsigned batch, int sm_count, bool in
     if (groups < 1) continue;
     if (pair && M <= 128 && force_pair < 0) continue;  // a second CTA would only hold padding
     for (int bn : {256, 128, 64}) {
-      // int8 stages BN (or BN/2 per CTA of a pair) one-byte columns: 128 bytes at least
-      if (int8 && (pair ? bn < 256 : bn < 128)) continue;
+      // a CTA stages BN (BN/2 in a pair) columns of B: 128 bytes at least
+      if ((pair ? bn / 2 : bn) * elem_bytes < 128) continue;
       if (bn > 64 && static_cast<unsigned>(bn) >= 2 * N) continue;  // mostly padding
       const double penalty = (bn == 256 ? 1.0 : bn == 128 ? 1.25 : 1.6) * (pair ? 0.85 : 1.0);
       const double c = tile_cost(M, N, batch, tile_m, bn, groups, penalty);
@@ -144,9 +144,17 @@ UmmaPlan umma_plan(unsigned M, unsigned N, unsigned batch, int sm_count, bool in
   }
   if (best.bn == 0) {  // nothing admissible (e.g. int8 with tiny N): widest legal tile
     best.pair = force_pair == 1;
-    best.bn = int8 ? (best.pair ? 256 : 128) : 64;
+    best.bn = (best.pair ? 256 : 128) / elem_bytes;
+    if (best.bn < 64) best.bn = 64;
   }
   return best;
+}
+
+size_t bf16_staging_bytes(unsigned M, unsigned N, unsigned K, unsigned batch, unsigned strideA,
+                          unsigned strideB) {
+  const size_t na = static_cast<size_t>((batch > 1 && strideA) ? batch : 1) * M * K;
+  const size_t nb = static_cast<size_t>((batch > 1 && strideB) ? batch : 1) * K * N;
+  return ((na * 2 + 255) / 256 + (nb * 2 + 255) / 256) * 256;
 }
 
 bool umma_sgemm_supported(const SgemmArgs& a) {
@@ -173,7 +181,55 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
 
   const bool a_batched = a.batch > 1 && a.strideA != 0;
   const bool b_batched = a.batch > 1 && a.strideB != 0;
-  const int bn = umma_plan(a.M, a.N, a.batch, di->sm_count, false, pair ? 1 : 0).bn;
+  const int bn = umma_plan(a.M, a.N, a.batch, di->sm_count,
+                           a.precision == TFCCB200_PRECISION_BF16 ? 2 : 4, pair ? 1 : 0).bn;
+
+  if (a.precision == TFCCB200_PRECISION_BF16) {
+    // Opt-in low precision: a pre-pass rounds both operands to bfloat16 in the caller's
+    // scratch, then the bfloat16 tensor-core kernel runs on the copies (fp32 accumulate/out).
+    if (a.K % 8 != 0 || a.N % 8 != 0) return TFCCB200_EALIGN;
+    const size_t na = static_cast<size_t>(a_batched ? a.batch : 1) * a.M * a.K;
+    const size_t nb = static_cast<size_t>(b_batched ? a.batch : 1) * a.K * a.N;
+    const size_t a_bytes = (na * 2 + 255) / 256 * 256;
+    if (!a.workspace || (reinterpret_cast<uintptr_t>(a.workspace) & 255u) ||
+        a.workspace_bytes < bf16_staging_bytes(a.M, a.N, a.K, a.batch, a.strideA, a.strideB))
+      return TFCCB200_EWORKSPACE;
+    void* a16 = a.workspace;
+    void* b16 = static_cast<char*>(a.workspace) + a_bytes;
+    int st = convert_f32_to_bf16(a.stream, a.A, a16, na);
+    if (st != TFCCB200_OK) return st;
+    st = convert_f32_to_bf16(a.stream, a.B, b16, nb);
+    if (st != TFCCB200_OK) return st;
+    CUtensorMap ta16, tb16;
+    if (!make_tmap(&ta16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a16, a.K, a.M,
+                   a_batched ? a.batch : 1, a.strideA, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+      return TFCCB200_EINVAL;
+    if (!make_tmap(&tb16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b16, a.N, a.K,
+                   b_batched ? a.batch : 1, a.strideB, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+      return TFCCB200_EINVAL;
+    UmmaGemmParams q = {};
+    q.num_dst = a.num_dst ? a.num_dst : 1;
+    if (q.num_dst > kMaxDestinations) return TFCCB200_EINVAL;
+    q.dst[0] = a.C;
+    for (unsigned d = 0; d < a.num_dst; ++d) q.dst[d] = a.dst[d];
+    q.ldc = a.ldc ? a.ldc : a.N;
+    q.col_offset = a.col_offset;
+    q.bias = a.bias;
+    q.M = a.M; q.N = a.N; q.K = a.K; q.batch = a.batch;
+    q.strideC = a.strideC;
+    q.a_batched = a_batched; q.b_batched = b_batched;
+    q.status = a.status;
+    q.timeout_ns = kDefaultTimeoutNs;
+    constexpr auto H = ptx::MmaKind::BF16;
+    const int sms16 = di->sm_count;
+    if (!pair) {
+      if (bn == 256) return launch<H, false, 1, 256, 4>(a.stream, ta16, tb16, q, sms16);
+      if (bn == 128) return launch<H, false, 1, 128, 6>(a.stream, ta16, tb16, q, sms16);
+      return launch<H, false, 1, 64, 8>(a.stream, ta16, tb16, q, sms16);
+    }
+    if (bn == 256) return launch<H, false, 2, 256, 6>(a.stream, ta16, tb16, q, sms16);
+    return launch<H, false, 2, 128, 8>(a.stream, ta16, tb16, q, sms16);
+  }
 
   CUtensorMap ta, tb;
   if (!make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.A, a.K, a.M, a_batched ? a.batch : 1,
@@ -253,7 +309,7 @@ int umma_qgemm(const QgemmArgs& a, bool pair) {
 
   const bool a_batched = a.batch > 1 && a.strideA != 0;
   const bool b_batched = a.batch > 1 && a.strideB != 0;
-  const int bn = umma_plan(a.M, a.N, a.batch, di->sm_count, true, pair ? 1 : 0).bn;
+  const int bn = umma_plan(a.M, a.N, a.batch, di->sm_count, 1, pair ? 1 : 0).bn;
 
   CUtensorMap ta, tb;
   if (!make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.A, a.K, a.M, a_batched ? a.batch : 1,
