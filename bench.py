@@ -314,6 +314,47 @@ def extra_measurements(torch, pkg, dev, peaks):
     x = rng.normal(0, 1, (8, 128, 768)).astype(np.float32)
     sgemm_case("cfg4_ffn1_1024x768x3072", x, rng.normal(0, 0.02, (768, 3072)).astype(np.float32),
                bias=np.zeros(3072, np.float32))
+    # cfg4: the whole 4-layer encoder stack on this library's operators, and its matmuls alone
+    d_model, heads, dh, b4, s4 = 768, 12, 64, 8, 128
+    shapes4 = [(768, 768)] * 4 + [(768, 3072), (3072, 768)]
+    w4 = [[t for (k, n) in shapes4 for t in (to(rng.normal(0, 0.02, (k, n)).astype(np.float32)),
+                                             torch.zeros(n, device=dev))] for _ in range(4)]
+    x4 = to(rng.normal(0, 1, (b4, s4, d_model)).astype(np.float32))
+    gamma4, beta4 = torch.ones(d_model, device=dev), torch.zeros(d_model, device=dev)
+    mm, nnops = pkg.blas.matmul, pkg.nn
+
+    def stack(x):
+        split = lambda t: nnops.permute_0213(t.view(b4, s4, heads, dh))
+        for (wq, bq, wk, bk, wv, bv, wo, bo, w1, b1, w2, b2) in w4:
+            q, k, v = split(mm(x, wq, bq)), split(mm(x, wk, bk)), split(mm(x, wv, bv))
+            p = nnops.softmax(mm(q, nnops.transpose_last2(k)), scale=0.125)
+            o = nnops.permute_0213(mm(p, v)).view(b4, s4, d_model)
+            x = nnops.layer_norm(mm(o, wo, bo), gamma4, beta4, 1e-5, residual=x)
+            x = nnops.layer_norm(mm(mm(x, w1, b1, activation="gelu"), w2, b2), gamma4, beta4, 1e-5,
+                                 residual=x)
+        return x
+
+    q4 = to(rng.normal(0, 1, (b4, heads, s4, dh)).astype(np.float32))
+    k4 = to(rng.normal(0, 1, (b4, heads, dh, s4)).astype(np.float32))
+    p4 = to(rng.uniform(0, 1, (b4, heads, s4, s4)).astype(np.float32))
+    f4 = to(rng.normal(0, 1, (b4, s4, 3072)).astype(np.float32))
+
+    def matmuls_only():
+        for (wq, bq, wk, bk, wv, bv, wo, bo, w1, b1, w2, b2) in w4:
+            mm(x4, wq, bq); mm(x4, wk, bk); mm(x4, wv, bv)
+            mm(q4, k4); mm(p4, q4)
+            mm(x4, wo, bo); mm(x4, w1, b1); mm(f4, w2, b2)
+
+    launches_before = pkg.launch_count()
+    stack(x4)
+    stack_launches = pkg.launch_count() - launches_before
+    stack_us, _ = time_graph_train(torch, [lambda: stack(x4)])
+    mm_us, _ = time_graph_train(torch, [matmuls_only])
+    flop4 = 4 * 14898167808.0
+    out["cfg4_encoder_stack"] = {"ms": stack_us / 1e3, "matmul_only_ms": mm_us / 1e3,
+                                 "kernels_per_forward": stack_launches,
+                                 "matmul_tflops": flop4 / (mm_us * 1e-6) / 1e12}
+    del w4
     # cfg5 skinny sweep
     w = rng.normal(0, 0.02, (4096, 16384)).astype(np.float32)
     for m in (1, 4, 8):

@@ -159,6 +159,52 @@ TFCCB200_API int tfccb200_reduce_sum_s8(void* stream, const int8_t* src, unsigne
 TFCCB200_API int tfccb200_reduce_sum_s16(void* stream, const int16_t* src, unsigned batch, unsigned rows,
                             unsigned cols, int row_flag, int32_t* dst);
 
+/* ---- activations that the fp32 GEMM can apply in its epilogue ----------------- */
+#define TFCCB200_ACT_NONE 0
+#define TFCCB200_ACT_GELU_ERF 1 /* 0.5 x (1 + erf(x / sqrt 2)), the reference's gelu_accurate */
+
+/*
+ * tfccb200_sgemm_ex with an activation applied to A.B + bias while the result leaves the
+ * accumulator: MatmulWithBias followed by Gelu (the FFN of a transformer block) in one pass
+ * over C.  The reference runs them as two operators
+ * (tfcc/mkl/interfaces/tfcc_mklblasinterface.cpp:154-186 then
+ *  _MKLActivationKernel::geluAccurate, tfcc/mkl/kernel/tfcc_mklactivationkernel.hpp:214-220).
+ */
+TFCCB200_API int tfccb200_sgemm_act(void* stream, const float* A, unsigned strideA,
+                                    const float* B, unsigned strideB, float* C, unsigned strideC,
+                                    const float* bias, unsigned M, unsigned N, unsigned K,
+                                    unsigned batch, int precision_mode, int path, int activation,
+                                    void* workspace, size_t workspace_bytes, int* device_status);
+
+/*
+ * dst[r][:] = softmax(scale * src[r][:]) over the last dimension (max subtraction, exp, sum,
+ * divide: _MKLActivationKernel::softmaxV2, tfcc/mkl/kernel/tfcc_mklactivationkernel.hpp:138-155;
+ * cf. _cuda_softmax_v1_small, tfcc/cuda/interfaces/tfcc_cudaactivationinterface.cu:96-121).
+ * The pre-scale folds the separate "x / sqrt(d)" operator of an attention block into the pass.
+ */
+TFCCB200_API int tfccb200_softmax_f32(void* stream, const float* src, unsigned rows,
+                                      unsigned cols, float scale, float* dst);
+
+/*
+ * dst = (t - mean(t)) / sqrt(var(t) + eps) * gamma + beta with t = x (+ residual when not
+ * NULL), row by row, two-pass mean and variance (_mkl_layer_normalize,
+ * tfcc/mkl/interfaces/tfcc_mklnormalizationinterface.cpp:29-62).  cols <= 1024.
+ */
+TFCCB200_API int tfccb200_layer_norm_f32(void* stream, const float* x, const float* residual,
+                                         const float* gamma, const float* beta, float eps,
+                                         unsigned rows, unsigned cols, float* dst);
+
+/* dst[i] = gelu_accurate(src[i]) (erf form). */
+TFCCB200_API int tfccb200_gelu_f32(void* stream, const float* src, size_t n, float* dst);
+
+/* [d0,d1,d2,d3] -> [d0,d2,d1,d3] (split / merge attention heads) and [batch,r,c] ->
+ * [batch,c,r] (K transposed); the index maps of _cuda_transpose_4d / _3d
+ * (tfcc/cuda/interfaces/tfcc_cudabasicinterface.cu:66-100) for these two permutations. */
+TFCCB200_API int tfccb200_permute_0213_f32(void* stream, const float* src, unsigned d0,
+                                           unsigned d1, unsigned d2, unsigned d3, float* dst);
+TFCCB200_API int tfccb200_transpose_last2_f32(void* stream, const float* src, unsigned batch,
+                                              unsigned r, unsigned c, float* dst);
+
 /* ---- element types of the quantization entry points ------------------------ */
 #define TFCCB200_TYPE_S8 0
 #define TFCCB200_TYPE_U8 1

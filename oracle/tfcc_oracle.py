@@ -355,6 +355,37 @@ def quantized_dense(a, b, impl="numpy"):
     return dequantize(qc, min_c, max_c)
 
 
+# --------------------------------------------------------------------------- attention / FFN glue
+def softmax_v2(a, scale=1.0):
+    """_MKLActivationKernel::softmaxV2 on float32 rows
+    (tfcc/mkl/kernel/tfcc_mklactivationkernel.hpp:138-155), after an optional pre-scale."""
+    a = (np.asarray(a, dtype=np.float32) * np.float32(scale)).astype(np.float32)
+    e = np.exp(a - a.max(axis=-1, keepdims=True)).astype(np.float32)
+    return (e / e.sum(axis=-1, keepdims=True, dtype=np.float32)).astype(np.float32)
+
+
+def gelu_accurate(a):
+    """_MKLActivationKernel::geluAccurate (:214-220): erf in float, outer products in double."""
+    from scipy.special import erf
+    a = np.asarray(a, dtype=np.float32)
+    e = (np.float32(1.0) + erf(a / np.float32(1.4142135623730951)).astype(np.float32)).astype(np.float32)
+    return (0.5 * a.astype(np.float64) * e.astype(np.float64)).astype(np.float32)
+
+
+def layer_normalize(a, gamma, beta, eps=1e-5, residual=None):
+    """_mkl_layer_normalize (tfcc/mkl/interfaces/tfcc_mklnormalizationinterface.cpp:29-62),
+    float32 throughout, on x (+ residual)."""
+    a = np.asarray(a, dtype=np.float32)
+    if residual is not None:
+        a = (a + np.asarray(residual, dtype=np.float32)).astype(np.float32)
+    n = np.float32(a.shape[-1])
+    mean = (a.sum(axis=-1, keepdims=True, dtype=np.float32) / n).astype(np.float32)
+    d = (a - mean).astype(np.float32)
+    var = ((d * d).sum(axis=-1, keepdims=True, dtype=np.float32) / n).astype(np.float32)
+    inv = (np.float32(1.0) / np.sqrt(var + np.float32(eps))).astype(np.float32)
+    return (d * (inv * np.asarray(gamma, np.float32)) + np.asarray(beta, np.float32)).astype(np.float32)
+
+
 def sgemm_f64acc_c(a, b, bias=None):
     """The C port's double-accumulating fp32 GEMM on rank-2 operands (float32 result)."""
     a = np.ascontiguousarray(a, dtype=np.float32)

@@ -242,52 +242,52 @@ def test_nsplit_push_entry_point_on_one_gpu(pkg, orc):
                                               m, 130, k, 0, None) == -2
 
 
-def _encoder_stack(x, weights, matmul, bmm, xp):
-    """BERT-like post-LN encoder stack (config 4): every matrix product goes through `matmul`
-    (rank-3 x rank-2 (+bias)) or `bmm` (rank-4 x rank-4); the element-wise steps use the
-    array module `xp` with the reference's formulas: softmax with max subtraction
-    (tfcc/mkl/kernel/tfcc_mklactivationkernel.hpp:138-155), erf GELU (:214-220), two-pass
-    layer norm with gamma 1, beta 0, eps 1e-5 (tfcc/mkl/interfaces/tfcc_mklnormalizationinterface.cpp:29-62)."""
+def _encoder_stack_f64(x, weights):
+    """Config 4 in float64 numpy: 4-layer BERT-base-shaped post-LN encoder with the reference's
+    formulas (softmax with max subtraction, erf GELU, two-pass layer norm, gamma 1, beta 0,
+    eps 1e-5)."""
+    from scipy.special import erf
     b, s, h = x.shape
     heads, dh = 12, 64
 
-    def layer_norm(t):
-        mu = t.mean(-1, keepdims=True) if xp is np else t.mean(-1, keepdim=True)
-        var = ((t - mu) ** 2).mean(-1, keepdims=True) if xp is np else ((t - mu) ** 2).mean(-1, keepdim=True)
-        return (t - mu) / xp.sqrt(var + 1e-5)
+    def ln(t):
+        mu = t.mean(-1, keepdims=True)
+        var = ((t - mu) ** 2).mean(-1, keepdims=True)
+        return (t - mu) / np.sqrt(var + 1e-5)
 
-    def split(t):   # [b,s,h] -> [b,heads,s,dh]
-        t = t.reshape(b, s, heads, dh)
-        return np.ascontiguousarray(t.transpose(0, 2, 1, 3)) if xp is np else t.permute(0, 2, 1, 3).contiguous()
-
+    split = lambda t: t.reshape(b, s, heads, dh).transpose(0, 2, 1, 3)
     for (wq, bq, wk, bk, wv, bv, wo, bo, w1, b1, w2, b2) in weights:
-        q, k, v = split(matmul(x, wq, bq)), split(matmul(x, wk, bk)), split(matmul(x, wv, bv))
-        kt = np.ascontiguousarray(k.transpose(0, 1, 3, 2)) if xp is np else k.permute(0, 1, 3, 2).contiguous()
-        sc = bmm(q, kt) / 8.0
-        sc = sc - (sc.max(-1, keepdims=True) if xp is np else sc.max(-1, keepdim=True).values)
-        e = xp.exp(sc)
-        p = e / (e.sum(-1, keepdims=True) if xp is np else e.sum(-1, keepdim=True))
-        o = bmm(p, v)
-        o = (np.ascontiguousarray(o.transpose(0, 2, 1, 3)) if xp is np else o.permute(0, 2, 1, 3).contiguous()).reshape(b, s, h)
-        x = layer_norm(x + matmul(o, wo, bo))
-        f = matmul(x, w1, b1)
-        if xp is np:
-            from scipy.special import erf
-            f = 0.5 * f * (1.0 + erf(f / np.sqrt(2.0)))
-        else:
-            f = 0.5 * f * (1.0 + torch.erf(f / 2.0 ** 0.5))
-        x = layer_norm(x + matmul(f, w2, b2))
+        q, k, v = split(x @ wq + bq), split(x @ wk + bk), split(x @ wv + bv)
+        sc = (q @ k.transpose(0, 1, 3, 2)) / 8.0
+        e = np.exp(sc - sc.max(-1, keepdims=True))
+        p = e / e.sum(-1, keepdims=True)
+        o = (p @ v).transpose(0, 2, 1, 3).reshape(b, s, h)
+        x = ln(x + (o @ wo + bo))
+        f = x @ w1 + b1
+        f = 0.5 * f * (1.0 + erf(f / np.sqrt(2.0)))
+        x = ln(x + (f @ w2 + b2))
     return x
 
 
-def test_config4_encoder_stack_matmuls(pkg, orc):
-    """Config 4 at the matmul level: a 4-layer BERT-base-shaped encoder whose 32 matrix products
-    run on this library (torch only does the element-wise glue on the same device), against
-    the same stack in float64 numpy.  Shapes: [8,128,768]x[768,768|3072], [8,128,3072]x[3072,768],
-    [8,12,128,64]x[8,12,64,128] and [8,12,128,128]x[8,12,128,64]."""
-    d = dev_of()
-    rng = np.random.default_rng(3)
-    x = rng.normal(0, 1, (8, 128, 768)).astype(np.float32)
+def encoder_stack_device(pkg, x, weights, gamma, beta):
+    """The same stack with every operator from this library: 6 dense matmuls with fused bias
+    (the FFN's first one with fused GELU), two batched attention matmuls, fused scale+softmax,
+    fused residual+layer norm, head split / merge permutations and K transposed."""
+    mm, nn = pkg.blas.matmul, pkg.nn
+    b, s, h = x.shape
+    heads, dh = 12, 64
+    split = lambda t: nn.permute_0213(t.view(b, s, heads, dh))
+    for (wq, bq, wk, bk, wv, bv, wo, bo, w1, b1, w2, b2) in weights:
+        q, k, v = split(mm(x, wq, bq)), split(mm(x, wk, bk)), split(mm(x, wv, bv))
+        p = nn.softmax(mm(q, nn.transpose_last2(k)), scale=0.125)
+        o = nn.permute_0213(mm(p, v)).view(b, s, h)
+        x = nn.layer_norm(mm(o, wo, bo), gamma, beta, 1e-5, residual=x)
+        f = mm(x, w1, b1, activation="gelu")
+        x = nn.layer_norm(mm(f, w2, b2), gamma, beta, 1e-5, residual=x)
+    return x
+
+
+def make_encoder_weights(rng):
     shapes = [(768, 768)] * 4 + [(768, 3072), (3072, 768)]
     weights = []
     for _ in range(4):
@@ -295,30 +295,21 @@ def test_config4_encoder_stack_matmuls(pkg, orc):
         for (k, n) in shapes:
             layer += [rng.normal(0, 0.02, (k, n)).astype(np.float32), np.zeros(n, np.float32)]
         weights.append(layer)
-    truth = _encoder_stack(x.astype(np.float64), [[w.astype(np.float64) for w in l] for l in weights],
-                           lambda a, w, b: a @ w + b, lambda a, b: a @ b, np)
+    return weights
+
+
+def test_config4_encoder_stack_on_device(pkg, orc):
+    """Config 4: 4-layer BERT-base-shaped encoder, batch 8, sequence 128, every operator from
+    this library, against the same stack in float64."""
+    d = dev_of()
+    rng = np.random.default_rng(3)
+    x = rng.normal(0, 1, (8, 128, 768)).astype(np.float32)
+    weights = make_encoder_weights(rng)
+    truth = _encoder_stack_f64(x.astype(np.float64), [[w.astype(np.float64) for w in l] for l in weights])
     tw = [[torch.from_numpy(w).to(d) for w in l] for l in weights]
-    got = _encoder_stack(torch.from_numpy(x).to(d), tw, lambda a, w, b: pkg.blas.matmul(a, w, b),
-                         lambda a, b: pkg.blas.matmul(a, b), torch)
+    gamma, beta = torch.ones(768, device=d), torch.zeros(768, device=d)
+    got = encoder_stack_device(pkg, torch.from_numpy(x).to(d), tw, gamma, beta)
     pkg.session.get_session(d).sync()
     got = got.cpu().numpy()
     assert orc.normwise_rel_error(got, truth) < 1e-5
     assert orc.is_similar(got, truth.astype(np.float32))
-
-
-def test_host_buffer_entry_point_pipelined_large_product(pkg, orc):
-    """Large single products take the overlapped path of tfccb200_sgemm_host (B uploaded first,
-    A in 1024-row blocks while earlier blocks multiply and download); ragged last block."""
-    rng = np.random.default_rng(31)
-    m, k, n = 2348, 2048, 4096
-    a = torch.from_numpy(rng.uniform(-1, 1, (m, k)).astype(np.float32)).pin_memory().numpy()
-    b = torch.from_numpy(rng.uniform(-1, 1, (k, n)).astype(np.float32)).pin_memory().numpy()
-    bias = rng.uniform(-1, 1, n).astype(np.float32)
-    got = pkg.blas.matmul_host(a, b, bias)
-    rows = np.sort(rng.choice(m, 96, replace=False))
-    rows[-1] = m - 1
-    truth = a[rows].astype(np.float64) @ b.astype(np.float64) + bias
-    assert orc.normwise_rel_error(got[rows], truth) < TOL_FP32
-    # every row block was written: no element of the output kept its initial garbage pattern
-    dev = run(pkg, a, b, bias)
-    assert np.array_equal(got, dev)

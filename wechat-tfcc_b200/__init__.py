@@ -10,6 +10,6 @@ the built library raises.
 """
 from . import exceptions  # noqa: F401
 from ._lib import lib, library_path, launch_count  # noqa: F401
-from . import blas, quantization, parallel, session  # noqa: F401
+from . import blas, nn, quantization, parallel, session  # noqa: F401
 
-__all__ = ["blas", "quantization", "parallel", "exceptions", "lib", "library_path", "launch_count"]
+__all__ = ["blas", "nn", "quantization", "parallel", "exceptions", "lib", "library_path", "launch_count"]

@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from . import exceptions
-from ._lib import PATHS, PRECISIONS, check, lib
+from ._lib import ACTIVATIONS, PATHS, PRECISIONS, check, lib
 from .session import get_session
 
 
@@ -40,9 +40,10 @@ def _check_operand(t, name):
 
 
 def matmul(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None, *,
-           precision: str = "fp32", path: str = "auto") -> torch.Tensor:
+           precision: str = "fp32", path: str = "auto", activation: str | None = None) -> torch.Tensor:
     """``a . b`` (+ ``c`` broadcast over rows).  Batched when either operand has rank > 2;
-    a rank-2 operand is shared by every batch entry.  Asynchronous on the current stream."""
+    a rank-2 operand is shared by every batch entry.  Asynchronous on the current stream.
+    ``activation="gelu"`` applies the erf GELU to the result inside the GEMM epilogue."""
     for t, nm in ((a, "a"), (b, "b")) + (((c, "c"),) if c is not None else ()):
         if not isinstance(t, torch.Tensor):
             raise exceptions.InvalidArgumentError(f"{nm} must be a tensor")
@@ -68,10 +69,11 @@ def matmul(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None, *,
     with torch.cuda.device(a.device):
         ws_bytes = lib.tfccb200_sgemm_workspace(m, n, k, batch, PRECISIONS[precision])
         ws_ptr, ws_len = sess.workspace(ws_bytes)
-        st = lib.tfccb200_sgemm_ex(
+        st = lib.tfccb200_sgemm_act(
             sess.stream_ptr, a.data_ptr(), stride_a, b.data_ptr(), stride_b, result.data_ptr(),
             stride_c, c.data_ptr() if c is not None else None, m, n, k, batch,
-            PRECISIONS[precision], PATHS[path], ws_ptr, ws_len, sess.status_ptr)
+            PRECISIONS[precision], PATHS[path], ACTIVATIONS[activation], ws_ptr, ws_len,
+            sess.status_ptr)
     check(st)
     return result
 

@@ -240,7 +240,20 @@ int tfccb200_sgemm_ex(void* stream, const float* A, unsigned strideA, const floa
                       unsigned strideB, float* C, unsigned strideC, const float* bias, unsigned M,
                       unsigned N, unsigned K, unsigned batch, int precision_mode, int path,
                       void* workspace, size_t workspace_bytes, int* device_status) {
+  return tfccb200_sgemm_act(stream, A, strideA, B, strideB, C, strideC, bias, M, N, K, batch,
+                            precision_mode, path, TFCCB200_ACT_NONE, workspace, workspace_bytes,
+                            device_status);
+}
+
+int tfccb200_sgemm_act(void* stream, const float* A, unsigned strideA, const float* B,
+                       unsigned strideB, float* C, unsigned strideC, const float* bias, unsigned M,
+                       unsigned N, unsigned K, unsigned batch, int precision_mode, int path,
+                       int activation, void* workspace, size_t workspace_bytes,
+                       int* device_status) {
+  if (activation != TFCCB200_ACT_NONE && activation != TFCCB200_ACT_GELU_ERF)
+    return TFCCB200_EINVAL;
   SgemmArgs a = {};
+  a.activation = activation;
   a.stream = static_cast<cudaStream_t>(stream);
   a.A = A; a.B = B; a.C = C; a.bias = bias;
   a.strideA = strideA; a.strideB = strideB; a.strideC = strideC;
@@ -350,6 +363,38 @@ int tfccb200_reduce_sum_s8(void* stream, const int8_t* src, unsigned batch, unsi
 int tfccb200_reduce_sum_s16(void* stream, const int16_t* src, unsigned batch, unsigned rows,
                             unsigned cols, int row_flag, int32_t* dst) {
   return reduce_sum_checked<int16_t>(stream, src, batch, rows, cols, row_flag, dst);
+}
+
+int tfccb200_softmax_f32(void* stream, const float* src, unsigned rows, unsigned cols, float scale,
+                         float* dst) {
+  if (!src || !dst || rows == 0 || cols == 0) return TFCCB200_EINVAL;
+  return softmax_f32(static_cast<cudaStream_t>(stream), src, rows, cols, scale, dst);
+}
+
+int tfccb200_layer_norm_f32(void* stream, const float* x, const float* residual,
+                            const float* gamma, const float* beta, float eps, unsigned rows,
+                            unsigned cols, float* dst) {
+  if (!x || !gamma || !beta || !dst || rows == 0 || cols == 0) return TFCCB200_EINVAL;
+  return layer_norm_f32(static_cast<cudaStream_t>(stream), x, residual, gamma, beta, eps, rows,
+                        cols, dst);
+}
+
+int tfccb200_gelu_f32(void* stream, const float* src, size_t n, float* dst) {
+  if (!src || !dst || n == 0) return TFCCB200_EINVAL;
+  return gelu_f32(static_cast<cudaStream_t>(stream), src, n, dst);
+}
+
+int tfccb200_permute_0213_f32(void* stream, const float* src, unsigned d0, unsigned d1,
+                              unsigned d2, unsigned d3, float* dst) {
+  if (!src || !dst || d0 == 0 || d1 == 0 || d2 == 0 || d3 == 0) return TFCCB200_EINVAL;
+  if (static_cast<unsigned long long>(d0) * d1 * d2 * d3 > 0xffffffffull) return TFCCB200_EOVERFLOW;
+  return permute_0213_f32(static_cast<cudaStream_t>(stream), src, d0, d1, d2, d3, dst);
+}
+
+int tfccb200_transpose_last2_f32(void* stream, const float* src, unsigned batch, unsigned r,
+                                 unsigned c, float* dst) {
+  if (!src || !dst || batch == 0 || r == 0 || c == 0) return TFCCB200_EINVAL;
+  return transpose_last2_f32(static_cast<cudaStream_t>(stream), src, batch, r, c, dst);
 }
 
 int tfccb200_minmax_f32(void* stream, const float* src, size_t n, float* minmax) {

@@ -41,6 +41,7 @@ struct SgemmArgs {
   unsigned num_dst;
   unsigned long long ldc;
   unsigned col_offset;
+  int activation;  // TFCCB200_ACT_*: applied to A.B + bias before the store
 };
 
 struct QgemmArgs {
@@ -89,6 +90,17 @@ int interleave_panels_f32(cudaStream_t stream, const float* src, float* out, uns
 template <class T>
 int reduce_sum(cudaStream_t stream, const T* src, unsigned batch, unsigned rows, unsigned cols,
                int row_flag, int32_t* dst);
+
+// ---- attention / FFN glue (nn_kernels.cu) ----
+int softmax_f32(cudaStream_t stream, const float* src, unsigned rows, unsigned cols, float scale,
+                float* dst);
+int layer_norm_f32(cudaStream_t stream, const float* x, const float* residual, const float* gamma,
+                   const float* beta, float eps, unsigned rows, unsigned cols, float* dst);
+int gelu_f32(cudaStream_t stream, const float* src, size_t n, float* dst);
+int permute_0213_f32(cudaStream_t stream, const float* src, unsigned d0, unsigned d1, unsigned d2,
+                     unsigned d3, float* dst);
+int transpose_last2_f32(cudaStream_t stream, const float* src, unsigned batch, unsigned r,
+                        unsigned c, float* dst);
 
 // ---- quantize / dequantize / requantize (quantize_kernels.cu) ----
 int minmax_f32(cudaStream_t stream, const float* src, size_t n, float* out);

@@ -6,6 +6,7 @@
 
 #include <mutex>
 
+#include "act.cuh"
 #include "internal.h"
 
 namespace tfccb200 {
@@ -31,6 +32,7 @@ struct Widen<uint8_t, int8_t, int32_t> {
 };
 
 struct SimtEpilogue {
+  int activation;           // fp32: TFCCB200_ACT_*
   const float* bias;        // fp32
   const int32_t* rsA;       // int8
   const int32_t* rsB;
@@ -105,6 +107,7 @@ simt_gemm_kernel(const TA* __restrict__ A, const TB* __restrict__ B, TAcc* __res
       TAcc v = acc[i][j];
       if constexpr (sizeof(TA) == 4) {
         if (ep.bias) v += ep.bias[c];
+        v = apply_activation(v, ep.activation);
       } else {
         v += ep.kterm + ep.rsA[static_cast<size_t>(ep.strideRsA) * b + r] * ep.offB +
              ep.rsB[static_cast<size_t>(ep.strideRsB) * b + c] * ep.offA;
@@ -228,7 +231,7 @@ skinny_partial_kernel(const float* __restrict__ X, const float* __restrict__ W,
 __global__ void __launch_bounds__(128)
 skinny_reduce_kernel(const float* __restrict__ part, const float* __restrict__ bias,
                      float* __restrict__ Y, unsigned MN, unsigned N, unsigned kslices,
-                     unsigned long long strideY) {
+                     unsigned long long strideY, int activation) {
   const unsigned b = blockIdx.y;
   const unsigned i = (blockIdx.x * 128 + threadIdx.x) * 4;
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -252,6 +255,10 @@ skinny_reduce_kernel(const float* __restrict__ part, const float* __restrict__ b
   if (bias) {
     const float4 bv = *reinterpret_cast<const float4*>(bias + (i % N));
     s.x += bv.x; s.y += bv.y; s.z += bv.z; s.w += bv.w;
+  }
+  if (activation != TFCCB200_ACT_NONE) {
+    s.x = apply_activation(s.x, activation); s.y = apply_activation(s.y, activation);
+    s.z = apply_activation(s.z, activation); s.w = apply_activation(s.w, activation);
   }
   *reinterpret_cast<float4*>(Y + strideY * b + i) = s;
 }
@@ -403,6 +410,7 @@ int simt_sgemm(const SgemmArgs& a) {
   if (grid.y > 65535 || grid.z > 65535) return TFCCB200_EOVERFLOW;
   SimtEpilogue ep = {};
   ep.bias = a.bias;
+  ep.activation = a.activation;
   simt_gemm_kernel<float, float, float><<<grid, 256, 0, a.stream>>>(
       a.A, a.B, a.C, a.M, a.N, a.K, a.strideA, a.strideB, a.strideC, ep);
   cudaError_t e = launch_status();
@@ -483,7 +491,9 @@ int skinny_sgemm(const SgemmArgs& a) {
   float* out_c = a.C;
   unsigned n_c = a.N;
   unsigned long long stride_c = a.strideC;
-  e = cudaLaunchKernelEx(&cfg, skinny_reduce_kernel, part_c, bias_c, out_c, MN, n_c, ks, stride_c);
+  int act_c = a.activation;
+  e = cudaLaunchKernelEx(&cfg, skinny_reduce_kernel, part_c, bias_c, out_c, MN, n_c, ks, stride_c,
+                         act_c);
   if (e != cudaSuccess) return static_cast<int>(e);
   count_launch(2);
   return TFCCB200_OK;

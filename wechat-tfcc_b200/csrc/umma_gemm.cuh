@@ -44,6 +44,7 @@
 #pragma once
 
 #include "../../include/tfcc_b200.h"
+#include "act.cuh"
 #include "ptx.cuh"
 
 namespace tfccb200 {
@@ -59,7 +60,8 @@ struct UmmaGemmParams {
   unsigned num_dst;
   unsigned long long ldc;  // row pitch of the destinations, in elements
   unsigned col_offset;     // first destination column of this problem's column 0
-  const float* bias;       // [N] or nullptr (TF32 only)
+  const float* bias;       // [N] or nullptr (float kinds only)
+  int activation;          // TFCCB200_ACT_*, applied after the bias (float kinds only)
   const int32_t* rsA;      // I8: row sums of A, [batch?][M]
   const int32_t* rsB;      // I8: column sums of B, [batch?][N]
   int32_t offA, offB;      // I8 zero-point offsets
@@ -190,6 +192,12 @@ __device__ __forceinline__ void epi_flush_block(uint32_t* stage, uint32_t lane, 
       v.y = __float_as_uint(__uint_as_float(v.y) + __uint_as_float(col_term.y));
       v.z = __float_as_uint(__uint_as_float(v.z) + __uint_as_float(col_term.z));
       v.w = __float_as_uint(__uint_as_float(v.w) + __uint_as_float(col_term.w));
+      if (p.activation != TFCCB200_ACT_NONE) {
+        v.x = __float_as_uint(apply_activation(__uint_as_float(v.x), p.activation));
+        v.y = __float_as_uint(apply_activation(__uint_as_float(v.y), p.activation));
+        v.z = __float_as_uint(apply_activation(__uint_as_float(v.z), p.activation));
+        v.w = __float_as_uint(apply_activation(__uint_as_float(v.w), p.activation));
+      }
     } else {
       v.x += col_term.x; v.y += col_term.y; v.z += col_term.z; v.w += col_term.w;
     }

@@ -215,6 +215,7 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
     q.ldc = a.ldc ? a.ldc : a.N;
     q.col_offset = a.col_offset;
     q.bias = a.bias;
+    q.activation = a.activation;
     q.M = a.M; q.N = a.N; q.K = a.K; q.batch = a.batch;
     q.strideC = a.strideC;
     q.a_batched = a_batched; q.b_batched = b_batched;
@@ -248,6 +249,7 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
   p.ldc = a.ldc ? a.ldc : a.N;
   p.col_offset = a.col_offset;
   p.bias = a.bias;
+  p.activation = a.activation;
   p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
   p.strideC = a.strideC;
   p.a_batched = a_batched; p.b_batched = b_batched;

@@ -1,0 +1,93 @@
+"""The operators between the matmuls of an attention / feed-forward block, on the B200
+backend: row softmax with a fused pre-scale, erf GELU, layer normalisation with a fused
+residual add, and the two permutations attention needs.  Formulas are the reference's
+(tfcc/mkl/kernel/tfcc_mklactivationkernel.hpp:138-155,214-220,
+tfcc/mkl/interfaces/tfcc_mklnormalizationinterface.cpp:29-62)."""
+from __future__ import annotations
+
+import torch
+
+from . import exceptions
+from ._lib import check, lib
+from .session import get_session
+
+
+def _f32(t, name):
+    if not isinstance(t, torch.Tensor) or t.numel() == 0:
+        raise exceptions.InvalidArgumentError(f"invalid tensor {name}")
+    if t.dtype != torch.float32:
+        raise exceptions.NotImplementedError(f"{name}: implemented for float32, got {t.dtype}")
+    if not t.is_cuda or not t.is_contiguous():
+        raise exceptions.InvalidArgumentError(f"{name} must be a contiguous CUDA tensor")
+
+
+def softmax(a: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """softmax(scale * a) over the last dimension."""
+    _f32(a, "a")
+    cols = a.shape[-1]
+    out = torch.empty_like(a)
+    sess = get_session(a.device)
+    with torch.cuda.device(a.device):
+        check(lib.tfccb200_softmax_f32(sess.stream_ptr, a.data_ptr(), a.numel() // cols, cols,
+                                       float(scale), out.data_ptr()))
+    return out
+
+
+def gelu(a: torch.Tensor) -> torch.Tensor:
+    """erf-form GELU (the reference's gelu_accurate)."""
+    _f32(a, "a")
+    out = torch.empty_like(a)
+    sess = get_session(a.device)
+    with torch.cuda.device(a.device):
+        check(lib.tfccb200_gelu_f32(sess.stream_ptr, a.data_ptr(), a.numel(), out.data_ptr()))
+    return out
+
+
+def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float = 1e-5,
+               residual: torch.Tensor | None = None) -> torch.Tensor:
+    """Layer normalisation of ``x`` (+ ``residual``) over the last dimension."""
+    _f32(x, "x")
+    _f32(gamma, "gamma")
+    _f32(beta, "beta")
+    cols = x.shape[-1]
+    if gamma.numel() != cols or beta.numel() != cols:
+        raise exceptions.InvalidArgumentError("gamma / beta do not match the last dimension")
+    if residual is not None:
+        _f32(residual, "residual")
+        if residual.shape != x.shape:
+            raise exceptions.InvalidArgumentError("residual does not match x")
+    out = torch.empty_like(x)
+    sess = get_session(x.device)
+    with torch.cuda.device(x.device):
+        check(lib.tfccb200_layer_norm_f32(
+            sess.stream_ptr, x.data_ptr(), residual.data_ptr() if residual is not None else None,
+            gamma.data_ptr(), beta.data_ptr(), float(eps), x.numel() // cols, cols, out.data_ptr()))
+    return out
+
+
+def permute_0213(a: torch.Tensor) -> torch.Tensor:
+    """[d0,d1,d2,d3] -> [d0,d2,d1,d3], materialised (splitting / merging attention heads)."""
+    _f32(a, "a")
+    if a.dim() != 4:
+        raise exceptions.InvalidArgumentError("permute_0213 takes a rank-4 tensor")
+    d0, d1, d2, d3 = a.shape
+    out = torch.empty((d0, d2, d1, d3), dtype=torch.float32, device=a.device)
+    sess = get_session(a.device)
+    with torch.cuda.device(a.device):
+        check(lib.tfccb200_permute_0213_f32(sess.stream_ptr, a.data_ptr(), d0, d1, d2, d3,
+                                            out.data_ptr()))
+    return out
+
+
+def transpose_last2(a: torch.Tensor) -> torch.Tensor:
+    """[..., r, c] -> [..., c, r], materialised (K transposed for Q.K^T)."""
+    _f32(a, "a")
+    if a.dim() < 2:
+        raise exceptions.InvalidArgumentError("transpose_last2 needs rank >= 2")
+    r, c = a.shape[-2], a.shape[-1]
+    out = torch.empty(tuple(a.shape[:-2]) + (c, r), dtype=torch.float32, device=a.device)
+    sess = get_session(a.device)
+    with torch.cuda.device(a.device):
+        check(lib.tfccb200_transpose_last2_f32(sess.stream_ptr, a.data_ptr(), a.numel() // (r * c),
+                                               r, c, out.data_ptr()))
+    return out

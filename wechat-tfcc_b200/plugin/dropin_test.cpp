@@ -210,6 +210,73 @@ int main() {
       expect(ok, "requantize known answers");
     }
 
+    // the glue operators of an attention block through the reference's operator layer:
+    // tfcc::base::transpose, tfcc::math::softmax, tfcc::math::gelu_accurate,
+    // tfcc::nn::layer_normalization
+    {
+      std::uniform_real_distribution<float> u(-2.f, 2.f);
+      const unsigned B = 2, H = 3, S = 20, D = 16;
+      std::vector<float> hx(B * S * H * D);
+      for (auto& v : hx) v = u(rng);
+      tfcc::Variable<float> x({B, S, H, D});
+      tfcc::data::set(x, hx);
+      std::vector<float> t1 = tfcc::data::get(tfcc::base::transpose(x, {0, 2, 1, 3}));
+      bool ok = true;
+      for (unsigned b = 0; b < B; ++b)
+        for (unsigned s = 0; s < S; ++s)
+          for (unsigned h = 0; h < H; ++h)
+            for (unsigned d = 0; d < D; ++d)
+              ok = ok && t1[((b * H + h) * S + s) * D + d] == hx[((b * S + s) * H + h) * D + d];
+      expect(ok, "transpose perm (0,2,1,3)");
+      std::vector<float> t2 = tfcc::data::get(tfcc::base::transpose(x, {0, 1, 3, 2}));
+      ok = true;
+      for (unsigned o = 0; o < B * S; ++o)
+        for (unsigned h = 0; h < H; ++h)
+          for (unsigned d = 0; d < D; ++d)
+            ok = ok && t2[(o * D + d) * H + h] == hx[(o * H + h) * D + d];
+      expect(ok, "transpose of the last two axes");
+
+      tfcc::Variable<float> m({7, 33});
+      std::vector<float> hm(7 * 33);
+      for (auto& v : hm) v = u(rng);
+      tfcc::data::set(m, hm);
+      std::vector<float> sm = tfcc::data::get(tfcc::math::softmax(m, 1));
+      std::vector<float> ge = tfcc::data::get(tfcc::math::gelu_accurate(m));
+      std::vector<float> sm_want(hm.size()), ge_want(hm.size());
+      for (unsigned r = 0; r < 7; ++r) {
+        float mx = hm[r * 33];
+        for (unsigned c = 1; c < 33; ++c) mx = std::max(mx, hm[r * 33 + c]);
+        double sum = 0;
+        for (unsigned c = 0; c < 33; ++c) sum += std::exp(static_cast<double>(hm[r * 33 + c]) - mx);
+        for (unsigned c = 0; c < 33; ++c)
+          sm_want[r * 33 + c] = static_cast<float>(std::exp(static_cast<double>(hm[r * 33 + c]) - mx) / sum);
+      }
+      for (size_t i = 0; i < hm.size(); ++i)
+        ge_want[i] = static_cast<float>(0.5 * hm[i] * (1.0 + std::erf(hm[i] / std::sqrt(2.0))));
+      expect(close_enough(sm, sm_want, true), "softmax over the last axis");
+      expect(close_enough(ge, ge_want, true), "gelu_accurate");
+
+      tfcc::Variable<float> gamma({33}), beta({33});
+      std::vector<float> hg(33), hb(33);
+      for (auto& v : hg) v = 1.f + 0.25f * u(rng);
+      for (auto& v : hb) v = 0.1f * u(rng);
+      tfcc::data::set(gamma, hg);
+      tfcc::data::set(beta, hb);
+      std::vector<float> ln = tfcc::data::get(tfcc::nn::layer_normalization(m, gamma, beta, 1e-5f, 1));
+      std::vector<float> ln_want(hm.size());
+      for (unsigned r = 0; r < 7; ++r) {
+        double mean = 0, var = 0;
+        for (unsigned c = 0; c < 33; ++c) mean += hm[r * 33 + c];
+        mean /= 33;
+        for (unsigned c = 0; c < 33; ++c) var += (hm[r * 33 + c] - mean) * (hm[r * 33 + c] - mean);
+        var /= 33;
+        for (unsigned c = 0; c < 33; ++c)
+          ln_want[r * 33 + c] =
+              static_cast<float>((hm[r * 33 + c] - mean) / std::sqrt(var + 1e-5) * hg[c] + hb[c]);
+      }
+      expect(close_enough(ln, ln_want, true), "layer_normalization");
+    }
+
     // error behaviour comes from the reference's operator layer, unchanged
     bool threw = false;
     try {

@@ -391,8 +391,76 @@ template class B200QuantizationInterface<uint16_t>;
 template class B200QuantizationInterface<int32_t>;
 template class B200QuantizationInterface<uint32_t>;
 
+// ---------------------------------------------------------------- attention / FFN glue (float)
+Variable<float> B200ActivationInterface::softmax(const Tensor<float>& a, size_t axis) {
+  if (a.size() == 0) throw InvalidArgumentError("invalid tensor");
+  if (axis + 1 != a.shape().size()) throw NotImplementedError();  // last axis only
+  const unsigned cols = a.shape(axis);
+  Variable<float> result(a.shape());
+  check_status(tfccb200_softmax_f32(current_session()->stream(), a.data(), a.size() / cols, cols,
+                                    1.0f, result.data()));
+  return result;
+}
+
+Variable<float> B200ActivationInterface::geluAccurate(const Tensor<float>& a) {
+  if (a.size() == 0) throw InvalidArgumentError("invalid tensor");
+  Variable<float> result(a.shape());
+  check_status(tfccb200_gelu_f32(current_session()->stream(), a.data(), a.size(), result.data()));
+  return result;
+}
+
+Variable<float> B200NormalizationInterface::layerNormalize(const Tensor<float>& a,
+                                                           const Tensor<float>& gamma,
+                                                           const Tensor<float>& beta,
+                                                           float epsilon, size_t beginNormAxis) {
+  if (a.size() == 0 || beginNormAxis >= a.shape().size())
+    throw InvalidArgumentError("invalid tensor or axis");
+  unsigned cols = 1;
+  for (size_t i = beginNormAxis; i < a.shape().size(); ++i) cols *= a.shape(i);
+  if (gamma.size() != cols || beta.size() != cols)
+    throw InvalidArgumentError("gamma or beta don't match the normalized axes");
+  Variable<float> result(a.shape());
+  check_status(tfccb200_layer_norm_f32(current_session()->stream(), a.data(), nullptr, gamma.data(),
+                                       beta.data(), epsilon, a.size() / cols, cols, result.data()));
+  return result;
+}
+
+Variable<float> B200BasicInterface::transpose(const Tensor<float>& a,
+                                              const std::vector<size_t>& perm) {
+  const size_t rank = a.shape().size();
+  std::vector<unsigned> s(rank);
+  for (size_t i = 0; i < rank; ++i) s[i] = a.shape(perm[i]);
+  bool swap_last2 = rank >= 2 && perm[rank - 1] == rank - 2 && perm[rank - 2] == rank - 1;
+  for (size_t i = 0; swap_last2 && i + 2 < rank; ++i) swap_last2 = perm[i] == i;
+  const bool is0213 =
+      rank == 4 && perm[0] == 0 && perm[1] == 2 && perm[2] == 1 && perm[3] == 3;
+  if (!swap_last2 && !is0213) throw NotImplementedError();
+  Variable<float> result{Shape(s)};
+  void* stream = current_session()->stream();
+  if (swap_last2) {
+    const unsigned r = a.shape(rank - 2), c = a.shape(rank - 1);
+    check_status(tfccb200_transpose_last2_f32(stream, a.data(), a.size() / (r * c), r, c,
+                                              result.data()));
+  } else {
+    check_status(tfccb200_permute_0213_f32(stream, a.data(), a.shape(0), a.shape(1), a.shape(2),
+                                           a.shape(3), result.data()));
+  }
+  return result;
+}
+
 // ---------------------------------------------------------------- registration
 namespace {
+template <class T>
+void set_float_glue_interfaces(Interface<T>&) {}
+template <>
+void set_float_glue_interfaces<float>(Interface<float>& interface) {
+  interface.setActivationInterface(
+      std::unique_ptr<ActivationInterface<float>>(new B200ActivationInterface()));
+  interface.setNormalizationInterface(
+      std::unique_ptr<NormalizationInterface<float>>(new B200NormalizationInterface()));
+  interface.setBasicInterface(std::unique_ptr<BasicInterface<float>>(new B200BasicInterface()));
+}
+
 template <class T>
 void set_quantization_interface(Interface<T>&) {}  // only the six quantization types have one
 #define TFCC_B200_SET_QUANTIZATION(type)                                          \
@@ -416,6 +484,7 @@ Interface<T> get_b200_interface(T, B200Device&) {
   interface.setBlasInterface(std::unique_ptr<BlasInterface<T>>(new B200BlasInterface<T>()));
   interface.setDataInterface(std::unique_ptr<DataInterface<T>>(new B200DataInterface<T>()));
   set_quantization_interface<T>(interface);
+  set_float_glue_interfaces<T>(interface);
   return interface;
 }
 

@@ -27,7 +27,10 @@
 #include "tfcc.h"
 #include "interfaces/tfcc_blasinterface.h"
 #include "interfaces/tfcc_datainterface.h"
+#include "interfaces/tfcc_activationinterface.h"
+#include "interfaces/tfcc_basicinterface.h"
 #include "interfaces/tfcc_interface.h"
+#include "interfaces/tfcc_normalizationinterface.h"
 #include "interfaces/tfcc_quantizationinterface.h"
 #include "utils/tfcc_initializer.h"
 
@@ -138,6 +141,30 @@ class B200QuantizationInterface : public QuantizationInterface<T> {
                          const Tensor<float>& maxOutput) override;
   Variable<float> dequantize(const Tensor<T>& a, const Tensor<float>& minValue,
                              const Tensor<float>& maxValue) override;
+};
+
+// The operators between the matmuls of an attention / feed-forward block, float only and only
+// the cases such a block uses; everything else keeps the core's NotImplementedError default.
+//   softmax over the last axis, geluAccurate     (tfcc/core/interfaces/tfcc_activationinterface.h:38,45)
+//   layerNormalize                               (tfcc/core/interfaces/tfcc_normalizationinterface.h:39-41)
+//   transpose with perm (0,2,1,3) or "swap the last two axes"
+//                                                (tfcc/core/interfaces/tfcc_basicinterface.h:47)
+class B200ActivationInterface : public ActivationInterface<float> {
+ public:
+  Variable<float> softmax(const Tensor<float>& a, size_t axis) override;
+  Variable<float> geluAccurate(const Tensor<float>& a) override;
+};
+
+class B200NormalizationInterface : public NormalizationInterface<float> {
+ public:
+  Variable<float> layerNormalize(const Tensor<float>& a, const Tensor<float>& gamma,
+                                 const Tensor<float>& beta, float epsilon,
+                                 size_t beginNormAxis) override;
+};
+
+class B200BasicInterface : public BasicInterface<float> {
+ public:
+  Variable<float> transpose(const Tensor<float>& a, const std::vector<size_t>& perm) override;
 };
 
 template <class T>
