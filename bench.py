@@ -254,6 +254,25 @@ def profile_case(torch, pkg, dev, name):
         w = to(rng.normal(0, 0.02, (768, 3072)).astype(np.float32))
         b = to(np.zeros(3072, np.float32))
         fn = lambda: pkg.blas.matmul(x, w, b)
+    elif name == "encoder_stack":
+        shapes4 = [(768, 768)] * 4 + [(768, 3072), (3072, 768)]
+        w4 = [[t for (k, n) in shapes4 for t in (to(rng.normal(0, 0.02, (k, n)).astype(np.float32)),
+                                                 torch.zeros(n, device=dev))] for _ in range(4)]
+        x4 = to(rng.normal(0, 1, (8, 128, 768)).astype(np.float32))
+        g4, b4 = torch.ones(768, device=dev), torch.zeros(768, device=dev)
+        mm, nnops = pkg.blas.matmul, pkg.nn
+
+        def fn():
+            x = x4
+            split = lambda t: nnops.permute_0213(t.view(8, 128, 12, 64))
+            for (wq, bq, wk, bk, wv, bv, wo, bo, w1, b1, w2, b2) in w4:
+                q, k, v = split(mm(x, wq, bq)), split(mm(x, wk, bk)), split(mm(x, wv, bv))
+                p = nnops.softmax(mm(q, nnops.transpose_last2(k)), scale=0.125)
+                o = nnops.permute_0213(mm(p, v)).view(8, 128, 768)
+                x = nnops.layer_norm(mm(o, wo, bo), g4, b4, 1e-5, residual=x)
+                x = nnops.layer_norm(mm(mm(x, w1, b1, activation="gelu"), w2, b2), g4, b4, 1e-5,
+                                     residual=x)
+            return x
     else:
         raise SystemExit(f"unknown --profile-case {name}")
     for _ in range(5):
