@@ -133,6 +133,14 @@ UmmaPlan umma_plan(unsigned M, unsigned N, unsigned batch, int sm_count, int ele
       // a CTA stages BN (BN/2 in a pair) columns of B: 128 bytes at least
       if ((pair ? bn / 2 : bn) * elem_bytes < 128) continue;
       if (bn > 64 && static_cast<unsigned>(bn) >= 2 * N) continue;  // mostly padding
+      if (pair && force_pair < 0) {
+        // Measured: CTA pairs only win with full-width tiles and enough of them to occupy
+        // most pairs; on smaller problems the extra cluster hops per k-block cost more than
+        // the halved B traffic saves (1024x768x768: 32 us in pairs, 23 us single).
+        const unsigned long long tiles = static_cast<unsigned long long>((M + 255) / 256) *
+                                         ((N + bn - 1) / bn) * batch;
+        if (bn != 256 || tiles * 5 < static_cast<unsigned long long>(groups) * 3) continue;
+      }
       const double penalty = (bn == 256 ? 1.0 : bn == 128 ? 1.25 : 1.6) * (pair ? 0.85 : 1.0);
       const double c = tile_cost(M, N, batch, tile_m, bn, groups, penalty);
       if (best.bn == 0 || c < best_cost) {
