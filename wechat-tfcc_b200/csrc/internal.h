@@ -64,9 +64,10 @@ struct QgemmArgs {
 struct UmmaPlan {
   bool pair;
   int bn;
+  unsigned cluster_k;  // > 1: K of one tile is shared by a cluster of that many single CTAs
 };
-UmmaPlan umma_plan(unsigned M, unsigned N, unsigned batch, int sm_count, int elem_bytes,
-                   int force_pair);
+UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count,
+                   int elem_bytes, int force_pair, bool allow_cluster_k);
 bool umma_sgemm_supported(const SgemmArgs& a);
 int umma_sgemm(const SgemmArgs& a, bool pair);
 bool umma_qgemm_supported(const QgemmArgs& a);

@@ -75,6 +75,11 @@ struct UmmaGemmParams {
                            // the tensor core narrows fp32), 0 = feed the raw fp32 as head
   unsigned kb_per_chunk;   // kSplit: k-blocks accumulated inside tensor memory before the
                            // partial sum is promoted to registers (>= 1)
+  unsigned cluster_k;      // kSplit, one CTA per tile only: >= 1.  With k > 1 a cluster of k CTAs
+                           // shares one tile, each CTA taking a contiguous range of k-blocks;
+                           // ranks 1.. hand their fp32 partial sums to rank 0 through its
+                           // shared memory and rank 0 adds them in rank order (deterministic)
+                           // before the store.  The grid must hold every tile at once.
   int* status;             // device int or nullptr
   unsigned long long timeout_ns;
 };
@@ -258,10 +263,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t cta_rank = (kCtaGroup == 2) ? ptx::cluster_ctarank() : 0u;
   const bool is_leader = (cta_rank == 0);
-  const unsigned num_groups = gridDim.x / kCtaGroup;        // CTAs (or pairs) walking the tiles
-  const unsigned group_id = blockIdx.x / kCtaGroup;
+  // K split over a cluster (see UmmaGemmParams::cluster_k)
+  const unsigned ksplit = (kSplit && kCtaGroup == 1 && p.cluster_k > 1) ? p.cluster_k : 1u;
+  const unsigned krank = ksplit > 1 ? ptx::cluster_ctarank() : 0u;
+  const bool in_cluster = (kCtaGroup == 2) || ksplit > 1;
+  const unsigned num_groups = gridDim.x / (kCtaGroup * ksplit);  // CTAs / pairs / clusters walking the tiles
+  const unsigned group_id = blockIdx.x / (kCtaGroup * ksplit);
   const unsigned total_tiles = p.batch * p.tiles_m * p.tiles_n;
   const unsigned num_kb = (p.K + Cfg::kBK - 1) / Cfg::kBK;
+  const unsigned kb_per_rank = (num_kb + ksplit - 1) / ksplit;
+  const unsigned kb_lo = krank * kb_per_rank;                  // this CTA's k-blocks: [kb_lo, kb_hi)
+  const unsigned kb_hi = min(num_kb, kb_lo + kb_per_rank);
+  const uint32_t red_free = bar_base + 8u * (3 * kStages + 5);   // rank 0 -> others: buffer usable
+  const uint32_t red_ready = bar_base + 8u * (3 * kStages + 6);  // others -> rank 0: partials written
 
   UmmaCtl ctl{abort_flag, p.status, p.timeout_ns};
 
@@ -275,6 +289,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       ptx::mbar_init(tmem_full(a), 1);
       ptx::mbar_init(tmem_empty(a), Cfg::kNumEpilogueWarps * kCtaGroup);
     }
+    ptx::mbar_init(red_free, 1);
+    ptx::mbar_init(red_ready, ksplit > 1 ? (ksplit - 1) * Cfg::kNumEpilogueWarps * 32 : 1);
     *abort_flag = 0;
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmapA);
@@ -286,7 +302,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if constexpr (kCtaGroup == 2) {  // peer barriers must exist before anyone signals them
+  if (in_cluster) {  // peer barriers must exist before anyone signals them
     ptx::cluster_arrive();
     ptx::cluster_wait();
   }
@@ -312,7 +328,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         const int n0 = static_cast<int>(tn * BN + cta_rank * Cfg::kBNLocal);
         const int ba = p.a_batched ? static_cast<int>(b) : 0;
         const int bb = p.b_batched ? static_cast<int>(b) : 0;
-        for (unsigned kb = 0; kb < num_kb; ++kb) {
+        for (unsigned kb = kb_lo; kb < kb_hi; ++kb) {
           bounded_wait<false>(empty_bar(s), ph ^ 1u, TFCCB200_DEV_TIMEOUT_TMA, ctl);
           const uint32_t stage = smem_base + s * Cfg::kStageBytes;
           const int k0 = static_cast<int>(kb * Cfg::kBK);
@@ -347,14 +363,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       unsigned it = 0;  // accumulator hand-offs so far (tiles, or chunks when kSplit)
       const uint16_t pair_mask = 0x3;
       for (unsigned t = group_id; t < total_tiles; t += num_groups) {
-        for (unsigned kb0 = 0; kb0 < num_kb; kb0 += kb_per_chunk, ++it) {
+        for (unsigned kb0 = kb_lo; kb0 < kb_hi; kb0 += kb_per_chunk, ++it) {
           const unsigned acc = it & 1u;
           const uint32_t acc_ph = (it >> 1) & 1u;
           bounded_wait<(kCtaGroup == 2)>(tmem_empty(acc), acc_ph ^ 1u, TFCCB200_DEV_TIMEOUT_MMA,
                                          ctl);
           ptx::tc_fence_after_sync();
           const uint32_t d_tmem = tmem_base + acc * BN;
-          const unsigned kb_end = min(num_kb, kb0 + kb_per_chunk);
+          const unsigned kb_end = min(kb_hi, kb0 + kb_per_chunk);
           for (unsigned kb = kb0; kb < kb_end; ++kb) {
             if constexpr (kSplit) {
               bounded_wait<(kCtaGroup == 2)>(full_cvt(s), ph, TFCCB200_DEV_TIMEOUT_MMA, ctl);
@@ -432,7 +448,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         float sum[Cfg::kEpiCols];
 #pragma unroll
         for (int j = 0; j < Cfg::kEpiCols; ++j) sum[j] = 0.f;
-        for (unsigned kb0 = 0; kb0 < num_kb; kb0 += kb_per_chunk, ++it) {
+        for (unsigned kb0 = kb_lo; kb0 < kb_hi; kb0 += kb_per_chunk, ++it) {
           const unsigned acc = it & 1u;
           const uint32_t acc_ph = (it >> 1) & 1u;
           bounded_wait<false>(tmem_full(acc), acc_ph, TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
@@ -447,6 +463,38 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             for (int j = 0; j < 16; ++j) sum[c * 16 + j] += __uint_as_float(r[j]);
           }
           release_acc(acc);
+        }
+        if (ksplit > 1) {
+          // ---- K split over the cluster: partial sums meet in rank 0's (now idle) stage
+          // buffers, laid out [rank-1][warp][4-column group][lane] so that every access is a
+          // conflict-free 128-bit one.  Rank 0's last tmem_full above means all its MMAs have
+          // retired, so its stages are dead and may be overwritten.
+          const unsigned ew = warp - Cfg::kFirstEpilogueWarp;
+          constexpr int kVec = Cfg::kEpiCols / 4;
+          if (krank == 0) {
+            if (ew == 0 && lane == 0)
+              for (unsigned r = 1; r < ksplit; ++r) ptx::mbar_arrive_cluster(ptx::mapa(red_free, r));
+            bounded_wait<true>(red_ready, 0u, TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
+            const float4* red = reinterpret_cast<const float4*>(smem_gen);
+            for (unsigned r = 1; r < ksplit; ++r) {  // fixed order: rank 1, 2, ...
+#pragma unroll
+              for (int v = 0; v < kVec; ++v) {
+                const float4 t = red[(((r - 1) * Cfg::kNumEpilogueWarps + ew) * kVec + v) * 32 + lane];
+                sum[4 * v + 0] += t.x; sum[4 * v + 1] += t.y;
+                sum[4 * v + 2] += t.z; sum[4 * v + 3] += t.w;
+              }
+            }
+          } else {
+            bounded_wait<true>(red_free, 0u, TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
+            const uint32_t remote = ptx::mapa(smem_base, 0);
+#pragma unroll
+            for (int v = 0; v < kVec; ++v)
+              ptx::st_shared_cluster_v4(
+                  remote + 16u * ((((krank - 1) * Cfg::kNumEpilogueWarps + ew) * kVec + v) * 32 + lane),
+                  make_float4(sum[4 * v], sum[4 * v + 1], sum[4 * v + 2], sum[4 * v + 3]));
+            ptx::mbar_arrive_cluster(ptx::mapa(red_ready, 0));  // every lane: releases its own stores
+            continue;  // rank 0 stores the tile
+          }
         }
 #pragma unroll
         for (int c = 0; c < Cfg::kEpiCols / 32; ++c) {
@@ -535,7 +583,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       int s = 0;
       uint32_t ph = 0;
       for (unsigned t = group_id; t < total_tiles; t += num_groups) {
-        for (unsigned kb = 0; kb < num_kb; ++kb) {
+        for (unsigned kb = kb_lo; kb < kb_hi; ++kb) {
           bounded_wait<false>(full_raw(s), ph, TFCCB200_DEV_TIMEOUT_CONVERT, ctl);
           float4* raw = reinterpret_cast<float4*>(smem_gen + s * Cfg::kStageBytes);
           float4* tail = reinterpret_cast<float4*>(smem_gen + s * Cfg::kStageBytes + Cfg::kRawBytes);
@@ -585,7 +633,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     const uint64_t t0 = ptx::globaltimer_ns();
     while (ptx::globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
   }
-  if constexpr (kCtaGroup == 2) {
+  if (in_cluster) {
     ptx::cluster_arrive();
     ptx::cluster_wait();
   }

@@ -79,6 +79,18 @@ int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, Um
   if (total == 0 || total > 0x7fffffffull) return TFCCB200_EOVERFLOW;
   unsigned groups = static_cast<unsigned>(sm_count / kCtaGroup);
   if (total < groups) groups = static_cast<unsigned>(total);
+  unsigned cluster = kCtaGroup;
+  if (p.cluster_k > 1) {
+    // K split over a cluster: one tile per cluster, all tiles resident at once
+    if (!kSplit || kCtaGroup != 1 || total * p.cluster_k > static_cast<unsigned>(sm_count))
+      return TFCCB200_EUNSUPPORTED;
+    if ((p.cluster_k - 1) * 128u * BN * 4u > static_cast<unsigned>(kStages * Cfg::kStageBytes))
+      return TFCCB200_EUNSUPPORTED;  // partial tiles would not fit rank 0's stage buffers
+    groups = static_cast<unsigned>(total) * p.cluster_k;
+    cluster = p.cluster_k;
+  } else {
+    p.cluster_k = 1;
+  }
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(groups * kCtaGroup, 1, 1);
@@ -87,7 +99,7 @@ int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, Um
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = kCtaGroup;
+  attr[0].val.clusterDim.x = cluster;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
@@ -98,17 +110,69 @@ int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, Um
   return TFCCB200_OK;
 }
 
-// Tile choice.  A tile row-block costs time proportional to its width BN, with a penalty
-// for narrow tiles (their A operand is re-read from shared memory more often per flop) and
-// a bonus for CTA pairs (each CTA stages only half of B); the grid runs in waves of `groups`
-// tiles.  The cheapest (waves x width x penalty) wins.
-double tile_cost(unsigned M, unsigned N, unsigned batch, int tile_m, int bn, int groups,
-                 double penalty) {
-  const unsigned long long tiles =
-      static_cast<unsigned long long>((M + tile_m - 1) / tile_m) * ((N + bn - 1) / bn) * batch;
-  const unsigned long long waves = (tiles + groups - 1) / groups;
-  return static_cast<double>(waves) * bn * penalty;
+// How many clusters of `ks` single CTAs of the fp32 kernel the device holds at once.  The SMs
+// of a cluster must share a GPC, so this is not sm_count / ks (a cluster of 3 fits 48 times in
+// 148 SMs by count, yet fewer are co-resident and the grid then runs in two waves).
+template <int BN, int kStages>
+int query_active_clusters(unsigned ks) {
+  using Cfg = UmmaGemmConfig<ptx::MmaKind::TF32, true, 1, BN, kStages>;
+  auto kernel = umma_gemm_kernel<ptx::MmaKind::TF32, true, 1, BN, kStages>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           Cfg::kSmemBytes) != cudaSuccess)
+    return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ks * 64, 1, 1);
+  cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = ks;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return n;
 }
+
+// Cached per device, tile width and cluster size; 0 = not available.
+int active_clusters_fp32(int bn, unsigned ks) {
+  if (ks < 2 || ks > 4) return 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  static std::atomic<int> cache[64][3][5];  // value + 1; 0 = not queried yet
+  const int w = bn == 256 ? 0 : (bn == 128 ? 1 : 2);
+  std::atomic<int>& slot = cache[dev & 63][w][ks];
+  int v = slot.load(std::memory_order_acquire);
+  if (v == 0) {
+    const int n = bn == 256 ? query_active_clusters<256, 2>(ks)
+                            : (bn == 128 ? query_active_clusters<128, 3>(ks)
+                                         : query_active_clusters<64, 4>(ks));
+    v = n + 1;
+    slot.store(v, std::memory_order_release);
+  }
+  return v - 1;
+}
+
+// Time model behind the tile choice, in microseconds, fitted to measurements on B200
+// (graph-replayed launches over rotating operands).  A CTA spends a fixed cost (launch,
+// prologue, first loads, and an epilogue that grows with the tile width) plus its k-blocks times
+// a per-k-block cost that is the larger of the MMA time of the tile and the pipeline round trip
+// divided by the stages that fit.  The grid runs in waves.  A K split over a cluster adds the
+// hand-off of (ks - 1) partial tiles to rank 0 and their summation.
+double per_kblock_us(bool pair, int bn) {
+  if (pair) return bn == 256 ? 1.24 : (bn == 128 ? 0.95 : 0.9);
+  return bn == 256 ? 1.48 : (bn == 128 ? 0.81 : 0.70);
+}
+double fixed_us(bool pair, int bn) {
+  if (pair) return 11.0;
+  return bn == 256 ? 12.5 : 3.8 + 0.042 * bn;
+}
+double cluster_k_us(unsigned ks, int bn) { return ks > 1 ? 1.2 + 0.8 * (ks - 1) + 0.018 * bn : 0.0; }
 
 int env_int(const char* name, int fallback) {
   const char* v = std::getenv(name);
@@ -119,41 +183,59 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 }  // namespace
 
-UmmaPlan umma_plan(unsigned M, unsigned N, unsigned batch, int sm_count, int elem_bytes,
-                   int force_pair) {
-  UmmaPlan best = {false, 0};
-  double best_cost = 0;
+UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count,
+                   int elem_bytes, int force_pair, bool allow_cluster_k) {
+  UmmaPlan best = {false, 0, 1};
+  double best_time = 0;
+  const unsigned num_kb = (K + 128 / elem_bytes - 1) / (128 / elem_bytes);
   for (int pair = 0; pair <= 1; ++pair) {
     if (force_pair >= 0 && pair != force_pair) continue;
     const int tile_m = pair ? 256 : 128;
     const int groups = pair ? sm_count / 2 : sm_count;
     if (groups < 1) continue;
-    if (pair && M <= 128 && force_pair < 0) continue;  // a second CTA would only hold padding
     for (int bn : {256, 128, 64}) {
       // a CTA stages BN (BN/2 in a pair) columns of B: 128 bytes at least
       if ((pair ? bn / 2 : bn) * elem_bytes < 128) continue;
       if (bn > 64 && static_cast<unsigned>(bn) >= 2 * N) continue;  // mostly padding
+      const unsigned long long tiles = static_cast<unsigned long long>((M + tile_m - 1) / tile_m) *
+                                       ((N + bn - 1) / bn) * batch;
       if (pair && force_pair < 0) {
         // Measured: CTA pairs only win with full-width tiles and enough of them to occupy
         // most pairs; on smaller problems the extra cluster hops per k-block cost more than
         // the halved B traffic saves (1024x768x768: 32 us in pairs, 23 us single).
-        const unsigned long long tiles = static_cast<unsigned long long>((M + 255) / 256) *
-                                         ((N + bn - 1) / bn) * batch;
         if (bn != 256 || tiles * 5 < static_cast<unsigned long long>(groups) * 3) continue;
       }
-      const double penalty = (bn == 256 ? 1.0 : bn == 128 ? 1.25 : 1.6) * (pair ? 0.85 : 1.0);
-      const double c = tile_cost(M, N, batch, tile_m, bn, groups, penalty);
-      if (best.bn == 0 || c < best_cost) {
-        best_cost = c;
-        best.pair = pair != 0;
-        best.bn = bn;
+      for (unsigned ks = 1; ks <= 4; ++ks) {
+        if (ks > 1) {
+          // K split over a cluster of single CTAs: one co-resident cluster per tile,
+          // >= 4 k-blocks per rank
+          if (!allow_cluster_k || pair) break;
+          if (tiles > static_cast<unsigned long long>(active_clusters_fp32(bn, ks))) continue;
+          const unsigned per = (num_kb + ks - 1) / ks;
+          if (per < 4 || (num_kb + per - 1) / per != ks) continue;  // no empty rank
+          // the other ranks' partial tiles (128 x bn fp32 each) must fit rank 0's stage buffers
+          if ((ks - 1) * 128u * bn * 4u > 192u * 1024u) continue;
+        }
+        const unsigned long long units = tiles * ks;
+        const unsigned long long waves = (units + groups - 1) / groups;
+        const double kb = static_cast<double>((num_kb + ks - 1) / ks);
+        const double t = static_cast<double>(waves) *
+                             (fixed_us(pair != 0, bn) + kb * per_kblock_us(pair != 0, bn)) +
+                         cluster_k_us(ks, bn);
+        if (best.bn == 0 || t < best_time) {
+          best_time = t;
+          best.pair = pair != 0;
+          best.bn = bn;
+          best.cluster_k = ks;
+        }
       }
     }
   }
-  if (best.bn == 0) {  // nothing admissible (e.g. int8 with tiny N): widest legal tile
+  if (best.bn == 0) {  // nothing admissible (e.g. tiny N): widest legal tile
     best.pair = force_pair == 1;
     best.bn = (best.pair ? 256 : 128) / elem_bytes;
     if (best.bn < 64) best.bn = 64;
+    best.cluster_k = 1;
   }
   return best;
 }
@@ -189,8 +271,17 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
 
   const bool a_batched = a.batch > 1 && a.strideA != 0;
   const bool b_batched = a.batch > 1 && a.strideB != 0;
-  const int bn = umma_plan(a.M, a.N, a.batch, di->sm_count,
-                           a.precision == TFCCB200_PRECISION_BF16 ? 2 : 4, pair ? 1 : 0).bn;
+  static const int env_cluster_k = env_int("TFCCB200_CLUSTER_K", -1);  // -1: planned; 1: off
+  const bool fp32_split = a.precision == TFCCB200_PRECISION_FP32;
+  const UmmaPlan plan =
+      umma_plan(a.M, a.N, a.K, a.batch, di->sm_count,
+                a.precision == TFCCB200_PRECISION_BF16 ? 2 : 4, pair ? 1 : 0,
+                fp32_split && !pair && env_cluster_k != 1);
+  UmmaPlan tuned = plan;
+  static const int env_bn = env_int("TFCCB200_FORCE_BN", 0);  // tuning knobs, read once
+  if (env_bn == 64 || env_bn == 128 || env_bn == 256) tuned.bn = env_bn;
+  if (env_cluster_k > 1) tuned.cluster_k = static_cast<unsigned>(env_cluster_k);
+  const int bn = tuned.bn;
 
   if (a.precision == TFCCB200_PRECISION_BF16) {
     // Opt-in low precision: a pre-pass rounds both operands to bfloat16 in the caller's
@@ -271,6 +362,7 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
   static const int env_kb_per_chunk = env_int("TFCCB200_KB_PER_CHUNK", 4);
   p.write_head = env_write_head ? 1 : 0;
   p.kb_per_chunk = env_kb_per_chunk > 0 ? env_kb_per_chunk : 4;
+  p.cluster_k = (fp32_split && !pair) ? tuned.cluster_k : 1;
   p.status = a.status;
   p.timeout_ns = kDefaultTimeoutNs;
 
@@ -319,7 +411,7 @@ int umma_qgemm(const QgemmArgs& a, bool pair) {
 
   const bool a_batched = a.batch > 1 && a.strideA != 0;
   const bool b_batched = a.batch > 1 && a.strideB != 0;
-  const int bn = umma_plan(a.M, a.N, a.batch, di->sm_count, 1, pair ? 1 : 0).bn;
+  const int bn = umma_plan(a.M, a.N, a.K, a.batch, di->sm_count, 1, pair ? 1 : 0, false).bn;
 
   CUtensorMap ta, tb;
   if (!make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.A, a.K, a.M, a_batched ? a.batch : 1,
