@@ -100,7 +100,9 @@ TFCCB200_API int tfccb200_sgemm_ex(void* stream, const float* A, unsigned stride
                       unsigned N, unsigned K, unsigned batch, int precision_mode, int path,
                       void* workspace, size_t workspace_bytes, int* device_status);
 
-/* Scratch bytes tfccb200_sgemm needs for this problem on the current device. */
+/* Scratch bytes tfccb200_sgemm wants for this problem on the current device.  The M <= 8
+ * streaming kernel and the bf16 mode cannot run without theirs; the fp32 tensor-core kernel
+ * runs without but uses its share (partial tiles of a ragged last wave) when given. */
 TFCCB200_API size_t tfccb200_sgemm_workspace(unsigned M, unsigned N, unsigned K, unsigned batch,
                                 int precision_mode);
 
@@ -289,12 +291,16 @@ TFCCB200_API size_t tfccb200_sgemm_skinny_static_capacity(void);
  * still being multiplied; no TMA or multicast instruction touches peer memory.  When the
  * kernel has finished on every rank (the caller runs a cross-rank barrier after it), each
  * rank holds the complete C.  Needs K % 4 == 0, N_shard % 4 == 0, 16-byte aligned bases.
+ * `workspace` (256-byte aligned, tfccb200_sgemm_workspace(M, N_shard, K, 1, mode) bytes, may be
+ * NULL) lets the kernel share the tiles of a ragged last wave by k-block; the result is
+ * the same bit for bit with or without it.
  * No counterpart in the reference, which has no multi-device operator.
  */
 TFCCB200_API int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shard,
                                             float* const* C_ranks, unsigned num_ranks,
                                             unsigned rank, const float* bias_shard, unsigned M,
                                             unsigned N_shard, unsigned K, int precision_mode,
+                                            void* workspace, size_t workspace_bytes,
                                             int* device_status);
 
 /*

@@ -230,7 +230,7 @@ def test_nsplit_push_entry_point_on_one_gpu(pkg, orc):
         tb = torch.from_numpy(np.ascontiguousarray(b[:, r * ns:(r + 1) * ns])).to(d)
         tbias = torch.from_numpy(np.ascontiguousarray(bias[r * ns:(r + 1) * ns])).to(d)
         st = pkg.lib.tfccb200_sgemm_nsplit_push(stream, ta.data_ptr(), tb.data_ptr(), ptrs, g, r,
-                                                tbias.data_ptr(), m, ns, k, 0, None)
+                                                tbias.data_ptr(), m, ns, k, 0, None, 0, None)
         assert st == 0, pkg.lib.tfccb200_strerror(st)
         torch.cuda.synchronize()
     truth = orc.blas_matmul(a, b, bias)
@@ -239,7 +239,60 @@ def test_nsplit_push_entry_point_on_one_gpu(pkg, orc):
     assert torch.equal(outs[0], outs[1])
     # misaligned shard width is refused
     assert pkg.lib.tfccb200_sgemm_nsplit_push(stream, ta.data_ptr(), ta.data_ptr(), ptrs, g, 0, None,
-                                              m, 130, k, 0, None) == -2
+                                              m, 130, k, 0, None, 0, None) == -2
+
+
+def _sgemm_raw(pkg, a, b, bias, path, workspace):
+    """tfccb200_sgemm_ex on device tensors, with or without scratch."""
+    d = a.device
+    batch = a.shape[0] if a.dim() == 3 else 1
+    m, k, n = a.shape[-2], a.shape[-1], b.shape[-1]
+    out = torch.empty((batch, m, n) if a.dim() == 3 else (m, n), dtype=torch.float32, device=d)
+    ws = None
+    if workspace:
+        nbytes = pkg.lib.tfccb200_sgemm_workspace(m, n, k, batch, 0)
+        assert nbytes > 0
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=d)
+    st = pkg.lib.tfccb200_sgemm_ex(
+        torch.cuda.current_stream(d).cuda_stream, a.data_ptr(), m * k if a.dim() == 3 else 0,
+        b.data_ptr(), k * n if b.dim() == 3 else 0, out.data_ptr(), m * n,
+        bias.data_ptr() if bias is not None else None, m, n, k, batch, 0, pkg._lib.PATHS[path],
+        ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, None)
+    assert st == 0, pkg.lib.tfccb200_strerror(st)
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("path,m,n,k,batch", [
+    ("umma2", 4096, 4096, 1024, 1),   # 256 pair tiles on 74 pairs: 3.46 waves
+    ("umma", 1024, 3072, 768, 1),     # 192 tiles on 148 CTAs: 1.3 waves
+    ("umma", 2176, 2304, 512, 1),     # ragged edge tiles
+    ("umma", 256, 256, 384, 40),      # batched
+    ("umma2", 4096, 2048, 1000, 1),   # K not a whole number of chunks: falls back to tile order
+])
+def test_k_shared_last_wave_is_bit_identical(pkg, orc, path, m, n, k, batch):
+    """With scratch the fp32 tensor-core kernel shares the tiles of a ragged last wave by
+    k-block between CTAs; the cuts fall on accumulation-chunk boundaries and the finishing CTA
+    continues the running sums, so the result equals the tile-by-tile run bit for bit."""
+    d = dev_of()
+    g = torch.Generator(device=d)
+    g.manual_seed(m + n + k)
+    shape_a = (batch, m, k) if batch > 1 else (m, k)
+    shape_b = (batch, k, n) if batch > 1 else (k, n)
+    a = torch.empty(shape_a, dtype=torch.float32, device=d).uniform_(-1, 1, generator=g)
+    b = torch.empty(shape_b, dtype=torch.float32, device=d).uniform_(-1, 1, generator=g)
+    bias = torch.empty((n,), dtype=torch.float32, device=d).uniform_(-1, 1, generator=g)
+    plain = _sgemm_raw(pkg, a, b, bias, path, workspace=False)
+    shared = _sgemm_raw(pkg, a, b, bias, path, workspace=True)
+    again = _sgemm_raw(pkg, a, b, bias, path, workspace=True)
+    assert torch.equal(plain, shared)
+    assert torch.equal(shared, again)
+    rows = np.random.default_rng(0).choice(m, size=8, replace=False)
+    a0 = (a[0] if batch > 1 else a).cpu().numpy()
+    b0 = (b[0] if batch > 1 else b).cpu().numpy()
+    truth = a0[rows].astype(np.float64) @ b0.astype(np.float64) + bias.cpu().numpy().astype(np.float64)
+    got = (shared[0] if batch > 1 else shared)[torch.from_numpy(rows).to(d)].cpu().numpy()
+    assert orc.normwise_rel_error(got, truth) < TOL_FP32
 
 
 def _encoder_stack_f64(x, weights):

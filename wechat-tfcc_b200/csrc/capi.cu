@@ -282,9 +282,13 @@ size_t tfccb200_sgemm_workspace(unsigned M, unsigned N, unsigned K, unsigned bat
   cudaError_t e;
   const DeviceInfo* di = current_device_info(&e);
   const int sms = di ? di->sm_count : 148;
-  // Only the M <= 8 streaming kernel uses scratch (its per-slice partial sums).
-  // The bound covers both the batched and the batch-folded reading of the problem.
+  // The M <= 8 streaming kernel keeps its per-slice partial sums in scratch (the bound covers
+  // both the batched and the batch-folded reading of the problem); the fp32 tensor-core
+  // kernel keeps the partial tiles of a k-shared last wave there.
   size_t need = 0;
+  if (precision_mode == TFCCB200_PRECISION_FP32 &&
+      static_cast<unsigned long long>(M) * N * batch > static_cast<unsigned long long>(sms) * 128 * 64)
+    need = umma_stream_k_workspace(sms);
   if (precision_mode == TFCCB200_PRECISION_BF16)  // dense upper bound: both operands batched
     need = bf16_staging_bytes(M, N, K, batch, M * K, K * N);
   if (M <= 8) need = std::max(need, skinny_sgemm_workspace(M, N, K, batch, sms));
@@ -430,7 +434,8 @@ int tfccb200_requantize(void* stream, const void* src, int src_type, size_t n,
 int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shard,
                                float* const* C_ranks, unsigned num_ranks, unsigned rank,
                                const float* bias_shard, unsigned M, unsigned N_shard, unsigned K,
-                               int precision_mode, int* device_status) {
+                               int precision_mode, void* workspace, size_t workspace_bytes,
+                               int* device_status) {
   if (!A || !B_shard || !C_ranks || num_ranks == 0 || num_ranks > 8 || rank >= num_ranks)
     return TFCCB200_EINVAL;
   if (M == 0 || N_shard == 0 || K == 0) return TFCCB200_EINVAL;
@@ -446,6 +451,8 @@ int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shar
   a.strideC = 0;
   a.precision = precision_mode;
   a.status = device_status;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace ? workspace_bytes : 0;
   a.num_dst = num_ranks;
   for (unsigned d = 0; d < num_ranks; ++d) {
     if (!C_ranks[d] || (reinterpret_cast<uintptr_t>(C_ranks[d]) & 15u)) return TFCCB200_EALIGN;

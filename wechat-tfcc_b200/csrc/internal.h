@@ -68,6 +68,7 @@ struct UmmaPlan {
 };
 UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count,
                    int elem_bytes, int force_pair, bool allow_cluster_k);
+size_t umma_stream_k_workspace(int sm_count);  // scratch that lets umma_sgemm share tiles by k-block
 bool umma_sgemm_supported(const SgemmArgs& a);
 int umma_sgemm(const SgemmArgs& a, bool pair);
 bool umma_qgemm_supported(const QgemmArgs& a);

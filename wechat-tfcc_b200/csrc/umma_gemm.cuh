@@ -80,9 +80,31 @@ struct UmmaGemmParams {
                            // ranks 1.. hand their fp32 partial sums to rank 0 through its
                            // shared memory and rank 0 adds them in rank order (deterministic)
                            // before the store.  The grid must hold every tile at once.
+  // kSplit only, sk_tiles > 0: the first sk_tiles tiles (between one and two per CTA / pair)
+  // are shared out by k-block rather than by tile, so that a tile count that is not a
+  // multiple of the grid leaves no SM idle in the last wave.  Group g takes k-blocks
+  // [g, g+1) * sk_kb_per_group of those tiles laid end to end; a tile cut between groups g-1
+  // and g is begun by g-1, whose fp32 partial sums travel through sk_partials (one tile slot
+  // per CTA) guarded by sk_flags, and finished and stored by g.  The remaining tiles are
+  // walked tile by tile as usual.  Cuts fall on chunk boundaries and the finisher continues
+  // the running sum, so results are bit-identical to the unsplit order.
+  unsigned sk_tiles;
+  unsigned sk_kb_per_group;  // multiple of kb_per_chunk, >= k-blocks of one tile
+  float* sk_partials;        // [grid CTAs][128 x BN] fp32
+  unsigned* sk_flags;        // [grid CTAs], zero before the launch
+  unsigned long long sk_capacity;  // host only: bytes available behind sk_partials
   int* status;             // device int or nullptr
   unsigned long long timeout_ns;
 };
+
+// One stretch of k-blocks of one tile, as every role of a CTA walks them.
+struct UmmaSegment {
+  unsigned tile, kb_lo, kb_hi;
+  unsigned mode;  // 0: whole tile (or this rank's share of it); kSegHead; kSegTail
+};
+constexpr unsigned kSegHead = 1;  // k-blocks [0, kb_hi): partial sums go to the next group
+constexpr unsigned kSegTail = 2;  // k-blocks [kb_lo, end): continues the previous group's sums
+constexpr int kMaxSkSegments = 4;
 
 template <ptx::MmaKind kKind, bool kSplit, int kCtaGroup, int BN, int kStages>
 struct UmmaGemmConfig {
@@ -112,14 +134,14 @@ struct UmmaGemmConfig {
   static constexpr int kFirstConvertWarp = kFirstEpilogueWarp + kNumEpilogueWarps;
   static constexpr int kThreads = 32 * (kFirstConvertWarp + kNumConvertWarps);
   static constexpr int kEpiCols = kSplit ? BN / 2 : BN;  // accumulator columns owned by one thread
-  // setmaxnreg targets (kSplit): 128*40 + 256*208 + 128*48 = 64512 <= 65536 registers
-  static constexpr int kRegsControl = 40, kRegsEpilogue = 208, kRegsConvert = 48;
+  // setmaxnreg targets (kSplit): 128*48 + 256*208 + 128*48 = 65536 registers
+  static constexpr int kRegsControl = 48, kRegsEpilogue = 208, kRegsConvert = 48;
   static constexpr int kTmemCols = (2 * BN <= 32) ? 32 : 2 * BN;  // power of two by construction
   // Each epilogue warp transposes 32x32 blocks through 4 KB of shared memory so that its
   // global stores cover whole 128-byte lines (and peers' memory is written in full lines).
   static constexpr int kEpiStageBytes = 4096;
   static constexpr int kEpiStagingBytes = kNumEpilogueWarps * kEpiStageBytes;
-  static constexpr int kBarrierBytes = 256;
+  static constexpr int kBarrierBytes = 256 + 16 * kMaxSkSegments + 16;  // + segment table
   static constexpr int kSmemBytes =
       kStages * kStageBytes + kEpiStagingBytes + kBarrierBytes + 1024;  // +align slack
   static constexpr uint32_t kIdesc =
@@ -167,6 +189,55 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, int 
         return false;
       }
     }
+  }
+}
+
+// Wait (bounded like the barrier waits) until a counter in global memory that other CTAs of
+// the same grid increment reaches `expect`; an acquire on success.
+__device__ __forceinline__ bool bounded_flag_wait(const unsigned* flag, unsigned expect, int bit,
+                                                  const UmmaCtl& ctl) {
+  uint64_t start = 0;
+  uint32_t spins = 0;
+  while (true) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= expect) return true;
+    if ((++spins & 0x3F) == 0) {
+      if (*ctl.abort_flag) return false;
+      uint64_t now = ptx::globaltimer_ns();
+      if (start == 0) {
+        start = now;
+      } else if (now - start > ctl.timeout_ns) {
+        *ctl.abort_flag = 1;
+        if (ctl.status) atomicOr(ctl.status, bit);
+        return false;
+      }
+    }
+    __nanosleep(64);
+  }
+}
+
+// A thread's share of a partial-sum tile: kCount float4, 512 bytes apart (one base register,
+// immediate offsets, L2 only).
+template <int kCount, int V = 0>
+__device__ __forceinline__ void sk_load_partial(float* sum, const float4* src) {
+  if constexpr (V < kCount) {
+    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4 + %5];"
+                 : "=f"(sum[4 * V]), "=f"(sum[4 * V + 1]), "=f"(sum[4 * V + 2]), "=f"(sum[4 * V + 3])
+                 : "l"(src), "n"(V * 512)
+                 : "memory");
+    sk_load_partial<kCount, V + 1>(sum, src);
+  }
+}
+template <int kCount, int V = 0>
+__device__ __forceinline__ void sk_store_partial(const float* sum, float4* dst) {
+  if constexpr (V < kCount) {
+    asm volatile("st.global.cg.v4.f32 [%0 + %1], {%2, %3, %4, %5};"
+                 :
+                 : "l"(dst), "n"(V * 512), "f"(sum[4 * V]), "f"(sum[4 * V + 1]),
+                   "f"(sum[4 * V + 2]), "f"(sum[4 * V + 3])
+                 : "memory");
+    sk_store_partial<kCount, V + 1>(sum, dst);
   }
 }
 
@@ -277,6 +348,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   const uint32_t red_free = bar_base + 8u * (3 * kStages + 5);   // rank 0 -> others: buffer usable
   const uint32_t red_ready = bar_base + 8u * (3 * kStages + 6);  // others -> rank 0: partials written
 
+  // segment table of the k-shared tiles (see UmmaGemmParams::sk_tiles), filled by thread 0
+  uint4* seg_table = reinterpret_cast<uint4*>(bar_gen + 256);
+  volatile uint32_t* sk_count_gen =
+      reinterpret_cast<volatile uint32_t*>(bar_gen + 256 + 16 * kMaxSkSegments);
+
   UmmaCtl ctl{abort_flag, p.status, p.timeout_ns};
 
   if (threadIdx.x == 0) {
@@ -292,6 +368,27 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     ptx::mbar_init(red_free, 1);
     ptx::mbar_init(red_ready, ksplit > 1 ? (ksplit - 1) * Cfg::kNumEpilogueWarps * 32 : 1);
     *abort_flag = 0;
+    unsigned nseg = 0;
+    if (kSplit && p.sk_tiles) {
+      const unsigned long long total_kb = static_cast<unsigned long long>(p.sk_tiles) * num_kb;
+      const unsigned long long s0 = static_cast<unsigned long long>(group_id) * p.sk_kb_per_group;
+      const unsigned long long e0 = min(total_kb, s0 + p.sk_kb_per_group);
+      if (s0 < e0) {
+        const unsigned t_first = static_cast<unsigned>(s0 / num_kb);
+        const unsigned s_off = static_cast<unsigned>(s0 - static_cast<unsigned long long>(t_first) * num_kb);
+        const unsigned t_last = static_cast<unsigned>((e0 - 1) / num_kb);
+        const unsigned e_off = static_cast<unsigned>(e0 - static_cast<unsigned long long>(t_last) * num_kb);
+        const bool has_tail = s_off != 0, has_head = e_off != num_kb;
+        // The head goes first and the tail last: the previous group has then long published
+        // the sums this group's tail continues, and nobody waits on anybody in practice.
+        if (has_head) seg_table[nseg++] = make_uint4(t_last, 0u, e_off, kSegHead);
+        for (unsigned t = t_first + (has_tail ? 1u : 0u);
+             t + (has_head ? 1u : 0u) <= t_last && nseg < kMaxSkSegments - 1; ++t)
+          seg_table[nseg++] = make_uint4(t, 0u, num_kb, 0u);
+        if (has_tail) seg_table[nseg++] = make_uint4(t_first, s_off, num_kb, kSegTail);
+      }
+    }
+    *sk_count_gen = nseg;
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmapA);
     ptx::prefetch_tensormap(&tmapB);
@@ -309,6 +406,24 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_gen;
 
+  // The walk of this CTA: first its segments of the k-shared tiles, then whole tiles with a
+  // stride of the grid.  Every role iterates the same list.
+  const unsigned sk_count = kSplit ? *sk_count_gen : 0u;
+  const unsigned dp_first = (kSplit ? p.sk_tiles : 0u) + group_id;
+  const unsigned num_segments =
+      sk_count + (dp_first < total_tiles ? (total_tiles - dp_first + num_groups - 1) / num_groups : 0u);
+  auto segment = [&](unsigned i) {
+    UmmaSegment sg;
+    if (kSplit && i < sk_count) {
+      const uint4 v = seg_table[i];
+      sg.tile = v.x; sg.kb_lo = v.y; sg.kb_hi = v.z; sg.mode = v.w;
+    } else {
+      sg.tile = dp_first + (i - sk_count) * num_groups;
+      sg.kb_lo = kb_lo; sg.kb_hi = kb_hi; sg.mode = 0u;
+    }
+    return sg;
+  };
+
   // number of k-blocks per accumulator hand-off: the whole K unless partial sums are promoted
   const unsigned kb_per_chunk = kSplit ? max(1u, p.kb_per_chunk) : max(1u, num_kb);
 
@@ -321,14 +436,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
-      for (unsigned t = group_id; t < total_tiles; t += num_groups) {
+      for (unsigned si = 0; si < num_segments; ++si) {
+        const UmmaSegment sg = segment(si);
         unsigned b, tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, b, tm, tn);
+        tile_coords(sg.tile, p.tiles_m, p.tiles_n, b, tm, tn);
         const int m0 = static_cast<int>(tm * Cfg::kTileM + cta_rank * Cfg::kBM);
         const int n0 = static_cast<int>(tn * BN + cta_rank * Cfg::kBNLocal);
         const int ba = p.a_batched ? static_cast<int>(b) : 0;
         const int bb = p.b_batched ? static_cast<int>(b) : 0;
-        for (unsigned kb = kb_lo; kb < kb_hi; ++kb) {
+        for (unsigned kb = sg.kb_lo; kb < sg.kb_hi; ++kb) {
           bounded_wait<false>(empty_bar(s), ph ^ 1u, TFCCB200_DEV_TIMEOUT_TMA, ctl);
           const uint32_t stage = smem_base + s * Cfg::kStageBytes;
           const int k0 = static_cast<int>(kb * Cfg::kBK);
@@ -362,15 +478,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       uint32_t ph = 0;
       unsigned it = 0;  // accumulator hand-offs so far (tiles, or chunks when kSplit)
       const uint16_t pair_mask = 0x3;
-      for (unsigned t = group_id; t < total_tiles; t += num_groups) {
-        for (unsigned kb0 = kb_lo; kb0 < kb_hi; kb0 += kb_per_chunk, ++it) {
+      for (unsigned si = 0; si < num_segments; ++si) {
+        const UmmaSegment sg = segment(si);
+        for (unsigned kb0 = sg.kb_lo; kb0 < sg.kb_hi; kb0 += kb_per_chunk, ++it) {
           const unsigned acc = it & 1u;
           const uint32_t acc_ph = (it >> 1) & 1u;
           bounded_wait<(kCtaGroup == 2)>(tmem_empty(acc), acc_ph ^ 1u, TFCCB200_DEV_TIMEOUT_MMA,
                                          ctl);
           ptx::tc_fence_after_sync();
           const uint32_t d_tmem = tmem_base + acc * BN;
-          const unsigned kb_end = min(kb_hi, kb0 + kb_per_chunk);
+          const unsigned kb_end = min(sg.kb_hi, kb0 + kb_per_chunk);
           for (unsigned kb = kb0; kb < kb_end; ++kb) {
             if constexpr (kSplit) {
               bounded_wait<(kCtaGroup == 2)>(full_cvt(s), ph, TFCCB200_DEV_TIMEOUT_MMA, ctl);
@@ -427,13 +544,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         else ptx::mbar_arrive(tmem_empty(acc));
       }
     };
-    for (unsigned t = group_id; t < total_tiles; t += num_groups) {
-      unsigned b, tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, b, tm, tn);
-      const unsigned row0 = tm * Cfg::kTileM + cta_rank * Cfg::kBM + q * 32;  // lane 0's row
-      const unsigned col0 = tn * BN + col_half * Cfg::kEpiCols;
+    for (unsigned si = 0; si < num_segments; ++si) {
+      const UmmaSegment sg = segment(si);
+      // Where the tile goes.  (kSplit computes this only after the accumulation, when the
+      // registers holding the running sums are the only other long-lived values.)
+      unsigned b, row0, col0;
+      unsigned long long batch_off;
+      auto locate_tile = [&]() {
+        unsigned tm, tn;
+        tile_coords(sg.tile, p.tiles_m, p.tiles_n, b, tm, tn);
+        row0 = tm * Cfg::kTileM + cta_rank * Cfg::kBM + q * 32;  // lane 0's row
+        col0 = tn * BN + col_half * Cfg::kEpiCols;
+        batch_off = p.strideC * b;
+      };
+      if constexpr (!kSplit) locate_tile();
       const uint32_t lane_addr = tmem_base + ((q * 32u) << 16) + col_half * Cfg::kEpiCols;
-      const unsigned long long batch_off = p.strideC * b;
       uint32_t* stage = reinterpret_cast<uint32_t*>(
           epi_stage_gen + (warp - Cfg::kFirstEpilogueWarp) * Cfg::kEpiStageBytes);
       auto bias_term = [&](unsigned col_blk) {
@@ -446,9 +571,25 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       if constexpr (kSplit) {
         // ---- promote every chunk's partial sum into registers (round-to-nearest adds) ----
         float sum[Cfg::kEpiCols];
+        constexpr int kSkVec = Cfg::kEpiCols / 4;
+        // this thread's float4 slots in a partial-sum tile: [warp][4-column group][lane]
+        const unsigned sk_slot = ((warp - Cfg::kFirstEpilogueWarp) * kSkVec) * 32 + lane;
+        constexpr unsigned kSkTileVecs = Cfg::kNumEpilogueWarps * kSkVec * 32;  // float4 per CTA tile
+        if (sg.mode == kSegTail) {
+          // continue the sums the previous group published for the same rows of this tile
+          const unsigned src_cta = (group_id - 1) * kCtaGroup + cta_rank;
+          if (lane == 0)
+            bounded_flag_wait(p.sk_flags + src_cta, Cfg::kNumEpilogueWarps * 32u,
+                              TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
+          __syncwarp();
+          const float4* src = reinterpret_cast<const float4*>(p.sk_partials) +
+                              static_cast<size_t>(src_cta) * kSkTileVecs + sk_slot;
+          sk_load_partial<kSkVec>(sum, src);
+        } else {
 #pragma unroll
-        for (int j = 0; j < Cfg::kEpiCols; ++j) sum[j] = 0.f;
-        for (unsigned kb0 = kb_lo; kb0 < kb_hi; kb0 += kb_per_chunk, ++it) {
+          for (int j = 0; j < Cfg::kEpiCols; ++j) sum[j] = 0.f;
+        }
+        for (unsigned kb0 = sg.kb_lo; kb0 < sg.kb_hi; kb0 += kb_per_chunk, ++it) {
           const unsigned acc = it & 1u;
           const uint32_t acc_ph = (it >> 1) & 1u;
           bounded_wait<false>(tmem_full(acc), acc_ph, TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
@@ -463,6 +604,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             for (int j = 0; j < 16; ++j) sum[c * 16 + j] += __uint_as_float(r[j]);
           }
           release_acc(acc);
+        }
+        if (sg.mode == kSegHead) {
+          // publish the partial sums for the group that finishes this tile
+          const unsigned my_cta = group_id * kCtaGroup + cta_rank;
+          float4* out = reinterpret_cast<float4*>(p.sk_partials) +
+                        static_cast<size_t>(my_cta) * kSkTileVecs + sk_slot;
+          sk_store_partial<kSkVec>(sum, out);
+          __threadfence();
+          atomicAdd(p.sk_flags + my_cta, 1u);
+          continue;
         }
         if (ksplit > 1) {
           // ---- K split over the cluster: partial sums meet in rank 0's (now idle) stage
@@ -496,6 +647,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             continue;  // rank 0 stores the tile
           }
         }
+        locate_tile();
 #pragma unroll
         for (int c = 0; c < Cfg::kEpiCols / 32; ++c) {
           if (col0 + c * 32 >= p.N) break;  // warp-uniform
@@ -582,8 +734,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       const uint32_t leader_full_cvt0 = (kCtaGroup == 2) ? ptx::mapa(full_cvt(0), 0) : full_cvt(0);
       int s = 0;
       uint32_t ph = 0;
-      for (unsigned t = group_id; t < total_tiles; t += num_groups) {
-        for (unsigned kb = kb_lo; kb < kb_hi; ++kb) {
+      for (unsigned si = 0; si < num_segments; ++si) {
+        const UmmaSegment sg = segment(si);
+        for (unsigned kb = sg.kb_lo; kb < sg.kb_hi; ++kb) {
           bounded_wait<false>(full_raw(s), ph, TFCCB200_DEV_TIMEOUT_CONVERT, ctl);
           float4* raw = reinterpret_cast<float4*>(smem_gen + s * Cfg::kStageBytes);
           float4* tail = reinterpret_cast<float4*>(smem_gen + s * Cfg::kStageBytes + Cfg::kRawBytes);

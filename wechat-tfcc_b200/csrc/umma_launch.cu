@@ -56,6 +56,29 @@ bool make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const v
   return r == CUDA_SUCCESS;
 }
 
+int env_int(const char* name, int fallback);
+
+// Sharing the last one-to-two waves of tiles out by k-block (UmmaGemmParams::sk_tiles).
+// Worth it when the tile count leaves a noticeable part of the last wave idle.
+bool stream_k_split(unsigned long long tiles, unsigned groups, unsigned num_kb, unsigned kb_per_chunk,
+                    unsigned* sk_tiles, unsigned* sk_kb_per_group) {
+  static const int enabled = env_int("TFCCB200_STREAM_K", 1);
+  if (!enabled || groups == 0 || tiles <= groups || tiles % groups == 0) return false;
+  if (kb_per_chunk == 0 || num_kb % kb_per_chunk != 0) return false;
+  const unsigned long long waves = (tiles + groups - 1) / groups;
+  if (tiles * 100 >= waves * groups * 96) return false;  // >= 96 % busy already
+  const unsigned long long dp_tiles = (tiles / groups - 1) * groups;
+  const unsigned long long sk = tiles - dp_tiles;  // groups < sk < 2 * groups
+  const unsigned long long chunks = sk * (num_kb / kb_per_chunk);
+  const unsigned long long per = (chunks + groups - 1) / groups;
+  if (per * kb_per_chunk > 0xffffffffull) return false;
+  *sk_tiles = static_cast<unsigned>(sk);
+  *sk_kb_per_group = static_cast<unsigned>(per * kb_per_chunk);  // >= num_kb because sk >= groups
+  return true;
+}
+
+constexpr size_t kStreamKFlagBytes = 4096;  // one counter per CTA of the grid, padded
+
 template <ptx::MmaKind kKind, bool kSplit, int kCtaGroup, int BN, int kStages>
 int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, UmmaGemmParams p,
            int sm_count) {
@@ -90,6 +113,23 @@ int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, Um
     cluster = p.cluster_k;
   } else {
     p.cluster_k = 1;
+  }
+  unsigned sk_tiles = 0, sk_per = 0;
+  if (kSplit && p.sk_flags && p.cluster_k == 1 &&
+      stream_k_split(total, groups, (p.K + Cfg::kBK - 1) / Cfg::kBK, p.kb_per_chunk, &sk_tiles,
+                     &sk_per) &&
+      static_cast<size_t>(groups) * kCtaGroup * sizeof(unsigned) <= kStreamKFlagBytes &&
+      static_cast<unsigned long long>(groups) * kCtaGroup * Cfg::kBM * BN * 4ull <= p.sk_capacity) {
+    p.sk_tiles = sk_tiles;
+    p.sk_kb_per_group = sk_per;
+    e = cudaMemsetAsync(p.sk_flags, 0, static_cast<size_t>(groups) * kCtaGroup * sizeof(unsigned),
+                        stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  } else {
+    p.sk_tiles = 0;
+    p.sk_kb_per_group = 0;
+    p.sk_flags = nullptr;
+    p.sk_partials = nullptr;
   }
 
   cudaLaunchConfig_t cfg = {};
@@ -178,6 +218,15 @@ int env_int(const char* name, int fallback) {
   const char* v = std::getenv(name);
   return (v && *v) ? std::atoi(v) : fallback;
 }
+
+}  // namespace
+
+size_t umma_stream_k_workspace(int sm_count) {
+  // flags + one 128 x 256 fp32 partial tile per SM: enough for every tile shape
+  return kStreamKFlagBytes + static_cast<size_t>(sm_count) * 128 * 256 * 4;
+}
+
+namespace {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -362,6 +411,12 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
   static const int env_kb_per_chunk = env_int("TFCCB200_KB_PER_CHUNK", 4);
   p.write_head = env_write_head ? 1 : 0;
   p.kb_per_chunk = env_kb_per_chunk > 0 ? env_kb_per_chunk : 4;
+  if (fp32_split && a.workspace && (reinterpret_cast<uintptr_t>(a.workspace) & 255u) == 0 &&
+      a.workspace_bytes > kStreamKFlagBytes) {
+    p.sk_flags = static_cast<unsigned*>(a.workspace);
+    p.sk_partials = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + kStreamKFlagBytes);
+    p.sk_capacity = a.workspace_bytes - kStreamKFlagBytes;
+  }
   p.cluster_k = (fp32_split && !pair) ? tuned.cluster_k : 1;
   p.status = a.status;
   p.timeout_ns = kDefaultTimeoutNs;

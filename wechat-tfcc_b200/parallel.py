@@ -158,10 +158,13 @@ class FusedNSplit:
                 raise exceptions.InvalidArgumentError("operands must be contiguous float32 CUDA tensors")
         sess = get_session(self.device)
         with torch.cuda.device(self.device):
+            ws_bytes = lib.tfccb200_sgemm_workspace(self.m, self.ns, a.shape[1], 1,
+                                                    PRECISIONS[precision])
+            ws_ptr, ws_len = sess.workspace(ws_bytes) if ws_bytes else (None, 0)
             st = lib.tfccb200_sgemm_nsplit_push(
                 sess.stream_ptr, a.data_ptr(), b_shard.data_ptr(), self._ptrs, self.world, self.rank,
                 bias_shard.data_ptr() if bias_shard is not None else None, self.m, self.ns,
-                a.shape[1], PRECISIONS[precision], sess.status_ptr)
+                a.shape[1], PRECISIONS[precision], ws_ptr, ws_len, sess.status_ptr)
         check(st)
         self.barrier()
         return self.c
