@@ -441,6 +441,96 @@ def extra_measurements(torch, pkg, dev, peaks):
     return out
 
 
+def multi_gpu_extras(torch, dist, pkg, dev, world, rank, peaks):
+    """The other shard-natural cases at N GPUs.  Every rank times its own share with CUDA events
+    (mean of a train after warm-up); the job's figure uses the slowest rank.
+    * config 2 split by batch: 96 attention batches / N per rank, no communication;
+    * int8 u8[4096,4096] x s8[4096,4096] -> s32 split by columns of B: every rank keeps its
+      column shard of C (the layout a following row-split layer consumes), and, separately,
+      with an NCCL all-gather of the shards plus the panel interleave to the row-major C."""
+    lib = pkg.lib
+    sess = pkg.session.get_session(dev)
+    out = {}
+
+    def slowest(ms):
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def timed(fn, iters=20, warm=3):
+        for _ in range(warm):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return slowest(e0.elapsed_time(e1) / iters)
+
+    # ---- config 2, batch split
+    g = torch.Generator(device=dev)
+    g.manual_seed(2)
+    lo, hi = pkg.parallel.shard_range(96, world, rank)
+    sets = 8  # rotate operand sets so that the train does not sit in L2 for free
+    qs = [torch.randn((hi - lo, 128, 64), device=dev, generator=g) for _ in range(sets)]
+    kts = [torch.randn((hi - lo, 64, 128), device=dev, generator=g) for _ in range(sets)]
+    calls = [(lambda q=q, kt=kt: pkg.blas.matmul(q, kt)) for q, kt in zip(qs, kts)]
+    dist.barrier()
+    us, _ = time_graph_train(torch, calls * 2)  # graph replay: no host launch cost per step
+    ms = slowest(us * 1e-3)
+    out["cfg2_qk_batch_split"] = {"us_per_step": ms * 1e3, "batches_per_rank": hi - lo,
+                                  "tflops_whole_job": 2.0 * 96 * 128 * 64 * 128 / (ms * 1e-3) / 1e12}
+    del calls
+    del qs, kts
+
+    # ---- int8, column shards of B
+    m = n = k = 4096
+    ns = n // world
+    rng = np.random.default_rng(7)  # same A on every rank
+    qa = torch.from_numpy(rng.integers(0, 256, (m, k), dtype=np.uint8)).to(dev)
+    qb_full = rng.integers(-127, 128, (k, n), dtype=np.int8)
+    qb = torch.from_numpy(np.ascontiguousarray(qb_full[:, rank * ns:(rank + 1) * ns])).to(dev)
+    ra = pkg.quantization.reduce_sum(qa, True)
+    rb = pkg.quantization.reduce_sum(qb, False)
+    c_shard = torch.empty((m, ns), dtype=torch.int32, device=dev)
+    staging = torch.empty((world, m, ns), dtype=torch.int32, device=dev)
+    c_full = torch.empty((m, n), dtype=torch.int32, device=dev)
+
+    def local():
+        st = lib.tfccb200_qgemm_u8s8s32(
+            torch.cuda.current_stream().cuda_stream, qa.data_ptr(), 0, ra.data_ptr(), 0, -128,
+            qb.data_ptr(), 0, rb.data_ptr(), 0, 0, c_shard.data_ptr(), m * ns, m, ns, k, 1,
+            sess.status_ptr)
+        assert st == 0, st
+
+    def gathered():
+        local()
+        dist.all_gather_into_tensor(staging, c_shard)
+        # bit copy of 32-bit words: the panel interleave does not care that they are integers
+        pkg.parallel.interleave_panels(staging.view(torch.float32), c_full.view(torch.float32))
+
+    ops = 2.0 * m * n * k
+    ms = timed(local, iters=40)
+    out["int8_4096_column_shards"] = {"us_per_step": ms * 1e3, "tops_whole_job": ops / (ms * 1e-3) / 1e12}
+    ms = timed(gathered, iters=20)
+    out["int8_4096_column_shards_gathered"] = {"us_per_step": ms * 1e3,
+                                               "tops_whole_job": ops / (ms * 1e-3) / 1e12,
+                                               "gathered_bytes_per_rank": 4 * m * (n - ns)}
+    # exactness of the assembled matrix against the int64 product, on sampled rows
+    gathered()
+    torch.cuda.synchronize()
+    rows = np.random.default_rng(0).choice(m, size=4, replace=False)
+    a64 = qa[torch.from_numpy(rows).to(dev)].cpu().numpy().astype(np.int64) - 128
+    truth = (a64 @ qb_full.astype(np.int64)).astype(np.int32)
+    got = c_full[torch.from_numpy(rows).to(dev)].cpu().numpy()
+    out["int8_4096_column_shards_gathered"]["sampled_rows_exact"] = bool(np.array_equal(got, truth))
+    sess.sync()
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -641,6 +731,11 @@ def run_ours(args):
                                         "kind": "port", "sample": sample}
             if not args.no_extra:
                 line["extra"] = extra_measurements(torch, pkg, dev, peaks)
+    if world > 1 and not args.no_extra:
+        extra = multi_gpu_extras(torch, dist, pkg, dev, world, rank, peaks)
+        if rank == 0:
+            line["extra"] = extra
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

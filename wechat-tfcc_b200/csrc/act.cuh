@@ -8,11 +8,14 @@
 namespace tfccb200 {
 
 // 0.5 * v * (1 + erf(v / sqrt(2))) with the reference's mixed precision
-// (tfcc/mkl/kernel/tfcc_mklactivationkernel.hpp:214-220): the literal 0.5 is a double there,
-// so the two outer products are carried out in double and rounded to float once.
+// (tfcc/mkl/kernel/tfcc_mklactivationkernel.hpp:214-220).  There the literal 0.5 is a double,
+// so 0.5 * v * e is evaluated in double and rounded to float once.  Both factors are floats
+// (e = 1 + erf(float) is a float sum), so their product is exact in double and the single
+// rounding equals one float multiplication; halving e first is exact too.  No double
+// arithmetic is needed for the same bits.
 __device__ __forceinline__ float gelu_erf(float v) {
   const float e = 1.0f + erff(v / 1.4142135623730951f);
-  return static_cast<float>(__dmul_rn(__dmul_rn(0.5, static_cast<double>(v)), static_cast<double>(e)));
+  return __fmul_rn(v, 0.5f * e);
 }
 
 __device__ __forceinline__ float apply_activation(float v, int activation) {

@@ -80,8 +80,9 @@ int pick_sgemm_path(const SgemmArgs& a) {
     cudaError_t e;
     const DeviceInfo* di = current_device_info(&e);
     const int sms = di ? di->sm_count : 148;
+    const bool fp32 = a.precision == TFCCB200_PRECISION_FP32;
     return umma_plan(a.M, a.N, a.K, a.batch, sms, a.precision == TFCCB200_PRECISION_BF16 ? 2 : 4, -1,
-                     a.precision == TFCCB200_PRECISION_FP32)
+                     fp32, fp32 && stream_k_scratch_ok(a, sms))
                .pair ? TFCCB200_PATH_UMMA2
                                                              : TFCCB200_PATH_UMMA;
   }
@@ -118,7 +119,7 @@ int pick_qgemm_path(const QgemmArgs& a) {
     cudaError_t e;
     const DeviceInfo* di = current_device_info(&e);
     const int sms = di ? di->sm_count : 148;
-    return umma_plan(a.M, a.N, a.K, a.batch, sms, 1, -1, false).pair ? TFCCB200_PATH_UMMA2
+    return umma_plan(a.M, a.N, a.K, a.batch, sms, 1, -1, false, false).pair ? TFCCB200_PATH_UMMA2
                                                             : TFCCB200_PATH_UMMA;
   }
   return TFCCB200_PATH_SIMT;
@@ -465,7 +466,8 @@ int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shar
   cudaError_t e;
   const DeviceInfo* di = current_device_info(&e);
   if (!di) return static_cast<int>(e);
-  return umma_sgemm(a, umma_plan(M, N_shard, K, 1, di->sm_count, 4, -1, false).pair);
+  return umma_sgemm(a, umma_plan(M, N_shard, K, 1, di->sm_count, 4, -1, false,
+                                 stream_k_scratch_ok(a, di->sm_count)).pair);
 }
 
 int tfccb200_sgemm_skinny_static(void* stream, const float* A, const float* B, float* C,

@@ -67,7 +67,8 @@ struct UmmaPlan {
   unsigned cluster_k;  // > 1: K of one tile is shared by a cluster of that many single CTAs
 };
 UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count,
-                   int elem_bytes, int force_pair, bool allow_cluster_k);
+                   int elem_bytes, int force_pair, bool allow_cluster_k, bool allow_stream_k);
+bool stream_k_scratch_ok(const SgemmArgs& a, int sm_count);  // scratch lent for the k-shared wave
 size_t umma_stream_k_workspace(int sm_count);  // scratch that lets umma_sgemm share tiles by k-block
 bool umma_sgemm_supported(const SgemmArgs& a);
 int umma_sgemm(const SgemmArgs& a, bool pair);

@@ -9,9 +9,11 @@
 // All are HBM-bound: one read and one write of the tensor, 128-bit accesses where the row
 // length allows.
 #include <cuda_runtime.h>
+#include <stdint.h>
 
 #include "act.cuh"
 #include "internal.h"
+#include "pdl.cuh"
 
 namespace tfccb200 {
 
@@ -35,6 +37,8 @@ template <int PER_LANE>
 __global__ void __launch_bounds__(256)
 softmax_rows_kernel(const float* __restrict__ src, unsigned rows, unsigned cols, float scale,
                     float* __restrict__ dst) {
+  pdl_release();
+  pdl_wait();
   const unsigned row = blockIdx.x * 8 + (threadIdx.x >> 5);
   const unsigned lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -68,6 +72,8 @@ softmax_rows_kernel(const float* __restrict__ src, unsigned rows, unsigned cols,
 __global__ void __launch_bounds__(256)
 softmax_long_rows_kernel(const float* __restrict__ src, unsigned cols, float scale,
                          float* __restrict__ dst) {
+  pdl_release();
+  pdl_wait();
   __shared__ float red[8];
   __shared__ float bcast;
   const float* p = src + static_cast<size_t>(blockIdx.x) * cols;
@@ -111,6 +117,8 @@ __global__ void __launch_bounds__(256)
 layer_norm_kernel(const float* __restrict__ x, const float* __restrict__ residual,
                   const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
                   unsigned rows, unsigned cols, float* __restrict__ dst) {
+  pdl_release();
+  pdl_wait();
   const unsigned row = blockIdx.x * 8 + (threadIdx.x >> 5);
   const unsigned lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -145,16 +153,89 @@ layer_norm_kernel(const float* __restrict__ x, const float* __restrict__ residua
   }
 }
 
+// Same, for rows that are whole float4 vectors at 16-byte aligned addresses: VPL vectors per
+// lane, all loads of a row issued before the first use.
+template <int VPL>
 __global__ void __launch_bounds__(256)
-gelu_kernel(const float* __restrict__ src, size_t n, float* __restrict__ dst) {
+layer_norm_vec_kernel(const float4* __restrict__ x, const float4* __restrict__ residual,
+                      const float4* __restrict__ gamma, const float4* __restrict__ beta, float eps,
+                      unsigned rows, unsigned vecs, float4* __restrict__ dst) {
+  pdl_release();
+  pdl_wait();
+  const unsigned row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const unsigned lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const size_t off = static_cast<size_t>(row) * vecs;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 v[VPL], r[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const unsigned c = lane + 32 * i;
+    v[i] = c < vecs ? __ldcs(x + off + c) : zero;
+  }
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const unsigned c = lane + 32 * i;
+    r[i] = (residual && c < vecs) ? __ldcs(residual + off + c) : zero;
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    v[i].x += r[i].x; v[i].y += r[i].y; v[i].z += r[i].z; v[i].w += r[i].w;
+    sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  }
+  const float n = static_cast<float>(vecs * 4);
+  const float mean = warp_sum(sum) / n;
+  float var = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    if (lane + 32 * i < vecs) {
+      const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+      var += (a * a + b * b) + (c * c + d * d);
+    }
+  }
+  var = warp_sum(var) / n;
+  const float inv = 1.0f / sqrtf(var + eps);
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const unsigned c = lane + 32 * i;
+    if (c < vecs) {
+      const float4 g = __ldg(gamma + c), bt = __ldg(beta + c);
+      float4 o;
+      o.x = (v[i].x - mean) * (inv * g.x) + bt.x;
+      o.y = (v[i].y - mean) * (inv * g.y) + bt.y;
+      o.z = (v[i].z - mean) * (inv * g.z) + bt.z;
+      o.w = (v[i].w - mean) * (inv * g.w) + bt.w;
+      dst[off + c] = o;
+    }
+  }
+}
+
+// Element-wise, may run in place (src == dst).
+__global__ void __launch_bounds__(256)
+gelu_kernel(const float* src, size_t n, float* dst) {
+  pdl_release();
+  pdl_wait();
   for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull)
     dst[i] = gelu_erf(src[i]);
+}
+__global__ void __launch_bounds__(256)
+gelu_vec_kernel(const float4* src, size_t n4, float4* dst) {
+  pdl_release();
+  pdl_wait();
+  for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n4; i += gridDim.x * 256ull) {
+    float4 v = src[i];
+    v.x = gelu_erf(v.x); v.y = gelu_erf(v.y); v.z = gelu_erf(v.z); v.w = gelu_erf(v.w);
+    dst[i] = v;
+  }
 }
 
 // [d0,d1,d2,d3] -> [d0,d2,d1,d3]: rows of d3 contiguous floats move as a whole.
 __global__ void __launch_bounds__(256)
 permute_0213_kernel(const float* __restrict__ src, unsigned d0, unsigned d1, unsigned d2,
                     unsigned d3, float* __restrict__ dst) {
+  pdl_release();
+  pdl_wait();
   const size_t total = static_cast<size_t>(d0) * d1 * d2 * d3;
   for (size_t o = blockIdx.x * 256ull + threadIdx.x; o < total; o += gridDim.x * 256ull) {
     const unsigned i3 = o % d3;
@@ -167,10 +248,30 @@ permute_0213_kernel(const float* __restrict__ src, unsigned d0, unsigned d1, uns
   }
 }
 
+// Same with d3 a multiple of 4 and 16-byte aligned tensors: one float4 per thread step.
+__global__ void __launch_bounds__(256)
+permute_0213_vec_kernel(const float4* __restrict__ src, unsigned d0, unsigned d1, unsigned d2,
+                        unsigned v3, float4* __restrict__ dst) {
+  pdl_release();
+  pdl_wait();
+  const size_t total = static_cast<size_t>(d0) * d1 * d2 * v3;
+  for (size_t o = blockIdx.x * 256ull + threadIdx.x; o < total; o += gridDim.x * 256ull) {
+    const unsigned i3 = o % v3;
+    size_t r = o / v3;
+    const unsigned i1 = r % d1;  // destination order: [d0][d2][d1][v3]
+    r /= d1;
+    const unsigned i2 = r % d2;
+    const unsigned i0 = r / d2;
+    dst[o] = __ldcs(src + ((static_cast<size_t>(i0) * d1 + i1) * d2 + i2) * v3 + i3);
+  }
+}
+
 // [batch, r, c] -> [batch, c, r] through a padded 32x32 tile in shared memory.
 __global__ void __launch_bounds__(256)
 transpose_last2_kernel(const float* __restrict__ src, unsigned r, unsigned c,
                        float* __restrict__ dst) {
+  pdl_release();
+  pdl_wait();
   __shared__ float tile[32][33];
   const size_t base = static_cast<size_t>(blockIdx.z) * r * c;
   const unsigned r0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
@@ -208,14 +309,16 @@ int softmax_f32(cudaStream_t stream, const float* src, unsigned rows, unsigned c
                 float* dst) {
   const unsigned blocks = (rows + 7) / 8;
 #define TFCCB200_SOFTMAX(P)                                                                   \
-  softmax_rows_kernel<P><<<blocks, 256, 0, stream>>>(src, rows, cols, scale, dst)
+  launch_after_previous(softmax_rows_kernel<P>, dim3(blocks), dim3(256), 0, stream, src, rows, cols,  \
+                        scale, dst)
   if (cols <= 32) TFCCB200_SOFTMAX(1);
   else if (cols <= 64) TFCCB200_SOFTMAX(2);
   else if (cols <= 128) TFCCB200_SOFTMAX(4);
   else if (cols <= 256) TFCCB200_SOFTMAX(8);
   else if (cols <= 512) TFCCB200_SOFTMAX(16);
   else if (cols <= 1024) TFCCB200_SOFTMAX(32);
-  else softmax_long_rows_kernel<<<rows, 256, 0, stream>>>(src, cols, scale, dst);
+  else launch_after_previous(softmax_long_rows_kernel, dim3(rows), dim3(256), 0, stream, src, cols,
+                             scale, dst);
 #undef TFCCB200_SOFTMAX
   return done();
 }
@@ -224,8 +327,27 @@ int layer_norm_f32(cudaStream_t stream, const float* x, const float* residual, c
                    const float* beta, float eps, unsigned rows, unsigned cols, float* dst) {
   if (cols > 32u * kMaxPerLane) return TFCCB200_EUNSUPPORTED;
   const unsigned blocks = (rows + 7) / 8;
+  auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (cols % 4 == 0 && a16(x) && a16(residual) && a16(gamma) && a16(beta) && a16(dst)) {
+    const unsigned vecs = cols / 4;
+#define TFCCB200_LNV(V)                                                                       \
+  launch_after_previous(layer_norm_vec_kernel<V>, dim3(blocks), dim3(256), 0, stream,         \
+                        reinterpret_cast<const float4*>(x),                                   \
+                        reinterpret_cast<const float4*>(residual),                            \
+                        reinterpret_cast<const float4*>(gamma),                               \
+                        reinterpret_cast<const float4*>(beta), eps, rows, vecs,               \
+                        reinterpret_cast<float4*>(dst))
+    if (vecs <= 32) TFCCB200_LNV(1);
+    else if (vecs <= 64) TFCCB200_LNV(2);
+    else if (vecs <= 128) TFCCB200_LNV(4);
+    else if (vecs <= 192) TFCCB200_LNV(6);
+    else TFCCB200_LNV(8);
+#undef TFCCB200_LNV
+    return done();
+  }
 #define TFCCB200_LN(P)                                                                        \
-  layer_norm_kernel<P><<<blocks, 256, 0, stream>>>(x, residual, gamma, beta, eps, rows, cols, dst)
+  launch_after_previous(layer_norm_kernel<P>, dim3(blocks), dim3(256), 0, stream, x, residual,   \
+                        gamma, beta, eps, rows, cols, dst)
   if (cols <= 128) TFCCB200_LN(4);
   else if (cols <= 256) TFCCB200_LN(8);
   else if (cols <= 512) TFCCB200_LN(16);
@@ -239,7 +361,14 @@ int gelu_f32(cudaStream_t stream, const float* src, size_t n, float* dst) {
   cudaError_t ce;
   const DeviceInfo* di = current_device_info(&ce);
   if (!di) return static_cast<int>(ce);
-  gelu_kernel<<<flat_grid(n, di->sm_count), 256, 0, stream>>>(src, n, dst);
+  if (n % 4 == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0) {
+    launch_after_previous(gelu_vec_kernel, dim3(flat_grid(n / 4, di->sm_count)), dim3(256), 0, stream,
+                          reinterpret_cast<const float4*>(src), n / 4,
+                          reinterpret_cast<float4*>(dst));
+    return done();
+  }
+  launch_after_previous(gelu_kernel, dim3(flat_grid(n, di->sm_count)), dim3(256), 0, stream, src, n,
+                        dst);
   return done();
 }
 
@@ -249,7 +378,14 @@ int permute_0213_f32(cudaStream_t stream, const float* src, unsigned d0, unsigne
   const DeviceInfo* di = current_device_info(&ce);
   if (!di) return static_cast<int>(ce);
   const size_t n = static_cast<size_t>(d0) * d1 * d2 * d3;
-  permute_0213_kernel<<<flat_grid(n, di->sm_count), 256, 0, stream>>>(src, d0, d1, d2, d3, dst);
+  if (d3 % 4 == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0) {
+    launch_after_previous(permute_0213_vec_kernel, dim3(flat_grid(n / 4, di->sm_count)), dim3(256), 0,
+                          stream, reinterpret_cast<const float4*>(src), d0, d1, d2, d3 / 4,
+                          reinterpret_cast<float4*>(dst));
+    return done();
+  }
+  launch_after_previous(permute_0213_kernel, dim3(flat_grid(n, di->sm_count)), dim3(256), 0,
+                        stream, src, d0, d1, d2, d3, dst);
   return done();
 }
 
@@ -257,7 +393,7 @@ int transpose_last2_f32(cudaStream_t stream, const float* src, unsigned batch, u
                         unsigned c, float* dst) {
   if (batch > 65535 || (r + 31) / 32 > 65535) return TFCCB200_EOVERFLOW;
   dim3 grid((c + 31) / 32, (r + 31) / 32, batch);
-  transpose_last2_kernel<<<grid, 256, 0, stream>>>(src, r, c, dst);
+  launch_after_previous(transpose_last2_kernel, grid, dim3(256), 0, stream, src, r, c, dst);
   return done();
 }
 

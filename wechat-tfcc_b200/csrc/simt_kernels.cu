@@ -8,6 +8,7 @@
 
 #include "act.cuh"
 #include "internal.h"
+#include "pdl.cuh"
 
 namespace tfccb200 {
 
@@ -167,6 +168,7 @@ skinny_partial_kernel(const float* __restrict__ X, const float* __restrict__ W,
                       unsigned slice_rows, unsigned long long strideX, unsigned long long strideW,
                       unsigned kslices) {
   __shared__ __align__(16) float xs[kSkinnyMaxSlice * MP];
+  pdl_wait();  // launched to overlap the previous kernel's tail: no global access before this
   const unsigned b = blockIdx.z;
   X += strideX * b;
   W += strideW * b;
@@ -467,8 +469,8 @@ int skinny_sgemm(const SgemmArgs& a) {
   dim3 grid((a.N + kSkinnyCols - 1) / kSkinnyCols, ks, a.batch);
   if (grid.y > 65535) return TFCCB200_EOVERFLOW;
 #define TFCCB200_SKINNY(MP)                                                                  \
-  skinny_partial_kernel<MP><<<grid, kSkinnyThreads, 0, a.stream>>>(                          \
-      a.A, a.B, part, a.M, a.N, a.K, rows, a.strideA, a.strideB, ks)
+  launch_after_previous(skinny_partial_kernel<MP>, grid, dim3(kSkinnyThreads), 0, a.stream, a.A,  \
+                        a.B, part, a.M, a.N, a.K, rows, a.strideA, a.strideB, ks)
   if (a.M == 1) TFCCB200_SKINNY(1);
   else if (a.M == 2) TFCCB200_SKINNY(2);
   else if (a.M <= 4) TFCCB200_SKINNY(4);

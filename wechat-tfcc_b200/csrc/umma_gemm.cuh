@@ -45,6 +45,7 @@
 
 #include "../../include/tfcc_b200.h"
 #include "act.cuh"
+#include "pdl.cuh"
 #include "ptx.cuh"
 
 namespace tfccb200 {
@@ -311,6 +312,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                  const UmmaGemmParams p) {
   using Cfg = UmmaGemmConfig<kKind, kSplit, kCtaGroup, BN, kStages>;
   extern __shared__ uint8_t smem_raw[];
+  pdl_release();  // the next kernel in the stream may begin its preamble
 
   // ---- carve shared memory (stage buffers need 1024-byte alignment for the swizzle) ----
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -405,6 +407,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   }
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_gen;
+  // Everything above touched only shared and tensor memory and may have overlapped the tail of
+  // the previous kernel in the stream; operands, bias, scratch and results come after this.
+  pdl_wait();
 
   // The walk of this CTA: first its segments of the k-shared tiles, then whole tiles with a
   // stride of the grid.  Every role iterates the same list.

@@ -137,13 +137,15 @@ int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, Um
   cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = cluster;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
   if (e != cudaSuccess) return static_cast<int>(e);
   count_launch();
@@ -221,6 +223,11 @@ int env_int(const char* name, int fallback) {
 
 }  // namespace
 
+bool stream_k_scratch_ok(const SgemmArgs& a, int sm_count) {
+  return a.workspace && (reinterpret_cast<uintptr_t>(a.workspace) & 255u) == 0 &&
+         a.workspace_bytes >= umma_stream_k_workspace(sm_count);
+}
+
 size_t umma_stream_k_workspace(int sm_count) {
   // flags + one 128 x 256 fp32 partial tile per SM: enough for every tile shape
   return kStreamKFlagBytes + static_cast<size_t>(sm_count) * 128 * 256 * 4;
@@ -233,7 +240,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 }  // namespace
 
 UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count,
-                   int elem_bytes, int force_pair, bool allow_cluster_k) {
+                   int elem_bytes, int force_pair, bool allow_cluster_k, bool allow_stream_k) {
   UmmaPlan best = {false, 0, 1};
   double best_time = 0;
   const unsigned num_kb = (K + 128 / elem_bytes - 1) / (128 / elem_bytes);
@@ -266,11 +273,18 @@ UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_co
           if ((ks - 1) * 128u * bn * 4u > 192u * 1024u) continue;
         }
         const unsigned long long units = tiles * ks;
-        const unsigned long long waves = (units + groups - 1) / groups;
+        double waves = static_cast<double>((units + groups - 1) / groups);
+        double extra = cluster_k_us(ks, bn);
+        unsigned sk_tiles, sk_per;
+        if (allow_stream_k && ks == 1 &&
+            stream_k_split(tiles, static_cast<unsigned>(groups), num_kb, 4, &sk_tiles, &sk_per)) {
+          // the ragged last wave is shared by k-block: fractional waves, plus the hand-off
+          waves = static_cast<double>(tiles) / groups;
+          extra = 2.0;
+        }
         const double kb = static_cast<double>((num_kb + ks - 1) / ks);
-        const double t = static_cast<double>(waves) *
-                             (fixed_us(pair != 0, bn) + kb * per_kblock_us(pair != 0, bn)) +
-                         cluster_k_us(ks, bn);
+        const double t =
+            waves * (fixed_us(pair != 0, bn) + kb * per_kblock_us(pair != 0, bn)) + extra;
         if (best.bn == 0 || t < best_time) {
           best_time = t;
           best.pair = pair != 0;
@@ -325,7 +339,8 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
   const UmmaPlan plan =
       umma_plan(a.M, a.N, a.K, a.batch, di->sm_count,
                 a.precision == TFCCB200_PRECISION_BF16 ? 2 : 4, pair ? 1 : 0,
-                fp32_split && !pair && env_cluster_k != 1);
+                fp32_split && !pair && env_cluster_k != 1,
+                fp32_split && stream_k_scratch_ok(a, di->sm_count));
   UmmaPlan tuned = plan;
   static const int env_bn = env_int("TFCCB200_FORCE_BN", 0);  // tuning knobs, read once
   if (env_bn == 64 || env_bn == 128 || env_bn == 256) tuned.bn = env_bn;
@@ -424,24 +439,41 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
   constexpr auto T = ptx::MmaKind::TF32;
   const bool split = a.precision == TFCCB200_PRECISION_FP32;
   const int sms = di->sm_count;
+
+  // With fewer than two tiles per CTA little or nothing overlaps the epilogue, and an erf per
+  // element on the 256 epilogue threads of an SM costs more there (measured +12..15 us on
+  // 1024x768x3072) than one more pass over C by a full grid (about 6 us).  The activation is
+  // then applied in place by the element-wise kernel; same formula, same bits.
+  const unsigned long long tiles = static_cast<unsigned long long>((a.M + (pair ? 256 : 128) - 1) /
+                                                                   (pair ? 256 : 128)) *
+                                   ((a.N + bn - 1) / bn) * a.batch;
+  const bool unfuse = a.activation != TFCCB200_ACT_NONE && a.num_dst <= 1 && a.col_offset == 0 &&
+                      (a.ldc == 0 || a.ldc == a.N) &&
+                      (a.batch == 1 || a.strideC == static_cast<unsigned long long>(a.M) * a.N) &&
+                      tiles < 2ull * static_cast<unsigned long long>(pair ? sms / 2 : sms);
+  if (unfuse) p.activation = TFCCB200_ACT_NONE;
+  auto finish = [&](int st) {
+    if (st != TFCCB200_OK || !unfuse) return st;
+    return gelu_f32(a.stream, a.C, static_cast<size_t>(a.batch) * a.M * a.N, a.C);
+  };
   if (split) {
     if (!pair) {
-      if (bn == 256) return launch<T, true, 1, 256, 2>(a.stream, ta, tb, p, sms);
-      if (bn == 128) return launch<T, true, 1, 128, 3>(a.stream, ta, tb, p, sms);
-      return launch<T, true, 1, 64, 4>(a.stream, ta, tb, p, sms);
+      if (bn == 256) return finish(launch<T, true, 1, 256, 2>(a.stream, ta, tb, p, sms));
+      if (bn == 128) return finish(launch<T, true, 1, 128, 3>(a.stream, ta, tb, p, sms));
+      return finish(launch<T, true, 1, 64, 4>(a.stream, ta, tb, p, sms));
     }
-    if (bn == 256) return launch<T, true, 2, 256, 3>(a.stream, ta, tb, p, sms);
-    if (bn == 128) return launch<T, true, 2, 128, 4>(a.stream, ta, tb, p, sms);
-    return launch<T, true, 2, 64, 4>(a.stream, ta, tb, p, sms);
+    if (bn == 256) return finish(launch<T, true, 2, 256, 3>(a.stream, ta, tb, p, sms));
+    if (bn == 128) return finish(launch<T, true, 2, 128, 4>(a.stream, ta, tb, p, sms));
+    return finish(launch<T, true, 2, 64, 4>(a.stream, ta, tb, p, sms));
   }
   if (!pair) {
-    if (bn == 256) return launch<T, false, 1, 256, 4>(a.stream, ta, tb, p, sms);
-    if (bn == 128) return launch<T, false, 1, 128, 6>(a.stream, ta, tb, p, sms);
-    return launch<T, false, 1, 64, 8>(a.stream, ta, tb, p, sms);
+    if (bn == 256) return finish(launch<T, false, 1, 256, 4>(a.stream, ta, tb, p, sms));
+    if (bn == 128) return finish(launch<T, false, 1, 128, 6>(a.stream, ta, tb, p, sms));
+    return finish(launch<T, false, 1, 64, 8>(a.stream, ta, tb, p, sms));
   }
-  if (bn == 256) return launch<T, false, 2, 256, 6>(a.stream, ta, tb, p, sms);
-  if (bn == 128) return launch<T, false, 2, 128, 8>(a.stream, ta, tb, p, sms);
-  return launch<T, false, 2, 64, 8>(a.stream, ta, tb, p, sms);
+  if (bn == 256) return finish(launch<T, false, 2, 256, 6>(a.stream, ta, tb, p, sms));
+  if (bn == 128) return finish(launch<T, false, 2, 128, 8>(a.stream, ta, tb, p, sms));
+  return finish(launch<T, false, 2, 64, 8>(a.stream, ta, tb, p, sms));
 }
 
 bool umma_qgemm_supported(const QgemmArgs& a) {
@@ -466,7 +498,7 @@ int umma_qgemm(const QgemmArgs& a, bool pair) {
 
   const bool a_batched = a.batch > 1 && a.strideA != 0;
   const bool b_batched = a.batch > 1 && a.strideB != 0;
-  const int bn = umma_plan(a.M, a.N, a.K, a.batch, di->sm_count, 1, pair ? 1 : 0, false).bn;
+  const int bn = umma_plan(a.M, a.N, a.K, a.batch, di->sm_count, 1, pair ? 1 : 0, false, false).bn;
 
   CUtensorMap ta, tb;
   if (!make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.A, a.K, a.M, a_batched ? a.batch : 1,
