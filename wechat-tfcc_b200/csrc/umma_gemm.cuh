@@ -122,7 +122,16 @@ struct UmmaGemmConfig {
   static constexpr int kBChunkBytes = kBK * 128;
   static constexpr int kBBytes = kBChunks * kBChunkBytes;
   static constexpr int kRawBytes = kABytes + kBBytes;
-  static constexpr int kStageBytes = kRawBytes * (kSplit ? 2 : 1);
+  static constexpr int kStageBytes = kRawBytes;  // one slot of the ring TMA fills
+  // kSplit: the low-order (tail) copies live in a ring of their own.  A raw tile is in flight
+  // from the moment its TMA is issued, a tail tile only from its conversion to the end of
+  // its MMAs, so a few tail slots serve any number of raw slots and the bytes saved buy a
+  // deeper load pipeline.  A tail slot frees when its MMAs retire and the next use needs a
+  // conversion plus two barrier hops before its MMAs can be queued: with CTA pairs (32 KB to
+  // convert per k-block, MMAs of about a microsecond) two slots left the tensor pipe waiting
+  // (measured 6 % slower than three), single CTAs do well with two.
+  static constexpr int kTailStages = kSplit ? (kCtaGroup == 2 ? 3 : 2) : 0;
+  static constexpr int kRingBytes = (kStages + kTailStages) * kRawBytes;
   static constexpr int kBKStepBytes = kUmmaK * 128;    // B advance per MMA k-step
   // MN-major B: 8-bit data uses the plain 128-byte swizzle (atoms of 8 k-rows, 1024 B apart);
   // 32-bit data must use the 128-byte swizzle with 32-byte units (atoms of 4 k-rows, 512 B).
@@ -144,7 +153,7 @@ struct UmmaGemmConfig {
   static constexpr int kEpiStagingBytes = kNumEpilogueWarps * kEpiStageBytes;
   static constexpr int kBarrierBytes = 256 + 16 * kMaxSkSegments + 16;  // + segment table
   static constexpr int kSmemBytes =
-      kStages * kStageBytes + kEpiStagingBytes + kBarrierBytes + 1024;  // +align slack
+      kRingBytes + kEpiStagingBytes + kBarrierBytes + 1024;  // +align slack
   static constexpr uint32_t kIdesc =
       (kKind == ptx::MmaKind::TF32)
           ? ptx::make_idesc(1u, 2u, 2u, 0u, 1u, static_cast<uint32_t>(kTileM), BN)
@@ -317,9 +326,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   // ---- carve shared memory (stage buffers need 1024-byte alignment for the swizzle) ----
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-  uint8_t* epi_stage_gen = smem_gen + kStages * Cfg::kStageBytes;
-  const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes + Cfg::kEpiStagingBytes;
-  uint8_t* bar_gen = smem_gen + kStages * Cfg::kStageBytes + Cfg::kEpiStagingBytes;
+  uint8_t* epi_stage_gen = smem_gen + Cfg::kRingBytes;
+  const uint32_t bar_base = smem_base + Cfg::kRingBytes + Cfg::kEpiStagingBytes;
+  uint8_t* bar_gen = smem_gen + Cfg::kRingBytes + Cfg::kEpiStagingBytes;
+  // Where raw stage s and tail slot t live.  With fewer tail slots than raw stages the tail
+  // ring follows the raw ring; with equally many, every raw stage is followed by its own tail
+  // tile (one combined stage).
+  constexpr bool kTailPerStage = Cfg::kTailStages == kStages;
+  constexpr uint32_t kRawPitch = kTailPerStage ? 2u * Cfg::kRawBytes : 1u * Cfg::kRawBytes;
+  constexpr uint32_t kTailBase = kTailPerStage ? 1u * Cfg::kRawBytes : kStages * Cfg::kRawBytes;
+  constexpr uint32_t kTailPitch = kRawPitch;
   // barrier slots (8 bytes each)
   auto full_raw = [&](int s) { return bar_base + 8u * s; };                 // TMA -> converter / MMA
   auto full_cvt = [&](int s) { return bar_base + 8u * (kStages + s); };     // converter -> MMA
@@ -349,6 +365,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   const unsigned kb_hi = min(num_kb, kb_lo + kb_per_rank);
   const uint32_t red_free = bar_base + 8u * (3 * kStages + 5);   // rank 0 -> others: buffer usable
   const uint32_t red_ready = bar_base + 8u * (3 * kStages + 6);  // others -> rank 0: partials written
+  static_assert(8 * (3 * kStages + 7) <= 256, "barrier slots overrun their area");
+  static_assert(Cfg::kTailStages <= kStages, "a tail slot is released by the raw-stage barrier");
 
   // segment table of the k-shared tiles (see UmmaGemmParams::sk_tiles), filled by thread 0
   uint4* seg_table = reinterpret_cast<uint4*>(bar_gen + 256);
@@ -451,7 +469,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         const int bb = p.b_batched ? static_cast<int>(b) : 0;
         for (unsigned kb = sg.kb_lo; kb < sg.kb_hi; ++kb) {
           bounded_wait<false>(empty_bar(s), ph ^ 1u, TFCCB200_DEV_TIMEOUT_TMA, ctl);
-          const uint32_t stage = smem_base + s * Cfg::kStageBytes;
+          const uint32_t stage = smem_base + s * kRawPitch;
           const int k0 = static_cast<int>(kb * Cfg::kBK);
           if constexpr (kCtaGroup == 2 && !kSplit) {
             // Both CTAs' bytes are counted on the leader's barrier; the MMA
@@ -481,6 +499,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     if (lane == 0 && is_leader) {
       int s = 0;
       uint32_t ph = 0;
+      int ts = 0;       // slot of the tail ring (kSplit)
       unsigned it = 0;  // accumulator hand-offs so far (tiles, or chunks when kSplit)
       const uint16_t pair_mask = 0x3;
       for (unsigned si = 0; si < num_segments; ++si) {
@@ -500,10 +519,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
               bounded_wait<false>(full_raw(s), ph, TFCCB200_DEV_TIMEOUT_MMA, ctl);
             }
             ptx::tc_fence_after_sync();
-            const uint32_t a_hi = smem_base + s * Cfg::kStageBytes;
+            const uint32_t a_hi = smem_base + s * kRawPitch;
             const uint32_t b_hi = a_hi + Cfg::kABytes;
-            const uint32_t a_lo = a_hi + Cfg::kRawBytes;
-            const uint32_t b_lo = b_hi + Cfg::kRawBytes;
+            const uint32_t a_lo = smem_base + kTailBase + ts * kTailPitch;
+            const uint32_t b_lo = a_lo + Cfg::kABytes;
 #pragma unroll
             for (int ks = 0; ks < Cfg::kKSteps; ++ks) {
               const uint64_t da_hi = ptx::smem_desc(a_hi + ks * 32, 16, 1024, ptx::kLayoutSw128);
@@ -522,6 +541,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
               }
             }
             ptx::umma_commit<kCtaGroup>(empty_bar(s), pair_mask);  // stage free when MMAs retire
+            if constexpr (kSplit) {
+              if (++ts == Cfg::kTailStages) ts = 0;
+            }
             if (++s == kStages) { s = 0; ph ^= 1u; }
           }
           ptx::umma_commit<kCtaGroup>(tmem_full(acc), pair_mask);  // this accumulator is complete
@@ -739,12 +761,27 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       const uint32_t leader_full_cvt0 = (kCtaGroup == 2) ? ptx::mapa(full_cvt(0), 0) : full_cvt(0);
       int s = 0;
       uint32_t ph = 0;
+      int ts = 0;  // tail ring slot
+      // A tail slot is free again when the MMAs of the k-block that used it kTailStages
+      // k-blocks ago have retired, which is what that k-block's raw-stage barrier (empty_bar)
+      // reports: the converter follows the raw ring with that lag.
+      unsigned done = 0;  // k-blocks converted so far
+      int ls = 0;         // raw stage of the k-block kTailStages back, and its phase
+      uint32_t lph = 0;
       for (unsigned si = 0; si < num_segments; ++si) {
         const UmmaSegment sg = segment(si);
         for (unsigned kb = sg.kb_lo; kb < sg.kb_hi; ++kb) {
+          if constexpr (Cfg::kTailStages < kStages) {
+            // (with as many tail slots as raw stages the raw tile's arrival implies it)
+            if (done >= static_cast<unsigned>(Cfg::kTailStages)) {
+              bounded_wait<false>(empty_bar(ls), lph, TFCCB200_DEV_TIMEOUT_CONVERT, ctl);
+              if (++ls == kStages) { ls = 0; lph ^= 1u; }
+            }
+            ++done;
+          }
           bounded_wait<false>(full_raw(s), ph, TFCCB200_DEV_TIMEOUT_CONVERT, ctl);
-          float4* raw = reinterpret_cast<float4*>(smem_gen + s * Cfg::kStageBytes);
-          float4* tail = reinterpret_cast<float4*>(smem_gen + s * Cfg::kStageBytes + Cfg::kRawBytes);
+          float4* raw = reinterpret_cast<float4*>(smem_gen + s * kRawPitch);
+          float4* tail = reinterpret_cast<float4*>(smem_gen + kTailBase + ts * kTailPitch);
           constexpr int kIter = kVecs / kCThreads;
           constexpr int kUnroll = (kIter % 4 == 0) ? 4 : (kIter % 2 == 0 ? 2 : 1);
 #pragma unroll 1
@@ -777,6 +814,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             else ptx::mbar_arrive(full_cvt(s));
           }
           if (++s == kStages) { s = 0; ph ^= 1u; }
+          if (++ts == Cfg::kTailStages) ts = 0;
         }
       }
     }

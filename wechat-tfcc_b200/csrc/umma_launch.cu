@@ -107,7 +107,7 @@ int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, Um
     // K split over a cluster: one tile per cluster, all tiles resident at once
     if (!kSplit || kCtaGroup != 1 || total * p.cluster_k > static_cast<unsigned>(sm_count))
       return TFCCB200_EUNSUPPORTED;
-    if ((p.cluster_k - 1) * 128u * BN * 4u > static_cast<unsigned>(kStages * Cfg::kStageBytes))
+    if ((p.cluster_k - 1) * 128u * BN * 4u > static_cast<unsigned>(Cfg::kRingBytes))
       return TFCCB200_EUNSUPPORTED;  // partial tiles would not fit rank 0's stage buffers
     groups = static_cast<unsigned>(total) * p.cluster_k;
     cluster = p.cluster_k;
@@ -192,8 +192,8 @@ int active_clusters_fp32(int bn, unsigned ks) {
   int v = slot.load(std::memory_order_acquire);
   if (v == 0) {
     const int n = bn == 256 ? query_active_clusters<256, 2>(ks)
-                            : (bn == 128 ? query_active_clusters<128, 3>(ks)
-                                         : query_active_clusters<64, 4>(ks));
+                            : (bn == 128 ? query_active_clusters<128, 4>(ks)
+                                         : query_active_clusters<64, 6>(ks));
     v = n + 1;
     slot.store(v, std::memory_order_release);
   }
@@ -208,13 +208,13 @@ int active_clusters_fp32(int bn, unsigned ks) {
 // hand-off of (ks - 1) partial tiles to rank 0 and their summation.
 double per_kblock_us(bool pair, int bn) {
   if (pair) return bn == 256 ? 1.24 : (bn == 128 ? 0.95 : 0.9);
-  return bn == 256 ? 1.48 : (bn == 128 ? 0.81 : 0.70);
+  return bn == 256 ? 1.48 : (bn == 128 ? 0.71 : 0.64);
 }
 double fixed_us(bool pair, int bn) {
   if (pair) return 11.0;
-  return bn == 256 ? 12.5 : 3.8 + 0.042 * bn;
+  return bn == 256 ? 12.5 : (bn == 128 ? 7.2 : 5.5);
 }
-double cluster_k_us(unsigned ks, int bn) { return ks > 1 ? 1.2 + 0.8 * (ks - 1) + 0.018 * bn : 0.0; }
+double cluster_k_us(unsigned ks, int bn) { return ks > 1 ? 0.3 + 1.0 * ks + 0.02 * (bn - 64) : 0.0; }
 
 int env_int(const char* name, int fallback) {
   const char* v = std::getenv(name);
@@ -280,7 +280,7 @@ UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_co
             stream_k_split(tiles, static_cast<unsigned>(groups), num_kb, 4, &sk_tiles, &sk_per)) {
           // the ragged last wave is shared by k-block: fractional waves, plus the hand-off
           waves = static_cast<double>(tiles) / groups;
-          extra = 2.0;
+          extra = 4.0;
         }
         const double kb = static_cast<double>((num_kb + ks - 1) / ks);
         const double t =
@@ -459,12 +459,12 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
   if (split) {
     if (!pair) {
       if (bn == 256) return finish(launch<T, true, 1, 256, 2>(a.stream, ta, tb, p, sms));
-      if (bn == 128) return finish(launch<T, true, 1, 128, 3>(a.stream, ta, tb, p, sms));
-      return finish(launch<T, true, 1, 64, 4>(a.stream, ta, tb, p, sms));
+      if (bn == 128) return finish(launch<T, true, 1, 128, 4>(a.stream, ta, tb, p, sms));
+      return finish(launch<T, true, 1, 64, 6>(a.stream, ta, tb, p, sms));
     }
     if (bn == 256) return finish(launch<T, true, 2, 256, 3>(a.stream, ta, tb, p, sms));
-    if (bn == 128) return finish(launch<T, true, 2, 128, 4>(a.stream, ta, tb, p, sms));
-    return finish(launch<T, true, 2, 64, 4>(a.stream, ta, tb, p, sms));
+    if (bn == 128) return finish(launch<T, true, 2, 128, 5>(a.stream, ta, tb, p, sms));
+    return finish(launch<T, true, 2, 64, 6>(a.stream, ta, tb, p, sms));
   }
   if (!pair) {
     if (bn == 256) return finish(launch<T, false, 1, 256, 4>(a.stream, ta, tb, p, sms));
