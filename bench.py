@@ -38,7 +38,7 @@ FLOP_PER_STEP = 2.0 * M * N * K
 # dram__bytes_read.sum + dram__bytes_write.sum of one umma_gemm_kernel launch on the 8192^3
 # problem, from the ncu capture summarised in profiles/umma_gemm_tf32x3_pair_8192_traffic.md
 # (2,288,931,584 B read + 256,376,832 B written).  Only valid for the single-GPU headline size.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 2545308416
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2536176640
 
 
 def measured_peaks():
