@@ -291,6 +291,10 @@ TFCCB200_API size_t tfccb200_sgemm_skinny_static_capacity(void);
  * still being multiplied; no TMA or multicast instruction touches peer memory.  When the
  * kernel has finished on every rank (the caller runs a cross-rank barrier after it), each
  * rank holds the complete C.  Needs K % 4 == 0, N_shard % 4 == 0, 16-byte aligned bases.
+ * `C_multicast` (may be NULL) is the address of the same C through an NVLink multicast object
+ * that every rank's C is bound to (NVLS; torch symmetric memory's multicast_ptr): when given,
+ * each line is stored once with multimem.st and the switch replicates it to all ranks, so a
+ * GPU sends its shard once instead of num_ranks - 1 times; C_ranks is then only checked.
  * `workspace` (256-byte aligned, tfccb200_sgemm_workspace(M, N_shard, K, 1, mode) bytes, may be
  * NULL) lets the kernel share the tiles of a ragged last wave by k-block; the result is
  * the same bit for bit with or without it.
@@ -300,8 +304,8 @@ TFCCB200_API int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const 
                                             float* const* C_ranks, unsigned num_ranks,
                                             unsigned rank, const float* bias_shard, unsigned M,
                                             unsigned N_shard, unsigned K, int precision_mode,
-                                            void* workspace, size_t workspace_bytes,
-                                            int* device_status);
+                                            float* C_multicast, void* workspace,
+                                            size_t workspace_bytes, int* device_status);
 
 /*
  * dst[m][g*ns + j] = src[g][m][j] for g < G, m < M, j < ns (fp32, ns % 4 == 0).

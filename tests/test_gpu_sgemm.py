@@ -230,7 +230,7 @@ def test_nsplit_push_entry_point_on_one_gpu(pkg, orc):
         tb = torch.from_numpy(np.ascontiguousarray(b[:, r * ns:(r + 1) * ns])).to(d)
         tbias = torch.from_numpy(np.ascontiguousarray(bias[r * ns:(r + 1) * ns])).to(d)
         st = pkg.lib.tfccb200_sgemm_nsplit_push(stream, ta.data_ptr(), tb.data_ptr(), ptrs, g, r,
-                                                tbias.data_ptr(), m, ns, k, 0, None, 0, None)
+                                                tbias.data_ptr(), m, ns, k, 0, None, None, 0, None)
         assert st == 0, pkg.lib.tfccb200_strerror(st)
         torch.cuda.synchronize()
     truth = orc.blas_matmul(a, b, bias)
@@ -239,7 +239,7 @@ def test_nsplit_push_entry_point_on_one_gpu(pkg, orc):
     assert torch.equal(outs[0], outs[1])
     # misaligned shard width is refused
     assert pkg.lib.tfccb200_sgemm_nsplit_push(stream, ta.data_ptr(), ta.data_ptr(), ptrs, g, 0, None,
-                                              m, 130, k, 0, None, 0, None) == -2
+                                              m, 130, k, 0, None, None, 0, None) == -2
 
 
 def _sgemm_raw(pkg, a, b, bias, path, workspace):

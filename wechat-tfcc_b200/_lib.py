@@ -54,7 +54,7 @@ class _Lib:
             "tfccb200_quantize_f32": (i, [vp, vp, sz, vp, vp, vp, i]),
             "tfccb200_dequantize_f32": (i, [vp, vp, i, sz, vp, vp, vp]),
             "tfccb200_requantize": (i, [vp, vp, i, sz, vp, vp, vp, vp, vp, i]),
-            "tfccb200_sgemm_nsplit_push": (i, [vp, vp, vp, C.POINTER(C.c_void_p), u, u, vp, u, u, u, i, vp, C.c_size_t, vp]),
+            "tfccb200_sgemm_nsplit_push": (i, [vp, vp, vp, C.POINTER(C.c_void_p), u, u, vp, u, u, u, i, vp, vp, C.c_size_t, vp]),
             "tfccb200_sgemm_skinny_static": (i, [vp, vp, vp, vp, vp, u, u, u]),
             "tfccb200_sgemm_skinny_static_capacity": (sz, []),
             "tfccb200_interleave_panels_f32": (i, [vp, vp, vp, u, u, u]),

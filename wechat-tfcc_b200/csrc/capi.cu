@@ -435,8 +435,8 @@ int tfccb200_requantize(void* stream, const void* src, int src_type, size_t n,
 int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shard,
                                float* const* C_ranks, unsigned num_ranks, unsigned rank,
                                const float* bias_shard, unsigned M, unsigned N_shard, unsigned K,
-                               int precision_mode, void* workspace, size_t workspace_bytes,
-                               int* device_status) {
+                               int precision_mode, float* C_multicast, void* workspace,
+                               size_t workspace_bytes, int* device_status) {
   if (!A || !B_shard || !C_ranks || num_ranks == 0 || num_ranks > 8 || rank >= num_ranks)
     return TFCCB200_EINVAL;
   if (M == 0 || N_shard == 0 || K == 0) return TFCCB200_EINVAL;
@@ -460,6 +460,8 @@ int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shar
     a.dst[d] = C_ranks[d];
   }
   a.C = C_ranks[rank];
+  if (C_multicast && (reinterpret_cast<uintptr_t>(C_multicast) & 15u)) return TFCCB200_EALIGN;
+  a.mc_dst = C_multicast;
   a.ldc = n_total;
   a.col_offset = rank * N_shard;
   if (!umma_sgemm_supported(a)) return TFCCB200_EALIGN;  // N_shard % 4, K % 4, 16-byte bases

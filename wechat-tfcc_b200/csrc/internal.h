@@ -39,6 +39,7 @@ struct SgemmArgs {
   // starting at column `col_offset` (num_dst == 0: the plain case, C with pitch N).
   float* dst[8];
   unsigned num_dst;
+  float* mc_dst;  // NVLink multicast alias of the destinations, or nullptr
   unsigned long long ldc;
   unsigned col_offset;
   int activation;  // TFCCB200_ACT_*: applied to A.B + bias before the store

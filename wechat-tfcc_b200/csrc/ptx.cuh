@@ -148,6 +148,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void* tmap,
       : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// One store that the NVLink switch delivers to the same offset of every GPU bound to the
+// multicast object behind `mc_addr` (this GPU included).
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               :
+               : "l"(mc_addr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)),
+                 "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
 // Same, issued by both CTAs of a cta_group::2 pair; the byte count lands on the
 // barrier at `bar` in the pair's even-ranked CTA (peer bit cleared by the caller).
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const void* tmap,

@@ -59,6 +59,9 @@ struct UmmaGemmParams {
   // dst[d] + b*strideC + i*ldc + col_offset + j.
   void* dst[kMaxDestinations];
   unsigned num_dst;
+  // float kinds: when set, the tile goes out through this NVLink multicast address instead
+  // (one store reaches the same offset of every GPU bound to it) and dst[] is not written
+  void* mc_dst;
   unsigned long long ldc;  // row pitch of the destinations, in elements
   unsigned col_offset;     // first destination column of this problem's column 0
   const float* bias;       // [N] or nullptr (float kinds only)
@@ -291,8 +294,12 @@ __device__ __forceinline__ void epi_flush_block(uint32_t* stage, uint32_t lane, 
     if (grow < p.M && col_ok) {
       const unsigned long long off =
           batch_off + static_cast<unsigned long long>(grow) * p.ldc + p.col_offset + col;
-      for (unsigned d = 0; d < p.num_dst; ++d)
-        *reinterpret_cast<uint4*>(static_cast<uint32_t*>(p.dst[d]) + off) = v;
+      if (kIsFloat && p.mc_dst) {
+        ptx::multimem_st_v4(static_cast<uint32_t*>(p.mc_dst) + off, v);
+      } else {
+        for (unsigned d = 0; d < p.num_dst; ++d)
+          *reinterpret_cast<uint4*>(static_cast<uint32_t*>(p.dst[d]) + off) = v;
+      }
     }
   }
   __syncwarp();

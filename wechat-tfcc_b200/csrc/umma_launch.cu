@@ -375,6 +375,7 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
     if (q.num_dst > kMaxDestinations) return TFCCB200_EINVAL;
     q.dst[0] = a.C;
     for (unsigned d = 0; d < a.num_dst; ++d) q.dst[d] = a.dst[d];
+    q.mc_dst = a.mc_dst;
     q.ldc = a.ldc ? a.ldc : a.N;
     q.col_offset = a.col_offset;
     q.bias = a.bias;
@@ -409,6 +410,7 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
   if (p.num_dst > kMaxDestinations) return TFCCB200_EINVAL;
   p.dst[0] = a.C;
   for (unsigned d = 0; d < a.num_dst; ++d) p.dst[d] = a.dst[d];
+  p.mc_dst = a.mc_dst;
   p.ldc = a.ldc ? a.ldc : a.N;
   p.col_offset = a.col_offset;
   p.bias = a.bias;
