@@ -295,6 +295,28 @@ def test_k_shared_last_wave_is_bit_identical(pkg, orc, path, m, n, k, batch):
     assert orc.normwise_rel_error(got, truth) < TOL_FP32
 
 
+def test_k_shared_by_consecutive_ctas_through_scratch(pkg, orc):
+    """Few tiles and a long K (the encoder's second FFN layer): with scratch the plan lets
+    three consecutive CTAs share a tile's k-blocks and the first of them adds the others'
+    partial tiles in rank order.  Deterministic, within the fp32 tolerance; the grouping of the
+    sum differs from the unsplit run, so the two are compared by error, not bit for bit."""
+    d = dev_of()
+    g = torch.Generator(device=d)
+    g.manual_seed(77)
+    m, k, n = 1024, 3072, 768
+    a = torch.empty((m, k), dtype=torch.float32, device=d).uniform_(-1, 1, generator=g)
+    b = torch.empty((k, n), dtype=torch.float32, device=d).normal_(0, 0.02, generator=g)
+    bias = torch.empty((n,), dtype=torch.float32, device=d).uniform_(-1, 1, generator=g)
+    plain = _sgemm_raw(pkg, a, b, bias, "auto", workspace=False)
+    shared = _sgemm_raw(pkg, a, b, bias, "auto", workspace=True)
+    again = _sgemm_raw(pkg, a, b, bias, "auto", workspace=True)
+    assert torch.equal(shared, again)
+    truth = a.cpu().numpy().astype(np.float64) @ b.cpu().numpy().astype(np.float64) + \
+        bias.cpu().numpy().astype(np.float64)
+    assert orc.normwise_rel_error(shared.cpu().numpy(), truth) < TOL_FP32
+    assert orc.normwise_rel_error(plain.cpu().numpy(), truth) < TOL_FP32
+
+
 def _encoder_stack_f64(x, weights):
     """Config 4 in float64 numpy: 4-layer BERT-base-shaped post-LN encoder with the reference's
     formulas (softmax with max subtraction, erf GELU, two-pass layer norm, gamma 1, beta 0,

@@ -288,7 +288,7 @@ size_t tfccb200_sgemm_workspace(unsigned M, unsigned N, unsigned K, unsigned bat
   // kernel keeps the partial tiles of a k-shared last wave there.
   size_t need = 0;
   if (precision_mode == TFCCB200_PRECISION_FP32 &&
-      static_cast<unsigned long long>(M) * N * batch > static_cast<unsigned long long>(sms) * 128 * 64)
+      static_cast<unsigned long long>(M) * N * K * batch >= (1ull << 22))  // tensor-core sized
     need = umma_stream_k_workspace(sms);
   if (precision_mode == TFCCB200_PRECISION_BF16)  // dense upper bound: both operands batched
     need = bf16_staging_bytes(M, N, K, batch, M * K, K * N);

@@ -66,6 +66,7 @@ struct UmmaPlan {
   bool pair;
   int bn;
   unsigned cluster_k;  // > 1: K of one tile is shared by a cluster of that many single CTAs
+  unsigned global_k;   // > 1: ... by that many consecutive CTAs, partial tiles through scratch
 };
 UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count,
                    int elem_bytes, int force_pair, bool allow_cluster_k, bool allow_stream_k);

@@ -94,6 +94,12 @@ struct UmmaGemmParams {
   // the running sum, so results are bit-identical to the unsplit order.
   unsigned sk_tiles;
   unsigned sk_kb_per_group;  // multiple of kb_per_chunk, >= k-blocks of one tile
+  // kSplit, single CTAs, global_k > 1 (instead of the above): fewer tiles than SMs, so
+  // global_k consecutive CTAs share one tile's k-blocks.  Ranks 1.. publish their sums like a
+  // head piece; rank 0 adds them to its own in rank order (deterministic) and stores the tile.
+  // Unlike cluster_k this needs no co-scheduled cluster, so any global_k that fits the SM
+  // count works; the partial tiles cross L2 instead of distributed shared memory.
+  unsigned global_k;
   float* sk_partials;        // [grid CTAs][128 x BN] fp32
   unsigned* sk_flags;        // [grid CTAs], zero before the launch
   unsigned long long sk_capacity;  // host only: bytes available behind sk_partials
@@ -108,6 +114,7 @@ struct UmmaSegment {
 };
 constexpr unsigned kSegHead = 1;  // k-blocks [0, kb_hi): partial sums go to the next group
 constexpr unsigned kSegTail = 2;  // k-blocks [kb_lo, end): continues the previous group's sums
+constexpr unsigned kSegGather = 3;  // rank 0 of a global K split: adds the other ranks' sums
 constexpr int kMaxSkSegments = 4;
 
 template <ptx::MmaKind kKind, bool kSplit, int kCtaGroup, int BN, int kStages>
@@ -240,6 +247,18 @@ __device__ __forceinline__ void sk_load_partial(float* sum, const float4* src) {
                  : "l"(src), "n"(V * 512)
                  : "memory");
     sk_load_partial<kCount, V + 1>(sum, src);
+  }
+}
+template <int kCount, int V = 0>
+__device__ __forceinline__ void sk_add_partial(float* sum, const float4* src) {
+  if constexpr (V < kCount) {
+    float a, b, c, d;
+    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4 + %5];"
+                 : "=f"(a), "=f"(b), "=f"(c), "=f"(d)
+                 : "l"(src), "n"(V * 512)
+                 : "memory");
+    sum[4 * V] += a; sum[4 * V + 1] += b; sum[4 * V + 2] += c; sum[4 * V + 3] += d;
+    sk_add_partial<kCount, V + 1>(sum, src);
   }
 }
 template <int kCount, int V = 0>
@@ -396,7 +415,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     ptx::mbar_init(red_ready, ksplit > 1 ? (ksplit - 1) * Cfg::kNumEpilogueWarps * 32 : 1);
     *abort_flag = 0;
     unsigned nseg = 0;
-    if (kSplit && p.sk_tiles) {
+    if (kSplit && p.global_k > 1) {
+      const unsigned tile = group_id / p.global_k, r = group_id % p.global_k;
+      const unsigned per = (num_kb + p.global_k - 1) / p.global_k;
+      const unsigned lo = min(num_kb, r * per), hi = min(num_kb, lo + per);
+      if (tile < total_tiles) seg_table[nseg++] = make_uint4(tile, lo, hi, r == 0 ? kSegGather : kSegHead);
+    } else if (kSplit && p.sk_tiles) {
       const unsigned long long total_kb = static_cast<unsigned long long>(p.sk_tiles) * num_kb;
       const unsigned long long s0 = static_cast<unsigned long long>(group_id) * p.sk_kb_per_group;
       const unsigned long long e0 = min(total_kb, s0 + p.sk_kb_per_group);
@@ -648,6 +672,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           __threadfence();
           atomicAdd(p.sk_flags + my_cta, 1u);
           continue;
+        }
+        if (sg.mode == kSegGather) {
+          // rank 0 of a global K split: the other ranks' sums, in rank order
+          for (unsigned r = 1; r < p.global_k; ++r) {
+            const unsigned src_cta = group_id + r;
+            if (lane == 0)
+              bounded_flag_wait(p.sk_flags + src_cta, Cfg::kNumEpilogueWarps * 32u,
+                                TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
+            __syncwarp();
+            sk_add_partial<kSkVec>(sum, reinterpret_cast<const float4*>(p.sk_partials) +
+                                            static_cast<size_t>(src_cta) * kSkTileVecs + sk_slot);
+          }
         }
         if (ksplit > 1) {
           // ---- K split over the cluster: partial sums meet in rank 0's (now idle) stage

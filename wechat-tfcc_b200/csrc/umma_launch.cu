@@ -115,17 +115,29 @@ int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, Um
     p.cluster_k = 1;
   }
   unsigned sk_tiles = 0, sk_per = 0;
-  if (kSplit && p.sk_flags && p.cluster_k == 1 &&
+  if (kSplit && kCtaGroup == 1 && p.global_k > 1 && p.sk_flags && p.cluster_k == 1 &&
+      total * p.global_k <= static_cast<unsigned>(sm_count) &&
+      static_cast<size_t>(total) * p.global_k * sizeof(unsigned) <= kStreamKFlagBytes &&
+      total * p.global_k * Cfg::kBM * BN * 4ull <= p.sk_capacity) {
+    // K shared by global_k consecutive CTAs per tile, partial tiles through the scratch
+    groups = static_cast<unsigned>(total) * p.global_k;
+    p.sk_tiles = static_cast<unsigned>(total);  // no tile is walked whole
+    p.sk_kb_per_group = 0;
+    e = cudaMemsetAsync(p.sk_flags, 0, static_cast<size_t>(groups) * sizeof(unsigned), stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  } else if (kSplit && p.sk_flags && p.cluster_k == 1 &&
       stream_k_split(total, groups, (p.K + Cfg::kBK - 1) / Cfg::kBK, p.kb_per_chunk, &sk_tiles,
                      &sk_per) &&
       static_cast<size_t>(groups) * kCtaGroup * sizeof(unsigned) <= kStreamKFlagBytes &&
       static_cast<unsigned long long>(groups) * kCtaGroup * Cfg::kBM * BN * 4ull <= p.sk_capacity) {
+    p.global_k = 1;
     p.sk_tiles = sk_tiles;
     p.sk_kb_per_group = sk_per;
     e = cudaMemsetAsync(p.sk_flags, 0, static_cast<size_t>(groups) * kCtaGroup * sizeof(unsigned),
                         stream);
     if (e != cudaSuccess) return static_cast<int>(e);
   } else {
+    p.global_k = 1;
     p.sk_tiles = 0;
     p.sk_kb_per_group = 0;
     p.sk_flags = nullptr;
@@ -241,7 +253,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count,
                    int elem_bytes, int force_pair, bool allow_cluster_k, bool allow_stream_k) {
-  UmmaPlan best = {false, 0, 1};
+  UmmaPlan best = {false, 0, 1, 1};
   double best_time = 0;
   const unsigned num_kb = (K + 128 / elem_bytes - 1) / (128 / elem_bytes);
   for (int pair = 0; pair <= 1; ++pair) {
@@ -290,6 +302,26 @@ UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_co
           best.pair = pair != 0;
           best.bn = bn;
           best.cluster_k = ks;
+          best.global_k = 1;
+        }
+      }
+      // K shared by consecutive CTAs through the scratch: any split that fits the SMs, at a
+      // higher fixed price than the cluster form (flag reset, partial tiles through L2, the
+      // gather; measured 8-11 us) -- pays for long K on few tiles (1024x3072x768: 48 -> 41 us).
+      if (allow_stream_k && allow_cluster_k && !pair) {
+        for (unsigned gk = 2; gk <= 6; ++gk) {
+          if (tiles * gk > static_cast<unsigned long long>(sm_count)) break;
+          const unsigned per = (num_kb + gk - 1) / gk;
+          if (per < 4) break;
+          const double t = fixed_us(false, bn) + per * per_kblock_us(false, bn) +
+                           (bn == 64 ? 8.5 : (bn == 128 ? 10.5 : 13.0));
+          if (t < best_time) {
+            best_time = t;
+            best.pair = false;
+            best.bn = bn;
+            best.cluster_k = 1;
+            best.global_k = gk;
+          }
         }
       }
     }
@@ -299,6 +331,7 @@ UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_co
     best.bn = (best.pair ? 256 : 128) / elem_bytes;
     if (best.bn < 64) best.bn = 64;
     best.cluster_k = 1;
+    best.global_k = 1;
   }
   return best;
 }
@@ -435,6 +468,10 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
     p.sk_capacity = a.workspace_bytes - kStreamKFlagBytes;
   }
   p.cluster_k = (fp32_split && !pair) ? tuned.cluster_k : 1;
+  static const int env_global_k = env_int("TFCCB200_GLOBAL_K", -1);  // -1: planned; 1: off
+  p.global_k = (fp32_split && !pair) ? tuned.global_k : 1;
+  if (env_global_k >= 1) p.global_k = (fp32_split && !pair) ? env_global_k : 1;
+  if (p.global_k > 1) p.cluster_k = 1;
   p.status = a.status;
   p.timeout_ns = kDefaultTimeoutNs;
 
