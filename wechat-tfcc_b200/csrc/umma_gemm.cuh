@@ -24,7 +24,9 @@
 //               B: (BN_local*elem/128) boxes of [k-block rows x 128 B], MN-major
 //                  canonical layout: 128B swizzle of 16-byte units for int8, of
 //                  32-byte units for fp32 (the TMA mode SWIZZLE_128B_ATOM_32B)
-//               (+ a second copy of both for the TF32 tails when kSplit)
+//               (+ tail tiles of the same shape for the TF32 tails when kSplit:
+//                one per stage for CTA pairs, a ring of two of their own for single
+//                CTAs, which leaves room for a deeper ring of raw stages)
 // Warps without kSplit: 0 = TMA producer, 1 = MMA issuer and TMEM owner,
 // 2..5 = epilogue (one TMEM lane quarter each).
 //
@@ -37,6 +39,18 @@
 // the MMA issuer fills the other buffer.  The register budget is rebalanced
 // with setmaxnreg: warpgroup 0 = {TMA, MMA, 2 idle warps}, warpgroups 1-2 =
 // epilogue (hold a 128 x BN fp32 running sum), warpgroup 3 = converters.
+//
+// How the tiles of a problem reach the CTAs (kSplit; see UmmaGemmParams):
+//   * by default every CTA / pair walks whole tiles with a stride of the grid;
+//   * cluster_k > 1: fewer tiles than SMs -- a thread-block cluster shares one tile's
+//     k-blocks and reduces through distributed shared memory;
+//   * global_k > 1: the same without a cluster, partial tiles through scratch in L2;
+//   * sk_tiles > 0: more tiles than the grid but a ragged last wave -- the last one to two
+//     waves are cut into equal k-block ranges, a cut tile being started by one group and
+//     finished (same summation order, same bits) by the next.
+// The kernel is launched with programmatic stream serialisation: everything up to
+// pdl_wait() (barriers, tensor memory, descriptor prefetch) may overlap the previous
+// kernel's tail.
 //
 // Every wait on an mbarrier is bounded: after `timeout_ns` the waiter raises a
 // CTA-wide abort flag, ORs a bit into *status and carries on without the data,
