@@ -317,6 +317,40 @@ def test_k_shared_by_consecutive_ctas_through_scratch(pkg, orc):
     assert orc.normwise_rel_error(plain.cpu().numpy(), truth) < TOL_FP32
 
 
+def test_random_shapes_through_the_planner(pkg, orc):
+    """Forty seeded shapes in the tensor-core range, with scratch (so that the planner may pick
+    any of: whole tiles, K split over a cluster, K split through scratch, k-shared last wave,
+    CTA pairs): every result within the fp32 tolerance of the float64 product on sampled rows,
+    and identical on a second run."""
+    d = dev_of()
+    rng = np.random.default_rng(2024)
+    g = torch.Generator(device=d)
+    g.manual_seed(2024)
+    for case in range(40):
+        batch = int(rng.choice([1, 1, 1, 2, 5, 24]))
+        m = int(rng.choice([32, 96, 128, 200, 256, 520, 1024, 1536, 2048, 3000]))
+        n = 4 * int(rng.integers(16, 800))
+        k = 4 * int(rng.integers(8, 1100))
+        if batch * m * n * k > 3 * 10 ** 10:
+            continue
+        shape_a = (batch, m, k) if batch > 1 else (m, k)
+        shape_b = (batch, k, n) if batch > 1 else (k, n)
+        a = torch.empty(shape_a, dtype=torch.float32, device=d).uniform_(-1, 1, generator=g)
+        b = torch.empty(shape_b, dtype=torch.float32, device=d).uniform_(-1, 1, generator=g)
+        bias = torch.empty((n,), dtype=torch.float32, device=d).uniform_(-1, 1, generator=g)
+        got = _sgemm_raw(pkg, a, b, bias, "auto", workspace=True)
+        again = _sgemm_raw(pkg, a, b, bias, "auto", workspace=True)
+        assert torch.equal(got, again), (case, batch, m, n, k)
+        rows = rng.choice(m, size=min(m, 6), replace=False)
+        bi = int(rng.integers(0, batch))
+        a0 = (a[bi] if batch > 1 else a).cpu().numpy()
+        b0 = (b[bi] if batch > 1 else b).cpu().numpy()
+        truth = a0[rows].astype(np.float64) @ b0.astype(np.float64) + \
+            bias.cpu().numpy().astype(np.float64)
+        sel = (got[bi] if batch > 1 else got)[torch.from_numpy(rows).to(d)].cpu().numpy()
+        assert orc.normwise_rel_error(sel, truth) < TOL_FP32, (case, batch, m, n, k)
+
+
 def _encoder_stack_f64(x, weights):
     """Config 4 in float64 numpy: 4-layer BERT-base-shaped post-LN encoder with the reference's
     formulas (softmax with max subtraction, erf GELU, two-pass layer norm, gamma 1, beta 0,
