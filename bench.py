@@ -437,6 +437,31 @@ def extra_measurements(torch, pkg, dev, peaks):
                 _, med = time_launches(torch, f, 20, fl)
                 out[nm] = {"us": med * 1e3, "gbs": nb / (med * 1e-3) / 1e9}
         del ops, calls
+    # int8 at the headline size: u8[8192,8192] x s8[8192,8192] -> s32 (13.8 waves of pair tiles)
+    n8 = 8192
+    ops = []
+    for _ in range(2):
+        qa = torch.randint(0, 256, (n8, n8), dtype=torch.uint8, device=dev)
+        qb = torch.randint(-127, 128, (n8, n8), dtype=torch.int8, device=dev)
+        ops.append((qa, qb, pkg.quantization.reduce_sum(qa, True),
+                    pkg.quantization.reduce_sum(qb, False),
+                    torch.empty((n8, n8), dtype=torch.int32, device=dev)))
+
+    def make8(qa, qb, ra, rb, c):
+        def fn():
+            st = lib.tfccb200_qgemm_u8s8s32(
+                torch.cuda.current_stream().cuda_stream, qa.data_ptr(), 0, ra.data_ptr(), 0, -128,
+                qb.data_ptr(), 0, rb.data_ptr(), 0, 0, c.data_ptr(), n8 * n8, n8, n8, n8, 1,
+                sess.status_ptr)
+            assert st == 0, st
+        return fn
+    calls = [make8(*o) for o in ops]
+    for c in calls:
+        c()
+    train_us, _ = time_graph_train(torch, calls * 3)
+    out["int8_8192"] = {"train_us": train_us, "tops": 2.0 * n8 ** 3 / (train_us * 1e-6) / 1e12,
+                        "frac_of_nominal_dense_int8": 2.0 * n8 ** 3 / (train_us * 1e-6) / 4.5e15}
+    del ops, calls
     sess.sync()
     return out
 

@@ -83,6 +83,12 @@ TFCCB200_API int tfccb200_version(void);
  * added in the epilogue, so C is written once instead of being pre-filled and
  * accumulated into.
  *
+ * Non-finite inputs: NaN propagates as NaN on every path.  On the tensor-core paths an
+ * infinite element makes its whole output row (column) NaN where IEEE arithmetic would give
+ * +-inf, because the fp32 product is rebuilt from head and tail parts and inf has no tail
+ * (inf - inf); the CUDA-core paths (M <= 8, unaligned shapes) follow IEEE.  The reference's
+ * own tests feed finite values only.
+ *
  * workspace / workspace_bytes: scratch in device memory of at least
  * tfccb200_sgemm_workspace() bytes (may be NULL when that returns 0).
  * device_status: optional int in device memory; kernels OR a TFCCB200_DEV_*
