@@ -14,9 +14,19 @@
  *  tfcc/cuda/interfaces/tfcc_cudablasinterface.cu:201-217).
  *
  * Launches are asynchronous on the given stream; nothing here synchronises
- * unless the comment of the function says so.  The library keeps no mutable
- * global state besides per-device caches of immutable facts (SM count, driver
- * entry point for tensor-map encoding).
+ * unless the comment of the function says so.  Entry points are re-entrant
+ * across host threads and streams.  State the library keeps per process:
+ * per-device caches of immutable facts (SM count, driver entry point for
+ * tensor-map encoding, occupancy of cluster launches); a stream-ordered memory
+ * pool of its own per device, used only by the *_host entry points for their
+ * staging buffers (the device's default pool is never touched); the 20 MiB
+ * device array behind tfccb200_sgemm_skinny_static, shared by all calls of that
+ * one entry point; the launch counter; the device groups created by
+ * tfccb200_group_create.
+ *
+ * Scratch memory ("workspace") passed to an entry point belongs to that call
+ * until the call's kernels have finished: two calls that can run on the GPU at
+ * the same time (different streams) must be given different workspaces.
  */
 #ifndef TFCC_B200_H_
 #define TFCC_B200_H_
@@ -269,10 +279,13 @@ TFCCB200_API int tfccb200_requantize(void* stream, const void* src, int src_type
  * image, so the call allocates nothing: no cudaMalloc, no cudaFree, no pool.
  *
  * Limits and rules:
- *  - the problem's scratch need (what tfccb200_sgemm_workspace(M,N,K,1,..) reports) must fit
- *    tfccb200_sgemm_skinny_static_capacity() bytes, else TFCCB200_ESTATICLIMIT; M = 8,
- *    K = 4096, N = 16384 fits.  N % 4 == 0 and 16-byte aligned B, C, bias are required as for
- *    the workspace form (TFCCB200_EUNSUPPORTED otherwise);
+ *  - the problem's scratch need -- tfccb200_sgemm_skinny_static_need(M, N, K) bytes: one
+ *    M x N fp32 partial result per K slice, the slice count chosen for the current device --
+ *    must fit tfccb200_sgemm_skinny_static_capacity() bytes, else TFCCB200_ESTATICLIMIT; M = 8,
+ *    K = 4096, N = 16384 needs 9 MiB on a 148-SM part.  (tfccb200_sgemm_workspace may report
+ *    more for the same shape: it also covers what other kernel paths would like to borrow.)
+ *    N % 4 == 0 and 16-byte aligned B, C, bias are required as for the workspace form
+ *    (TFCCB200_EUNSUPPORTED otherwise);
  *  - the first call on each device looks up the array's device address (a one-time host-side
  *    set-up); make that first call before starting any stream capture;
  *  - the array is shared by every call on the device and is never cleared -- no call reads
@@ -285,6 +298,9 @@ TFCCB200_API int tfccb200_sgemm_skinny_static(void* stream, const float* A, cons
                                               float* C, const float* bias, unsigned M,
                                               unsigned N, unsigned K);
 TFCCB200_API size_t tfccb200_sgemm_skinny_static_capacity(void);
+/* Scratch bytes the call above would use for this problem on the current device (0 for
+ * M > 8 or an empty problem). */
+TFCCB200_API size_t tfccb200_sgemm_skinny_static_need(unsigned M, unsigned N, unsigned K);
 
 /*
  * N-split GEMM with the all-gather fused into the epilogue.  Rank `rank` of `num_ranks`

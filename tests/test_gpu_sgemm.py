@@ -194,6 +194,25 @@ def test_host_buffer_entry_point(pkg, orc):
     assert orc.normwise_rel_error(pkg.blas.matmul_host(x, w), orc.blas_matmul(x, w)) < TOL_FP32
 
 
+@pytest.mark.parametrize("m", [2049, 2056, 2057, 3000])
+def test_host_buffer_pipelined_path_ragged_rows(pkg, orc, m):
+    """Large single products go up in 1024-row blocks while earlier blocks are multiplied and
+    downloaded.  A row count that leaves eight rows or fewer for the last block must not send
+    that block to the M <= 8 kernel (which would need scratch of another size): it is merged
+    into the block before it.  Sampled rows, including the very last ones, against float64."""
+    rng = np.random.default_rng(m)
+    n, k = 3072, 3076  # 4 (m k + k n + m n) is past the 64 MB that turns the pipeline on
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    bias = rng.uniform(-1, 1, n).astype(np.float32)
+    got = pkg.blas.matmul_host(a, b, bias)
+    rows = np.unique(np.concatenate([rng.choice(m, 24, replace=False), np.arange(m - 10, m),
+                                     np.arange(1020, 1028)]))
+    want = orc.blas_matmul(a[rows], b, bias)
+    assert orc.normwise_rel_error(got[rows], want) < TOL_FP32
+    assert np.isfinite(got).all()
+
+
 def test_head_truncation_setting_does_not_change_bits(pkg):
     """The library feeds raw fp32 tiles as the TF32 head operand.  That is only right if the
     tensor core ignores the 13 low mantissa bits; masking them explicitly on the host must

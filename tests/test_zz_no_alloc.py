@@ -59,7 +59,8 @@ def test_static_scratch_refuses_what_does_not_fit(pkg):
     lib = pkg.lib
     d = torch.device("cuda:0")
     m, k, n = 8, 16, 1 << 20
-    assert lib.tfccb200_sgemm_workspace(m, n, k, 1, 0) > lib.tfccb200_sgemm_skinny_static_capacity()
+    assert lib.tfccb200_sgemm_skinny_static_need(m, n, k) > lib.tfccb200_sgemm_skinny_static_capacity()
+    assert 0 < lib.tfccb200_sgemm_skinny_static_need(8, 16384, 4096) <= 20 << 20
     x = torch.zeros((m, k), dtype=torch.float32, device=d)
     w = torch.zeros((k, n), dtype=torch.float32, device=d)
     y = torch.zeros((m, n), dtype=torch.float32, device=d)

@@ -57,6 +57,7 @@ class _Lib:
             "tfccb200_sgemm_nsplit_push": (i, [vp, vp, vp, C.POINTER(C.c_void_p), u, u, vp, u, u, u, i, vp, vp, C.c_size_t, vp]),
             "tfccb200_sgemm_skinny_static": (i, [vp, vp, vp, vp, vp, u, u, u]),
             "tfccb200_sgemm_skinny_static_capacity": (sz, []),
+            "tfccb200_sgemm_skinny_static_need": (sz, [u, u, u]),
             "tfccb200_interleave_panels_f32": (i, [vp, vp, vp, u, u, u]),
             "tfccb200_sgemm_host": (i, [vp, vp, u, vp, u, vp, u, vp, u, u, u, u, i]),
             "tfccb200_qgemm_u8s8s32_host": (i, [vp, vp, u, vp, u, f, f, f, f, vp, u,
@@ -85,7 +86,7 @@ EXPORTED_SYMBOLS = (
     "tfccb200_permute_0213_f32", "tfccb200_transpose_last2_f32",
     "tfccb200_minmax_f32", "tfccb200_quantize_f32", "tfccb200_dequantize_f32", "tfccb200_requantize",
     "tfccb200_sgemm_nsplit_push", "tfccb200_sgemm_skinny_static",
-    "tfccb200_sgemm_skinny_static_capacity",
+    "tfccb200_sgemm_skinny_static_capacity", "tfccb200_sgemm_skinny_static_need",
     "tfccb200_interleave_panels_f32", "tfccb200_sgemm_host", "tfccb200_qgemm_u8s8s32_host",
 )
 

@@ -182,30 +182,65 @@ struct ScopedEvent {
   }
 };
 
-// The staging buffers of the host-buffer entry points come from the device's default
-// stream-ordered pool.  Its release threshold is raised once so that the pool keeps the
-// memory between calls instead of returning it to the driver at every synchronisation.
-void retain_pool_memory() {
-  static std::atomic<unsigned long long> done{0};
+// The staging buffers of the host-buffer entry points come from a stream-ordered pool that
+// belongs to this library (one per device, created on first use, kept until the process
+// exits).  Its release threshold is unlimited, so the pool keeps the memory between calls
+// instead of returning it to the driver at every synchronisation; the device's default pool
+// and its settings are left alone.
+cudaError_t staging_pool(cudaMemPool_t* out) {
+  static std::mutex mu;
+  static cudaMemPool_t pools[kMaxDevices] = {};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
-  const unsigned long long bit = 1ull << dev;
-  if (done.load(std::memory_order_acquire) & bit) return;
-  cudaMemPool_t pool;
-  if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!pools[dev]) {
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    cudaMemPool_t pool = nullptr;
+    if ((e = cudaMemPoolCreate(&pool, &props)) != cudaSuccess) return e;
     unsigned long long threshold = ~0ull;
-    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold);
+    if ((e = cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold)) !=
+        cudaSuccess) {
+      cudaMemPoolDestroy(pool);
+      return e;
+    }
+    pools[dev] = pool;
   }
-  done.fetch_or(bit, std::memory_order_release);
+  *out = pools[dev];
+  return cudaSuccess;
 }
 
 struct DeviceBuffer {
   void* p = nullptr;
   cudaStream_t s;
   explicit DeviceBuffer(cudaStream_t st) : s(st) {}
-  cudaError_t alloc(size_t bytes) { return cudaMallocAsync(&p, bytes ? bytes : 16, s); }
+  cudaError_t alloc(size_t bytes) {
+    cudaMemPool_t pool;
+    cudaError_t e = staging_pool(&pool);
+    if (e != cudaSuccess) return e;
+    return cudaMallocFromPoolAsync(&p, bytes ? bytes : 16, pool, s);
+  }
   ~DeviceBuffer() {
     if (p) cudaFreeAsync(p, s);
+  }
+};
+
+// Leaving a host-buffer call early must not leave copies in flight: they touch the caller's
+// host buffers, and the staging buffers are freed in the caller's stream order only.  While
+// armed, the destructor waits for every stream the call has used.
+struct JoinStreams {
+  cudaStream_t streams[3] = {nullptr, nullptr, nullptr};
+  int count = 0;
+  bool armed = true;
+  void add(cudaStream_t st) { streams[count++] = st; }
+  ~JoinStreams() {
+    if (!armed) return;
+    for (int i = 0; i < count; ++i) cudaStreamSynchronize(streams[i]);
   }
 };
 
@@ -482,6 +517,13 @@ int tfccb200_sgemm_skinny_static(void* stream, const float* A, const float* B, f
 
 size_t tfccb200_sgemm_skinny_static_capacity(void) { return skinny_sgemm_static_capacity(); }
 
+size_t tfccb200_sgemm_skinny_static_need(unsigned M, unsigned N, unsigned K) {
+  if (M == 0 || M > 8 || N == 0 || K == 0) return 0;
+  cudaError_t e;
+  const DeviceInfo* di = current_device_info(&e);
+  return skinny_sgemm_workspace(M, N, K, 1, di ? di->sm_count : 148);
+}
+
 int tfccb200_interleave_panels_f32(void* stream, const float* src, float* dst, unsigned M,
                                    unsigned ns, unsigned G) {
   if (!src || !dst || M == 0 || ns == 0 || G == 0) return TFCCB200_EINVAL;
@@ -509,26 +551,39 @@ int tfccb200_sgemm_host(void* stream, const float* hA, unsigned strideA, const f
   // is multiplied on the caller's stream and the block before that comes down on a third
   // stream.  (Pinned host buffers are needed for the copies to really overlap.)
   constexpr unsigned kRowBlock = 1024;
-  retain_pool_memory();
   static const bool pipeline = [] {
     const char* v = std::getenv("TFCCB200_HOST_PIPELINE");
     return !(v && v[0] == '0');
   }();
   if (pipeline && batch == 1 && M >= 2 * kRowBlock &&
       (nA + nB + nC) * 4 >= (size_t(64) << 20)) {
+    // Row blocks of kRowBlock; a last block of eight rows or fewer is merged into the one
+    // before it, so that every block takes the tensor-core path and one scratch size fits all.
+    unsigned blocks = (M + kRowBlock - 1) / kRowBlock;
+    if (M - (blocks - 1) * kRowBlock <= 8) --blocks;
+    const unsigned last_rows = M - (blocks - 1) * kRowBlock;
+    const size_t ws_block = std::max(tfccb200_sgemm_workspace(kRowBlock, N, K, 1, precision_mode),
+                                     tfccb200_sgemm_workspace(last_rows, N, K, 1, precision_mode));
     ScopedStream up, down;
-    ScopedEvent b_ready, c_done_all;
+    ScopedEvent b_ready, c_done_all, alloc_done;
     if ((e = up.create()) != cudaSuccess || (e = down.create()) != cudaSuccess) return e;
-    if ((e = b_ready.create()) != cudaSuccess || (e = c_done_all.create()) != cudaSuccess) return e;
+    if ((e = b_ready.create()) != cudaSuccess || (e = c_done_all.create()) != cudaSuccess ||
+        (e = alloc_done.create()) != cudaSuccess)
+      return e;
+    std::vector<ScopedEvent> a_ready(blocks), c_ready(blocks);
+    for (unsigned i = 0; i < blocks; ++i)
+      if ((e = a_ready[i].create()) != cudaSuccess || (e = c_ready[i].create()) != cudaSuccess)
+        return e;
+    JoinStreams join;  // from here on an early return waits for all three streams
+    join.add(up.s); join.add(down.s); join.add(s);
     if ((e = dA.alloc(nA * 4)) != cudaSuccess) return e;
     if ((e = dB.alloc(nB * 4)) != cudaSuccess) return e;
     if ((e = dC.alloc(nC * 4)) != cudaSuccess) return e;
+    if ((e = dW.alloc(ws_block)) != cudaSuccess) return e;
     if ((e = dS.alloc(sizeof(int))) != cudaSuccess) return e;
     if (hbias && (e = dBias.alloc(size_t(N) * 4)) != cudaSuccess) return e;
     if ((e = cudaMemsetAsync(dS.p, 0, sizeof(int), s)) != cudaSuccess) return e;
     // the buffers come from the caller's stream: the side streams start after that point
-    ScopedEvent alloc_done;
-    if ((e = alloc_done.create()) != cudaSuccess) return e;
     if ((e = cudaEventRecord(alloc_done.e, s)) != cudaSuccess) return e;
     if ((e = cudaStreamWaitEvent(up.s, alloc_done.e, 0)) != cudaSuccess) return e;
     if ((e = cudaStreamWaitEvent(down.s, alloc_done.e, 0)) != cudaSuccess) return e;
@@ -539,15 +594,11 @@ int tfccb200_sgemm_host(void* stream, const float* hA, unsigned strideA, const f
       return e;
     if ((e = cudaEventRecord(b_ready.e, up.s)) != cudaSuccess) return e;
     if ((e = cudaStreamWaitEvent(s, b_ready.e, 0)) != cudaSuccess) return e;
-    const unsigned blocks = (M + kRowBlock - 1) / kRowBlock;
-    std::vector<ScopedEvent> a_ready(blocks), c_ready(blocks);
     for (unsigned i = 0; i < blocks; ++i) {
       const unsigned r0 = i * kRowBlock;
-      const unsigned rows = (M - r0 < kRowBlock) ? M - r0 : kRowBlock;
+      const unsigned rows = (i + 1 == blocks) ? M - r0 : kRowBlock;
       float* dAi = static_cast<float*>(dA.p) + size_t(r0) * K;
       float* dCi = static_cast<float*>(dC.p) + size_t(r0) * N;
-      if ((e = a_ready[i].create()) != cudaSuccess || (e = c_ready[i].create()) != cudaSuccess)
-        return e;
       if ((e = cudaMemcpyAsync(dAi, hA + size_t(r0) * K, size_t(rows) * K * 4,
                                cudaMemcpyHostToDevice, up.s)) != cudaSuccess)
         return e;
@@ -555,8 +606,7 @@ int tfccb200_sgemm_host(void* stream, const float* hA, unsigned strideA, const f
       if ((e = cudaStreamWaitEvent(s, a_ready[i].e, 0)) != cudaSuccess) return e;
       int st = tfccb200_sgemm(s, dAi, 0, static_cast<float*>(dB.p), 0, dCi, rows * N,
                               hbias ? static_cast<float*>(dBias.p) : nullptr, rows, N, K, 1,
-                              precision_mode, nullptr, 0, static_cast<int*>(dS.p));
-      if (st == TFCCB200_EWORKSPACE) return st;  // cannot happen: row blocks have more than 8 rows
+                              precision_mode, dW.p, ws_block, static_cast<int*>(dS.p));
       if (st != TFCCB200_OK) return st;
       if ((e = cudaEventRecord(c_ready[i].e, s)) != cudaSuccess) return e;
       if ((e = cudaStreamWaitEvent(down.s, c_ready[i].e, 0)) != cudaSuccess) return e;
@@ -572,9 +622,12 @@ int tfccb200_sgemm_host(void* stream, const float* hA, unsigned strideA, const f
     if ((e = cudaEventRecord(c_done_all.e, down.s)) != cudaSuccess) return e;
     if ((e = cudaStreamWaitEvent(s, c_done_all.e, 0)) != cudaSuccess) return e;
     if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return e;
+    join.armed = false;  // s has followed both side streams to their end
     return dev_status ? TFCCB200_EDEVICE : TFCCB200_OK;
   }
 
+  JoinStreams join;
+  join.add(s);
   if ((e = dA.alloc(nA * 4)) != cudaSuccess) return e;
   if ((e = dB.alloc(nB * 4)) != cudaSuccess) return e;
   if ((e = dC.alloc(nC * 4)) != cudaSuccess) return e;
@@ -620,6 +673,8 @@ int tfccb200_qgemm_u8s8s32_host(void* stream, const uint8_t* hA, unsigned stride
   const size_t nC = static_cast<size_t>(strideC) * (batch - 1) + size_t(M) * N;
   if ((strideA && strideA != M * K) || (strideB && strideB != K * N)) return TFCCB200_EINVAL;
   DeviceBuffer dA(s), dB(s), dC(s), dRa(s), dRb(s), dS(s);
+  JoinStreams join;  // an early return waits for the copies already queued
+  join.add(s);
   cudaError_t e;
   if ((e = dA.alloc(nA)) != cudaSuccess) return e;
   if ((e = dB.alloc(nB)) != cudaSuccess) return e;

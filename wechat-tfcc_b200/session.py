@@ -23,7 +23,7 @@ class Session:
         if self.device.type != "cuda":
             raise exceptions.InvalidArgumentError("a B200 session needs a CUDA device")
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._workspace = None
+        self._workspaces = {}  # one scratch buffer per stream: calls on two streams may overlap
 
     @property
     def stream_ptr(self) -> int:
@@ -34,12 +34,22 @@ class Session:
         return self._status.data_ptr()
 
     def workspace(self, nbytes: int):
-        """Scratch of at least ``nbytes`` (grown geometrically, reused across calls)."""
+        """Scratch of at least ``nbytes`` for calls on the current stream (grown
+        geometrically, reused by later calls on that stream).  A buffer that is outgrown is
+        handed back to torch's allocator, which keeps it out of other streams' hands until
+        the kernels queued on this stream have used it."""
         if nbytes == 0:
             return None, 0
-        if self._workspace is None or self._workspace.numel() < nbytes:
-            self._workspace = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=self.device)
-        return self._workspace.data_ptr(), self._workspace.numel()
+        stream = torch.cuda.current_stream(self.device)
+        key = stream.cuda_stream
+        ws = self._workspaces.get(key)
+        if ws is None or ws.numel() < nbytes:
+            with torch.cuda.stream(stream):
+                new = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=self.device)
+            if ws is not None:
+                ws.record_stream(stream)
+            ws = self._workspaces[key] = new
+        return ws.data_ptr(), ws.numel()
 
     def sync(self) -> None:
         torch.cuda.current_stream(self.device).synchronize()
