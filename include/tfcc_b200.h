@@ -356,6 +356,20 @@ TFCCB200_API int tfccb200_qgemm_u8s8s32_host(void* stream, const uint8_t* hA, un
                                 float* minC, float* maxC, unsigned M, unsigned N, unsigned K,
                                 unsigned batch);
 
+/*
+ * Test hook for the give-up path of the fp32 tensor-core kernel.  CTAs that share a tile's
+ * k-blocks through scratch wait, with a time limit, on counters that other CTAs of the same
+ * launch raise; when a wait runs out the kernel ORs TFCCB200_DEV_TIMEOUT_EPILOGUE into
+ * *device_status, every role of the CTA stops waiting, and the kernel runs to its normal end
+ * (tensor memory freed, context intact) with an undefined C.  This call changes, for every later
+ * launch of the process, the limit of those waits (nanoseconds; 0 = the normal 2 s) and makes
+ * them expect `expect_extra` more arrivals than a launch ever delivers (0 = normal), so that a
+ * test can see the status word and the orderly return without anything having to hang:
+ * tfccb200_test_flag_wait(1000000, 1) before the launch, tfccb200_test_flag_wait(0, 0) after.
+ * Not for production use.  No counterpart in the reference.
+ */
+TFCCB200_API void tfccb200_test_flag_wait(unsigned long long timeout_ns, unsigned expect_extra);
+
 /* Number of kernels this library has launched in the calling process since it
  * was loaded (monotonic; for benchmarks that must report their launch count). */
 TFCCB200_API unsigned long long tfccb200_launch_count(void);

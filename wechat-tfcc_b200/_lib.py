@@ -33,6 +33,7 @@ class _Lib:
             "tfccb200_strerror": (C.c_char_p, [i]),
             "tfccb200_version": (i, []),
             "tfccb200_launch_count": (C.c_ulonglong, []),
+            "tfccb200_test_flag_wait": (None, [C.c_ulonglong, u]),
             "tfccb200_sgemm": (i, [vp, vp, u, vp, u, vp, u, vp, u, u, u, u, i, vp, sz, vp]),
             "tfccb200_sgemm_ex": (i, [vp, vp, u, vp, u, vp, u, vp, u, u, u, u, i, i, vp, sz, vp]),
             "tfccb200_sgemm_workspace": (sz, [u, u, u, u, i]),
@@ -78,7 +79,8 @@ class _Lib:
 lib = _Lib()
 
 EXPORTED_SYMBOLS = (
-    "tfccb200_strerror", "tfccb200_version", "tfccb200_launch_count", "tfccb200_sgemm",
+    "tfccb200_strerror", "tfccb200_version", "tfccb200_launch_count", "tfccb200_test_flag_wait",
+    "tfccb200_sgemm",
     "tfccb200_sgemm_ex", "tfccb200_sgemm_workspace", "tfccb200_sgemm_path",
     "tfccb200_qgemm_u8s8s32", "tfccb200_qgemm_u8s8s32_ex", "tfccb200_quantized_matmul_params",
     "tfccb200_reduce_sum_u8", "tfccb200_reduce_sum_s8", "tfccb200_reduce_sum_s16",

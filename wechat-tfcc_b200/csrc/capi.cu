@@ -270,6 +270,10 @@ const char* tfccb200_strerror(int status) {
 
 int tfccb200_version(void) { return 100; }
 
+void tfccb200_test_flag_wait(unsigned long long timeout_ns, unsigned expect_extra) {
+  set_test_flag_wait(timeout_ns, expect_extra);
+}
+
 unsigned long long tfccb200_launch_count(void) {
   return g_launches.load(std::memory_order_relaxed);
 }

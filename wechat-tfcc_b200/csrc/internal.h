@@ -72,6 +72,7 @@ UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_co
                    int elem_bytes, int force_pair, bool allow_cluster_k, bool allow_stream_k);
 bool stream_k_scratch_ok(const SgemmArgs& a, int sm_count);  // scratch lent for the k-shared wave
 size_t umma_stream_k_workspace(int sm_count);  // scratch that lets umma_sgemm share tiles by k-block
+void set_test_flag_wait(unsigned long long timeout_ns, unsigned expect_extra);
 bool umma_sgemm_supported(const SgemmArgs& a);
 int umma_sgemm(const SgemmArgs& a, bool pair);
 bool umma_qgemm_supported(const QgemmArgs& a);

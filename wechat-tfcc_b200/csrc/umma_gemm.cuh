@@ -119,6 +119,12 @@ struct UmmaGemmParams {
   unsigned long long sk_capacity;  // host only: bytes available behind sk_partials
   int* status;             // device int or nullptr
   unsigned long long timeout_ns;
+  // Waits on the scratch counters above have their own limit and may be told to expect more
+  // arrivals than any launch delivers: the test hook tfccb200_test_flag_wait() uses the two to
+  // make such a wait run out at once, which drives the give-up path (status word, abort flag,
+  // orderly teardown) without anything hanging.  Normal launches: timeout_ns and 0.
+  unsigned long long flag_timeout_ns;
+  unsigned flag_expect_extra;
 };
 
 // One stretch of k-blocks of one tile, as every role of a CTA walks them.
@@ -197,6 +203,7 @@ struct UmmaCtl {
   volatile uint32_t* abort_flag;  // shared
   int* status;                    // global or nullptr
   unsigned long long timeout_ns;
+  unsigned long long flag_timeout_ns;  // limit of bounded_flag_wait
 };
 
 template <bool kClusterAcquire>
@@ -241,7 +248,7 @@ __device__ __forceinline__ bool bounded_flag_wait(const unsigned* flag, unsigned
       uint64_t now = ptx::globaltimer_ns();
       if (start == 0) {
         start = now;
-      } else if (now - start > ctl.timeout_ns) {
+      } else if (now - start > ctl.flag_timeout_ns) {
         *ctl.abort_flag = 1;
         if (ctl.status) atomicOr(ctl.status, bit);
         return false;
@@ -413,7 +420,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   volatile uint32_t* sk_count_gen =
       reinterpret_cast<volatile uint32_t*>(bar_gen + 256 + 16 * kMaxSkSegments);
 
-  UmmaCtl ctl{abort_flag, p.status, p.timeout_ns};
+  UmmaCtl ctl{abort_flag, p.status, p.timeout_ns, p.flag_timeout_ns};
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -504,7 +511,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
-      for (unsigned si = 0; si < num_segments; ++si) {
+      bool live = true;  // cleared when a wait is abandoned: nothing more is loaded
+      for (unsigned si = 0; si < num_segments && live; ++si) {
         const UmmaSegment sg = segment(si);
         unsigned b, tm, tn;
         tile_coords(sg.tile, p.tiles_m, p.tiles_n, b, tm, tn);
@@ -513,7 +521,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         const int ba = p.a_batched ? static_cast<int>(b) : 0;
         const int bb = p.b_batched ? static_cast<int>(b) : 0;
         for (unsigned kb = sg.kb_lo; kb < sg.kb_hi; ++kb) {
-          bounded_wait<false>(empty_bar(s), ph ^ 1u, TFCCB200_DEV_TIMEOUT_TMA, ctl);
+          if (!bounded_wait<false>(empty_bar(s), ph ^ 1u, TFCCB200_DEV_TIMEOUT_TMA, ctl)) {
+            live = false;
+            break;
+          }
           const uint32_t stage = smem_base + s * kRawPitch;
           const int k0 = static_cast<int>(kb * Cfg::kBK);
           if constexpr (kCtaGroup == 2 && !kSplit) {
@@ -547,21 +558,30 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       int ts = 0;       // slot of the tail ring (kSplit)
       unsigned it = 0;  // accumulator hand-offs so far (tiles, or chunks when kSplit)
       const uint16_t pair_mask = 0x3;
-      for (unsigned si = 0; si < num_segments; ++si) {
+      bool live = true;  // cleared when a wait is abandoned: no further MMA is issued
+      for (unsigned si = 0; si < num_segments && live; ++si) {
         const UmmaSegment sg = segment(si);
-        for (unsigned kb0 = sg.kb_lo; kb0 < sg.kb_hi; kb0 += kb_per_chunk, ++it) {
+        for (unsigned kb0 = sg.kb_lo; kb0 < sg.kb_hi && live; kb0 += kb_per_chunk, ++it) {
           const unsigned acc = it & 1u;
           const uint32_t acc_ph = (it >> 1) & 1u;
-          bounded_wait<(kCtaGroup == 2)>(tmem_empty(acc), acc_ph ^ 1u, TFCCB200_DEV_TIMEOUT_MMA,
-                                         ctl);
+          if (!bounded_wait<(kCtaGroup == 2)>(tmem_empty(acc), acc_ph ^ 1u,
+                                              TFCCB200_DEV_TIMEOUT_MMA, ctl)) {
+            live = false;
+            break;
+          }
           ptx::tc_fence_after_sync();
           const uint32_t d_tmem = tmem_base + acc * BN;
           const unsigned kb_end = min(sg.kb_hi, kb0 + kb_per_chunk);
           for (unsigned kb = kb0; kb < kb_end; ++kb) {
+            bool ready;
             if constexpr (kSplit) {
-              bounded_wait<(kCtaGroup == 2)>(full_cvt(s), ph, TFCCB200_DEV_TIMEOUT_MMA, ctl);
+              ready = bounded_wait<(kCtaGroup == 2)>(full_cvt(s), ph, TFCCB200_DEV_TIMEOUT_MMA, ctl);
             } else {
-              bounded_wait<false>(full_raw(s), ph, TFCCB200_DEV_TIMEOUT_MMA, ctl);
+              ready = bounded_wait<false>(full_raw(s), ph, TFCCB200_DEV_TIMEOUT_MMA, ctl);
+            }
+            if (!ready) {
+              live = false;
+              break;
             }
             ptx::tc_fence_after_sync();
             const uint32_t a_hi = smem_base + s * kRawPitch;
@@ -591,6 +611,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             }
             if (++s == kStages) { s = 0; ph ^= 1u; }
           }
+          if (!live) break;
           ptx::umma_commit<kCtaGroup>(tmem_full(acc), pair_mask);  // this accumulator is complete
         }
       }
@@ -651,7 +672,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           // continue the sums the previous group published for the same rows of this tile
           const unsigned src_cta = (group_id - 1) * kCtaGroup + cta_rank;
           if (lane == 0)
-            bounded_flag_wait(p.sk_flags + src_cta, Cfg::kNumEpilogueWarps * 32u,
+            bounded_flag_wait(p.sk_flags + src_cta,
+                              Cfg::kNumEpilogueWarps * 32u + p.flag_expect_extra,
                               TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
           __syncwarp();
           const float4* src = reinterpret_cast<const float4*>(p.sk_partials) +
@@ -692,7 +714,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           for (unsigned r = 1; r < p.global_k; ++r) {
             const unsigned src_cta = group_id + r;
             if (lane == 0)
-              bounded_flag_wait(p.sk_flags + src_cta, Cfg::kNumEpilogueWarps * 32u,
+              bounded_flag_wait(p.sk_flags + src_cta,
+                                Cfg::kNumEpilogueWarps * 32u + p.flag_expect_extra,
                                 TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
             __syncwarp();
             sk_add_partial<kSkVec>(sum, reinterpret_cast<const float4*>(p.sk_partials) +
@@ -825,18 +848,25 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       unsigned done = 0;  // k-blocks converted so far
       int ls = 0;         // raw stage of the k-block kTailStages back, and its phase
       uint32_t lph = 0;
-      for (unsigned si = 0; si < num_segments; ++si) {
+      bool live = true;  // cleared when a wait is abandoned: nothing more is converted
+      for (unsigned si = 0; si < num_segments && live; ++si) {
         const UmmaSegment sg = segment(si);
         for (unsigned kb = sg.kb_lo; kb < sg.kb_hi; ++kb) {
           if constexpr (Cfg::kTailStages < kStages) {
             // (with as many tail slots as raw stages the raw tile's arrival implies it)
             if (done >= static_cast<unsigned>(Cfg::kTailStages)) {
-              bounded_wait<false>(empty_bar(ls), lph, TFCCB200_DEV_TIMEOUT_CONVERT, ctl);
+              if (!bounded_wait<false>(empty_bar(ls), lph, TFCCB200_DEV_TIMEOUT_CONVERT, ctl)) {
+                live = false;
+                break;
+              }
               if (++ls == kStages) { ls = 0; lph ^= 1u; }
             }
             ++done;
           }
-          bounded_wait<false>(full_raw(s), ph, TFCCB200_DEV_TIMEOUT_CONVERT, ctl);
+          if (!bounded_wait<false>(full_raw(s), ph, TFCCB200_DEV_TIMEOUT_CONVERT, ctl)) {
+            live = false;
+            break;
+          }
           float4* raw = reinterpret_cast<float4*>(smem_gen + s * kRawPitch);
           float4* tail = reinterpret_cast<float4*>(smem_gen + kTailBase + ts * kTailPitch);
           constexpr int kIter = kVecs / kCThreads;

@@ -58,6 +58,11 @@ bool make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const v
 
 int env_int(const char* name, int fallback);
 
+// Test hook (tfccb200_test_flag_wait): limit and surplus expectation of the waits on scratch
+// counters.  0 / 0 = the normal limit and no surplus.
+std::atomic<unsigned long long> g_flag_timeout_ns{0};
+std::atomic<unsigned> g_flag_expect_extra{0};
+
 // Sharing the last one-to-two waves of tiles out by k-block (UmmaGemmParams::sk_tiles).
 // Worth it when the tile count leaves a noticeable part of the last wave idle.
 bool stream_k_split(unsigned long long tiles, unsigned groups, unsigned num_kb, unsigned kb_per_chunk,
@@ -234,6 +239,11 @@ int env_int(const char* name, int fallback) {
 }
 
 }  // namespace
+
+void set_test_flag_wait(unsigned long long timeout_ns, unsigned expect_extra) {
+  g_flag_timeout_ns.store(timeout_ns, std::memory_order_relaxed);
+  g_flag_expect_extra.store(expect_extra, std::memory_order_relaxed);
+}
 
 bool stream_k_scratch_ok(const SgemmArgs& a, int sm_count) {
   return a.workspace && (reinterpret_cast<uintptr_t>(a.workspace) & 255u) == 0 &&
@@ -418,6 +428,7 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
     q.a_batched = a_batched; q.b_batched = b_batched;
     q.status = a.status;
     q.timeout_ns = kDefaultTimeoutNs;
+    q.flag_timeout_ns = kDefaultTimeoutNs;
     constexpr auto H = ptx::MmaKind::BF16;
     const int sms16 = di->sm_count;
     if (!pair) {
@@ -474,6 +485,9 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
   if (p.global_k > 1) p.cluster_k = 1;
   p.status = a.status;
   p.timeout_ns = kDefaultTimeoutNs;
+  const unsigned long long flag_ns = g_flag_timeout_ns.load(std::memory_order_relaxed);
+  p.flag_timeout_ns = flag_ns ? flag_ns : kDefaultTimeoutNs;
+  p.flag_expect_extra = g_flag_expect_extra.load(std::memory_order_relaxed);
 
   constexpr auto T = ptx::MmaKind::TF32;
   const bool split = a.precision == TFCCB200_PRECISION_FP32;
@@ -562,6 +576,7 @@ int umma_qgemm(const QgemmArgs& a, bool pair) {
   p.a_batched = a_batched; p.b_batched = b_batched;
   p.status = a.status;
   p.timeout_ns = kDefaultTimeoutNs;
+  p.flag_timeout_ns = kDefaultTimeoutNs;
 
   constexpr auto I = ptx::MmaKind::I8;
   const int sms = di->sm_count;
