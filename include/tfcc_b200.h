@@ -329,6 +329,118 @@ TFCCB200_API int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const 
                                             float* C_multicast, void* workspace,
                                             size_t workspace_bytes, int* device_status);
 
+/* Same, with two more controls.  An entry of C_ranks other than C_ranks[rank] may be NULL: that
+ * rank's copy is then not written by this call.  max_ctas > 0 limits the launch to that many
+ * SMs (rounded down to whole CTA pairs), so that two products -- for instance two steps of a
+ * pipeline, each with its own C and workspace, on two streams -- can run side by side on
+ * disjoint parts of the chip: the pushes of one then overlap the arithmetic of the other. */
+TFCCB200_API int tfccb200_sgemm_nsplit_push_ex(void* stream, const float* A, const float* B_shard,
+                                               float* const* C_ranks, unsigned num_ranks,
+                                               unsigned rank, const float* bias_shard, unsigned M,
+                                               unsigned N_shard, unsigned K, int precision_mode,
+                                               float* C_multicast, void* workspace,
+                                               size_t workspace_bytes, unsigned max_ctas,
+                                               int* device_status);
+
+/*
+ * The quantized matmul of tfccb200_qgemm_u8s8s32 (single matrices) with the same fused gather:
+ * rank `rank` holds A [M,K] with its row sums, the column shard B_shard [K,N_shard] with that
+ * shard's column sums, and stores its int32 tiles, zero-point correction applied, into columns
+ * [rank*N_shard, (rank+1)*N_shard) of every non-NULL C_ranks[r] ([M, num_ranks*N_shard]
+ * row-major), or once through C_multicast.  Integer results do not depend on the split, so the
+ * assembled C equals the single-GPU result bit for bit.  Needs K % 16 == 0, N_shard % 16 == 0,
+ * K >= 128, N_shard >= 128 (tensor-core path only).  No counterpart in the reference.
+ */
+TFCCB200_API int tfccb200_qgemm_nsplit_push(void* stream, const uint8_t* A, const int32_t* rsA,
+                                            int32_t offA, const int8_t* B_shard,
+                                            const int32_t* rsB_shard, int32_t offB,
+                                            int32_t* const* C_ranks, unsigned num_ranks,
+                                            unsigned rank, unsigned M, unsigned N_shard,
+                                            unsigned K, int32_t* C_multicast, int* device_status);
+
+/*
+ * Cross-rank barrier supplied by a one-process-per-GPU caller: must enqueue on `stream` a
+ * barrier behind which everything the other ranks enqueued before their own matching call has
+ * completed (e.g. a symmetric-memory barrier kernel, or a tiny NCCL all-reduce).  Returns 0 or
+ * a status that the entry point hands back unchanged.
+ */
+typedef int (*tfccb200_barrier_fn)(void* ctx, void* stream);
+
+/*
+ * One rank's share of an N-split product whose operands start in HOST memory and whose result
+ * returns to host memory -- the data::set -> matmul -> data::get round trip
+ * (tfcc/cuda/interfaces/tfcc_cudadatainterface.cu:62-90) spread over num_ranks GPUs so that the
+ * job's host traffic crosses num_ranks PCIe links once instead of every link carrying all of it:
+ *   1. rank r uploads rows [r*M/G, (r+1)*M/G) of A (hA_rows) into its own A buffer and stores
+ *      them on into the same rows of every peer's A buffer over NVLink, and uploads its column
+ *      shard of B (hB_shard, row pitch ldb_host elements) into B_shard_dev;
+ *   2. barrier; tfccb200_sgemm_nsplit_push; barrier;
+ *   3. rank r downloads rows [r*M/G, (r+1)*M/G) of the assembled C into hC_rows
+ *      ([M/G, num_ranks*N_shard]).
+ * Per rank 4 (M K / G + K N_shard) bytes go up and 4 M N / G come down.  A_ranks / C_ranks are
+ * every rank's device buffers mapped into this process ([M,K] and [M, num_ranks*N_shard]);
+ * A_multicast / C_multicast their NVLink multicast aliases or NULL.  M % num_ranks == 0,
+ * K % 4 == 0, N_shard % 4 == 0.  Host buffers should be pinned.  Synchronises `stream` before
+ * returning; *device_status is left for the caller to read.  `barrier` may be NULL when
+ * num_ranks == 1.  No counterpart in the reference.
+ */
+TFCCB200_API int tfccb200_sgemm_nsplit_host(void* stream, const float* hA_rows,
+                                            const float* hB_shard, unsigned ldb_host,
+                                            float* hC_rows, float* const* A_ranks,
+                                            float* A_multicast, float* B_shard_dev,
+                                            float* const* C_ranks, float* C_multicast,
+                                            unsigned num_ranks, unsigned rank, unsigned M,
+                                            unsigned N_shard, unsigned K, int precision_mode,
+                                            void* workspace, size_t workspace_bytes,
+                                            tfccb200_barrier_fn barrier, void* barrier_ctx,
+                                            int* device_status);
+
+/*
+ * Device group for a process that drives several GPUs itself -- the shape of a TFCC program
+ * with one Device per GPU (tfcc/core/utils/tfcc_initializer.cpp:50-66,
+ * tfcc/cuda/utils/tfcc_cudautils.cpp:23-50).  Creating a group enables peer access between
+ * every pair of its devices and gives each member a stream, a device status word and scratch
+ * for the tensor-core kernel; members are ordered against each other with CUDA events, never
+ * by blocking the host.  The calls below may be made from any one host thread at a time and
+ * restore the caller's current device.  `devices` may name the same GPU more than once (the
+ * members then share it; useful for exercising the multi-rank logic on one GPU).
+ */
+typedef struct tfccb200_group tfccb200_group;
+TFCCB200_API int tfccb200_group_create(int ndev, const int* devices, tfccb200_group** out);
+TFCCB200_API int tfccb200_group_destroy(tfccb200_group* group);
+TFCCB200_API int tfccb200_group_size(const tfccb200_group* group);
+TFCCB200_API int tfccb200_group_device(const tfccb200_group* group, int member);
+TFCCB200_API void* tfccb200_group_stream(const tfccb200_group* group, int member);
+/* Waits for every member's stream; TFCCB200_EDEVICE if a kernel abandoned a bounded wait. */
+TFCCB200_API int tfccb200_group_sync(tfccb200_group* group);
+
+/*
+ * N-split product on device-resident operands: arrays of one pointer per member, A[i] [M,K] and
+ * B_shards[i] [K,N_shard] on member i's device, C[i] that member's full [M, G*N_shard].  Each
+ * member's kernel is queued on its group stream; when the call returns nothing has been waited
+ * for, and work queued later on any member's group stream sees the complete C.
+ */
+TFCCB200_API int tfccb200_group_sgemm_nsplit(tfccb200_group* group, const float* const* A,
+                                             const float* const* B_shards, float* const* C,
+                                             const float* const* bias_shards, unsigned M,
+                                             unsigned N_shard, unsigned K, int precision_mode);
+TFCCB200_API int tfccb200_group_qgemm_nsplit(tfccb200_group* group, const uint8_t* const* A,
+                                             const int32_t* const* rsA, int32_t offA,
+                                             const int8_t* const* B_shards,
+                                             const int32_t* const* rsB_shards, int32_t offB,
+                                             int32_t* const* C, unsigned M, unsigned N_shard,
+                                             unsigned K);
+/*
+ * C = A . B with all three matrices in host memory (row-major [M,K], [K,N], [M,N]; pinned for
+ * the copies to overlap), N split over the group: every member uploads M/G rows of A and its
+ * column shard of B, the rows are exchanged over NVLink, and every member downloads M/G rows of
+ * the assembled C.  M and N must be multiples of the group size, K and N/G of 4.  Staging
+ * buffers belong to the group and are kept between calls.  Synchronous.
+ */
+TFCCB200_API int tfccb200_group_sgemm_nsplit_host(tfccb200_group* group, const float* hA,
+                                                  const float* hB, float* hC, unsigned M,
+                                                  unsigned N, unsigned K, int precision_mode);
+
 /*
  * dst[m][g*ns + j] = src[g][m][j] for g < G, m < M, j < ns (fp32, ns % 4 == 0).
  * Turns the rank-major result of an all-gather of column shards of C into the

@@ -125,6 +125,51 @@ def blas_matmul(a, b, c=None, dtype=np.float64):
     return out.reshape(shape)
 
 
+def host_cores() -> int:
+    """Cores this process may run on."""
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+def set_cpu_threads(n: int) -> int:
+    """Make every CPU arm of the oracle use ``n`` threads, whatever the environment says
+    (launchers such as torch.distributed.run export OMP_NUM_THREADS=1): torch's intra-op pool
+    (MKL sgemm / oneDNN), numpy's BLAS, and the OpenMP runtime of the C port and of the
+    reference kernel in oracle/_ref.  The reference states its thread count the same way
+    (``omp_set_num_threads(4)``, tfcc/test/environment.cpp:40).  Returns ``n``."""
+    n = max(1, int(n))
+    try:
+        import torch
+        torch.set_num_threads(n)
+    except Exception:
+        pass
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=n)
+    except Exception:
+        pass
+    try:
+        C.CDLL("libgomp.so.1").omp_set_num_threads(C.c_int(n))
+    except Exception:
+        pass
+    return n
+
+
+def blas_matmul_mkl(a, b, c=None):
+    """``a . b (+ c)`` in float32 by torch's CPU matmul (MKL sgemm / oneDNN, the vendor
+    libraries the reference's "MKL" backend wraps; its pinned oneDNN v1.8.1 is not buildable
+    here).  Batching and the rank-2 broadcast are torch's, which agree with
+    tfcc/mkl/interfaces/tfcc_mklblasinterface.cpp:127-186 for every shape the rules admit.
+    Returns a numpy float32 array.  This is the timed stand-in for the reference's fp32 path."""
+    import torch
+    ta = torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32))
+    tb = torch.from_numpy(np.ascontiguousarray(b, dtype=np.float32))
+    matmul_result_shape(ta.shape, tb.shape, None if c is None else np.asarray(c).shape)
+    out = torch.matmul(ta, tb)
+    if c is not None:
+        out += torch.from_numpy(np.ascontiguousarray(c, dtype=np.float32))
+    return out.numpy()
+
+
 def is_similar(a, b) -> bool:
     """tfcc::is_similar: integers exact; floats |a-b| < 1e-3*|a+b| or |a-b| < 1e-5."""
     a = np.asarray(a)

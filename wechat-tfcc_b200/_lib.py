@@ -8,6 +8,9 @@ from . import exceptions
 
 _HERE = Path(__file__).resolve().parent
 
+# int barrier(void* ctx, void* stream): see tfccb200_barrier_fn in include/tfcc_b200.h
+BARRIER_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p)
+
 
 def library_path() -> Path:
     return _HERE / "libtfcc_b200.so"
@@ -56,6 +59,22 @@ class _Lib:
             "tfccb200_dequantize_f32": (i, [vp, vp, i, sz, vp, vp, vp]),
             "tfccb200_requantize": (i, [vp, vp, i, sz, vp, vp, vp, vp, vp, i]),
             "tfccb200_sgemm_nsplit_push": (i, [vp, vp, vp, C.POINTER(C.c_void_p), u, u, vp, u, u, u, i, vp, vp, C.c_size_t, vp]),
+            "tfccb200_sgemm_nsplit_push_ex": (i, [vp, vp, vp, C.POINTER(C.c_void_p), u, u, vp, u, u, u, i, vp, vp, C.c_size_t, u, vp]),
+            "tfccb200_qgemm_nsplit_push": (i, [vp, vp, vp, i32, vp, vp, i32, C.POINTER(C.c_void_p), u, u, u, u, u, vp, vp]),
+            "tfccb200_sgemm_nsplit_host": (i, [vp, vp, vp, u, vp, C.POINTER(C.c_void_p), vp, vp,
+                                               C.POINTER(C.c_void_p), vp, u, u, u, u, u, i, vp, sz,
+                                               BARRIER_FN, vp, vp]),
+            "tfccb200_group_create": (i, [i, C.POINTER(i), C.POINTER(vp)]),
+            "tfccb200_group_destroy": (i, [vp]),
+            "tfccb200_group_size": (i, [vp]),
+            "tfccb200_group_device": (i, [vp, i]),
+            "tfccb200_group_stream": (vp, [vp, i]),
+            "tfccb200_group_sync": (i, [vp]),
+            "tfccb200_group_sgemm_nsplit": (i, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
+                                                C.POINTER(vp), u, u, u, i]),
+            "tfccb200_group_qgemm_nsplit": (i, [vp, C.POINTER(vp), C.POINTER(vp), i32, C.POINTER(vp),
+                                                C.POINTER(vp), i32, C.POINTER(vp), u, u, u]),
+            "tfccb200_group_sgemm_nsplit_host": (i, [vp, vp, vp, vp, u, u, u, i]),
             "tfccb200_sgemm_skinny_static": (i, [vp, vp, vp, vp, vp, u, u, u]),
             "tfccb200_sgemm_skinny_static_capacity": (sz, []),
             "tfccb200_sgemm_skinny_static_need": (sz, [u, u, u]),
@@ -87,7 +106,11 @@ EXPORTED_SYMBOLS = (
     "tfccb200_sgemm_act", "tfccb200_softmax_f32", "tfccb200_layer_norm_f32", "tfccb200_gelu_f32",
     "tfccb200_permute_0213_f32", "tfccb200_transpose_last2_f32",
     "tfccb200_minmax_f32", "tfccb200_quantize_f32", "tfccb200_dequantize_f32", "tfccb200_requantize",
-    "tfccb200_sgemm_nsplit_push", "tfccb200_sgemm_skinny_static",
+    "tfccb200_sgemm_nsplit_push", "tfccb200_sgemm_nsplit_push_ex", "tfccb200_qgemm_nsplit_push",
+    "tfccb200_sgemm_nsplit_host", "tfccb200_group_create", "tfccb200_group_destroy",
+    "tfccb200_group_size", "tfccb200_group_device", "tfccb200_group_stream", "tfccb200_group_sync",
+    "tfccb200_group_sgemm_nsplit", "tfccb200_group_qgemm_nsplit",
+    "tfccb200_group_sgemm_nsplit_host", "tfccb200_sgemm_skinny_static",
     "tfccb200_sgemm_skinny_static_capacity", "tfccb200_sgemm_skinny_static_need",
     "tfccb200_interleave_panels_f32", "tfccb200_sgemm_host", "tfccb200_qgemm_u8s8s32_host",
 )

@@ -359,7 +359,7 @@ int tfccb200_qgemm_u8s8s32_ex(void* stream, const uint8_t* A, unsigned strideA,
                               unsigned strideRsB, int32_t offB, int32_t* C, unsigned strideC,
                               unsigned M, unsigned N, unsigned K, unsigned batch, int path,
                               int* device_status) {
-  QgemmArgs a;
+  QgemmArgs a = {};
   a.stream = static_cast<cudaStream_t>(stream);
   a.A = A; a.B = B; a.C = C; a.rsA = rsA; a.rsB = rsB;
   a.strideA = strideA; a.strideB = strideB; a.strideC = strideC;
@@ -471,11 +471,12 @@ int tfccb200_requantize(void* stream, const void* src, int src_type, size_t n,
                     min_output, max_output, dst, dst_type);
 }
 
-int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shard,
-                               float* const* C_ranks, unsigned num_ranks, unsigned rank,
-                               const float* bias_shard, unsigned M, unsigned N_shard, unsigned K,
-                               int precision_mode, float* C_multicast, void* workspace,
-                               size_t workspace_bytes, int* device_status) {
+int tfccb200_sgemm_nsplit_push_ex(void* stream, const float* A, const float* B_shard,
+                                  float* const* C_ranks, unsigned num_ranks, unsigned rank,
+                                  const float* bias_shard, unsigned M, unsigned N_shard,
+                                  unsigned K, int precision_mode, float* C_multicast,
+                                  void* workspace, size_t workspace_bytes, unsigned max_ctas,
+                                  int* device_status) {
   if (!A || !B_shard || !C_ranks || num_ranks == 0 || num_ranks > 8 || rank >= num_ranks)
     return TFCCB200_EINVAL;
   if (M == 0 || N_shard == 0 || K == 0) return TFCCB200_EINVAL;
@@ -484,6 +485,7 @@ int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shar
   const unsigned long long n_total = static_cast<unsigned long long>(N_shard) * num_ranks;
   if (n_total > 0xffffffffull || shape_overflows(M, static_cast<unsigned>(n_total), K, 1))
     return TFCCB200_EOVERFLOW;
+  if (!C_ranks[rank]) return TFCCB200_EINVAL;
   SgemmArgs a = {};
   a.stream = static_cast<cudaStream_t>(stream);
   a.A = A; a.B = B_shard; a.bias = bias_shard;
@@ -493,10 +495,11 @@ int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shar
   a.status = device_status;
   a.workspace = workspace;
   a.workspace_bytes = workspace ? workspace_bytes : 0;
-  a.num_dst = num_ranks;
+  a.max_ctas = max_ctas;
   for (unsigned d = 0; d < num_ranks; ++d) {
-    if (!C_ranks[d] || (reinterpret_cast<uintptr_t>(C_ranks[d]) & 15u)) return TFCCB200_EALIGN;
-    a.dst[d] = C_ranks[d];
+    if (!C_ranks[d]) continue;  // that rank's copy is not written by this call
+    if (reinterpret_cast<uintptr_t>(C_ranks[d]) & 15u) return TFCCB200_EALIGN;
+    a.dst[a.num_dst++] = C_ranks[d];
   }
   a.C = C_ranks[rank];
   if (C_multicast && (reinterpret_cast<uintptr_t>(C_multicast) & 15u)) return TFCCB200_EALIGN;
@@ -507,8 +510,57 @@ int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shar
   cudaError_t e;
   const DeviceInfo* di = current_device_info(&e);
   if (!di) return static_cast<int>(e);
-  return umma_sgemm(a, umma_plan(M, N_shard, K, 1, di->sm_count, 4, -1, false,
-                                 stream_k_scratch_ok(a, di->sm_count)).pair);
+  const int sms = umma_sm_budget(di->sm_count, max_ctas);
+  return umma_sgemm(a, umma_plan(M, N_shard, K, 1, sms, 4, -1, false,
+                                 stream_k_scratch_ok(a, sms)).pair);
+}
+
+int tfccb200_sgemm_nsplit_push(void* stream, const float* A, const float* B_shard,
+                               float* const* C_ranks, unsigned num_ranks, unsigned rank,
+                               const float* bias_shard, unsigned M, unsigned N_shard, unsigned K,
+                               int precision_mode, float* C_multicast, void* workspace,
+                               size_t workspace_bytes, int* device_status) {
+  return tfccb200_sgemm_nsplit_push_ex(stream, A, B_shard, C_ranks, num_ranks, rank, bias_shard,
+                                       M, N_shard, K, precision_mode, C_multicast, workspace,
+                                       workspace_bytes, 0, device_status);
+}
+
+int tfccb200_qgemm_nsplit_push(void* stream, const uint8_t* A, const int32_t* rsA, int32_t offA,
+                               const int8_t* B_shard, const int32_t* rsB_shard, int32_t offB,
+                               int32_t* const* C_ranks, unsigned num_ranks, unsigned rank,
+                               unsigned M, unsigned N_shard, unsigned K, int32_t* C_multicast,
+                               int* device_status) {
+  if (!A || !rsA || !B_shard || !rsB_shard || !C_ranks || num_ranks == 0 || num_ranks > 8 ||
+      rank >= num_ranks)
+    return TFCCB200_EINVAL;
+  if (M == 0 || N_shard == 0 || K == 0) return TFCCB200_EINVAL;
+  const unsigned long long n_total = static_cast<unsigned long long>(N_shard) * num_ranks;
+  if (n_total > 0xffffffffull || shape_overflows(M, static_cast<unsigned>(n_total), K, 1))
+    return TFCCB200_EOVERFLOW;
+  if (!C_ranks[rank]) return TFCCB200_EINVAL;
+  QgemmArgs a = {};
+  a.stream = static_cast<cudaStream_t>(stream);
+  a.A = A; a.B = B_shard; a.rsA = rsA; a.rsB = rsB_shard;
+  a.offA = offA; a.offB = offB;
+  a.M = M; a.N = N_shard; a.K = K; a.batch = 1;
+  a.strideC = 0;
+  a.status = device_status;
+  for (unsigned d = 0; d < num_ranks; ++d) {
+    if (!C_ranks[d]) continue;
+    if (reinterpret_cast<uintptr_t>(C_ranks[d]) & 15u) return TFCCB200_EALIGN;
+    a.dst[a.num_dst++] = C_ranks[d];
+  }
+  a.C = C_ranks[rank];
+  if (C_multicast && (reinterpret_cast<uintptr_t>(C_multicast) & 15u)) return TFCCB200_EALIGN;
+  a.mc_dst = C_multicast;
+  a.ldc = n_total;
+  a.col_offset = rank * N_shard;
+  // the tensor-core kernel is the only one that can store into several matrices
+  if (!umma_qgemm_supported(a) || K < 128 || N_shard < 128) return TFCCB200_EALIGN;
+  cudaError_t e;
+  const DeviceInfo* di = current_device_info(&e);
+  if (!di) return static_cast<int>(e);
+  return umma_qgemm(a, umma_plan(M, N_shard, K, 1, di->sm_count, 1, -1, false, false).pair);
 }
 
 int tfccb200_sgemm_skinny_static(void* stream, const float* A, const float* B, float* C,

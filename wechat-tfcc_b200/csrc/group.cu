@@ -1,0 +1,441 @@
+// Multi-GPU shim of the matmul path on one box.
+//
+// The reference has no multi-device operator: its model is one Device per GPU, each driven by
+// its own thread and session (tfcc/core/utils/tfcc_initializer.cpp:50-66,
+// tfcc/cuda/utils/tfcc_cudautils.cpp:23-50).  What is added here is the N split of one large
+// product: GPU g holds A and the column shard B[:, g*N/G:(g+1)*N/G], multiplies it on the
+// tensor-core path and stores every finished tile into the same columns of EVERY GPU's
+// row-major C with ordinary stores over NVLink (tfccb200_*_nsplit_push), so that each GPU ends
+// up with the whole C and no separate all-gather runs.
+//
+// Two ways to drive it:
+//   * one process per GPU (torch.distributed, MPI, ...): the caller maps its peers' buffers
+//     (CUDA IPC, symmetric memory) and calls the per-rank entry points, passing a barrier
+//     callback where a cross-rank barrier is needed (tfccb200_sgemm_nsplit_host);
+//   * one process for all GPUs -- how a TFCC program with one Device per GPU looks: a
+//     tfccb200_group enables peer access between its devices, owns one stream per device and
+//     orders the devices with events (tfccb200_group_*).
+// Nothing here uses a TMA or multicast LOAD on peer memory; peers are only ever written, with
+// st.global or multimem.st.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <new>
+#include <vector>
+
+#include "internal.h"
+#include "pdl.cuh"
+
+namespace tfccb200 {
+
+namespace {
+
+// dst[d][i] = src[i] for every destination: one pass over the source, 128 bits per thread.
+// With `mc` set the line is stored once through the NVLink multicast alias instead.
+struct BroadcastTargets {
+  float4* dst[8];
+  unsigned num_dst;
+  float4* mc;
+};
+
+__global__ void __launch_bounds__(256)
+broadcast_kernel(const float4* __restrict__ src, BroadcastTargets t, size_t n4) {
+  for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n4; i += gridDim.x * 256ull) {
+    const float4 v = __ldcs(src + i);
+    if (t.mc) {
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                   :
+                   : "l"(t.mc + i), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                   : "memory");
+    } else {
+      for (unsigned d = 0; d < t.num_dst; ++d) t.dst[d][i] = v;
+    }
+  }
+}
+
+int broadcast_bytes(cudaStream_t stream, const void* src, void* const* dst, unsigned num_dst,
+                    void* mc, size_t bytes) {
+  if (bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(src) & 15u)) return TFCCB200_EALIGN;
+  BroadcastTargets t = {};
+  for (unsigned d = 0; d < num_dst; ++d) {
+    if (reinterpret_cast<uintptr_t>(dst[d]) & 15u) return TFCCB200_EALIGN;
+    t.dst[t.num_dst++] = static_cast<float4*>(dst[d]);
+  }
+  t.mc = static_cast<float4*>(mc);
+  if (t.num_dst == 0 && !t.mc) return TFCCB200_OK;
+  cudaError_t ce;
+  const DeviceInfo* di = current_device_info(&ce);
+  if (!di) return static_cast<int>(ce);
+  const size_t n4 = bytes / 16;
+  size_t blocks = (n4 + 255) / 256;
+  blocks = std::min<size_t>(blocks, static_cast<size_t>(di->sm_count) * 8);
+  broadcast_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      static_cast<const float4*>(src), t, n4);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  count_launch();
+  return TFCCB200_OK;
+}
+
+}  // namespace
+
+// ---- one rank's share of an N-split product whose operands start in host memory ----------
+int nsplit_host_upload(const NsplitHostRank& r) {
+  const unsigned rows = r.M / r.num_ranks;
+  float* my_rows = r.A_ranks[r.rank] + static_cast<size_t>(r.rank) * rows * r.K;
+  cudaError_t e;
+  // A rows first: the peers wait for them; B follows while the rows cross NVLink
+  if ((e = cudaMemcpyAsync(my_rows, r.hA_rows, static_cast<size_t>(rows) * r.K * 4,
+                           cudaMemcpyHostToDevice, r.stream)) != cudaSuccess)
+    return static_cast<int>(e);
+  void* dst[8];
+  unsigned n = 0;
+  for (unsigned d = 0; d < r.num_ranks; ++d)
+    if (d != r.rank && r.A_ranks[d])
+      dst[n++] = r.A_ranks[d] + static_cast<size_t>(r.rank) * rows * r.K;
+  void* mc = r.A_multicast ? r.A_multicast + static_cast<size_t>(r.rank) * rows * r.K : nullptr;
+  int st = broadcast_bytes(r.stream, my_rows, dst, n, mc, static_cast<size_t>(rows) * r.K * 4);
+  if (st != TFCCB200_OK) return st;
+  if ((e = cudaMemcpy2DAsync(r.B_shard_dev, static_cast<size_t>(r.N_shard) * 4, r.hB_shard,
+                             static_cast<size_t>(r.ldb_host) * 4,
+                             static_cast<size_t>(r.N_shard) * 4, r.K, cudaMemcpyHostToDevice,
+                             r.stream)) != cudaSuccess)
+    return static_cast<int>(e);
+  return TFCCB200_OK;
+}
+
+int nsplit_host_multiply(const NsplitHostRank& r) {
+  return tfccb200_sgemm_nsplit_push(r.stream, r.A_ranks[r.rank], r.B_shard_dev, r.C_ranks,
+                                    r.num_ranks, r.rank, nullptr, r.M, r.N_shard, r.K,
+                                    r.precision, r.C_multicast, r.workspace, r.workspace_bytes,
+                                    r.status);
+}
+
+int nsplit_host_download(const NsplitHostRank& r) {
+  const unsigned rows = r.M / r.num_ranks;
+  const size_t n_total = static_cast<size_t>(r.N_shard) * r.num_ranks;
+  const float* my_rows = r.C_ranks[r.rank] + static_cast<size_t>(r.rank) * rows * n_total;
+  cudaError_t e = cudaMemcpyAsync(r.hC_rows, my_rows, static_cast<size_t>(rows) * n_total * 4,
+                                  cudaMemcpyDeviceToHost, r.stream);
+  return e == cudaSuccess ? TFCCB200_OK : static_cast<int>(e);
+}
+
+int nsplit_host_check(const NsplitHostRank& r) {
+  if (!r.hA_rows || !r.hB_shard || !r.hC_rows || !r.A_ranks || !r.B_shard_dev || !r.C_ranks)
+    return TFCCB200_EINVAL;
+  if (r.num_ranks == 0 || r.num_ranks > 8 || r.rank >= r.num_ranks) return TFCCB200_EINVAL;
+  if (r.M == 0 || r.N_shard == 0 || r.K == 0 || r.M % r.num_ranks != 0) return TFCCB200_EINVAL;
+  if (r.ldb_host < r.N_shard) return TFCCB200_EINVAL;
+  if (r.K % 4 != 0 || r.N_shard % 4 != 0) return TFCCB200_EALIGN;
+  if (!r.A_ranks[r.rank] || !r.C_ranks[r.rank]) return TFCCB200_EINVAL;
+  return TFCCB200_OK;
+}
+
+}  // namespace tfccb200
+
+using namespace tfccb200;
+
+// ---- the in-process device group -------------------------------------------------------------
+struct tfccb200_group {
+  int ndev = 0;
+  int dev[8] = {};
+  cudaStream_t stream[8] = {};
+  cudaEvent_t done[8] = {};      // "everything queued on stream[i] so far"
+  int* status[8] = {};           // device status words
+  void* workspace[8] = {};
+  size_t workspace_bytes[8] = {};
+  // staging of the host-buffer entry point, grown on demand and kept
+  float* A[8] = {};
+  float* B[8] = {};
+  float* C[8] = {};
+  size_t a_elems = 0, b_elems = 0, c_elems = 0;
+};
+
+namespace {
+
+struct DeviceScope {  // restores the caller's current device
+  int saved = -1;
+  DeviceScope() { cudaGetDevice(&saved); }
+  ~DeviceScope() {
+    if (saved >= 0) cudaSetDevice(saved);
+  }
+};
+
+// Every stream of the group waits for everything queued so far on all the others.
+cudaError_t group_barrier(tfccb200_group* g) {
+  cudaError_t e;
+  for (int i = 0; i < g->ndev; ++i) {
+    if ((e = cudaSetDevice(g->dev[i])) != cudaSuccess) return e;
+    if ((e = cudaEventRecord(g->done[i], g->stream[i])) != cudaSuccess) return e;
+  }
+  for (int j = 0; j < g->ndev; ++j) {
+    if ((e = cudaSetDevice(g->dev[j])) != cudaSuccess) return e;
+    for (int i = 0; i < g->ndev; ++i)
+      if (i != j && (e = cudaStreamWaitEvent(g->stream[j], g->done[i], 0)) != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
+cudaError_t grow(float** p, size_t elems) {
+  if (*p) cudaFree(*p);
+  *p = nullptr;
+  return cudaMalloc(reinterpret_cast<void**>(p), elems * sizeof(float));
+}
+
+// Status of the device status words (and of the streams): TFCCB200_EDEVICE if a kernel of the
+// group abandoned a wait.  Synchronises every stream.
+int group_finish(tfccb200_group* g) {
+  int result = TFCCB200_OK;
+  for (int i = 0; i < g->ndev; ++i) {
+    cudaError_t e;
+    if ((e = cudaSetDevice(g->dev[i])) != cudaSuccess) return static_cast<int>(e);
+    int word = 0;
+    if ((e = cudaMemcpyAsync(&word, g->status[i], sizeof(int), cudaMemcpyDeviceToHost,
+                             g->stream[i])) != cudaSuccess)
+      return static_cast<int>(e);
+    if ((e = cudaStreamSynchronize(g->stream[i])) != cudaSuccess) return static_cast<int>(e);
+    if (word) {
+      cudaMemsetAsync(g->status[i], 0, sizeof(int), g->stream[i]);
+      result = TFCCB200_EDEVICE;
+    }
+  }
+  return result;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tfccb200_group_create(int ndev, const int* devices, tfccb200_group** out) {
+  if (!devices || !out || ndev < 1 || ndev > 8) return TFCCB200_EINVAL;
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  for (int i = 0; i < ndev; ++i)
+    if (devices[i] < 0 || devices[i] >= count) return TFCCB200_EINVAL;
+  DeviceScope scope;
+  tfccb200_group* g = new (std::nothrow) tfccb200_group;
+  if (!g) return static_cast<int>(cudaErrorMemoryAllocation);
+  g->ndev = ndev;
+  for (int i = 0; i < ndev; ++i) g->dev[i] = devices[i];
+  auto fail = [&](int st) {
+    tfccb200_group_destroy(g);
+    return st;
+  };
+  for (int i = 0; i < ndev; ++i) {
+    if ((e = cudaSetDevice(g->dev[i])) != cudaSuccess) return fail(static_cast<int>(e));
+    for (int j = 0; j < ndev; ++j) {
+      if (g->dev[j] == g->dev[i]) continue;
+      int can = 0;
+      if ((e = cudaDeviceCanAccessPeer(&can, g->dev[i], g->dev[j])) != cudaSuccess)
+        return fail(static_cast<int>(e));
+      if (!can) return fail(TFCCB200_EUNSUPPORTED);
+      e = cudaDeviceEnablePeerAccess(g->dev[j], 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();
+      } else if (e != cudaSuccess) {
+        return fail(static_cast<int>(e));
+      }
+    }
+    if ((e = cudaStreamCreateWithFlags(&g->stream[i], cudaStreamNonBlocking)) != cudaSuccess)
+      return fail(static_cast<int>(e));
+    if ((e = cudaEventCreateWithFlags(&g->done[i], cudaEventDisableTiming)) != cudaSuccess)
+      return fail(static_cast<int>(e));
+    if ((e = cudaMalloc(reinterpret_cast<void**>(&g->status[i]), sizeof(int))) != cudaSuccess)
+      return fail(static_cast<int>(e));
+    if ((e = cudaMemset(g->status[i], 0, sizeof(int))) != cudaSuccess)
+      return fail(static_cast<int>(e));
+    cudaError_t ie;
+    const DeviceInfo* di = current_device_info(&ie);
+    if (!di) return fail(static_cast<int>(ie));
+    g->workspace_bytes[i] = umma_stream_k_workspace(di->sm_count);
+    if ((e = cudaMalloc(&g->workspace[i], g->workspace_bytes[i])) != cudaSuccess)
+      return fail(static_cast<int>(e));
+  }
+  *out = g;
+  return TFCCB200_OK;
+}
+
+int tfccb200_group_destroy(tfccb200_group* g) {
+  if (!g) return TFCCB200_EINVAL;
+  DeviceScope scope;
+  for (int i = 0; i < g->ndev; ++i) {
+    if (cudaSetDevice(g->dev[i]) != cudaSuccess) continue;
+    if (g->stream[i]) cudaStreamSynchronize(g->stream[i]);
+    if (g->A[i]) cudaFree(g->A[i]);
+    if (g->B[i]) cudaFree(g->B[i]);
+    if (g->C[i]) cudaFree(g->C[i]);
+    if (g->workspace[i]) cudaFree(g->workspace[i]);
+    if (g->status[i]) cudaFree(g->status[i]);
+    if (g->done[i]) cudaEventDestroy(g->done[i]);
+    if (g->stream[i]) cudaStreamDestroy(g->stream[i]);
+  }
+  delete g;
+  return TFCCB200_OK;
+}
+
+int tfccb200_group_size(const tfccb200_group* g) { return g ? g->ndev : 0; }
+
+int tfccb200_group_device(const tfccb200_group* g, int member) {
+  return (g && member >= 0 && member < g->ndev) ? g->dev[member] : -1;
+}
+
+void* tfccb200_group_stream(const tfccb200_group* g, int member) {
+  return (g && member >= 0 && member < g->ndev) ? g->stream[member] : nullptr;
+}
+
+int tfccb200_group_sync(tfccb200_group* g) {
+  if (!g) return TFCCB200_EINVAL;
+  DeviceScope scope;
+  return group_finish(g);
+}
+
+int tfccb200_group_sgemm_nsplit(tfccb200_group* g, const float* const* A,
+                                const float* const* B_shards, float* const* C,
+                                const float* const* bias_shards, unsigned M, unsigned N_shard,
+                                unsigned K, int precision_mode) {
+  if (!g || !A || !B_shards || !C) return TFCCB200_EINVAL;
+  DeviceScope scope;
+  cudaError_t e;
+  // the members' earlier work (e.g. readers of the previous C) is finished before anyone writes
+  if ((e = group_barrier(g)) != cudaSuccess) return static_cast<int>(e);
+  for (int i = 0; i < g->ndev; ++i) {
+    if ((e = cudaSetDevice(g->dev[i])) != cudaSuccess) return static_cast<int>(e);
+    int st = tfccb200_sgemm_nsplit_push(g->stream[i], A[i], B_shards[i], C, g->ndev, i,
+                                        bias_shards ? bias_shards[i] : nullptr, M, N_shard, K,
+                                        precision_mode, nullptr, g->workspace[i],
+                                        g->workspace_bytes[i], g->status[i]);
+    if (st != TFCCB200_OK) return st;
+  }
+  if ((e = group_barrier(g)) != cudaSuccess) return static_cast<int>(e);
+  return TFCCB200_OK;
+}
+
+int tfccb200_group_qgemm_nsplit(tfccb200_group* g, const uint8_t* const* A,
+                                const int32_t* const* rsA, int32_t offA,
+                                const int8_t* const* B_shards, const int32_t* const* rsB_shards,
+                                int32_t offB, int32_t* const* C, unsigned M, unsigned N_shard,
+                                unsigned K) {
+  if (!g || !A || !rsA || !B_shards || !rsB_shards || !C) return TFCCB200_EINVAL;
+  DeviceScope scope;
+  cudaError_t e;
+  if ((e = group_barrier(g)) != cudaSuccess) return static_cast<int>(e);
+  for (int i = 0; i < g->ndev; ++i) {
+    if ((e = cudaSetDevice(g->dev[i])) != cudaSuccess) return static_cast<int>(e);
+    int st = tfccb200_qgemm_nsplit_push(g->stream[i], A[i], rsA[i], offA, B_shards[i],
+                                        rsB_shards[i], offB, C, g->ndev, i, M, N_shard, K,
+                                        nullptr, g->status[i]);
+    if (st != TFCCB200_OK) return st;
+  }
+  if ((e = group_barrier(g)) != cudaSuccess) return static_cast<int>(e);
+  return TFCCB200_OK;
+}
+
+int tfccb200_group_sgemm_nsplit_host(tfccb200_group* g, const float* hA, const float* hB,
+                                     float* hC, unsigned M, unsigned N, unsigned K,
+                                     int precision_mode) {
+  if (!g || !hA || !hB || !hC || M == 0 || N == 0 || K == 0) return TFCCB200_EINVAL;
+  const unsigned G = static_cast<unsigned>(g->ndev);
+  if (M % G != 0 || N % G != 0) return TFCCB200_EINVAL;
+  if (static_cast<unsigned long long>(M) * K > 0xffffffffull ||
+      static_cast<unsigned long long>(K) * N > 0xffffffffull ||
+      static_cast<unsigned long long>(M) * N > 0xffffffffull)
+    return TFCCB200_EOVERFLOW;
+  const unsigned ns = N / G, rows = M / G;
+  DeviceScope scope;
+  cudaError_t e;
+  const size_t need_a = static_cast<size_t>(M) * K, need_b = static_cast<size_t>(K) * ns,
+               need_c = static_cast<size_t>(M) * N;
+  if (need_a > g->a_elems || need_b > g->b_elems || need_c > g->c_elems) {
+    int st = group_finish(g);  // nobody may still use the buffers that are replaced
+    if (st != TFCCB200_OK) return st;
+    for (unsigned i = 0; i < G; ++i) {
+      if ((e = cudaSetDevice(g->dev[i])) != cudaSuccess) return static_cast<int>(e);
+      if (need_a > g->a_elems && (e = grow(&g->A[i], need_a)) != cudaSuccess) return static_cast<int>(e);
+      if (need_b > g->b_elems && (e = grow(&g->B[i], need_b)) != cudaSuccess) return static_cast<int>(e);
+      if (need_c > g->c_elems && (e = grow(&g->C[i], need_c)) != cudaSuccess) return static_cast<int>(e);
+    }
+    g->a_elems = std::max(g->a_elems, need_a);
+    g->b_elems = std::max(g->b_elems, need_b);
+    g->c_elems = std::max(g->c_elems, need_c);
+  }
+  NsplitHostRank r[8];
+  for (unsigned i = 0; i < G; ++i) {
+    r[i] = {};
+    r[i].stream = g->stream[i];
+    r[i].hA_rows = hA + static_cast<size_t>(i) * rows * K;
+    r[i].hB_shard = hB + static_cast<size_t>(i) * ns;
+    r[i].ldb_host = N;
+    r[i].hC_rows = hC + static_cast<size_t>(i) * rows * N;
+    r[i].A_ranks = g->A;
+    r[i].B_shard_dev = g->B[i];
+    r[i].C_ranks = g->C;
+    r[i].num_ranks = G; r[i].rank = i;
+    r[i].M = M; r[i].N_shard = ns; r[i].K = K;
+    r[i].precision = precision_mode;
+    r[i].workspace = g->workspace[i];
+    r[i].workspace_bytes = g->workspace_bytes[i];
+    r[i].status = g->status[i];
+    int st = nsplit_host_check(r[i]);
+    if (st != TFCCB200_OK) return st;
+  }
+  if ((e = group_barrier(g)) != cudaSuccess) return static_cast<int>(e);
+  for (unsigned i = 0; i < G; ++i) {
+    if ((e = cudaSetDevice(g->dev[i])) != cudaSuccess) return static_cast<int>(e);
+    int st = nsplit_host_upload(r[i]);
+    if (st != TFCCB200_OK) return st;
+  }
+  if ((e = group_barrier(g)) != cudaSuccess) return static_cast<int>(e);  // every A is whole
+  for (unsigned i = 0; i < G; ++i) {
+    if ((e = cudaSetDevice(g->dev[i])) != cudaSuccess) return static_cast<int>(e);
+    int st = nsplit_host_multiply(r[i]);
+    if (st != TFCCB200_OK) return st;
+  }
+  if ((e = group_barrier(g)) != cudaSuccess) return static_cast<int>(e);  // every C is whole
+  for (unsigned i = 0; i < G; ++i) {
+    if ((e = cudaSetDevice(g->dev[i])) != cudaSuccess) return static_cast<int>(e);
+    int st = nsplit_host_download(r[i]);
+    if (st != TFCCB200_OK) return st;
+  }
+  return group_finish(g);
+}
+
+int tfccb200_sgemm_nsplit_host(void* stream, const float* hA_rows, const float* hB_shard,
+                               unsigned ldb_host, float* hC_rows, float* const* A_ranks,
+                               float* A_multicast, float* B_shard_dev, float* const* C_ranks,
+                               float* C_multicast, unsigned num_ranks, unsigned rank, unsigned M,
+                               unsigned N_shard, unsigned K, int precision_mode, void* workspace,
+                               size_t workspace_bytes, tfccb200_barrier_fn barrier,
+                               void* barrier_ctx, int* device_status) {
+  NsplitHostRank r = {};
+  r.stream = static_cast<cudaStream_t>(stream);
+  r.hA_rows = hA_rows; r.hB_shard = hB_shard; r.ldb_host = ldb_host; r.hC_rows = hC_rows;
+  r.A_ranks = A_ranks; r.A_multicast = A_multicast;
+  r.B_shard_dev = B_shard_dev;
+  r.C_ranks = C_ranks; r.C_multicast = C_multicast;
+  r.num_ranks = num_ranks; r.rank = rank;
+  r.M = M; r.N_shard = N_shard; r.K = K;
+  r.precision = precision_mode;
+  r.workspace = workspace; r.workspace_bytes = workspace ? workspace_bytes : 0;
+  r.status = device_status;
+  int st = nsplit_host_check(r);
+  if (st != TFCCB200_OK) return st;
+  if (num_ranks > 1 && !barrier) return TFCCB200_EINVAL;
+  auto sync_ranks = [&]() { return num_ranks > 1 ? barrier(barrier_ctx, stream) : 0; };
+  // an early return must not leave copies from / into the caller's host buffers in flight
+  struct Join {
+    cudaStream_t s;
+    ~Join() { cudaStreamSynchronize(s); }
+  } join{r.stream};
+  if ((st = sync_ranks()) != 0) return st;  // the peers have finished with the previous A and C
+  if ((st = nsplit_host_upload(r)) != TFCCB200_OK) return st;
+  if ((st = sync_ranks()) != 0) return st;  // every rank's A is whole
+  if ((st = nsplit_host_multiply(r)) != TFCCB200_OK) return st;
+  if ((st = sync_ranks()) != 0) return st;  // every rank's C is whole
+  if ((st = nsplit_host_download(r)) != TFCCB200_OK) return st;
+  cudaError_t e = cudaStreamSynchronize(r.stream);
+  return e == cudaSuccess ? TFCCB200_OK : static_cast<int>(e);
+}
+
+}  // extern "C"

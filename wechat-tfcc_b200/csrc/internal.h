@@ -43,6 +43,8 @@ struct SgemmArgs {
   unsigned long long ldc;
   unsigned col_offset;
   int activation;  // TFCCB200_ACT_*: applied to A.B + bias before the store
+  unsigned max_ctas;  // tensor-core path: use at most this many SMs (0 = all); lets two
+                      // products run side by side on disjoint parts of the chip
 };
 
 struct QgemmArgs {
@@ -56,6 +58,13 @@ struct QgemmArgs {
   int32_t offA, offB;
   unsigned M, N, K, batch;
   int* status;
+  // Tensor-core path only (as in SgemmArgs): several destinations / a multicast alias, row
+  // pitch ldc, first column col_offset; num_dst == 0 is the plain case.
+  int32_t* dst[8];
+  unsigned num_dst;
+  int32_t* mc_dst;
+  unsigned long long ldc;
+  unsigned col_offset;
 };
 
 // ---- tcgen05 paths (umma_launch.cu) ----
@@ -70,6 +79,7 @@ struct UmmaPlan {
 };
 UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count,
                    int elem_bytes, int force_pair, bool allow_cluster_k, bool allow_stream_k);
+int umma_sm_budget(int sm_count, unsigned max_ctas);  // SMs a launch may use (whole pairs)
 bool stream_k_scratch_ok(const SgemmArgs& a, int sm_count);  // scratch lent for the k-shared wave
 size_t umma_stream_k_workspace(int sm_count);  // scratch that lets umma_sgemm share tiles by k-block
 void set_test_flag_wait(unsigned long long timeout_ns, unsigned expect_extra);
@@ -96,6 +106,31 @@ int interleave_panels_f32(cudaStream_t stream, const float* src, float* out, uns
 template <class T>
 int reduce_sum(cudaStream_t stream, const T* src, unsigned batch, unsigned rows, unsigned cols,
                int row_flag, int32_t* dst);
+
+// ---- multi-GPU shim (group.cu) ----
+// One rank's view of an N-split product whose operands start in host memory.
+struct NsplitHostRank {
+  cudaStream_t stream;
+  const float* hA_rows;    // host: this rank's M / num_ranks rows of A
+  const float* hB_shard;   // host: first element of this rank's column shard of B
+  unsigned ldb_host;       // row pitch of hB_shard in elements
+  float* hC_rows;          // host: this rank's M / num_ranks rows of the full-width C
+  float* const* A_ranks;   // device: every rank's [M,K] buffer (peers may be NULL = not written)
+  float* A_multicast;      // NVLink multicast alias of the A buffers, or nullptr
+  float* B_shard_dev;      // device: [K, N_shard]
+  float* const* C_ranks;   // device: every rank's [M, N_shard * num_ranks]
+  float* C_multicast;
+  unsigned num_ranks, rank;
+  unsigned M, N_shard, K;
+  int precision;
+  void* workspace;
+  size_t workspace_bytes;
+  int* status;
+};
+int nsplit_host_check(const NsplitHostRank& r);
+int nsplit_host_upload(const NsplitHostRank& r);    // rows of A up and on to the peers, B shard up
+int nsplit_host_multiply(const NsplitHostRank& r);  // product, tiles stored into every rank's C
+int nsplit_host_download(const NsplitHostRank& r);  // this rank's rows of C down
 
 // ---- attention / FFN glue (nn_kernels.cu) ----
 int softmax_f32(cudaStream_t stream, const float* src, unsigned rows, unsigned cols, float scale,

@@ -73,8 +73,8 @@ struct UmmaGemmParams {
   // dst[d] + b*strideC + i*ldc + col_offset + j.
   void* dst[kMaxDestinations];
   unsigned num_dst;
-  // float kinds: when set, the tile goes out through this NVLink multicast address instead
-  // (one store reaches the same offset of every GPU bound to it) and dst[] is not written
+  // When set, the tile goes out through this NVLink multicast address instead (one store
+  // reaches the same offset of every GPU bound to it) and dst[] is not written
   void* mc_dst;
   unsigned long long ldc;  // row pitch of the destinations, in elements
   unsigned col_offset;     // first destination column of this problem's column 0
@@ -334,7 +334,7 @@ __device__ __forceinline__ void epi_flush_block(uint32_t* stage, uint32_t lane, 
     if (grow < p.M && col_ok) {
       const unsigned long long off =
           batch_off + static_cast<unsigned long long>(grow) * p.ldc + p.col_offset + col;
-      if (kIsFloat && p.mc_dst) {
+      if (p.mc_dst) {
         ptx::multimem_st_v4(static_cast<uint32_t*>(p.mc_dst) + off, v);
       } else {
         for (unsigned d = 0; d < p.num_dst; ++d)
@@ -800,9 +800,32 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           if (row_ok)
             row_term += static_cast<uint32_t>(p.rsA[static_cast<size_t>(p.strideRsA) * b + row]) *
                         static_cast<uint32_t>(p.offB);
+          const uint32_t oa = static_cast<uint32_t>(p.offA);
+          if (p.num_dst > 1 || p.mc_dst) {
+            // column shards pushed to several GPUs: go through the transposing stage so that
+            // every store instruction covers whole 128-byte lines of the peers' memory
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+              if (col0 + c * 32 >= p.N) break;
+              uint32_t r[32];
+              ptx::tmem_ld_32x32(taddr + c * 32, r);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int qq = 0; qq < 8; ++qq)
+                epi_stage_chunk(stage, lane, qq,
+                                make_uint4(r[4 * qq] + row_term, r[4 * qq + 1] + row_term,
+                                           r[4 * qq + 2] + row_term, r[4 * qq + 3] + row_term));
+              uint4 ct = make_uint4(0u, 0u, 0u, 0u);
+              const unsigned col = col0 + c * 32 + (lane & 7u) * 4;
+              if (col < p.N) {
+                ct = __ldg(reinterpret_cast<const uint4*>(rsB + col));
+                ct.x *= oa; ct.y *= oa; ct.z *= oa; ct.w *= oa;
+              }
+              epi_flush_block<false>(stage, lane, row0, col0 + c * 32, p, batch_off, ct);
+            }
+          } else {
           uint32_t* crow = static_cast<uint32_t*>(p.dst[0]) + batch_off +
                            static_cast<unsigned long long>(row) * p.ldc + p.col_offset + col0;
-          const uint32_t oa = static_cast<uint32_t>(p.offA);
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             if (col0 + c * 32 >= p.N) break;
@@ -824,6 +847,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                 }
               }
             }
+          }
           }
         }
         release_acc(acc);

@@ -245,6 +245,13 @@ void set_test_flag_wait(unsigned long long timeout_ns, unsigned expect_extra) {
   g_flag_expect_extra.store(expect_extra, std::memory_order_relaxed);
 }
 
+int umma_sm_budget(int sm_count, unsigned max_ctas) {
+  int n = sm_count;
+  if (max_ctas && static_cast<int>(max_ctas) < n) n = static_cast<int>(max_ctas);
+  n &= ~1;  // whole CTA pairs
+  return n < 2 ? 2 : n;
+}
+
 bool stream_k_scratch_ok(const SgemmArgs& a, int sm_count) {
   return a.workspace && (reinterpret_cast<uintptr_t>(a.workspace) & 255u) == 0 &&
          a.workspace_bytes >= umma_stream_k_workspace(sm_count);
@@ -379,11 +386,12 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
   const bool b_batched = a.batch > 1 && a.strideB != 0;
   static const int env_cluster_k = env_int("TFCCB200_CLUSTER_K", -1);  // -1: planned; 1: off
   const bool fp32_split = a.precision == TFCCB200_PRECISION_FP32;
+  const int sm_avail = umma_sm_budget(di->sm_count, a.max_ctas);
   const UmmaPlan plan =
-      umma_plan(a.M, a.N, a.K, a.batch, di->sm_count,
+      umma_plan(a.M, a.N, a.K, a.batch, sm_avail,
                 a.precision == TFCCB200_PRECISION_BF16 ? 2 : 4, pair ? 1 : 0,
                 fp32_split && !pair && env_cluster_k != 1,
-                fp32_split && stream_k_scratch_ok(a, di->sm_count));
+                fp32_split && stream_k_scratch_ok(a, sm_avail));
   UmmaPlan tuned = plan;
   static const int env_bn = env_int("TFCCB200_FORCE_BN", 0);  // tuning knobs, read once
   if (env_bn == 64 || env_bn == 128 || env_bn == 256) tuned.bn = env_bn;
@@ -430,7 +438,7 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
     q.timeout_ns = kDefaultTimeoutNs;
     q.flag_timeout_ns = kDefaultTimeoutNs;
     constexpr auto H = ptx::MmaKind::BF16;
-    const int sms16 = di->sm_count;
+    const int sms16 = sm_avail;
     if (!pair) {
       if (bn == 256) return launch<H, false, 1, 256, 4>(a.stream, ta16, tb16, q, sms16);
       if (bn == 128) return launch<H, false, 1, 128, 6>(a.stream, ta16, tb16, q, sms16);
@@ -491,7 +499,7 @@ int umma_sgemm(const SgemmArgs& a, bool pair) {
 
   constexpr auto T = ptx::MmaKind::TF32;
   const bool split = a.precision == TFCCB200_PRECISION_FP32;
-  const int sms = di->sm_count;
+  const int sms = sm_avail;
 
   // With fewer than two tiles per CTA little or nothing overlaps the epilogue, and an erf per
   // element on the 256 epilogue threads of an SM costs more there (measured +12..15 us on
@@ -562,10 +570,13 @@ int umma_qgemm(const QgemmArgs& a, bool pair) {
     return TFCCB200_EINVAL;
 
   UmmaGemmParams p = {};
-  p.num_dst = 1;
+  p.num_dst = a.num_dst ? a.num_dst : 1;
+  if (p.num_dst > kMaxDestinations) return TFCCB200_EINVAL;
   p.dst[0] = a.C;
-  p.ldc = a.N;
-  p.col_offset = 0;
+  for (unsigned d = 0; d < a.num_dst; ++d) p.dst[d] = a.dst[d];
+  p.mc_dst = a.mc_dst;
+  p.ldc = a.ldc ? a.ldc : a.N;
+  p.col_offset = a.col_offset;
   p.rsA = a.rsA; p.rsB = a.rsB;
   p.offA = a.offA; p.offB = a.offB;
   p.kterm = static_cast<int32_t>(static_cast<uint32_t>(a.offA) * static_cast<uint32_t>(a.offB) *

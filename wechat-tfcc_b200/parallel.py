@@ -23,7 +23,7 @@ import ctypes as C
 import os
 
 from . import blas, exceptions
-from ._lib import PRECISIONS, check, lib
+from ._lib import BARRIER_FN, PRECISIONS, check, lib
 from .session import get_session
 
 
@@ -91,76 +91,147 @@ def nsplit_matmul(a, b_shard, bias_shard=None, *, group=None, matmul_fn=None,
 class FusedNSplit:
     """N-split matmul whose all-gather happens inside the GEMM epilogue.
 
-    Every rank owns a full row-major ``C [M, N]`` that its peers can address (symmetric
+    Every rank owns full row-major ``C [M, N]`` buffers that its peers can address (symmetric
     memory, or CUDA IPC handles when that is unavailable).  ``matmul`` runs the tensor-core
     GEMM on this rank's column shard of B and stores each finished tile into the matching
-    columns of every rank's C with ordinary 128-byte-line stores over NVLink, overlapping the
-    transfer with the remaining tiles; a cross-rank barrier then closes the step.  The result
-    is valid on every rank until the next ``matmul`` on any rank starts writing again.
+    columns of every rank's C with ordinary 128-byte-line stores over NVLink (or one multimem
+    store through the switch), overlapping the transfer with the remaining tiles; a cross-rank
+    barrier then closes the step.  ``dtype=torch.int32`` plans the same for the quantized
+    matmul (``qmatmul``).
+
+    Result buffers.  Every lane alternates between two C buffers, so a call never writes the
+    buffer its predecessor returned: the result of a call may be read by work enqueued before
+    the next call of this object on the same rank, with no extra barrier.
+
+    ``in_flight=2`` keeps two products in flight: calls alternate between two lanes, each with
+    its own stream, C buffers, scratch and barrier channel, and each limited to half of the
+    SMs.  The last tiles of one product are then pushed while the other product is still
+    multiplying, which hides the burst of NVLink traffic at the end of a product (every GPU
+    finishes its last tiles at the same moment and every GPU receives from all the others).
+    Use ``matmul(..., wait=False)`` and ``join()`` to get the overlap.
     """
 
-    def __init__(self, m: int, n_total: int, device, group=None):
+    def __init__(self, m: int, n_total: int, device, group=None, *, in_flight: int = 1,
+                 dtype=torch.float32):
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         self.device = torch.device(device)
         if n_total % self.world != 0:
             raise exceptions.InvalidArgumentError("N must divide evenly over the ranks")
+        if in_flight not in (1, 2):
+            raise exceptions.InvalidArgumentError("in_flight is 1 or 2")
+        if dtype not in (torch.float32, torch.int32):
+            raise exceptions.InvalidArgumentError("C is float32 (matmul) or int32 (qmatmul)")
         self.m, self.n_total, self.ns = m, n_total, n_total // self.world
-        self.handle = None
+        self.dtype = dtype
+        self.in_flight = in_flight
         self.how = None
-        self._mc_ptr = None
+        self._keep = []
+        self._calls = 0
+        want_mc = os.environ.get("TFCCB200_MULTICAST", "1" if self.world >= 4 else "0") != "0"
+        # buffers[lane][slot] -> (tensor, ctypes array of every rank's pointer, multicast ptr, handle)
+        self.buffers = [[self._shared((m, n_total), dtype, want_mc) for _slot in range(2)]
+                        for _lane in range(in_flight)]
+        self.handle = self.buffers[0][0][3]
+        self.c = self.buffers[0][0][0]
+        self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._streams = ([torch.cuda.Stream(self.device) for _ in range(2)]
+                         if in_flight == 2 else [None])
+        self._done = [None] * in_flight
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self._max_ctas = (sms // 2) & ~1 if in_flight == 2 else 0
+        self._host = None
+
+    # ---- peer-addressable buffers ------------------------------------------------------------
+    def _shared(self, shape, dtype, want_mc):
+        """A tensor every rank can address: (tensor, pointers by rank, multicast ptr or None,
+        symmetric-memory handle or None)."""
         try:
             import torch.distributed._symmetric_memory as symm_mem
-            self.c = symm_mem.empty((m, n_total), dtype=torch.float32, device=self.device)
-            self.handle = symm_mem.rendezvous(self.c, group=self.group)
-            ptrs = [int(p) for p in self.handle.buffer_ptrs]
-            self.how = "symmetric memory"
-            # NVLink multicast alias of C (0 when the fabric has no NVLS): one store reaches
-            # every rank, so a GPU sends its shard once instead of world - 1 times.  With two
-            # ranks the plain peer store is as cheap (measured 476 against 461 TFLOP/s), so
-            # multicast is the default from four ranks on (864 against 833 TFLOP/s on four GPUs,
-            # 1374 against 1377 on eight); TFCCB200_MULTICAST=0/1 overrides.
-            mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
-            want = os.environ.get("TFCCB200_MULTICAST", "1" if self.world >= 4 else "0")
-            if mc and want != "0":
-                self._mc_ptr = mc + (self.c.data_ptr() - ptrs[self.rank])
-                self.how = "symmetric memory, NVLink multicast stores"
+            t = symm_mem.empty(shape, dtype=dtype, device=self.device)
+            handle = symm_mem.rendezvous(t, group=self.group)
+            ptrs = [int(p) for p in handle.buffer_ptrs]
+            how = "symmetric memory"
+            # NVLink multicast alias (0 when the fabric has no NVLS): one store reaches every
+            # rank, so a GPU sends its shard once instead of world - 1 times.  With two ranks the
+            # plain peer store is as cheap, so multicast is the default from four ranks on;
+            # TFCCB200_MULTICAST=0/1 overrides.
+            mc = int(getattr(handle, "multicast_ptr", 0) or 0)
+            mc_ptr = None
+            if mc and want_mc:
+                mc_ptr = mc + (t.data_ptr() - ptrs[self.rank])
+                how = "symmetric memory, NVLink multicast stores"
         except Exception as exc:  # fall back to classic CUDA IPC handles
-            self.handle = None
             self._symm_error = repr(exc)
-            self.c = torch.empty((m, n_total), dtype=torch.float32, device=self.device)
-            ptrs = self._exchange_ipc()
-            self.how = "CUDA IPC handles"
-        self._ptrs = (C.c_void_p * self.world)(*ptrs)
-        self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
+            handle, mc_ptr = None, None
+            t = torch.empty(shape, dtype=dtype, device=self.device)
+            ptrs = self._exchange_ipc(t)
+            how = "CUDA IPC handles"
+        self.how = how
+        return t, (C.c_void_p * self.world)(*ptrs), mc_ptr, handle
 
-    def _exchange_ipc(self):
-        storage = self.c.untyped_storage()
+    def _exchange_ipc(self, t):
+        storage = t.untyped_storage()
         handle = storage._share_cuda_()
         gathered = [None] * self.world
-        dist.all_gather_object(gathered, (handle, self.c.storage_offset()), group=self.group)
-        self._peers = []
+        dist.all_gather_object(gathered, (handle, t.storage_offset()), group=self.group)
         ptrs = []
         for r, (h, off) in enumerate(gathered):
             if r == self.rank:
-                ptrs.append(self.c.data_ptr())
+                ptrs.append(t.data_ptr())
                 continue
             st = torch.UntypedStorage._new_shared_cuda(*h)
-            t = torch.empty(0, dtype=torch.float32, device=st.device).set_(
-                st, off, (self.m, self.n_total), (self.n_total, 1))
-            self._peers.append(t)  # keeps the mapping alive
-            ptrs.append(t.data_ptr())
+            peer = torch.empty(0, dtype=t.dtype, device=st.device).set_(st, off, t.shape, t.stride())
+            self._keep.append(peer)  # keeps the mapping alive
+            ptrs.append(peer.data_ptr())
         return ptrs
 
-    def barrier(self):
+    def barrier(self, channel: int = 0):
         """All ranks' kernels issued so far on the current streams have completed."""
         if self.handle is not None and hasattr(self.handle, "barrier"):
-            self.handle.barrier(channel=0)
+            self.handle.barrier(channel=channel)
         else:
             dist.all_reduce(self._flag, group=self.group)
 
-    def matmul(self, a, b_shard, bias_shard=None, *, precision: str = "fp32"):
+    # ---- the product -------------------------------------------------------------------------
+    def _next(self):
+        lane = self._calls % self.in_flight
+        slot = (self._calls // self.in_flight) % 2
+        self._calls += 1
+        return lane, self.buffers[lane][slot]
+
+    def _run(self, launch, wait):
+        """Run ``launch(buffer)`` plus the closing barrier on the next lane."""
+        lane, buf = self._next()
+        stream = self._streams[lane]
+        if stream is None:
+            with torch.cuda.device(self.device):
+                launch(buf)
+                self.barrier(0)
+            return buf[0]
+        cur = torch.cuda.current_stream(self.device)
+        stream.wait_event(cur.record_event())   # operands, and readers of older results
+        with torch.cuda.device(self.device), torch.cuda.stream(stream):
+            launch(buf)
+            self.barrier(lane)
+            self._done[lane] = stream.record_event()
+        if wait:
+            cur.wait_event(self._done[lane])
+        return buf[0]
+
+    def join(self):
+        """The current stream waits for every product issued so far."""
+        cur = torch.cuda.current_stream(self.device)
+        for ev in self._done:
+            if ev is not None:
+                cur.wait_event(ev)
+
+    def matmul(self, a, b_shard, bias_shard=None, *, precision: str = "fp32", wait: bool = True,
+               destinations=None):
+        """``destinations``: ranks whose C is written (default all); for measurements."""
+        if self.dtype != torch.float32:
+            raise exceptions.InvalidArgumentError("this plan holds an int32 C: use qmatmul")
         if a.dim() != 2 or b_shard.dim() != 2 or a.shape[1] != b_shard.shape[0]:
             raise exceptions.InvalidArgumentError("shape invalid")
         if a.shape[0] != self.m or b_shard.shape[1] != self.ns:
@@ -168,15 +239,155 @@ class FusedNSplit:
         for t in (a, b_shard) + ((bias_shard,) if bias_shard is not None else ()):
             if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
                 raise exceptions.InvalidArgumentError("operands must be contiguous float32 CUDA tensors")
-        sess = get_session(self.device)
-        with torch.cuda.device(self.device):
-            ws_bytes = lib.tfccb200_sgemm_workspace(self.m, self.ns, a.shape[1], 1,
-                                                    PRECISIONS[precision])
+        k = a.shape[1]
+
+        def launch(buf):
+            _t, ptrs, mc_ptr, _h = buf
+            if destinations is not None:
+                ptrs = (C.c_void_p * self.world)(*[ptrs[r] if (r in destinations or r == self.rank)
+                                                   else None for r in range(self.world)])
+                mc_ptr = None
+            sess = get_session(self.device)
+            ws_bytes = lib.tfccb200_sgemm_workspace(self.m, self.ns, k, 1, PRECISIONS[precision])
             ws_ptr, ws_len = sess.workspace(ws_bytes) if ws_bytes else (None, 0)
-            st = lib.tfccb200_sgemm_nsplit_push(
-                sess.stream_ptr, a.data_ptr(), b_shard.data_ptr(), self._ptrs, self.world, self.rank,
-                bias_shard.data_ptr() if bias_shard is not None else None, self.m, self.ns,
-                a.shape[1], PRECISIONS[precision], self._mc_ptr, ws_ptr, ws_len, sess.status_ptr)
+            check(lib.tfccb200_sgemm_nsplit_push_ex(
+                sess.stream_ptr, a.data_ptr(), b_shard.data_ptr(), ptrs, self.world, self.rank,
+                bias_shard.data_ptr() if bias_shard is not None else None, self.m, self.ns, k,
+                PRECISIONS[precision], mc_ptr, ws_ptr, ws_len, self._max_ctas, sess.status_ptr))
+
+        return self._run(launch, wait)
+
+    def qmatmul(self, a, rs_a, off_a: int, b_shard, rs_b_shard, off_b: int, *, wait: bool = True):
+        """Quantized u8 x s8 -> s32 product with the zero-point correction, column shards of B
+        (and of its column sums) per rank, tiles stored into every rank's int32 C."""
+        if self.dtype != torch.int32:
+            raise exceptions.InvalidArgumentError("this plan holds a float32 C: use matmul")
+        if a.dim() != 2 or b_shard.dim() != 2 or a.shape[1] != b_shard.shape[0]:
+            raise exceptions.InvalidArgumentError("tensor a and b don't match")
+        if a.shape[0] != self.m or b_shard.shape[1] != self.ns:
+            raise exceptions.InvalidArgumentError("operands do not match the planned C")
+        if rs_a.numel() != self.m or rs_b_shard.numel() != self.ns:
+            raise exceptions.InvalidArgumentError("tensor a and reduceSumA don't match")
+        for t, dt in ((a, torch.uint8), (b_shard, torch.int8), (rs_a, torch.int32),
+                      (rs_b_shard, torch.int32)):
+            if t.dtype != dt or not t.is_cuda or not t.is_contiguous():
+                raise exceptions.InvalidArgumentError("operands must be contiguous CUDA tensors of "
+                                                      "uint8 / int8 / int32")
+        k = a.shape[1]
+
+        def launch(buf):
+            _t, ptrs, mc_ptr, _h = buf
+            sess = get_session(self.device)
+            check(lib.tfccb200_qgemm_nsplit_push(
+                sess.stream_ptr, a.data_ptr(), rs_a.data_ptr(), int(off_a), b_shard.data_ptr(),
+                rs_b_shard.data_ptr(), int(off_b), ptrs, self.world, self.rank, self.m, self.ns, k,
+                mc_ptr, sess.status_ptr))
+
+        return self._run(launch, wait)
+
+    # ---- host buffers in, host buffer out ------------------------------------------------------
+    def prepare_host(self, k: int):
+        """Collective: peer-addressable staging for ``matmul_host`` (every rank's A [M,K], this
+        rank's B shard)."""
+        want_mc = os.environ.get("TFCCB200_MULTICAST", "1" if self.world >= 4 else "0") != "0"
+        a_buf = self._shared((self.m, k), torch.float32, want_mc)
+        b_buf = torch.empty((k, self.ns), dtype=torch.float32, device=self.device)
+        self._host = (k, a_buf, b_buf)
+
+    def matmul_host(self, ha_rows, hb_shard, hc_rows, *, precision: str = "fp32"):
+        """This rank's share of ``C = A . B`` with all operands in (pinned) host memory:
+        ``ha_rows`` = rows ``[rank*M/G, (rank+1)*M/G)`` of A, ``hb_shard`` = this rank's
+        ``[K, N/G]`` shard of B, ``hc_rows`` receives the same rows of the full-width C.
+        Synchronous.  Through ``tfccb200_sgemm_nsplit_host``."""
+        if self._host is None:
+            raise exceptions.InvalidArgumentError("call prepare_host(k) on every rank first")
+        k, (a_t, a_ptrs, a_mc, _h), b_buf = self._host
+        rows = self.m // self.world
+        for t, shape in ((ha_rows, (rows, k)), (hb_shard, (k, self.ns)), (hc_rows, (rows, self.n_total))):
+            if t.dtype != torch.float32 or t.is_cuda or not t.is_contiguous() or tuple(t.shape) != shape:
+                raise exceptions.InvalidArgumentError(f"host operand must be contiguous float32 {shape}")
+        _lane, (c_t, c_ptrs, c_mc, _h2) = 0, self.buffers[0][0]
+        sess = get_session(self.device)
+        errors = []
+
+        def _barrier(_ctx, _stream):
+            try:
+                self.barrier(0)
+                return 0
+            except Exception as exc:  # an exception must not cross the C frame
+                errors.append(exc)
+                return -6
+
+        cb = BARRIER_FN(_barrier)
+        with torch.cuda.device(self.device):
+            ws_bytes = lib.tfccb200_sgemm_workspace(self.m, self.ns, k, 1, PRECISIONS[precision])
+            ws_ptr, ws_len = sess.workspace(ws_bytes) if ws_bytes else (None, 0)
+            st = lib.tfccb200_sgemm_nsplit_host(
+                sess.stream_ptr, ha_rows.data_ptr(), hb_shard.data_ptr(), self.ns, hc_rows.data_ptr(),
+                a_ptrs, a_mc, b_buf.data_ptr(), c_ptrs, c_mc, self.world, self.rank, self.m, self.ns,
+                k, PRECISIONS[precision], ws_ptr, ws_len, cb, None, sess.status_ptr)
+        if errors:
+            raise errors[0]
         check(st)
-        self.barrier()
-        return self.c
+        return hc_rows
+
+
+class DeviceGroup:
+    """One process driving several GPUs: thin wrapper of ``tfccb200_group_*`` (how a TFCC
+    program with one Device per GPU would use the N split; the reference's own multi-GPU model
+    is independent Devices, tfcc/core/utils/tfcc_initializer.cpp:50-66)."""
+
+    def __init__(self, devices):
+        devs = (C.c_int * len(devices))(*[int(d) for d in devices])
+        h = C.c_void_p()
+        check(lib.tfccb200_group_create(len(devices), devs, C.byref(h)))
+        self._h = h
+        self.devices = [int(d) for d in devices]
+
+    def close(self):
+        if self._h is not None:
+            check(lib.tfccb200_group_destroy(self._h))
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __len__(self):
+        return len(self.devices)
+
+    def stream(self, member: int) -> int:
+        return int(lib.tfccb200_group_stream(self._h, member) or 0)
+
+    def sync(self):
+        check(lib.tfccb200_group_sync(self._h))
+
+    def _ptrs(self, tensors):
+        return (C.c_void_p * len(tensors))(*[t.data_ptr() if t is not None else None
+                                             for t in tensors])
+
+    def sgemm_nsplit(self, a, b_shards, c, bias_shards=None, *, precision: str = "fp32"):
+        """``a[i]``, ``b_shards[i]`` on member i's device; ``c[i]`` that member's full C."""
+        m, k = a[0].shape
+        ns = b_shards[0].shape[1]
+        check(lib.tfccb200_group_sgemm_nsplit(
+            self._h, self._ptrs(a), self._ptrs(b_shards), self._ptrs(c),
+            self._ptrs(bias_shards) if bias_shards is not None else None, m, ns, k,
+            PRECISIONS[precision]))
+
+    def qgemm_nsplit(self, a, rs_a, off_a, b_shards, rs_b_shards, off_b, c):
+        m, k = a[0].shape
+        ns = b_shards[0].shape[1]
+        check(lib.tfccb200_group_qgemm_nsplit(
+            self._h, self._ptrs(a), self._ptrs(rs_a), int(off_a), self._ptrs(b_shards),
+            self._ptrs(rs_b_shards), int(off_b), self._ptrs(c), m, ns, k))
+
+    def sgemm_nsplit_host(self, ha, hb, hc, *, precision: str = "fp32"):
+        """Host tensors (pinned for overlap) ``[M,K] . [K,N] -> [M,N]``; synchronous."""
+        m, k = ha.shape
+        n = hb.shape[1]
+        check(lib.tfccb200_group_sgemm_nsplit_host(self._h, ha.data_ptr(), hb.data_ptr(),
+                                                   hc.data_ptr(), m, n, k, PRECISIONS[precision]))
+        return hc
