@@ -4,16 +4,19 @@
 
 Headline workload (one "step"): the fp32 GEMM A[8192,8192] . B[8192,8192] through
 ``blas.matmul`` (3xTF32 on tcgen05 tensor cores).  With N > 1 ranks B is column-sharded,
-every rank multiplies its shard and one NCCL all-gather plus a local interleave leaves the
-full row-major C on every rank (strong scaling: the job is the same GEMM at every N).
+every rank multiplies its shard and the GEMM epilogue stores every finished tile into the
+same columns of every rank's row-major C over NVLink, so the all-gather of C is part of the
+kernel (``--gather nccl`` selects an NCCL all-gather plus a local interleave instead).
+Strong scaling: the job is the same GEMM at every N.
 
 One JSON line is printed by rank 0.  ``value`` is TFLOP/s (2*M*N*K per step) with operands
 resident in HBM; ``e2e`` is the same metric through the host-buffer C-ABI call, uploads
-and download inside the timed region; ``roofline`` describes the tcgen05 kernel;
-``cpu_baseline`` is the CPU oracle (numpy sgemm, all host threads) timed on a bounded
-row panel of the same GEMM; ``extra`` holds the other configurations of the path
-(attention-shaped batches, int8, M<=8 streaming) measured with an L2 flush between
-launches.  ``--impl reference`` times only the CPU implementation.
+and download inside the timed region (N > 1: every rank moves only its share of A, B and C
+over its own PCIe link); ``roofline`` describes the tcgen05 kernel against tensor-core peaks
+measured in the same run with library probes; ``cpu_baseline`` is the CPU arm (torch's MKL
+sgemm, the stand-in for the reference's MKL backend, all host threads, thread count set by this
+program) on a bounded row panel of the same GEMM; ``extra`` holds the other configurations of
+the path with their own CPU baselines.  ``--impl reference`` times only the CPU implementation.
 """
 from __future__ import annotations
 
@@ -36,9 +39,10 @@ M = N = K = 8192   # --size overrides this for profiler captures; the headline i
 FLOP_PER_STEP = 2.0 * M * N * K
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one umma_gemm_kernel launch on the 8192^3
-# problem, from the ncu capture summarised in profiles/umma_gemm_tf32x3_pair_8192_traffic.md
-# (2,288,931,584 B read + 256,376,832 B written).  Only valid for the single-GPU headline size.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 2536176640
+# problem, from one ncu capture of that launch (read + written).  Only valid for the
+# single-GPU headline size.
+NCU_TRAFFIC_READ, NCU_TRAFFIC_WRITTEN = 2280496128, 255680512
+NCU_TRAFFIC_BYTES_PER_LAUNCH = NCU_TRAFFIC_READ + NCU_TRAFFIC_WRITTEN
 
 
 def measured_peaks():
@@ -107,55 +111,136 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- CPU arm
-def blas_threads() -> int:
-    """Threads numpy's BLAS really uses (falls back to the visible core count)."""
-    try:
-        from threadpoolctl import threadpool_info
-        n = [p.get("num_threads", 0) for p in threadpool_info() if p.get("user_api") == "blas"]
-        if n:
-            return int(max(n))
-    except Exception:
-        pass
-    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+def workload_config():
+    """`config` of the JSON line: the same dictionary for both arms."""
+    return {"workload": f"cfg5-large: fp32 A[{M},{K}] x B[{K},{N}], U(-1,1), seed 4",
+            "flop_per_step": FLOP_PER_STEP, "seed": 4}
 
 
-def cpu_sgemm_panel(seconds_target: float = 12.0):
-    """The oracle's fp32 GEMM (numpy sgemm, every host thread) on a bounded sample of the
-    8192^3 problem: a row panel sized for about `seconds_target` of CPU work, or the whole
-    GEMM repeated when one pass is shorter than that.  Returns (TFLOP/s, threads, text)."""
-    orc = load_oracle()
+def cpu_sgemm_panel(orc, threads, seconds_target=12.0):
+    """The CPU arm's fp32 GEMM (torch's MKL sgemm on `threads` threads, set here and not
+    inherited from the environment) on a bounded sample of the 8192^3 problem: a row panel
+    sized for about `seconds_target` of CPU work, or the whole GEMM repeated when one pass is
+    shorter than that.  Returns (TFLOP/s, threads, text)."""
+    threads = orc.set_cpu_threads(threads)
     rng = np.random.default_rng(4)
     b = rng.uniform(-1, 1, (K, N)).astype(np.float32)
     rows = 64
     a = rng.uniform(-1, 1, (rows, K)).astype(np.float32)
-    orc.blas_matmul(a, b, dtype=np.float32)  # warm the BLAS threads
+    orc.blas_matmul_mkl(a, b)  # warm the thread pool
     t0 = time.perf_counter()
-    orc.blas_matmul(a, b, dtype=np.float32)
+    orc.blas_matmul_mkl(a, b)
     dt = time.perf_counter() - t0
     rate = 2.0 * rows * N * K / dt
     rows = int(min(M, max(64, (seconds_target * rate) / (2.0 * N * K) // 64 * 64)))
     a = rng.uniform(-1, 1, (rows, K)).astype(np.float32)
-    orc.blas_matmul(a, b, dtype=np.float32)
+    orc.blas_matmul_mkl(a, b)
     reps, t0 = 0, time.perf_counter()
     while True:
-        orc.blas_matmul(a, b, dtype=np.float32)
+        orc.blas_matmul_mkl(a, b)
         reps += 1
         dt = time.perf_counter() - t0
         if dt >= seconds_target * 0.8 or reps >= 50:
             break
-    return (2.0 * rows * N * K * reps / dt / 1e12, blas_threads(),
-            f"rows 0..{rows} of the {M}^3 GEMM x {reps} passes ({dt:.2f} s)")
+    return (2.0 * rows * N * K * reps / dt / 1e12, threads,
+            f"rows 0..{rows} of the {M}^3 GEMM x {reps} passes ({dt:.2f} s), torch CPU matmul "
+            f"(MKL sgemm), {threads} threads")
+
+
+def _median_time(fn, reps=5, warm=1):
+    for _ in range(warm):
+        fn()
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        fn()
+        ts.append(time.perf_counter() - t0)
+    return float(np.median(ts))
+
+
+def cpu_baselines_per_config(orc):
+    """CPU baselines of configurations 1-4 and of the GEMV sweep, each at all host cores and
+    at 4 threads (the reference's own test setting, tfcc/test/environment.cpp:40).  fp32: torch
+    CPU matmul (MKL); int8: the reference's own AVX2 kernel from oracle/_ref when it is built
+    (else the C port), preceded by the offset-matrix pass, i.e. the reference algorithm end to
+    end; the encoder stack: the same operator sequence in torch on CPU."""
+    import torch
+    out = {}
+    rng = np.random.default_rng(5)
+    cores = orc.host_cores()
+    f32 = lambda *shape: rng.normal(0, 1, shape).astype(np.float32)
+    qa = rng.integers(0, 256, (256, 4096), dtype=np.uint8)
+    qb = rng.integers(-127, 128, (4096, 4096), dtype=np.int8)
+    rs_a, rs_b = orc.reduce_sum(qa, True), orc.reduce_sum(qb, False)
+    impl = "ref" if orc.ref_lib() is not None else "port"
+    a1, b1 = f32(32, 512), f32(512, 2048)
+    q2, k2, p2, v2 = f32(96, 128, 64), f32(96, 64, 128), f32(96, 128, 128), f32(96, 128, 64)
+    x1, w1 = f32(1, 4096), f32(4096, 16384)
+    xs, ws = torch.from_numpy(f32(8, 128, 768)), None
+    shapes4 = [(768, 768)] * 4 + [(768, 3072), (3072, 768)]
+    ws = [[torch.from_numpy((0.02 * f32(k, n))) for (k, n) in shapes4] for _ in range(4)]
+
+    def encoder(matmul_only=False):
+        x = xs
+        for (wq, wk, wv, wo, w1_, w2_) in ws:
+            q, k, v = x @ wq, x @ wk, x @ wv
+            sp = lambda t: t.view(8, 128, 12, 64).permute(0, 2, 1, 3)
+            s_ = sp(q) @ sp(k).transpose(-1, -2)
+            p_ = s_ if matmul_only else torch.softmax(s_ * 0.125, dim=-1)
+            o = (p_ @ sp(v)).permute(0, 2, 1, 3).reshape(8, 128, 768)
+            y = o @ wo
+            x = y if matmul_only else torch.nn.functional.layer_norm(x + y, (768,), eps=1e-5)
+            h = x @ w1_
+            h = h if matmul_only else torch.nn.functional.gelu(h)
+            y = h @ w2_
+            x = y if matmul_only else torch.nn.functional.layer_norm(x + y, (768,), eps=1e-5)
+        return x
+
+    for label, threads in (("all_cores", cores), ("4_threads", min(4, cores))):
+        orc.set_cpu_threads(threads)
+        r = {"threads": threads}
+        t = _median_time(lambda: orc.blas_matmul_mkl(a1, b1), reps=9)
+        r["cfg1_us"] = t * 1e6
+        r["cfg2_qk_us"] = _median_time(lambda: orc.blas_matmul_mkl(q2, k2), reps=7) * 1e6
+        r["cfg2_pv_us"] = _median_time(lambda: orc.blas_matmul_mkl(p2, v2), reps=7) * 1e6
+        t = _median_time(lambda: orc.quantized_matmul(qa, rs_a, -128.0, 127.0, qb, rs_b, -128.0,
+                                                      127.0, impl=impl), reps=5)
+        r["cfg3_int8_M256_us"] = t * 1e6
+        r["cfg3_int8_M256_tops"] = 2.0 * 256 * 4096 * 4096 / t / 1e12
+        r["cfg3_kind"] = "reference" if impl == "ref" else "port"
+        r["cfg3_reduce_sum_rows_us"] = _median_time(lambda: orc.reduce_sum(qa, True), reps=5) * 1e6
+        r["cfg3_reduce_sum_cols_us"] = _median_time(lambda: orc.reduce_sum(qb, False), reps=5) * 1e6
+        with torch.no_grad():
+            r["cfg4_encoder_ms"] = _median_time(encoder, reps=5) * 1e3
+            r["cfg4_matmul_only_ms"] = _median_time(lambda: encoder(True), reps=5) * 1e3
+        r["cfg5_gemv_M1_us"] = _median_time(lambda: orc.blas_matmul_mkl(x1, w1), reps=9) * 1e6
+        out[label] = r
+    out["cpu_model"] = _cpu_model()
+    out["host_cores"] = cores
+    return out
+
+
+def _cpu_model():
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    orc = load_oracle()
+    cores = orc.host_cores()
     vals = []
     sample = ""
-    cores = 1
     for i in range(args.warmup + args.steps):
-        v, cores, sample = cpu_sgemm_panel(seconds_target=max(0.5, 60.0 / (args.warmup + args.steps)))
+        v, cores, sample = cpu_sgemm_panel(
+            orc, cores, seconds_target=max(0.5, 60.0 / (args.warmup + args.steps)))
         if i >= args.warmup:
             vals.append(v)
     value = float(np.mean(vals))
@@ -164,9 +249,11 @@ def run_reference(args):
         "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": FLOP_PER_STEP / (value * 1e12) * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"cfg5-large: fp32 A[{M},{K}] x B[{K},{N}], U(-1,1), seed 4",
-                   "note": "CPU arm: oneDNN v1.8.1 (the reference's fp32 backend) is not in the "
-                           "reference tree and cannot be built; the oracle's numpy sgemm stands in"},
+        "config": workload_config(),
+        "setup": {"arm": "CPU: oneDNN v1.8.1 (the reference's fp32 backend) is not in the reference "
+                         "tree and cannot be built; torch's CPU matmul (MKL sgemm) stands in",
+                  "threads": cores, "cpu_model": _cpu_model(),
+                  "thread_count_set_by": "this program (torch.set_num_threads), not the environment"},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
@@ -281,7 +368,71 @@ def profile_case(torch, pkg, dev, name):
     print(json.dumps({"profile_case": name, "launches": pkg.launch_count()}))
 
 
-def extra_measurements(torch, pkg, dev, peaks):
+def library_probes(torch, dev, sustained_seconds=1.5):
+    """Dense tensor-core peaks of this GPU measured with library kernels (cuBLAS through
+    torch), outside every timed region: TF32 and bf16 (torch.matmul) and INT8 (torch._int_mm)
+    on 8192^3 as a burst (best of 10) and, for TF32, as a back-to-back loop of
+    `sustained_seconds` (clocks settle under the power cap); plus cuBLAS fp32 with TF32 off on
+    the headline shape, which is what the reference's CUDA backend would have called
+    (cublasSgemm, tfcc/cuda/interfaces/tfcc_cudablasinterface.cu:62-95,145-166).  These are
+    roofline denominators and a same-GPU library column, never part of the product path."""
+    n = 8192
+    flop = 2.0 * n ** 3
+    out = {"shape": f"{n}^3", "how": "torch.matmul / torch._int_mm (cuBLAS), CUDA events"}
+
+    def burst(fn, reps=10):
+        for _ in range(3):
+            fn()
+        best = None
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            t = e0.elapsed_time(e1)
+            best = t if best is None else min(best, t)
+        return best
+
+    old = torch.backends.cuda.matmul.allow_tf32
+    try:
+        a = torch.empty((n, n), dtype=torch.float32, device=dev).uniform_(-1, 1)
+        b = torch.empty((n, n), dtype=torch.float32, device=dev).uniform_(-1, 1)
+        c = torch.empty((n, n), dtype=torch.float32, device=dev)
+        torch.backends.cuda.matmul.allow_tf32 = True
+        f = lambda: torch.matmul(a, b, out=c)
+        out["tf32_tflops"] = flop / (burst(f) * 1e-3) / 1e12
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(10, int(sustained_seconds / (flop / (out["tf32_tflops"] * 1e12))))
+        e0.record()
+        for _ in range(reps):
+            f()
+        e1.record()
+        torch.cuda.synchronize()
+        out["tf32_tflops_sustained"] = flop * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12
+        torch.backends.cuda.matmul.allow_tf32 = False
+        t = burst(f, reps=5)
+        out["cublas_fp32_8192"] = {"ms": t, "tflops": flop / (t * 1e-3) / 1e12,
+                                   "what": "torch.matmul fp32, TF32 off (cuBLAS sgemm on CUDA cores)"}
+        del c
+        a16, b16 = a.to(torch.bfloat16), b.to(torch.bfloat16)
+        out["bf16_tflops"] = flop / (burst(lambda: torch.matmul(a16, b16)) * 1e-3) / 1e12
+        del a16, b16, a, b
+    except Exception as exc:
+        out["float_probe_error"] = repr(exc)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    try:
+        qa = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev)
+        qb = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev)
+        out["int8_tops"] = flop / (burst(lambda: torch._int_mm(qa, qb)) * 1e-3) / 1e12
+        del qa, qb
+    except Exception as exc:
+        out["int8_probe_error"] = repr(exc)
+    return out
+
+
+def extra_measurements(torch, pkg, dev, peaks, probes):
     """Other configurations of the path, single GPU, L2 flushed between launches."""
     lib = pkg.lib
     sess = pkg.session.get_session(dev)
@@ -459,8 +610,10 @@ def extra_measurements(torch, pkg, dev, peaks):
     for c in calls:
         c()
     train_us, _ = time_graph_train(torch, calls * 3)
-    out["int8_8192"] = {"train_us": train_us, "tops": 2.0 * n8 ** 3 / (train_us * 1e-6) / 1e12,
-                        "frac_of_nominal_dense_int8": 2.0 * n8 ** 3 / (train_us * 1e-6) / 4.5e15}
+    tops8 = 2.0 * n8 ** 3 / (train_us * 1e-6) / 1e12
+    out["int8_8192"] = {"train_us": train_us, "tops": tops8,
+                        "frac_of_measured_int8_peak": (tops8 / probes["int8_tops"]
+                                                       if probes.get("int8_tops") else None)}
     del ops, calls
     sess.sync()
     return out
@@ -544,7 +697,22 @@ def multi_gpu_extras(torch, dist, pkg, dev, world, rank, peaks):
     out["int8_4096_column_shards_gathered"] = {"us_per_step": ms * 1e3,
                                                "tops_whole_job": ops / (ms * 1e-3) / 1e12,
                                                "gathered_bytes_per_rank": 4 * m * (n - ns)}
-    # exactness of the assembled matrix against the int64 product, on sampled rows
+    # the same with the gather inside the GEMM epilogue (tfccb200_qgemm_nsplit_push): every
+    # rank stores its int32 tiles, correction applied, into all ranks' C
+    fused_q = None
+    try:
+        fused_q = pkg.parallel.FusedNSplit(m, n, dev, dtype=torch.int32)
+    except Exception as exc:
+        out["int8_4096_column_shards_fused_gather"] = {"unavailable": repr(exc)}
+    ok = torch.tensor([1.0 if fused_q is not None else 0.0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if float(ok.item()) == 1.0:
+        ms = timed(lambda: fused_q.qmatmul(qa, ra, -128, qb, rb, 0), iters=40)
+        out["int8_4096_column_shards_fused_gather"] = {
+            "us_per_step": ms * 1e3, "tops_whole_job": ops / (ms * 1e-3) / 1e12,
+            "vs_ungathered_product": ms / (out["int8_4096_column_shards"]["us_per_step"] * 1e-3),
+            "how": fused_q.how}
+    # exactness of the assembled matrices against the int64 product, on sampled rows
     gathered()
     torch.cuda.synchronize()
     rows = np.random.default_rng(0).choice(m, size=4, replace=False)
@@ -552,6 +720,100 @@ def multi_gpu_extras(torch, dist, pkg, dev, world, rank, peaks):
     truth = (a64 @ qb_full.astype(np.int64)).astype(np.int32)
     got = c_full[torch.from_numpy(rows).to(dev)].cpu().numpy()
     out["int8_4096_column_shards_gathered"]["sampled_rows_exact"] = bool(np.array_equal(got, truth))
+    if float(ok.item()) == 1.0:
+        cq = fused_q.qmatmul(qa, ra, -128, qb, rb, 0)
+        dist.barrier()
+        torch.cuda.synchronize()
+        out["int8_4096_column_shards_fused_gather"]["equals_nccl_gather_bit_for_bit"] = bool(
+            torch.equal(cq, c_full))
+        out["int8_4096_column_shards_fused_gather"]["sampled_rows_exact"] = bool(
+            np.array_equal(cq[torch.from_numpy(rows).to(dev)].cpu().numpy(), truth))
+    sess.sync()
+    return out
+
+
+def nsplit_check(torch, pkg, dev, a, world, rank, ns, produce):
+    """The assembled C of one step against this rank's own product of A with every column
+    shard of B, bit for bit (the N split does not touch the order of the K sum), outside the
+    timed region.  `produce()` runs one step the way the timed loop does and returns C."""
+    full = produce()
+    torch.cuda.synchronize()
+    g2 = torch.Generator(device=dev)
+    g2.manual_seed(4)
+    torch.empty((M, K), dtype=torch.float32, device=dev).uniform_(-1, 1, generator=g2)
+    bf = torch.empty((K, N), dtype=torch.float32, device=dev).uniform_(-1, 1, generator=g2)
+    bad = 0
+    for r in range(world):
+        ref = pkg.blas.matmul(a, bf[:, r * ns:(r + 1) * ns].contiguous())
+        bad += int((ref != full[:, r * ns:(r + 1) * ns]).sum().item())
+        del ref
+    del bf
+    return bad
+
+
+def sampled_parity(torch, a, b, c, rows=16):
+    """Normwise relative error of sampled rows of C against the float64 product."""
+    idx = torch.from_numpy(np.random.default_rng(0).choice(a.shape[0], size=rows, replace=False)).to(a.device)
+    truth = a[idx].double() @ b.double()
+    got = c[idx].double()
+    return float(((got - truth).norm() / truth.norm()).item())
+
+
+def nsplit_breakdown(torch, dist, pkg, dev, fused, a, b, world, rank, steps=20):
+    """Where the time of one N-split step goes, every piece timed with CUDA events on a train
+    of `steps` launches, maximum over ranks: the product of this rank's shard alone; the same
+    kernel storing its tiles into every rank's C but with no barrier; the barrier alone; the
+    kernel storing only into its own C followed by the barrier; and the step as timed, one
+    product at a time and (when planned) two in flight."""
+    out = {}
+
+    def slowest(ms):
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def train(fn, finish=None):
+        for _ in range(3):
+            fn()
+        if finish:
+            finish()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        if finish:
+            finish()
+        e1.record()
+        torch.cuda.synchronize()
+        return slowest(e0.elapsed_time(e1) / steps) * 1e3
+
+    lib = pkg.lib
+    sess = pkg.session.get_session(dev)
+    one = fused["one"]
+    buf = one.buffers[0][0]
+    ws_bytes = lib.tfccb200_sgemm_workspace(M, b.shape[1], K, 1, 0)
+
+    def push(ptrs, mc, max_ctas=0):
+        ws_ptr, ws_len = sess.workspace(ws_bytes)
+        st = lib.tfccb200_sgemm_nsplit_push_ex(
+            sess.stream_ptr, a.data_ptr(), b.data_ptr(), ptrs, world, rank, None, M, b.shape[1], K,
+            0, mc, ws_ptr, ws_len, max_ctas, sess.status_ptr)
+        assert st == 0, st
+
+    import ctypes as C
+    own_only = (C.c_void_p * world)(*[buf[1][r] if r == rank else None for r in range(world)])
+    out["local_product_us"] = train(lambda: pkg.blas.matmul(a, b))
+    out["push_no_barrier_us"] = train(lambda: push(buf[1], buf[2]))
+    out["barrier_alone_us"] = train(lambda: one.barrier(0))
+    out["own_c_only_plus_barrier_us"] = train(lambda: (push(own_only, None), one.barrier(0)))
+    out["step_one_at_a_time_us"] = train(lambda: one.matmul(a, b))
+    if fused.get("two") is not None:
+        two = fused["two"]
+        out["step_two_in_flight_us"] = train(lambda: two.matmul(a, b, wait=False), finish=two.join)
+        out["half_chip_product_us"] = train(lambda: push(own_only, None, two._max_ctas))
+    out["exposed_us"] = out["step_one_at_a_time_us"] - out["local_product_us"]
     sess.sync()
     return out
 
@@ -574,7 +836,7 @@ def run_ours(args):
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    assert N % world == 0
+    assert N % world == 0 and M % world == 0
     ns = N // world
 
     # ---- synthetic operands (seed 4, U(-1,1)); every rank holds A and its column shard of B
@@ -585,34 +847,48 @@ def run_ours(args):
     b = b_full[:, rank * ns:(rank + 1) * ns].contiguous() if world > 1 else b_full
     if world > 1:
         del b_full
-    staging = c_out = fused = None
+    staging = c_out = None
+    fused = {}   # "one": one product at a time; "two": two in flight on half the SMs each
     mode = "single GPU"
+    in_flight = 1
     if world > 1:
         if args.gather == "fused":
             try:
-                fused = pkg.parallel.FusedNSplit(M, N, dev)
-                mode = (f"N-split x{world}: B column shards; C tiles pushed to every rank from the "
-                        f"GEMM epilogue over NVLink ({fused.how}) + barrier")
+                fused["one"] = pkg.parallel.FusedNSplit(M, N, dev)
+                if args.in_flight == 2 or (args.in_flight == 0 and world >= 4):
+                    fused["two"] = pkg.parallel.FusedNSplit(M, N, dev, in_flight=2)
+                    in_flight = 2
             except Exception as exc:  # peer mapping unavailable: NCCL gather of our local product
                 print(f"[bench] fused N-split unavailable ({exc!r}); using NCCL all-gather",
                       file=sys.stderr)
-                fused = None
-        ok = torch.tensor([1.0 if fused is not None else 0.0], device=dev)
+                fused = {}
+        ok = torch.tensor([1.0 if fused else 0.0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if float(ok.item()) == 0.0:
-            fused = None
-        if fused is None:
+            fused = {}
+            in_flight = 1
+        if fused:
+            mode = (f"N-split x{world}: B column shards; C tiles pushed to every rank from the "
+                    f"GEMM epilogue over NVLink ({fused['one'].how}) + barrier"
+                    + ("; two steps in flight, each on half of the SMs, so that the last tiles of "
+                       "one step cross NVLink while the next step multiplies" if in_flight == 2 else ""))
+        else:
             staging = torch.empty((world, M, ns), dtype=torch.float32, device=dev)
             c_out = torch.empty((M, N), dtype=torch.float32, device=dev)
             mode = f"N-split x{world}: B column shards, NCCL all-gather of C + interleave kernel"
     sess = pkg.session.get_session(dev)
+    timed = fused.get("two") if in_flight == 2 else fused.get("one")
 
     def step():
         if world == 1:
             return pkg.blas.matmul(a, b)
-        if fused is not None:
-            return fused.matmul(a, b)
+        if timed is not None:
+            return timed.matmul(a, b, wait=(in_flight == 1))
         return pkg.parallel.nsplit_matmul(a, b, staging=staging, out=c_out)
+
+    def finish():
+        if in_flight == 2:
+            timed.join()
 
     def barrier():
         if world > 1:
@@ -620,24 +896,29 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     for _ in range(max(args.warmup, 3)):
-        step()
+        last = step()
+    finish()
     barrier()
-    if world > 1 and args.check:
-        # the assembled C must equal the product computed locally against the matching
-        # shard of B, bit for bit (N-split does not touch the K order)
-        full = step()
+    # ---- correctness of what is about to be timed, outside the timed region
+    check_line = None
+    parity = None
+    if world > 1:
+        def produce():
+            c = step()
+            finish()
+            barrier()
+            return c
+        bad = nsplit_check(torch, pkg, dev, a, world, rank, ns, produce)
+        tb = torch.tensor([float(bad)], dtype=torch.float64, device=dev)
+        dist.all_reduce(tb, op=dist.ReduceOp.SUM)
+        check_line = {"mismatches": int(tb[0]), "elements_checked_per_rank": M * N,
+                      "against": "this rank's own product of A with every column shard of B, bit for bit",
+                      "multicast": bool(timed is not None and timed.buffers[0][0][2] is not None),
+                      "in_flight": in_flight}
         barrier()
-        bad = 0
-        for r in range(world):
-            g2 = torch.Generator(device=dev)
-            g2.manual_seed(4)
-            torch.empty((M, K), dtype=torch.float32, device=dev).uniform_(-1, 1, generator=g2)
-            bf = torch.empty((K, N), dtype=torch.float32, device=dev).uniform_(-1, 1, generator=g2)
-            ref = pkg.blas.matmul(a, bf[:, r * ns:(r + 1) * ns].contiguous())
-            bad += int((ref != full[:, r * ns:(r + 1) * ns]).sum().item())
-            del bf, ref
-        print(f"[bench] rank {rank}: N-split check, mismatching elements = {bad}", file=sys.stderr)
-        barrier()
+    else:
+        parity = {"normwise": sampled_parity(torch, a, b, last), "rows": 16,
+                  "against": "float64 product of the same operands", "bound": 1e-5}
     sampler = ClockSampler(local_rank)
     launches0 = pkg.launch_count()
     with sampler:
@@ -646,6 +927,7 @@ def run_ours(args):
         e0.record()
         for _ in range(args.steps):
             step()
+        finish()
         e1.record()
         barrier()
     launches = pkg.launch_count() - launches0
@@ -666,27 +948,38 @@ def run_ours(args):
         torch.cuda.synchronize()
         kern_mean_ms = k0.elapsed_time(k1) / reps
 
-    # ---- end to end: host buffers in, host buffer out, through the C-ABI host entry point
+    # ---- end to end: host buffers in, host buffer out, through the C-ABI host entry points.
+    # One GPU: tfccb200_sgemm_host.  N GPUs: tfccb200_sgemm_nsplit_host -- every rank uploads
+    # M/N rows of A and its shard of B, the rows are exchanged over NVLink, and every rank
+    # downloads M/N rows of the assembled C.
     e2e_steps = max(1, min(args.steps, 3))
-    ha = torch.empty((M, K), dtype=torch.float32).pin_memory()
+    rows = M // world
+    ha = torch.empty((rows, K), dtype=torch.float32).pin_memory()
     hb = torch.empty((K, ns), dtype=torch.float32).pin_memory()
-    hc = torch.empty((M, ns), dtype=torch.float32).pin_memory()
-    ha.copy_(a.cpu())
+    hc = torch.empty((rows, N), dtype=torch.float32).pin_memory()
+    ha.copy_(a[rank * rows:(rank + 1) * rows].cpu())
     hb.copy_(b.cpu())
-    h_full = torch.empty((M, N), dtype=torch.float32).pin_memory() if world > 1 else None
+    e2e_api = "tfccb200_sgemm_host"
+    host_plan = fused.get("one")
+    if world > 1 and host_plan is not None:
+        host_plan.prepare_host(K)
+        e2e_api = "tfccb200_sgemm_nsplit_host"
+    elif world > 1:
+        e2e_api = "torch copies around parallel.nsplit_matmul (no peer mapping available)"
+        ha_full = a.cpu().pin_memory()
+        h_full = torch.empty((M, N), dtype=torch.float32).pin_memory()
 
     def e2e_step():
         if world == 1:
             st = pkg.lib.tfccb200_sgemm_host(sess.stream_ptr, ha.data_ptr(), 0, hb.data_ptr(), 0,
                                              hc.data_ptr(), M * ns, None, M, ns, K, 1, 0)
             assert st == 0, st
+        elif host_plan is not None:
+            host_plan.matmul_host(ha, hb, hc)
         else:
-            da = ha.to(dev, non_blocking=True)
+            da = ha_full.to(dev, non_blocking=True)
             db = hb.to(dev, non_blocking=True)
-            if fused is not None:
-                full = fused.matmul(da, db)
-            else:
-                full = pkg.parallel.nsplit_matmul(da, db, staging=staging, out=c_out)
+            full = pkg.parallel.nsplit_matmul(da, db, staging=staging, out=c_out)
             h_full.copy_(full, non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
@@ -697,17 +990,32 @@ def run_ours(args):
         e2e_step()
     barrier()
     e2e_s = time.perf_counter() - t0
-    h2d = 4 * (M * K + K * ns)
-    d2h = 4 * (M * N if world > 1 else M * ns)
+    if world == 1 or host_plan is not None:
+        h2d = 4 * (rows * K + K * ns)
+        d2h = 4 * rows * N
+        # the rows this rank brought down, against the float64 product of the host operands
+        idx = np.random.default_rng(rank).choice(rows, size=8, replace=False)
+        bfull_cols = hb.numpy().astype(np.float64)
+        truth_shard = ha.numpy()[idx].astype(np.float64) @ bfull_cols
+        got_shard = hc.numpy()[idx][:, rank * ns:(rank + 1) * ns].astype(np.float64)
+        e2e_err = float(np.linalg.norm(got_shard - truth_shard) / np.linalg.norm(truth_shard))
+    else:
+        h2d = 4 * (M * K + K * ns)
+        d2h = 4 * M * N
+        e2e_err = None
+
+    probes = library_probes(torch, dev) if not args.no_probe else {}
 
     # ---- max over ranks
-    t = torch.tensor([ms_total, e2e_s * 1e3, float(launches)], dtype=torch.float64, device=dev)
+    t = torch.tensor([ms_total, e2e_s * 1e3, float(launches), e2e_err or 0.0],
+                     dtype=torch.float64, device=dev)
     if world > 1:
         tmax = t.clone()
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         tsum = t.clone()
         dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
         ms_total, e2e_ms, launches = float(tmax[0]), float(tmax[1]), int(tsum[2])
+        e2e_err = float(tmax[3]) if e2e_err is not None else None
     else:
         e2e_ms = float(t[1])
 
@@ -718,18 +1026,30 @@ def run_ours(args):
         kern_flop = FLOP_PER_STEP / world
         achieved = kern_flop / (kern_mean_ms * 1e-3) / 1e12
         # a kernel timed alone is judged against the burst figure, one timed inside a long
-        # region (power-capped clocks) against the sustained one
-        sustained = ms_total >= 250.0 and peaks.get("bf16_tflops_sustained")
-        bf16_peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
-        tensor_peak = bf16_peak / 2.0 / 3.0
+        # region (power-capped clocks) against the sustained one.  The TF32 peak is the library
+        # probe of this run; without it, the driver-measured bf16 peak halved (stated as such).
+        sustained = ms_total >= 250.0
+        if probes.get("tf32_tflops"):
+            tf32_peak = probes["tf32_tflops_sustained"] if sustained else probes["tf32_tflops"]
+            basis = (f"measured in this run: cuBLAS TF32 {n_fmt(tf32_peak)} TFLOP/s "
+                     f"({'sustained loop' if sustained else 'burst'}, 8192^3) / 3 (MMAs per fp32 product)")
+            tf32_burst = probes["tf32_tflops"]
+        else:
+            bf16_peak = (peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]) if sustained \
+                else peaks["bf16_tflops"]
+            tf32_peak = bf16_peak / 2.0
+            tf32_burst = peaks["bf16_tflops"] / 2.0
+            basis = (f"no library probe in this run; of {peaks['source']}: bf16 {bf16_peak} TFLOP/s / 2 "
+                     "(assumed TF32 : bf16 ratio) / 3 (MMAs per fp32 product)")
+        tensor_peak = tf32_peak / 3.0
         line = {
             "metric": f"fp32 matmul TFLOP/s ({M}^3)", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, fp32 accumulation)",
             "data": "synthetic",
-            "config": {
-                "workload": f"cfg5-large: fp32 A[{M},{K}] x B[{K},{N}], U(-1,1), seed 4",
+            "config": workload_config(),
+            "setup": {
                 "parallelism": mode,
                 "l2": f"operands ({4 * M * K >> 20} MiB each) exceed the 126 MB L2; no flush between steps",
                 "timing": "CUDA events on the launching stream, max over ranks"},
@@ -737,33 +1057,56 @@ def run_ours(args):
                 "bound": "tensor", "kernel": "umma_gemm_kernel<TF32, split, cta_group::2, BN=256>",
                 "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
                 "frac": achieved / tensor_peak,
-                "peak_basis": f"of {peaks['source']}: bf16 {'sustained' if sustained else 'burst'} "
-                              f"{bf16_peak} TFLOP/s / 2 (TF32 runs at half the bf16 rate) / 3 "
-                              "(MMAs per fp32 product)",
-                "frac_of_burst_peak": achieved / (peaks["bf16_tflops"] / 6.0),
+                "peak_basis": basis,
+                "frac_of_burst_peak": achieved / (tf32_burst / 3.0),
+                "frac_of_driver_bf16_burst_over_6": achieved / (peaks["bf16_tflops"] / 6.0),
                 "executed_tf32_tflops": 3.0 * achieved,
                 "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (world == 1 and M == 8192) else None,
                 "algorithmic_bytes": 4 * (M * K + K * ns + M * ns)},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+                    "d2h_bytes_per_step": d2h, "bytes_are": "per rank", "steps": e2e_steps,
+                    "api": e2e_api, "sampled_rows_normwise": e2e_err},
             "gpu_launches": launches,
             "clocks": sampler.summary(),
+            "measured_peaks": probes,
         }
+        if check_line is not None:
+            line["nsplit_check"] = check_line
+        if parity is not None:
+            line["parity"] = parity
         if world == 1:
+            orc = load_oracle()
             if not args.no_cpu:
-                v, cores, sample = cpu_sgemm_panel()
+                v, cores, sample = cpu_sgemm_panel(orc, orc.host_cores())
                 line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cores,
                                         "kind": "port", "sample": sample}
             if not args.no_extra:
-                line["extra"] = extra_measurements(torch, pkg, dev, peaks)
+                line["extra"] = extra_measurements(torch, pkg, dev, peaks, probes)
+                if probes.get("cublas_fp32_8192"):
+                    line["extra"]["cublas_fp32_8192"] = probes["cublas_fp32_8192"]
+                if not args.no_cpu:
+                    cpu = cpu_baselines_per_config(orc)
+                    for cfg in ("cfg1", "cfg2", "cfg3", "cfg4", "cfg5"):
+                        line["extra"][f"cpu_baseline_{cfg}"] = {
+                            label: {k: v for k, v in r.items() if k.startswith(cfg) or k == "threads"}
+                            for label, r in cpu.items() if isinstance(r, dict)}
+                    line["extra"]["cpu_baseline_host"] = {"cpu_model": cpu["cpu_model"],
+                                                          "host_cores": cpu["host_cores"]}
     if world > 1 and not args.no_extra:
         extra = multi_gpu_extras(torch, dist, pkg, dev, world, rank, peaks)
+        if fused:
+            extra["nsplit_breakdown"] = nsplit_breakdown(torch, dist, pkg, dev, fused, a, b, world, rank)
         if rank == 0:
             line["extra"] = extra
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+
+
+def n_fmt(x):
+    return f"{x:.1f}"
 
 
 def main():
@@ -780,8 +1123,11 @@ def main():
     ap.add_argument("--profile-case", default="",
                     help="run only one small configuration (gemv_M1, int8_M256, int8_M4096, "
                          "attention_qk, ffn1) a few times and exit: the target of ncu captures")
-    ap.add_argument("--check", action="store_true",
-                    help="N > 1: verify the assembled C against the single-GPU product")
+    ap.add_argument("--in-flight", type=int, default=0, choices=[0, 1, 2],
+                    help="N > 1, fused gather: products in flight (2 = two lanes on half the SMs "
+                         "each; 0 = two from four ranks on, else one)")
+    ap.add_argument("--no-probe", action="store_true",
+                    help="skip the library probes of the tensor-core peaks")
     ap.add_argument("--size", type=int, default=8192,
                     help="edge of the square GEMM (profiler captures use a smaller one)")
     args = ap.parse_args()
