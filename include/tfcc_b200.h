@@ -153,6 +153,27 @@ TFCCB200_API int tfccb200_qgemm_u8s8s32_ex(void* stream, const uint8_t* A, unsig
                               int* device_status);
 
 /*
+ * The quantized matmul with the operand ranges in DEVICE memory, which is where TFCC keeps them
+ * (Tensor<float> of one element each, tfcc/mkl/operations/tfcc_mklquantization.h:39-45): a
+ * one-thread prologue kernel derives the zero-point offsets and the float range of the result
+ * with the reference's double / float formulas (tfcc/mkl/operations/tfcc_mklquantization.cpp:
+ * 181-193) and the GEMM reads the offsets from device memory, so nothing returns to the host and
+ * nothing synchronises.  minA .. maxB: one float each (read); minC, maxC: one float each
+ * (written); offsets: two int32 of scratch that receive {offA, offB}.  `path` is a
+ * TFCCB200_PATH_* (AUTO for normal use).  Results equal tfccb200_qgemm_u8s8s32 fed by
+ * tfccb200_quantized_matmul_params.
+ */
+TFCCB200_API int tfccb200_qgemm_u8s8s32_dev(void* stream, const uint8_t* A, unsigned strideA,
+                                            const int32_t* rsA, unsigned strideRsA,
+                                            const float* minA, const float* maxA, const int8_t* B,
+                                            unsigned strideB, const int32_t* rsB,
+                                            unsigned strideRsB, const float* minB,
+                                            const float* maxB, int32_t* C, unsigned strideC,
+                                            float* minC, float* maxC, int32_t* offsets, unsigned M,
+                                            unsigned N, unsigned K, unsigned batch, int path,
+                                            int* device_status);
+
+/*
  * Host-side scalar math of the quantized matmul: zero-point offsets and the
  * float range of the int32 result, from the (min,max) float ranges of the
  * operands.  Restates get_quantized_scale_info<uint8_t/int8_t> minus
@@ -248,6 +269,21 @@ TFCCB200_API int tfccb200_minmax_f32(void* stream, const float* src, size_t n, f
 TFCCB200_API int tfccb200_quantize_f32(void* stream, const float* src, size_t n,
                                        const float* min_value, const float* max_value, void* dst,
                                        int dst_type);
+
+/*
+ * tfccb200_quantize_f32 on a [rows, cols] matrix together with reduce_sum(dst, row): row_sums[r]
+ * receives the int32 sum of the quantized values of row r, produced in the same pass, so that
+ * the sequence quantize -> reduce_sum -> matmul of a quantized dense layer
+ * (tfcc/test/quantization.cpp:105-121;
+ *  tfcc/mkl/interfaces/tfcc_mklquantizationinterface.cpp:150-189 then
+ *  tfcc/mkl/operations/tfcc_mklquantization.cpp:205-237) reads the activations once.
+ * dst_type is TFCCB200_TYPE_S8, _U8 or _S16 (the types reduce_sum exists for).  Results are
+ * identical to the two separate calls.
+ */
+TFCCB200_API int tfccb200_quantize_rowsum_f32(void* stream, const float* src, unsigned rows,
+                                              unsigned cols, const float* min_value,
+                                              const float* max_value, void* dst, int dst_type,
+                                              int32_t* row_sums);
 
 /*
  * dst[i] = float(min + (src[i] - lowest(T)) * scale); *min_value when the range is empty.

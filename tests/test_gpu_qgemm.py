@@ -93,6 +93,35 @@ def test_few_tiles_long_k_exact(pkg, orc, m, n, k):
         assert np.array_equal(got, want), path
 
 
+@pytest.mark.parametrize("path", ["simt", "umma"])
+def test_device_resident_ranges_match_host_derivation(pkg, orc, path):
+    """With (min, max) in device memory the offsets and the result range are derived by a
+    prologue kernel and read by the GEMM from device memory: same C, same (minC, maxC) bits as
+    the host derivation of tfcc_mklquantization.cpp:181-193, for many ranges."""
+    rng = np.random.default_rng(99)
+    d = dev_of()
+    m, n, k = 136, 272, 384
+    qa = rng.integers(0, 256, (m, k), dtype=np.uint8)
+    qb = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    ta, tb = torch.from_numpy(qa).to(d), torch.from_numpy(qb).to(d)
+    ra, rb = pkg.quantization.reduce_sum(ta, True), pkg.quantization.reduce_sum(tb, False)
+    dv = lambda v: torch.tensor([v], dtype=torch.float32, device=d)
+    cases = [(-128.0, 127.0, -128.0, 127.0), (0.0, 1.0, -1.0, 1.0), (-3.0, -3.0, 1.0, 2.0)]
+    for _ in range(20):
+        lo_a, lo_b = rng.uniform(-5, 5), rng.uniform(-5, 5)
+        cases.append((lo_a, lo_a + rng.uniform(0.05, 5), lo_b, lo_b + rng.uniform(0.05, 5)))
+    for c in cases:
+        c = tuple(float(np.float32(x)) for x in c)
+        if c[0] >= c[1]:
+            continue  # the reference divides by zero here; not a defined case
+        got, gmin, gmax = pkg.quantization.matmul(ta, ra, dv(c[0]), dv(c[1]), tb, rb, dv(c[2]), dv(c[3]),
+                                                  path=path)
+        want, wmin, wmax = orc.quantized_matmul(qa, orc.reduce_sum(qa, True), c[0], c[1], qb,
+                                                orc.reduce_sum(qb, False), c[2], c[3], impl="port")
+        assert np.array_equal(got.cpu().numpy(), want), c
+        assert np.float32(gmin.item()) == np.float32(wmin) and np.float32(gmax.item()) == np.float32(wmax), c
+
+
 def test_n_equals_one_fast_path_shape(pkg, orc):
     rng = np.random.default_rng(22)
     a = rng.integers(0, 256, (333, 401), dtype=np.uint8)
@@ -137,7 +166,8 @@ def test_reduce_sum_all_types(pkg, orc, dtype):
     rng = np.random.default_rng(24)
     info = np.iinfo(dtype)
     d = dev_of()
-    for shape in ((257, 515), (3, 64, 4096), (2, 2, 33, 17), (1, 1), (4096, 4096)):
+    for shape in ((257, 515), (3, 64, 4096), (2, 2, 33, 17), (1, 1), (4096, 4096), (256, 4096),
+                  (5, 1000, 48), (70, 16400), (3, 9, 2064), (1037, 640)):
         a = rng.integers(info.min, info.max + 1, shape).astype(dtype)
         t = torch.from_numpy(a).to(d)
         for row in (True, False):

@@ -106,3 +106,25 @@ def test_quantized_dense_layer_larger(pkg, orc):
     assert np.array_equal(got, orc.quantized_dense(a, w))
     # and the quantized product tracks the float product to quantization accuracy
     assert orc.normwise_rel_error(got, a.astype(np.float64) @ w.astype(np.float64)) < 2e-2
+
+
+@pytest.mark.parametrize("shape", [(256, 4096), (96, 768), (3, 7, 130), (5, 33), (2, 2051)])
+@pytest.mark.parametrize("dtype", [torch.uint8, torch.int8, torch.int16])
+def test_quantize_with_row_sums_equals_the_two_separate_calls(pkg, orc, shape, dtype):
+    """quantize + reduce_sum(row) fused into one pass over the activations
+    (tfcc/test/quantization.cpp:105-121 runs them as two operators): same bits."""
+    rng = np.random.default_rng(sum(shape))
+    a = rng.normal(0, 1, shape).astype(np.float32)
+    q = pkg.quantization
+    ta = torch.from_numpy(a).to(dev())
+    want_q, mn, mx = q.quantize(ta, dtype)
+    want_s = q.reduce_sum(want_q, True)
+    got_q, gmn, gmx, got_s = q.quantize_with_row_sums(ta, dtype)
+    assert torch.equal(got_q, want_q) and torch.equal(got_s, want_s)
+    assert torch.equal(gmn, mn) and torch.equal(gmx, mx)
+    got_q2, got_s2 = q.quantize_with_row_sums(ta, dtype, mn, mx)
+    assert torch.equal(got_q2, want_q) and torch.equal(got_s2, want_s)
+    np_t = {torch.uint8: np.uint8, torch.int8: np.int8, torch.int16: np.int16}[dtype]
+    oq, _, _ = orc.quantize(a, np_t)
+    assert np.array_equal(got_q.cpu().numpy(), oq)
+    assert np.array_equal(got_s.cpu().numpy(), orc.reduce_sum(oq, True))

@@ -43,6 +43,8 @@ class _Lib:
             "tfccb200_sgemm_path": (i, [u, u, u, u, u, u, i]),
             "tfccb200_qgemm_u8s8s32": (i, [vp, vp, u, vp, u, i32, vp, u, vp, u, i32, vp, u, u, u, u, u, vp]),
             "tfccb200_qgemm_u8s8s32_ex": (i, [vp, vp, u, vp, u, i32, vp, u, vp, u, i32, vp, u, u, u, u, u, i, vp]),
+            "tfccb200_qgemm_u8s8s32_dev": (i, [vp, vp, u, vp, u, vp, vp, vp, u, vp, u, vp, vp, vp, u,
+                                               vp, vp, vp, u, u, u, u, i, vp]),
             "tfccb200_quantized_matmul_params": (i, [f, f, f, f, C.POINTER(i32), C.POINTER(i32),
                                                      C.POINTER(f), C.POINTER(f)]),
             "tfccb200_reduce_sum_u8": (i, [vp, vp, u, u, u, i, vp]),
@@ -56,6 +58,7 @@ class _Lib:
             "tfccb200_transpose_last2_f32": (i, [vp, vp, u, u, u, vp]),
             "tfccb200_minmax_f32": (i, [vp, vp, sz, vp]),
             "tfccb200_quantize_f32": (i, [vp, vp, sz, vp, vp, vp, i]),
+            "tfccb200_quantize_rowsum_f32": (i, [vp, vp, u, u, vp, vp, vp, i, vp]),
             "tfccb200_dequantize_f32": (i, [vp, vp, i, sz, vp, vp, vp]),
             "tfccb200_requantize": (i, [vp, vp, i, sz, vp, vp, vp, vp, vp, i]),
             "tfccb200_sgemm_nsplit_push": (i, [vp, vp, vp, C.POINTER(C.c_void_p), u, u, vp, u, u, u, i, vp, vp, C.c_size_t, vp]),
@@ -101,11 +104,12 @@ EXPORTED_SYMBOLS = (
     "tfccb200_strerror", "tfccb200_version", "tfccb200_launch_count", "tfccb200_test_flag_wait",
     "tfccb200_sgemm",
     "tfccb200_sgemm_ex", "tfccb200_sgemm_workspace", "tfccb200_sgemm_path",
-    "tfccb200_qgemm_u8s8s32", "tfccb200_qgemm_u8s8s32_ex", "tfccb200_quantized_matmul_params",
+    "tfccb200_qgemm_u8s8s32", "tfccb200_qgemm_u8s8s32_ex", "tfccb200_qgemm_u8s8s32_dev",
+    "tfccb200_quantized_matmul_params",
     "tfccb200_reduce_sum_u8", "tfccb200_reduce_sum_s8", "tfccb200_reduce_sum_s16",
     "tfccb200_sgemm_act", "tfccb200_softmax_f32", "tfccb200_layer_norm_f32", "tfccb200_gelu_f32",
     "tfccb200_permute_0213_f32", "tfccb200_transpose_last2_f32",
-    "tfccb200_minmax_f32", "tfccb200_quantize_f32", "tfccb200_dequantize_f32", "tfccb200_requantize",
+    "tfccb200_minmax_f32", "tfccb200_quantize_f32", "tfccb200_quantize_rowsum_f32", "tfccb200_dequantize_f32", "tfccb200_requantize",
     "tfccb200_sgemm_nsplit_push", "tfccb200_sgemm_nsplit_push_ex", "tfccb200_qgemm_nsplit_push",
     "tfccb200_sgemm_nsplit_host", "tfccb200_group_create", "tfccb200_group_destroy",
     "tfccb200_group_size", "tfccb200_group_device", "tfccb200_group_stream", "tfccb200_group_sync",

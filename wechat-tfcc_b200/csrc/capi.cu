@@ -380,6 +380,30 @@ int tfccb200_qgemm_u8s8s32(void* stream, const uint8_t* A, unsigned strideA, con
                                    TFCCB200_PATH_AUTO, device_status);
 }
 
+int tfccb200_qgemm_u8s8s32_dev(void* stream, const uint8_t* A, unsigned strideA, const int32_t* rsA,
+                               unsigned strideRsA, const float* minA, const float* maxA,
+                               const int8_t* B, unsigned strideB, const int32_t* rsB,
+                               unsigned strideRsB, const float* minB, const float* maxB, int32_t* C,
+                               unsigned strideC, float* minC, float* maxC, int32_t* offsets,
+                               unsigned M, unsigned N, unsigned K, unsigned batch, int path,
+                               int* device_status) {
+  if (!minA || !maxA || !minB || !maxB || !minC || !maxC || !offsets) return TFCCB200_EINVAL;
+  if (!A || !B || !C || !rsA || !rsB || M == 0 || N == 0 || K == 0 || batch == 0)
+    return TFCCB200_EINVAL;
+  int st = quantized_matmul_params_dev(static_cast<cudaStream_t>(stream), minA, maxA, minB, maxB,
+                                       offsets, minC, maxC);
+  if (st != TFCCB200_OK) return st;
+  QgemmArgs a = {};
+  a.stream = static_cast<cudaStream_t>(stream);
+  a.A = A; a.B = B; a.C = C; a.rsA = rsA; a.rsB = rsB;
+  a.strideA = strideA; a.strideB = strideB; a.strideC = strideC;
+  a.strideRsA = strideRsA; a.strideRsB = strideRsB;
+  a.dev_offsets = offsets;
+  a.M = M; a.N = N; a.K = K; a.batch = batch;
+  a.status = device_status;
+  return run_qgemm(a, path);
+}
+
 int tfccb200_quantized_matmul_params(float minA, float maxA, float minB, float maxB,
                                      int32_t* offA, int32_t* offB, float* minC, float* maxC) {
   if (!offA || !offB || !minC || !maxC) return TFCCB200_EINVAL;
@@ -453,6 +477,16 @@ int tfccb200_quantize_f32(void* stream, const float* src, size_t n, const float*
   if (!src || !min_value || !max_value || !dst || n == 0) return TFCCB200_EINVAL;
   return quantize_f32(static_cast<cudaStream_t>(stream), src, n, min_value, max_value, dst,
                       dst_type);
+}
+
+int tfccb200_quantize_rowsum_f32(void* stream, const float* src, unsigned rows, unsigned cols,
+                                 const float* min_value, const float* max_value, void* dst,
+                                 int dst_type, int32_t* row_sums) {
+  if (!src || !min_value || !max_value || !dst || !row_sums || rows == 0 || cols == 0)
+    return TFCCB200_EINVAL;
+  if (static_cast<unsigned long long>(rows) * cols > 0xffffffffull) return TFCCB200_EOVERFLOW;
+  return quantize_rows_f32(static_cast<cudaStream_t>(stream), src, rows, cols, min_value,
+                           max_value, dst, dst_type, row_sums);
 }
 
 int tfccb200_dequantize_f32(void* stream, const void* src, int src_type, size_t n,

@@ -56,6 +56,7 @@ struct QgemmArgs {
   const int32_t* rsB;
   unsigned strideA, strideB, strideC, strideRsA, strideRsB;
   int32_t offA, offB;
+  const int32_t* dev_offsets;  // device {offA, offB}; when set, offA / offB above are ignored
   unsigned M, N, K, batch;
   int* status;
   // Tensor-core path only (as in SgemmArgs): several destinations / a multicast alias, row
@@ -147,6 +148,12 @@ int transpose_last2_f32(cudaStream_t stream, const float* src, unsigned batch, u
 int minmax_f32(cudaStream_t stream, const float* src, size_t n, float* out);
 int quantize_f32(cudaStream_t stream, const float* src, size_t n, const float* pmin,
                  const float* pmax, void* dst, int dst_type);
+int quantized_matmul_params_dev(cudaStream_t stream, const float* minA, const float* maxA,
+                                const float* minB, const float* maxB, int32_t* offsets,
+                                float* minC, float* maxC);
+int quantize_rows_f32(cudaStream_t stream, const float* src, unsigned rows, unsigned cols,
+                      const float* pmin, const float* pmax, void* dst, int dst_type,
+                      int32_t* row_sums);
 int dequantize_f32(cudaStream_t stream, const void* src, int src_type, size_t n, const float* pmin,
                    const float* pmax, float* dst);
 int requantize(cudaStream_t stream, const void* src, int src_type, size_t n, const float* pmin_in,

@@ -106,6 +106,29 @@ __global__ void minmax_decode_kernel(unsigned* out) {
   reinterpret_cast<float*>(out)[1] = hi;
 }
 
+// ---- scalars of the quantized matmul from device-resident ranges -----------------------------
+// offA = round(minA * scaleA) - lowest(u8), offB = round(minB * scaleB) - lowest(s8) and the
+// float range of the int32 result, as tfcc::mkl::quantization::matmul derives them on the
+// host (tfcc/mkl/operations/tfcc_mklquantization.cpp:181-193,
+// get_quantization_range_for_multiplication, tfcc/core/utils/tfcc_quantizationutils.h:23-43):
+// same double / float operations, none of them fused.
+__global__ void qmatmul_params_kernel(const float* __restrict__ minA, const float* __restrict__ maxA,
+                                      const float* __restrict__ minB, const float* __restrict__ maxB,
+                                      int32_t* __restrict__ offsets, float* __restrict__ minC,
+                                      float* __restrict__ maxC) {
+  double scale;
+  long long off;
+  quantized_scale_info<uint8_t>(*minA, *maxA, &scale, &off);
+  offsets[0] = static_cast<int32_t>(off - Limits<uint8_t>::lo);
+  quantized_scale_info<int8_t>(*minB, *maxB, &scale, &off);
+  offsets[1] = static_cast<int32_t>(off - Limits<int8_t>::lo);
+  const float a_level = __fdiv_rn(__fsub_rn(*maxA, *minA), 255.0f);
+  const float b_level = __fdiv_rn(__fsub_rn(*maxB, *minB), 255.0f);
+  const float c_level = __fmul_rn(a_level, b_level);
+  *minC = __fmul_rn(c_level, static_cast<float>(Limits<int32_t>::lo));
+  *maxC = __fmul_rn(c_level, static_cast<float>(Limits<int32_t>::hi));
+}
+
 // ---- element kernels ---------------------------------------------------------------------
 template <class T>
 __global__ void __launch_bounds__(256)
@@ -119,6 +142,67 @@ quantize_kernel(const float* __restrict__ src, size_t n, const float* __restrict
   for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull)
     dst[i] = degenerate ? static_cast<T>(Limits<T>::lo)
                         : quantize_value<T>(static_cast<double>(src[i]), scale, offset);
+}
+
+// quantize with the row sums of the quantized values produced in the same pass: the
+// `quantize<u8>(x)` followed by `reduce_sum(q, row)` of a quantized dense layer
+// (tfcc/test/quantization.cpp:105-121) without reading q back.  One CTA of 256 threads per row
+// group; a thread converts four adjacent floats per step (one 128-bit load) and keeps its share
+// of the row's integer sum; warps combine with shuffles, the row's warps through shared memory.
+template <class T, int TPR>
+__global__ void __launch_bounds__(256)
+quantize_rows_kernel(const float* __restrict__ src, unsigned rows, unsigned cols,
+                     const float* __restrict__ pmin, const float* __restrict__ pmax,
+                     T* __restrict__ dst, int32_t* __restrict__ row_sums) {
+  constexpr int kRowsPerCta = 256 / TPR;
+  __shared__ int32_t warp_sums[8];
+  const float mn = *pmin, mx = *pmax;
+  const bool degenerate = mn >= mx;
+  double scale = 0;
+  long long offset = 0;
+  if (!degenerate) quantized_scale_info<T>(mn, mx, &scale, &offset);
+  const unsigned row = blockIdx.x * kRowsPerCta + threadIdx.x / TPR;
+  const unsigned t = threadIdx.x % TPR;
+  int32_t s = 0;
+  if (row < rows) {
+    const float* p = src + static_cast<size_t>(row) * cols;
+    T* q = dst + static_cast<size_t>(row) * cols;
+    auto one = [&](float v) {
+      const T r = degenerate ? static_cast<T>(Limits<T>::lo)
+                             : quantize_value<T>(static_cast<double>(v), scale, offset);
+      s += static_cast<int32_t>(r);
+      return r;
+    };
+    const bool vec = cols % 4 == 0 && (reinterpret_cast<uintptr_t>(p) & 15u) == 0 &&
+                     (reinterpret_cast<uintptr_t>(q) & (4 * sizeof(T) - 1)) == 0;
+    if (vec) {
+      for (unsigned i = t; i < cols / 4; i += TPR) {
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(p) + i);
+        T r[4] = {one(v.x), one(v.y), one(v.z), one(v.w)};
+        if constexpr (sizeof(T) == 1) {
+          reinterpret_cast<uint32_t*>(q)[i] = *reinterpret_cast<const uint32_t*>(r);
+        } else {
+          reinterpret_cast<uint2*>(q)[i] = *reinterpret_cast<const uint2*>(r);
+        }
+      }
+    } else {
+      for (unsigned i = t; i < cols; i += TPR) q[i] = one(p[i]);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if constexpr (TPR == 32) {
+    if (t == 0 && row < rows) row_sums[row] = s;
+  } else {
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (t == 0 && row < rows) {
+      int32_t total = 0;
+#pragma unroll
+      for (int w = 0; w < TPR / 32; ++w) total += warp_sums[(threadIdx.x >> 5) + w];
+      row_sums[row] = total;
+    }
+  }
 }
 
 template <class T>
@@ -214,6 +298,39 @@ int quantize_f32(cudaStream_t stream, const float* src, size_t n, const float* p
     quantize_kernel<T><<<grid, 256, 0, stream>>>(src, n, pmin, pmax, static_cast<T*>(dst));
     return finish(1);
   });
+}
+
+int quantized_matmul_params_dev(cudaStream_t stream, const float* minA, const float* maxA,
+                                const float* minB, const float* maxB, int32_t* offsets,
+                                float* minC, float* maxC) {
+  qmatmul_params_kernel<<<1, 1, 0, stream>>>(minA, maxA, minB, maxB, offsets, minC, maxC);
+  return finish(1);
+}
+
+int quantize_rows_f32(cudaStream_t stream, const float* src, unsigned rows, unsigned cols,
+                      const float* pmin, const float* pmax, void* dst, int dst_type,
+                      int32_t* row_sums) {
+  auto run = [&](auto tag) {
+    using T = decltype(tag);
+    T* out = static_cast<T*>(dst);
+    if (cols <= 256) {
+      quantize_rows_kernel<T, 32><<<(rows + 7) / 8, 256, 0, stream>>>(src, rows, cols, pmin, pmax,
+                                                                      out, row_sums);
+    } else if (cols <= 1024) {
+      quantize_rows_kernel<T, 128><<<(rows + 1) / 2, 256, 0, stream>>>(src, rows, cols, pmin, pmax,
+                                                                       out, row_sums);
+    } else {
+      quantize_rows_kernel<T, 256><<<rows, 256, 0, stream>>>(src, rows, cols, pmin, pmax, out,
+                                                             row_sums);
+    }
+    return finish(1);
+  };
+  switch (dst_type) {  // the types reduce_sum exists for
+    case TFCCB200_TYPE_S8: return run(int8_t());
+    case TFCCB200_TYPE_U8: return run(uint8_t());
+    case TFCCB200_TYPE_S16: return run(int16_t());
+    default: return TFCCB200_EINVAL;
+  }
 }
 
 int dequantize_f32(cudaStream_t stream, const void* src, int src_type, size_t n, const float* pmin,

@@ -39,6 +39,7 @@ struct SimtEpilogue {
   const int32_t* rsB;
   unsigned strideRsA, strideRsB;
   int32_t offA, offB, kterm;
+  const int32_t* dev_offsets;  // int8: device {offA, offB} replacing the three above
 };
 
 template <class TA, class TB, class TAcc>
@@ -110,8 +111,18 @@ simt_gemm_kernel(const TA* __restrict__ A, const TB* __restrict__ B, TAcc* __res
         if (ep.bias) v += ep.bias[c];
         v = apply_activation(v, ep.activation);
       } else {
-        v += ep.kterm + ep.rsA[static_cast<size_t>(ep.strideRsA) * b + r] * ep.offB +
-             ep.rsB[static_cast<size_t>(ep.strideRsB) * b + c] * ep.offA;
+        int32_t oa = ep.offA, ob = ep.offB, kt = ep.kterm;
+        if (ep.dev_offsets) {
+          oa = ep.dev_offsets[0];
+          ob = ep.dev_offsets[1];
+          kt = static_cast<int32_t>(static_cast<uint32_t>(oa) * static_cast<uint32_t>(ob) * K);
+        }
+        v = static_cast<int32_t>(
+            static_cast<uint32_t>(v) + static_cast<uint32_t>(kt) +
+            static_cast<uint32_t>(ep.rsA[static_cast<size_t>(ep.strideRsA) * b + r]) *
+                static_cast<uint32_t>(ob) +
+            static_cast<uint32_t>(ep.rsB[static_cast<size_t>(ep.strideRsB) * b + c]) *
+                static_cast<uint32_t>(oa));
       }
       C[static_cast<size_t>(r) * N + c] = v;
     }
@@ -285,76 +296,146 @@ void skinny_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_coun
 // --------------------------------------------------------------------------
 // Integer sums for the zero-point correction.
 // --------------------------------------------------------------------------
-template <class T>
+template <class T, unsigned V>
+__device__ __forceinline__ int32_t sum_vec(const uint4& v) {
+  const T* e = reinterpret_cast<const T*>(&v);
+  int32_t s = 0;
+#pragma unroll
+  for (unsigned j = 0; j < V; ++j) s += static_cast<int32_t>(e[j]);
+  return s;
+}
+
+// Row sums.  TPR threads share a row (32 ... 256, chosen so that a thread issues one to four
+// 128-bit loads, all in flight together); a CTA of 256 threads holds 256 / TPR rows.
+template <class T, int TPR>
 __global__ void __launch_bounds__(256)
 reduce_rows_kernel(const T* __restrict__ src, unsigned total_rows, unsigned cols,
                    int32_t* __restrict__ dst) {
-  // one warp per row
-  const unsigned row = blockIdx.x * 8 + (threadIdx.x >> 5);
-  const unsigned lane = threadIdx.x & 31;
-  if (row >= total_rows) return;
-  const T* p = src + static_cast<size_t>(row) * cols;
-  int32_t s = 0;
   constexpr unsigned V = 16 / sizeof(T);
-  if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0 && cols % V == 0) {
-    const uint4* p4 = reinterpret_cast<const uint4*>(p);
-    for (unsigned i = lane; i < cols / V; i += 32) {
-      const uint4 v = __ldg(p4 + i);
-      const T* e = reinterpret_cast<const T*>(&v);
-#pragma unroll
-      for (unsigned j = 0; j < V; ++j) s += static_cast<int32_t>(e[j]);
+  constexpr int kRowsPerCta = 256 / TPR;
+  __shared__ int32_t warp_sums[8];
+  pdl_wait();
+  const unsigned row = blockIdx.x * kRowsPerCta + threadIdx.x / TPR;
+  const unsigned t = threadIdx.x % TPR;
+  int32_t s = 0;
+  if (row < total_rows) {
+    const T* p = src + static_cast<size_t>(row) * cols;
+    if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0 && cols % V == 0) {
+      const uint4* p4 = reinterpret_cast<const uint4*>(p);
+      const unsigned n4 = cols / V;
+      unsigned i = t;
+      for (; i + 3 * TPR < n4; i += 4 * TPR) {
+        const uint4 v0 = __ldg(p4 + i), v1 = __ldg(p4 + i + TPR), v2 = __ldg(p4 + i + 2 * TPR),
+                    v3 = __ldg(p4 + i + 3 * TPR);
+        s += sum_vec<T, V>(v0) + sum_vec<T, V>(v1) + sum_vec<T, V>(v2) + sum_vec<T, V>(v3);
+      }
+      for (; i < n4; i += TPR) s += sum_vec<T, V>(__ldg(p4 + i));
+    } else {
+      for (unsigned i = t; i < cols; i += TPR) s += static_cast<int32_t>(p[i]);
     }
-  } else {
-    for (unsigned i = lane; i < cols; i += 32) s += static_cast<int32_t>(p[i]);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (lane == 0) dst[row] = s;
-}
-
-// dst must be zero on entry: row slabs are combined with integer atomics,
-// which is exact and order-independent.  A thread owns the V = 4/sizeof(T) adjacent columns
-// of one 32-bit word and walks its slab of rows with 8 loads in flight.
-template <class T>
-__global__ void __launch_bounds__(256)
-reduce_cols_vec_kernel(const T* __restrict__ src, unsigned rows, unsigned cols, unsigned slab,
-                       int32_t* __restrict__ dst) {
-  constexpr unsigned V = 4 / sizeof(T);
-  const unsigned b = blockIdx.z;
-  const unsigned c = (blockIdx.x * 256 + threadIdx.x) * V;
-  if (c >= cols) return;
-  const unsigned r0 = blockIdx.y * slab;
-  const unsigned r1 = min(rows, r0 + slab);
-  const size_t pitch = cols / V;  // in 32-bit words
-  const uint32_t* p = reinterpret_cast<const uint32_t*>(src + static_cast<size_t>(b) * rows * cols) + c / V;
-  int32_t s[V];
+  if constexpr (TPR == 32) {
+    if (t == 0 && row < total_rows) dst[row] = s;
+  } else {
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (t == 0 && row < total_rows) {
+      constexpr int kWarpsPerRow = TPR / 32;
+      const int w0 = (threadIdx.x >> 5);
+      int32_t total = 0;
 #pragma unroll
-  for (unsigned v = 0; v < V; ++v) s[v] = 0;
-  constexpr unsigned U = 8;
-  unsigned r = r0;
-  for (; r + U <= r1; r += U) {
-    uint32_t w[U];
-#pragma unroll
-    for (unsigned u = 0; u < U; ++u) w[u] = __ldcs(p + (r + u) * pitch);
-#pragma unroll
-    for (unsigned u = 0; u < U; ++u) {
-      const T* e = reinterpret_cast<const T*>(&w[u]);
-#pragma unroll
-      for (unsigned v = 0; v < V; ++v) s[v] += static_cast<int32_t>(e[v]);
+      for (int w = 0; w < kWarpsPerRow; ++w) total += warp_sums[w0 + w];
+      dst[row] = total;
     }
   }
-  for (; r < r1; ++r) {
-    const uint32_t w = __ldcs(p + r * pitch);
-    const T* e = reinterpret_cast<const T*>(&w);
-#pragma unroll
-    for (unsigned v = 0; v < V; ++v) s[v] += static_cast<int32_t>(e[v]);
-  }
-  int32_t* d = dst + static_cast<size_t>(b) * cols + c;
-#pragma unroll
-  for (unsigned v = 0; v < V; ++v) atomicAdd(d + v, s[v]);
 }
 
-// Any alignment: one column per thread.
+// Column sums without atomics or a zeroed destination.  A CTA reads one 128-byte line of
+// each row it visits (8 threads x 128 bits = 8 V columns) with 32 rows in flight per pass and
+// several passes unrolled; a cluster of 8 CTAs shares the rows of one column block, and the
+// eight partial results meet in the first CTA's shared memory (distributed shared memory),
+// which adds them and writes the sums.  Needs cols % V == 0 and a 16-byte aligned base.
+constexpr int kColsCluster = 8;
+
+template <class T>
+__global__ void __launch_bounds__(256)
+reduce_cols_cluster_kernel(const T* __restrict__ src, unsigned rows, unsigned cols,
+                           int32_t* __restrict__ dst) {
+  constexpr unsigned V = 16 / sizeof(T);
+  constexpr unsigned CW = 8 * V;  // columns per CTA
+  __shared__ int32_t part[32][CW + 4];
+  __shared__ int32_t gather[kColsCluster][CW];
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  // every CTA of the cluster is running before anyone writes into a peer's shared memory
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  pdl_wait();
+  const unsigned b = blockIdx.z;
+  const unsigned lane8 = threadIdx.x & 7u, rlane = threadIdx.x >> 3;
+  const unsigned col = blockIdx.y * CW + lane8 * V;
+  const bool active = col < cols;
+  const unsigned slab = (rows + kColsCluster - 1) / kColsCluster;
+  const unsigned r0 = rank * slab;
+  const unsigned r1 = min(rows, r0 + slab);
+  const uint4* p = reinterpret_cast<const uint4*>(src + static_cast<size_t>(b) * rows * cols +
+                                                  (active ? col : 0));
+  const size_t pitch = cols / V;  // in 128-bit units
+  int32_t acc[V];
+#pragma unroll
+  for (unsigned v = 0; v < V; ++v) acc[v] = 0;
+  if (active) {
+    constexpr unsigned U = 8;
+    unsigned r = r0 + rlane;
+    for (; r + (U - 1) * 32 < r1; r += U * 32) {
+      uint4 w[U];
+#pragma unroll
+      for (unsigned u = 0; u < U; ++u) w[u] = __ldcs(p + static_cast<size_t>(r + u * 32) * pitch);
+#pragma unroll
+      for (unsigned u = 0; u < U; ++u) {
+        const T* e = reinterpret_cast<const T*>(&w[u]);
+#pragma unroll
+        for (unsigned v = 0; v < V; ++v) acc[v] += static_cast<int32_t>(e[v]);
+      }
+    }
+    for (; r < r1; r += 32) {
+      const uint4 w = __ldcs(p + static_cast<size_t>(r) * pitch);
+      const T* e = reinterpret_cast<const T*>(&w);
+#pragma unroll
+      for (unsigned v = 0; v < V; ++v) acc[v] += static_cast<int32_t>(e[v]);
+    }
+  }
+#pragma unroll
+  for (unsigned v = 0; v < V; ++v) part[rlane][lane8 * V + v] = acc[v];
+  __syncthreads();
+  int32_t s = 0;
+  if (threadIdx.x < CW) {
+#pragma unroll 8
+    for (unsigned r = 0; r < 32; ++r) s += part[r][threadIdx.x];
+  }
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (threadIdx.x < CW) {
+    const uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(&gather[rank][threadIdx.x]));
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0u));
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(s) : "memory");
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (rank == 0 && threadIdx.x < CW) {
+    const unsigned c = blockIdx.y * CW + threadIdx.x;
+    if (c < cols) {
+      int32_t total = 0;
+#pragma unroll
+      for (int k = 0; k < kColsCluster; ++k) total += gather[k][threadIdx.x];
+      dst[static_cast<size_t>(b) * cols + c] = total;
+    }
+  }
+}
+
+// Any alignment: one column per thread; dst must be zero on entry (row slabs are combined
+// with integer atomics, which is exact and order-independent).
 template <class T>
 __global__ void __launch_bounds__(256)
 reduce_cols_kernel(const T* __restrict__ src, unsigned rows, unsigned cols, unsigned slab,
@@ -428,6 +509,7 @@ int simt_qgemm(const QgemmArgs& a) {
   ep.rsA = a.rsA; ep.rsB = a.rsB;
   ep.strideRsA = a.strideRsA; ep.strideRsB = a.strideRsB;
   ep.offA = a.offA; ep.offB = a.offB;
+  ep.dev_offsets = a.dev_offsets;
   ep.kterm = static_cast<int32_t>(static_cast<uint32_t>(a.offA) * static_cast<uint32_t>(a.offB) *
                                   a.K);
   simt_gemm_kernel<uint8_t, int8_t, int32_t><<<grid, 256, 0, a.stream>>>(
@@ -594,37 +676,61 @@ int skinny_sgemm_static(cudaStream_t stream, const float* A, const float* B, flo
 
 size_t skinny_sgemm_static_capacity() { return kStaticScratchFloats * sizeof(float); }
 
+template <class T, int TPR>
+cudaError_t launch_reduce_rows(cudaStream_t stream, const T* src, unsigned total_rows,
+                               unsigned cols, int32_t* dst) {
+  constexpr unsigned kRowsPerCta = 256 / TPR;
+  const unsigned blocks = (total_rows + kRowsPerCta - 1) / kRowsPerCta;
+  return launch_after_previous(reduce_rows_kernel<T, TPR>, dim3(blocks), dim3(256), 0, stream, src,
+                               total_rows, cols, dst);
+}
+
 template <class T>
 int reduce_sum(cudaStream_t stream, const T* src, unsigned batch, unsigned rows, unsigned cols,
                int row_flag, int32_t* dst) {
+  constexpr unsigned V = 16 / sizeof(T);
   if (row_flag) {
     const unsigned long long total = static_cast<unsigned long long>(batch) * rows;
     if (total > 0xffffffffull) return TFCCB200_EOVERFLOW;
-    const unsigned blocks = static_cast<unsigned>((total + 7) / 8);
-    reduce_rows_kernel<T><<<blocks, 256, 0, stream>>>(src, static_cast<unsigned>(total), cols, dst);
-    cudaError_t e = launch_status();
+    const unsigned n = static_cast<unsigned>(total);
+    const unsigned loads = (cols + V - 1) / V;  // 128-bit loads per row
+    cudaError_t e;
+    if (loads <= 64) e = launch_reduce_rows<T, 32>(stream, src, n, cols, dst);
+    else if (loads <= 128) e = launch_reduce_rows<T, 64>(stream, src, n, cols, dst);
+    else if (loads <= 512) e = launch_reduce_rows<T, 128>(stream, src, n, cols, dst);
+    else e = launch_reduce_rows<T, 256>(stream, src, n, cols, dst);
     if (e != cudaSuccess) return static_cast<int>(e);
     count_launch();
     return TFCCB200_OK;
   }
   if (batch > 65535) return TFCCB200_EOVERFLOW;
+  if (cols % V == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0 &&
+      (cols + 8 * V - 1) / (8 * V) <= 65535) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kColsCluster, (cols + 8 * V - 1) / (8 * V), batch);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kColsCluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, reduce_cols_cluster_kernel<T>, src, rows, cols, dst);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    count_launch();
+    return TFCCB200_OK;
+  }
   cudaError_t e =
       cudaMemsetAsync(dst, 0, static_cast<size_t>(batch) * cols * sizeof(int32_t), stream);
   if (e != cudaSuccess) return static_cast<int>(e);
-  // row slabs of 64: fewer slabs mean fewer atomics per column, which is what bounds this
-  // kernel; the grid stays within a few thousand CTAs
   unsigned slab = 64;
   while ((rows + slab - 1) / slab > 4096) slab *= 2;
-  constexpr unsigned V = 4 / sizeof(T);
-  const bool vec = cols % V == 0 && (reinterpret_cast<uintptr_t>(src) & 3u) == 0 &&
-                   (static_cast<unsigned long long>(rows) * cols) % V == 0;
-  if (vec) {
-    dim3 grid((cols / V + 255) / 256, (rows + slab - 1) / slab, batch);
-    reduce_cols_vec_kernel<T><<<grid, 256, 0, stream>>>(src, rows, cols, slab, dst);
-  } else {
-    dim3 grid((cols + 255) / 256, (rows + slab - 1) / slab, batch);
-    reduce_cols_kernel<T><<<grid, 256, 0, stream>>>(src, rows, cols, slab, dst);
-  }
+  dim3 grid((cols + 255) / 256, (rows + slab - 1) / slab, batch);
+  reduce_cols_kernel<T><<<grid, 256, 0, stream>>>(src, rows, cols, slab, dst);
   e = launch_status();
   if (e != cudaSuccess) return static_cast<int>(e);
   count_launch();

@@ -84,6 +84,8 @@ struct UmmaGemmParams {
   const int32_t* rsB;      // I8: column sums of B, [batch?][N]
   int32_t offA, offB;      // I8 zero-point offsets
   int32_t kterm;           // I8: offA*offB*K (wrapped)
+  const int32_t* q_offsets;  // I8: when set, {offA, offB} are read from device memory instead
+                             // (written by a prologue kernel from device-resident ranges)
   unsigned strideRsA, strideRsB;
   unsigned M, N, K, batch;
   unsigned long long strideC;  // elements between batch entries of C
@@ -796,11 +798,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           const int32_t* rsB = p.rsB + static_cast<size_t>(p.strideRsB) * b;
           const unsigned row = row0 + lane;
           const bool row_ok = row < p.M;
+          uint32_t oa = static_cast<uint32_t>(p.offA), ob = static_cast<uint32_t>(p.offB);
           uint32_t row_term = static_cast<uint32_t>(p.kterm);
+          if (p.q_offsets) {
+            oa = static_cast<uint32_t>(__ldg(p.q_offsets));
+            ob = static_cast<uint32_t>(__ldg(p.q_offsets + 1));
+            row_term = oa * ob * p.K;
+          }
           if (row_ok)
-            row_term += static_cast<uint32_t>(p.rsA[static_cast<size_t>(p.strideRsA) * b + row]) *
-                        static_cast<uint32_t>(p.offB);
-          const uint32_t oa = static_cast<uint32_t>(p.offA);
+            row_term += static_cast<uint32_t>(p.rsA[static_cast<size_t>(p.strideRsA) * b + row]) * ob;
           if (p.num_dst > 1 || p.mc_dst) {
             // column shards pushed to several GPUs: go through the transposing stage so that
             // every store instruction covers whole 128-byte lines of the peers' memory

@@ -581,6 +581,7 @@ int umma_qgemm(const QgemmArgs& a, bool pair) {
   p.offA = a.offA; p.offB = a.offB;
   p.kterm = static_cast<int32_t>(static_cast<uint32_t>(a.offA) * static_cast<uint32_t>(a.offB) *
                                  a.K);
+  p.q_offsets = a.dev_offsets;
   p.strideRsA = a.strideRsA; p.strideRsB = a.strideRsB;
   p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
   p.strideC = a.strideC;

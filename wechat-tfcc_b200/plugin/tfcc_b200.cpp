@@ -544,8 +544,7 @@ namespace b200 {
 namespace quantization {
 
 // Argument checks and messages of tfcc::mkl::quantization::matmul
-// (tfcc/mkl/operations/tfcc_mklquantization.cpp:75-118); the min/max scalars are read back
-// to the host (one small synchronous copy each) to derive the zero-point offsets.
+// (tfcc/mkl/operations/tfcc_mklquantization.cpp:75-118).
 std::tuple<Variable<int32_t>, Variable<float>, Variable<float>> matmul(
     const Tensor<uint8_t>& a, const Tensor<int32_t>& reduceSumA, const Tensor<float>& minA,
     const Tensor<float>& maxA, const Tensor<int8_t>& b, const Tensor<int32_t>& reduceSumB,
@@ -582,25 +581,15 @@ std::tuple<Variable<int32_t>, Variable<float>, Variable<float>> matmul(
   Variable<float> minResult({1}), maxResult({1});
   B200Session* session = current_session();
 
-  float h[4];
-  const Tensor<float>* scalars[4] = {&minA, &maxA, &minB, &maxB};
-  for (int i = 0; i < 4; ++i) {
-    scalars[i]->sync();
-    check_cuda(cudaMemcpy(&h[i], scalars[i]->data(), sizeof(float), cudaMemcpyDeviceToHost));
-  }
-  int32_t offA = 0, offB = 0;
-  float hostMinC = 0.f, hostMaxC = 0.f;
-  check_status(tfccb200_quantized_matmul_params(h[0], h[1], h[2], h[3], &offA, &offB, &hostMinC,
-                                                &hostMaxC));
-  check_status(tfccb200_qgemm_u8s8s32(session->stream(), a.data(), strideA, reduceSumA.data(),
-                                      strideRsA, offA, b.data(), strideB, reduceSumB.data(),
-                                      strideRsB, offB, result.data(), g.m * g.n, g.m, g.n, g.k,
-                                      g.batch, session->deviceStatus()));
-  check_cuda(cudaMemcpyAsync(minResult.data(), &hostMinC, sizeof(float), cudaMemcpyHostToDevice,
-                             session->stream()));
-  check_cuda(cudaMemcpyAsync(maxResult.data(), &hostMaxC, sizeof(float), cudaMemcpyHostToDevice,
-                             session->stream()));
-  check_cuda(cudaStreamSynchronize(session->stream()));  // the two host floats leave scope
+  // The ranges live in device memory: offsets and result range are derived there by the
+  // library's prologue kernel, the GEMM reads them from device memory, and no value returns
+  // to the host -- the call stays asynchronous like every other operator of the backend.
+  Variable<int32_t> offsets({2});
+  check_status(tfccb200_qgemm_u8s8s32_dev(
+      session->stream(), a.data(), strideA, reduceSumA.data(), strideRsA, minA.data(), maxA.data(),
+      b.data(), strideB, reduceSumB.data(), strideRsB, minB.data(), maxB.data(), result.data(),
+      g.m * g.n, minResult.data(), maxResult.data(), offsets.data(), g.m, g.n, g.k, g.batch,
+      TFCCB200_PATH_AUTO, session->deviceStatus()));
   return std::make_tuple(std::move(result), std::move(minResult), std::move(maxResult));
 }
 

@@ -58,6 +58,35 @@ def quantize(a: torch.Tensor, dtype, min_value=None, max_value=None):
     return out
 
 
+def quantize_with_row_sums(a: torch.Tensor, dtype, min_value=None, max_value=None):
+    """``quantize`` and ``reduce_sum(q, row=True)`` in one pass over ``a`` (rank >= 2):
+    ``(q, row_sums)`` for a given range, ``(q, min, max, row_sums)`` when the range is reduced
+    from ``a`` here.  Same values as the two separate calls."""
+    if not isinstance(a, torch.Tensor) or a.numel() == 0 or a.dim() < 2:
+        raise exceptions.InvalidArgumentError("invalid tensor")
+    if dtype not in _REDUCE:
+        raise exceptions.NotImplementedError(f"row sums exist for int8/uint8/int16, got {dtype}")
+    _dev(a, "a", torch.float32)
+    sess = get_session(a.device)
+    cols = a.shape[-1]
+    rows = a.numel() // cols
+    out = torch.empty(a.shape, dtype=dtype, device=a.device)
+    sums = torch.empty(a.shape[:-1], dtype=torch.int32, device=a.device)
+    with torch.cuda.device(a.device):
+        given = min_value is not None or max_value is not None
+        if given:
+            mn = _scalar(min_value, "minValue", a.device)
+            mx = _scalar(max_value, "maxValue", a.device)
+        else:
+            rng = torch.empty(2, dtype=torch.float32, device=a.device)
+            check(lib.tfccb200_minmax_f32(sess.stream_ptr, a.data_ptr(), a.numel(), rng.data_ptr()))
+            mn, mx = rng[0:1], rng[1:2]
+        check(lib.tfccb200_quantize_rowsum_f32(sess.stream_ptr, a.data_ptr(), rows, cols,
+                                               mn.data_ptr(), mx.data_ptr(), out.data_ptr(),
+                                               _TYPE_IDS[dtype], sums.data_ptr()))
+    return (out, sums) if given else (out, mn, mx, sums)
+
+
 def dequantize(a: torch.Tensor, min_value, max_value) -> torch.Tensor:
     """``tfcc::quantization::dequantize``: float32 values of a quantized tensor."""
     if not isinstance(a, torch.Tensor) or a.numel() == 0:
@@ -132,9 +161,10 @@ def matmul_params(min_a: float, max_a: float, min_b: float, max_b: float):
 def matmul(a, reduce_sum_a, min_a, max_a, b, reduce_sum_b, min_b, max_b, *, path: str = "auto"):
     """Returns ``(C int32, minC float[1], maxC float[1])``.
 
-    ``min_*`` / ``max_*`` are one-element float tensors (on any device) as in the
-    reference; they are read on the host to derive the zero-point offsets, which
-    costs a device-to-host copy when they live on the GPU.
+    ``min_*`` / ``max_*`` are one-element float tensors as in the reference.  When all four
+    live on the operands' device the zero-point offsets and the result range are derived
+    there by a prologue kernel and nothing returns to the host; ranges given as CPU tensors
+    are read on the host instead.
     """
     if not isinstance(a, torch.Tensor) or a.numel() == 0 or a.dim() < 2:
         raise exceptions.InvalidArgumentError("invalid input tensor a")
@@ -173,9 +203,22 @@ def matmul(a, reduce_sum_a, min_a, max_a, b, reduce_sum_b, min_b, max_b, *, path
     stride_rs_b = 0 if reduce_sum_b.dim() == 1 else n
     stride_a = 0 if a.dim() == 2 else m * k
     stride_b = 0 if b.dim() == 2 else k * n
+    sess = get_session(a.device)
+    ranges = (min_a, max_a, min_b, max_b)
+    if all(t.device == a.device and t.dtype == torch.float32 and t.is_contiguous() for t in ranges):
+        out_range = torch.empty(2, dtype=torch.float32, device=a.device)
+        offsets = torch.empty(2, dtype=torch.int32, device=a.device)
+        with torch.cuda.device(a.device):
+            st = lib.tfccb200_qgemm_u8s8s32_dev(
+                sess.stream_ptr, a.data_ptr(), stride_a, reduce_sum_a.data_ptr(), stride_rs_a,
+                min_a.data_ptr(), max_a.data_ptr(), b.data_ptr(), stride_b, reduce_sum_b.data_ptr(),
+                stride_rs_b, min_b.data_ptr(), max_b.data_ptr(), result.data_ptr(), m * n,
+                out_range.data_ptr(), out_range.data_ptr() + 4, offsets.data_ptr(), m, n, k, batch,
+                PATHS[path], sess.status_ptr)
+        check(st)
+        return result, out_range[0:1], out_range[1:2]
     off_a, off_b, min_c, max_c = matmul_params(float(min_a.item()), float(max_a.item()),
                                                float(min_b.item()), float(max_b.item()))
-    sess = get_session(a.device)
     with torch.cuda.device(a.device):
         st = lib.tfccb200_qgemm_u8s8s32_ex(
             sess.stream_ptr, a.data_ptr(), stride_a, reduce_sum_a.data_ptr(), stride_rs_a, off_a,
