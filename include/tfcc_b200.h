@@ -225,6 +225,28 @@ TFCCB200_API int tfccb200_softmax_f32(void* stream, const float* src, unsigned r
                                       unsigned cols, float scale, float* dst);
 
 /*
+ * Scaled dot-product attention of one transformer block in one kernel, one CTA per
+ * (batch, head):  out = softmax(scale * Q . K^T) . V  with fp32 results (tensor-core products
+ * by three TF32 MMAs, softmax as tfccb200_softmax_f32).
+ *   q, k, v: element (b, s, h, d) at  base + (b*seq + s)*ld_qkv + h*dim + d  -- the layout the
+ *            Q/K/V projections produce ([batch, seq, heads*dim] matrices, or slices of one packed
+ *            [batch, seq, 3*heads*dim] matrix: pass the three slice bases and ld_qkv = 3*heads*dim);
+ *   out:     element (b, s, h, d) at  out + (b*seq + s)*ld_out + h*dim + d.
+ * It stands for this sequence of reference operators: transpose of q, k, v to
+ * [batch, head, seq, dim], transpose of k's last two axes, batched matmul, scale, softmax,
+ * batched matmul, transpose back (tfcc/cuda/interfaces/tfcc_cudabasicinterface.cu:83-100,
+ * tfcc/cuda/interfaces/tfcc_cudaactivationinterface.cu:96-121,
+ * tfcc/cuda/interfaces/tfcc_cudablasinterface.cu:201-248); none of the permutations is a pass
+ * over memory here, K is read as a K-major operand.
+ * Limits: seq <= 128, dim 32 or 64, 16-byte aligned bases, ld % 4 == 0; anything else returns
+ * TFCCB200_EUNSUPPORTED and the caller composes the separate operators.
+ */
+TFCCB200_API int tfccb200_attention_f32(void* stream, const float* q, const float* k,
+                                        const float* v, float* out, unsigned batch, unsigned seq,
+                                        unsigned heads, unsigned dim, unsigned ld_qkv,
+                                        unsigned ld_out, float scale, int* device_status);
+
+/*
  * dst = (t - mean(t)) / sqrt(var(t) + eps) * gamma + beta with t = x (+ residual when not
  * NULL), row by row, two-pass mean and variance (_mkl_layer_normalize,
  * tfcc/mkl/interfaces/tfcc_mklnormalizationinterface.cpp:29-62).  cols <= 1024.

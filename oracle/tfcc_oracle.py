@@ -409,6 +409,24 @@ def softmax_v2(a, scale=1.0):
     return (e / e.sum(axis=-1, keepdims=True, dtype=np.float32)).astype(np.float32)
 
 
+def attention(q, k, v, heads, scale=None):
+    """The operator sequence of one attention block as the reference graph runs it, in
+    float32: split heads (transpose to [batch, head, seq, dim],
+    tfcc/cuda/interfaces/tfcc_cudabasicinterface.cu:83-100), ``q . k^T`` (blas matmul), scale
+    and softmaxV2, ``. v``, merge heads.  Matmuls accumulate in float64 and round once, the
+    exact-product oracle of ``blas_matmul``.  Inputs and output ``[batch, seq, heads*dim]``."""
+    q, k, v = (np.asarray(t, dtype=np.float32) for t in (q, k, v))
+    b, s, w = q.shape
+    d = w // heads
+    if scale is None:
+        scale = 1.0 / np.sqrt(d)
+    sp = lambda t: t.reshape(b, s, heads, d).transpose(0, 2, 1, 3)
+    scores = blas_matmul(sp(q), np.ascontiguousarray(sp(k).transpose(0, 1, 3, 2))).astype(np.float32)
+    p = softmax_v2(scores, scale)
+    o = blas_matmul(p, np.ascontiguousarray(sp(v))).astype(np.float32)
+    return np.ascontiguousarray(o.transpose(0, 2, 1, 3)).reshape(b, s, w)
+
+
 def gelu_accurate(a):
     """_MKLActivationKernel::geluAccurate (:214-220): erf in float, outer products in double."""
     from scipy.special import erf

@@ -45,6 +45,10 @@ def generate(ref: Path) -> None:
         ("testcase/quantization/mklquantizationmatmul.py", "MKLQuantizationMatmul",
          "quantization_mklquantizationmatmul.npz"),
         ("testcase/quantization/quantize.py", "Quantize", "quantization_quantize.npz"),
+        ("testcase/math/softmax.py", "Softmax", "math_softmax.npz"),
+        ("testcase/math/gelu_accurate.py", "GeluAccurate", "math_gelu_accurate.npz"),
+        ("testcase/layer/layer_normalization.py", "LayerNormalization",
+         "layer_layer_normalization.npz"),
     ]
     for i, (rel, cls, out) in enumerate(jobs):
         np.random.seed(SEED + i)

@@ -78,3 +78,62 @@ def test_argument_errors(pkg):
         pkg.nn.layer_norm(torch.zeros(4, 8, device=dev()), torch.ones(7, device=dev()), torch.zeros(8, device=dev()))
     with pytest.raises(ex.InvalidArgumentError):
         pkg.nn.permute_0213(torch.zeros(4, 8, device=dev()))
+
+
+@pytest.mark.parametrize("batch,seq,heads,dim", [(8, 128, 12, 64), (2, 128, 4, 32), (3, 77, 5, 64),
+                                                  (1, 1, 1, 32), (2, 100, 3, 32)])
+@pytest.mark.parametrize("packed", [True, False])
+def test_fused_attention_matches_operator_sequence(pkg, orc, batch, seq, heads, dim, packed):
+    """One kernel for transpose / Q.K^T / scale / softmax / .V / transpose back: normwise 1e-5
+    against the float32 operator sequence with exact (float64-accumulated) products, also for
+    ragged sequence lengths (masked keys) and with Q, K, V as slices of one packed buffer."""
+    rng = np.random.default_rng(batch * 1000 + seq * 10 + heads)
+    w = heads * dim
+    qkv = rng.normal(0, 1, (batch, seq, 3 * w)).astype(np.float32)
+    d = dev()
+    if packed:
+        tq = torch.from_numpy(qkv).to(d)
+        q, k, v = tq[:, :, :w], tq[:, :, w:2 * w], tq[:, :, 2 * w:]
+    else:
+        q, k, v = (torch.from_numpy(np.ascontiguousarray(qkv[:, :, i * w:(i + 1) * w])).to(d)
+                   for i in range(3))
+    got = pkg.nn.attention(q, k, v, heads).cpu().numpy()
+    pkg.session.get_session(d).sync()
+    want = orc.attention(qkv[:, :, :w], qkv[:, :, w:2 * w], qkv[:, :, 2 * w:], heads)
+    assert got.shape == want.shape
+    assert orc.normwise_rel_error(got, want) < 1e-5
+    assert np.abs(got - want).max() < 2e-5 * max(1.0, np.abs(want).max())
+
+
+def test_fused_attention_refuses_what_it_cannot_take(pkg):
+    d = dev()
+    x = torch.zeros((2, 200, 128), dtype=torch.float32, device=d)
+    with pytest.raises(pkg.exceptions.InvalidArgumentError):
+        pkg.nn.attention(x, x, x, 2)          # seq > 128
+    y = torch.zeros((2, 64, 96), dtype=torch.float32, device=d)
+    with pytest.raises(pkg.exceptions.InvalidArgumentError):
+        pkg.nn.attention(y, y, y, 2)          # dim 48
+
+
+def test_glue_kernels_match_reference_generator_cases(pkg, orc, golden):
+    """The device softmax, erf GELU and layer normalisation on the cases of the reference's own
+    generators (tests/golden/make_golden.py), compared with the reference's predicate."""
+    from test_oracle_golden import _glue_cases
+    d = dev()
+    for kind, a, extra, expect in _glue_cases(golden):
+        ta = torch.from_numpy(np.ascontiguousarray(a)).to(d)
+        if kind == "softmax":
+            moved = ta.movedim(extra, -1).contiguous()
+            got = pkg.nn.softmax(moved).movedim(-1, extra)
+        elif kind == "gelu":
+            got = pkg.nn.gelu(ta)
+        else:
+            axis, gamma, beta = extra
+            cols = int(np.prod(a.shape[axis:]))
+            got = pkg.nn.layer_norm(ta.reshape(-1, cols).contiguous(),
+                                    torch.from_numpy(gamma.reshape(cols).astype(np.float32)).to(d),
+                                    torch.from_numpy(beta.reshape(cols).astype(np.float32)).to(d),
+                                    eps=1e-12).reshape(a.shape)
+        got = got.cpu().numpy()
+        assert orc.is_similar(got, expect), (kind, a.shape)
+        assert np.abs(got.astype(np.float64) - expect).max() < 5e-6, (kind, a.shape)

@@ -123,3 +123,43 @@ def test_dequantize_and_requantize_known_answers(orc):
     assert np.all(orc.quantize(np.full((3, 3), 1.5, np.float32), np.int8)[0] == -128)
     assert np.all(orc.dequantize(DEQUANT_IN, 2.0, 2.0) == np.float32(2.0))
     assert np.all(orc.requantize(DEQUANT_IN, -1.0, 1.0, 3.0, 3.0, np.int16) == -32768)
+
+
+def _glue_cases(golden):
+    """(kind, a float32, extra, expect) for the reference generators of softmax, gelu_accurate
+    and layer_normalization (tfcc/test/python/testcase/math/softmax.py, math/gelu_accurate.py,
+    layer/layer_normalization.py; consumed by tfcc/test/math.cpp:577-655, layer.cpp:36-50)."""
+    for _, c in golden_cases(golden["math_softmax"], "math/softmax"):
+        yield "softmax", c["a"], int(c["axis"][0]), c["expect"]
+    for _, c in golden_cases(golden["math_gelu_accurate"], "math/gelu_accurate"):
+        yield "gelu", c["a"], None, c["expect"]
+    for _, c in golden_cases(golden["layer_layer_normalization"], "layer/layer_normalization"):
+        yield "layer_norm", c["a"], (int(c["axis"][0]), c["LayerNorm/gamma"], c["LayerNorm/beta"]), c["expect"]
+
+
+def glue_oracle(orc, kind, a, extra):
+    """The oracle's restatement applied the way the reference operator is: softmax along any
+    axis is the last-axis softmax of the moved axis; layer normalisation over the trailing
+    axes is the row-wise one over their flattened extent (epsilon 1e-12 as the generator)."""
+    if kind == "softmax":
+        moved = np.moveaxis(a, extra, -1)
+        return np.moveaxis(orc.softmax_v2(np.ascontiguousarray(moved)), -1, extra)
+    if kind == "gelu":
+        return orc.gelu_accurate(a)
+    axis, gamma, beta = extra
+    cols = int(np.prod(a.shape[axis:]))
+    out = orc.layer_normalize(a.reshape(-1, cols), gamma.reshape(cols), beta.reshape(cols), eps=1e-12)
+    return out.reshape(a.shape)
+
+
+def test_glue_oracles_match_reference_expectations(orc, golden):
+    """softmaxV2, geluAccurate and the layer normalisation restated in the oracle, pinned to
+    the expectations of the reference's own generators with the reference's predicate."""
+    seen = {"softmax": 0, "gelu": 0, "layer_norm": 0}
+    for kind, a, extra, expect in _glue_cases(golden):
+        got = glue_oracle(orc, kind, a, extra)
+        assert got.shape == expect.shape
+        assert orc.is_similar(got, expect), (kind, a.shape)
+        assert np.abs(got.astype(np.float64) - expect).max() < 5e-6, (kind, a.shape)
+        seen[kind] += 1
+    assert all(v == 5 for v in seen.values()), seen

@@ -51,6 +51,7 @@ class _Lib:
             "tfccb200_reduce_sum_s8": (i, [vp, vp, u, u, u, i, vp]),
             "tfccb200_reduce_sum_s16": (i, [vp, vp, u, u, u, i, vp]),
             "tfccb200_sgemm_act": (i, [vp, vp, u, vp, u, vp, u, vp, u, u, u, u, i, i, i, vp, sz, vp]),
+            "tfccb200_attention_f32": (i, [vp, vp, vp, vp, vp, u, u, u, u, u, u, f, vp]),
             "tfccb200_softmax_f32": (i, [vp, vp, u, u, f, vp]),
             "tfccb200_layer_norm_f32": (i, [vp, vp, vp, vp, vp, f, u, u, vp]),
             "tfccb200_gelu_f32": (i, [vp, vp, sz, vp]),
@@ -107,7 +108,7 @@ EXPORTED_SYMBOLS = (
     "tfccb200_qgemm_u8s8s32", "tfccb200_qgemm_u8s8s32_ex", "tfccb200_qgemm_u8s8s32_dev",
     "tfccb200_quantized_matmul_params",
     "tfccb200_reduce_sum_u8", "tfccb200_reduce_sum_s8", "tfccb200_reduce_sum_s16",
-    "tfccb200_sgemm_act", "tfccb200_softmax_f32", "tfccb200_layer_norm_f32", "tfccb200_gelu_f32",
+    "tfccb200_sgemm_act", "tfccb200_attention_f32", "tfccb200_softmax_f32", "tfccb200_layer_norm_f32", "tfccb200_gelu_f32",
     "tfccb200_permute_0213_f32", "tfccb200_transpose_last2_f32",
     "tfccb200_minmax_f32", "tfccb200_quantize_f32", "tfccb200_quantize_rowsum_f32", "tfccb200_dequantize_f32", "tfccb200_requantize",
     "tfccb200_sgemm_nsplit_push", "tfccb200_sgemm_nsplit_push_ex", "tfccb200_qgemm_nsplit_push",

@@ -119,8 +119,8 @@ int pick_qgemm_path(const QgemmArgs& a) {
     cudaError_t e;
     const DeviceInfo* di = current_device_info(&e);
     const int sms = di ? di->sm_count : 148;
-    return umma_plan(a.M, a.N, a.K, a.batch, sms, 1, -1, false, false).pair ? TFCCB200_PATH_UMMA2
-                                                            : TFCCB200_PATH_UMMA;
+    return umma_qgemm_prefers_pair(a.M, a.N, a.K, a.batch, sms) ? TFCCB200_PATH_UMMA2
+                                                                  : TFCCB200_PATH_UMMA;
   }
   return TFCCB200_PATH_SIMT;
 }
@@ -449,6 +449,26 @@ int tfccb200_layer_norm_f32(void* stream, const float* x, const float* residual,
                         cols, dst);
 }
 
+int tfccb200_attention_f32(void* stream, const float* q, const float* k, const float* v,
+                           float* out, unsigned batch, unsigned seq, unsigned heads, unsigned dim,
+                           unsigned ld_qkv, unsigned ld_out, float scale, int* device_status) {
+  if (!q || !k || !v || !out || batch == 0 || seq == 0 || heads == 0 || dim == 0)
+    return TFCCB200_EINVAL;
+  if (static_cast<unsigned long long>(batch) * seq * ld_qkv > 0xffffffffull ||
+      static_cast<unsigned long long>(batch) * seq * ld_out > 0xffffffffull)
+    return TFCCB200_EOVERFLOW;
+  AttentionArgs a = {};
+  a.stream = static_cast<cudaStream_t>(stream);
+  a.q = q; a.k = k; a.v = v; a.out = out;
+  a.batch = batch; a.seq = seq; a.heads = heads; a.dim = dim;
+  a.ld = ld_qkv;
+  a.batch_stride = static_cast<unsigned long long>(seq) * ld_qkv;
+  a.ld_out = ld_out;
+  a.scale = scale;
+  a.status = device_status;
+  return attention_f32(a);
+}
+
 int tfccb200_gelu_f32(void* stream, const float* src, size_t n, float* dst) {
   if (!src || !dst || n == 0) return TFCCB200_EINVAL;
   return gelu_f32(static_cast<cudaStream_t>(stream), src, n, dst);
@@ -594,7 +614,7 @@ int tfccb200_qgemm_nsplit_push(void* stream, const uint8_t* A, const int32_t* rs
   cudaError_t e;
   const DeviceInfo* di = current_device_info(&e);
   if (!di) return static_cast<int>(e);
-  return umma_qgemm(a, umma_plan(M, N_shard, K, 1, di->sm_count, 1, -1, false, false).pair);
+  return umma_qgemm(a, umma_qgemm_prefers_pair(M, N_shard, K, 1, di->sm_count));
 }
 
 int tfccb200_sgemm_skinny_static(void* stream, const float* A, const float* B, float* C,

@@ -80,6 +80,11 @@ struct UmmaPlan {
 };
 UmmaPlan umma_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count,
                    int elem_bytes, int force_pair, bool allow_cluster_k, bool allow_stream_k);
+// Tiled fp32 tensor map of `rank` dimensions (dims[0] contiguous; strides_bytes[i] = pitch of
+// dimension i+1) into *map, a CUtensorMap; swizzle_mode 0 = 128-byte swizzle of 16-byte units,
+// 1 = of 32-byte units (MN-major 32-bit MMA operands).
+bool encode_tmap_f32(void* map, const void* base, int rank, const uint64_t* dims,
+                     const uint64_t* strides_bytes, const uint32_t* box, int swizzle_mode);
 int umma_sm_budget(int sm_count, unsigned max_ctas);  // SMs a launch may use (whole pairs)
 bool stream_k_scratch_ok(const SgemmArgs& a, int sm_count);  // scratch lent for the k-shared wave
 size_t umma_stream_k_workspace(int sm_count);  // scratch that lets umma_sgemm share tiles by k-block
@@ -87,6 +92,7 @@ void set_test_flag_wait(unsigned long long timeout_ns, unsigned expect_extra);
 bool umma_sgemm_supported(const SgemmArgs& a);
 int umma_sgemm(const SgemmArgs& a, bool pair);
 bool umma_qgemm_supported(const QgemmArgs& a);
+bool umma_qgemm_prefers_pair(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count);
 int umma_qgemm(const QgemmArgs& a, bool pair);
 
 // ---- CUDA-core paths (simt_kernels.cu) ----
@@ -132,6 +138,21 @@ int nsplit_host_check(const NsplitHostRank& r);
 int nsplit_host_upload(const NsplitHostRank& r);    // rows of A up and on to the peers, B shard up
 int nsplit_host_multiply(const NsplitHostRank& r);  // product, tiles stored into every rank's C
 int nsplit_host_download(const NsplitHostRank& r);  // this rank's rows of C down
+
+// ---- fused attention (attention.cu) ----
+struct AttentionArgs {
+  cudaStream_t stream;
+  const float* q;  // element (b, s, h, d) at q + b*batch_stride + s*ld + h*dim + d; same for k, v
+  const float* k;
+  const float* v;
+  float* out;      // element (b, s, h, d) at out + (b*seq + s)*ld_out + h*dim + d
+  unsigned batch, seq, heads, dim;
+  unsigned long long ld, batch_stride, ld_out;
+  float scale;
+  int* status;
+};
+bool attention_supported(const AttentionArgs& a);
+int attention_f32(const AttentionArgs& a);
 
 // ---- attention / FFN glue (nn_kernels.cu) ----
 int softmax_f32(cudaStream_t stream, const float* src, unsigned rows, unsigned cols, float scale,

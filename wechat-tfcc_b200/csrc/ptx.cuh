@@ -75,6 +75,13 @@ __device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, floa
                : "memory");
 }
 
+__device__ __forceinline__ void st_shared_cluster_v4_b32(uint32_t cluster_addr, uint32_t a,
+                                                         uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a),
+               "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
 // ---- mbarrier ---------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -146,6 +153,17 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void* tmap,
       " [%0], [%1, {%3, %4, %5}], [%2];"
       :
       : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// 4-D tiled load (attention operands addressed as [batch, seq, head, dim]).
+__device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const void* tmap, uint32_t bar,
+                                            int32_t c0, int32_t c1, int32_t c2, int32_t c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2),
+        "r"(c3)
       : "memory");
 }
 // One store that the NVLink switch delivers to the same offset of every GPU bound to the

@@ -95,11 +95,14 @@ struct UmmaGemmParams {
                            // the tensor core narrows fp32), 0 = feed the raw fp32 as head
   unsigned kb_per_chunk;   // kSplit: k-blocks accumulated inside tensor memory before the
                            // partial sum is promoted to registers (>= 1)
-  unsigned cluster_k;      // kSplit, one CTA per tile only: >= 1.  With k > 1 a cluster of k CTAs
-                           // shares one tile, each CTA taking a contiguous range of k-blocks;
-                           // ranks 1.. hand their fp32 partial sums to rank 0 through its
+  unsigned cluster_k;      // kSplit or I8, one CTA per tile only: >= 1.  With k > 1 a cluster of k
+                           // CTAs shares one tile, each CTA taking a contiguous range of k-blocks.
+                           // fp32: ranks 1.. hand their partial sums to rank 0 through its
                            // shared memory and rank 0 adds them in rank order (deterministic)
-                           // before the store.  The grid must hold every tile at once.
+                           // before the store.  int8: every rank owns BN / k columns of the
+                           // tile, receives the other ranks' int32 partial sums for them
+                           // through its shared memory, adds (exact in any order) and stores.
+                           // The grid must hold every tile at once.
   // kSplit only, sk_tiles > 0: the first sk_tiles tiles (between one and two per CTA / pair)
   // are shared out by k-block rather than by tile, so that a tile count that is not a
   // multiple of the grid leaves no SM idle in the last wave.  Group g takes k-blocks
@@ -401,8 +404,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t cta_rank = (kCtaGroup == 2) ? ptx::cluster_ctarank() : 0u;
   const bool is_leader = (cta_rank == 0);
-  // K split over a cluster (see UmmaGemmParams::cluster_k)
-  const unsigned ksplit = (kSplit && kCtaGroup == 1 && p.cluster_k > 1) ? p.cluster_k : 1u;
+  // K split over a cluster (see UmmaGemmParams::cluster_k): the fp32 split kernel and the int8
+  // kernel, single CTAs only
+  constexpr bool kClusterKCapable = kCtaGroup == 1 && (kSplit || kKind == ptx::MmaKind::I8);
+  const unsigned ksplit = (kClusterKCapable && p.cluster_k > 1) ? p.cluster_k : 1u;
   const unsigned krank = ksplit > 1 ? ptx::cluster_ctarank() : 0u;
   const bool in_cluster = (kCtaGroup == 2) || ksplit > 1;
   const unsigned num_groups = gridDim.x / (kCtaGroup * ksplit);  // CTAs / pairs / clusters walking the tiles
@@ -434,7 +439,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       ptx::mbar_init(tmem_full(a), 1);
       ptx::mbar_init(tmem_empty(a), Cfg::kNumEpilogueWarps * kCtaGroup);
     }
-    ptx::mbar_init(red_free, 1);
+    // fp32: rank 0 alone tells the others that its stage buffers are free; int8: every rank
+    // hears from all the others
+    ptx::mbar_init(red_free, (kSplit || ksplit < 2) ? 1 : ksplit - 1);
     ptx::mbar_init(red_ready, ksplit > 1 ? (ksplit - 1) * Cfg::kNumEpilogueWarps * 32 : 1);
     *abort_flag = 0;
     unsigned nseg = 0;
@@ -807,7 +814,70 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           }
           if (row_ok)
             row_term += static_cast<uint32_t>(p.rsA[static_cast<size_t>(p.strideRsA) * b + row]) * ob;
-          if (p.num_dst > 1 || p.mc_dst) {
+          if (ksplit > 1) {
+            // ---- K split over the cluster: reduce-scatter of the int32 accumulators.  Rank r
+            // owns columns [r, r+1) * BN / ksplit of the tile.  The tmem_full wait above means
+            // this CTA's MMAs have retired, so its stage buffers are dead; once every rank has
+            // said so, each sends the others their slices of its accumulator straight into
+            // their stage buffers, laid out [source][warp][4-column group][lane] (conflict-free
+            // 128-bit accesses), and then adds what it received to its own slice.
+            const unsigned ew = warp - Cfg::kFirstEpilogueWarp;
+            const unsigned slice = BN / ksplit;  // multiple of 32 (checked on the host)
+            const unsigned qper = slice / 4;     // 128-bit groups per row of a slice
+            if (ew == 0 && lane == 0)
+              for (unsigned r = 0; r < ksplit; ++r)
+                if (r != krank) ptx::mbar_arrive_cluster(ptx::mapa(red_free, r));
+            bounded_wait<true>(red_free, 0u, TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
+            for (unsigned d = 0; d < ksplit; ++d) {
+              if (d == krank) continue;
+              const unsigned si = krank < d ? krank : krank - 1;  // this rank among d's sources
+              const uint32_t remote = ptx::mapa(smem_base, d);
+              for (unsigned c = 0; c < slice / 32; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(taddr + d * slice + c * 32, r);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int v = 0; v < 8; ++v)
+                  ptx::st_shared_cluster_v4_b32(
+                      remote + 16u * (((si * Cfg::kNumEpilogueWarps + ew) * qper + c * 8 + v) * 32 + lane),
+                      r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+              }
+              ptx::mbar_arrive_cluster(ptx::mapa(red_ready, d));  // every lane: releases its stores
+            }
+            bounded_wait<true>(red_ready, 0u, TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
+            const uint4* red = reinterpret_cast<const uint4*>(smem_gen);
+            const unsigned colbase = col0 + krank * slice;
+            uint32_t* crow = static_cast<uint32_t*>(p.dst[0]) + batch_off +
+                             static_cast<unsigned long long>(row) * p.ldc + p.col_offset + colbase;
+            for (unsigned c = 0; c < slice / 32; ++c) {
+              if (colbase + c * 32 >= p.N) break;
+              uint32_t r[32];
+              ptx::tmem_ld_32x32(taddr + krank * slice + c * 32, r);
+              ptx::tmem_ld_wait();
+              for (unsigned s2 = 0; s2 + 1 < ksplit; ++s2) {
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                  const uint4 t = red[((s2 * Cfg::kNumEpilogueWarps + ew) * qper + c * 8 + v) * 32 + lane];
+                  r[4 * v] += t.x; r[4 * v + 1] += t.y; r[4 * v + 2] += t.z; r[4 * v + 3] += t.w;
+                }
+              }
+              if (row_ok) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                  const unsigned col = colbase + c * 32 + j;
+                  if (col < p.N) {
+                    const uint4 sb = __ldg(reinterpret_cast<const uint4*>(rsB + col));
+                    uint4 v;
+                    v.x = r[j + 0] + row_term + sb.x * oa;
+                    v.y = r[j + 1] + row_term + sb.y * oa;
+                    v.z = r[j + 2] + row_term + sb.z * oa;
+                    v.w = r[j + 3] + row_term + sb.w * oa;
+                    *reinterpret_cast<uint4*>(crow + c * 32 + j) = v;
+                  }
+                }
+              }
+            }
+          } else if (p.num_dst > 1 || p.mc_dst) {
             // column shards pushed to several GPUs: go through the transposing stage so that
             // every store instruction covers whole 128-byte lines of the peers' memory
 #pragma unroll 1

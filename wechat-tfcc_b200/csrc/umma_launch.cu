@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdlib>
 #include <mutex>
@@ -110,10 +111,16 @@ int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, Um
   unsigned cluster = kCtaGroup;
   if (p.cluster_k > 1) {
     // K split over a cluster: one tile per cluster, all tiles resident at once
-    if (!kSplit || kCtaGroup != 1 || total * p.cluster_k > static_cast<unsigned>(sm_count))
+    constexpr bool kCapable = kCtaGroup == 1 && (kSplit || kKind == ptx::MmaKind::I8);
+    if (!kCapable || total * p.cluster_k > static_cast<unsigned>(sm_count))
       return TFCCB200_EUNSUPPORTED;
-    if ((p.cluster_k - 1) * 128u * BN * 4u > static_cast<unsigned>(Cfg::kRingBytes))
-      return TFCCB200_EUNSUPPORTED;  // partial tiles would not fit rank 0's stage buffers
+    // fp32: the other ranks' whole partial tiles meet in rank 0's stage buffers; int8: every
+    // rank receives the other ranks' BN / cluster_k columns
+    const unsigned incoming = kSplit ? (p.cluster_k - 1) * 128u * BN * 4u
+                                     : (p.cluster_k - 1) * 128u * (BN / p.cluster_k) * 4u;
+    if (incoming > static_cast<unsigned>(Cfg::kRingBytes)) return TFCCB200_EUNSUPPORTED;
+    if (!kSplit && (BN % p.cluster_k != 0 || (BN / p.cluster_k) % 32 != 0))
+      return TFCCB200_EUNSUPPORTED;
     groups = static_cast<unsigned>(total) * p.cluster_k;
     cluster = p.cluster_k;
   } else {
@@ -172,10 +179,10 @@ int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, Um
 // How many clusters of `ks` single CTAs of the fp32 kernel the device holds at once.  The SMs
 // of a cluster must share a GPC, so this is not sm_count / ks (a cluster of 3 fits 48 times in
 // 148 SMs by count, yet fewer are co-resident and the grid then runs in two waves).
-template <int BN, int kStages>
+template <ptx::MmaKind kKind, bool kSplit, int BN, int kStages>
 int query_active_clusters(unsigned ks) {
-  using Cfg = UmmaGemmConfig<ptx::MmaKind::TF32, true, 1, BN, kStages>;
-  auto kernel = umma_gemm_kernel<ptx::MmaKind::TF32, true, 1, BN, kStages>;
+  using Cfg = UmmaGemmConfig<kKind, kSplit, 1, BN, kStages>;
+  auto kernel = umma_gemm_kernel<kKind, kSplit, 1, BN, kStages>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            Cfg::kSmemBytes) != cudaSuccess)
     return 0;
@@ -208,13 +215,85 @@ int active_clusters_fp32(int bn, unsigned ks) {
   std::atomic<int>& slot = cache[dev & 63][w][ks];
   int v = slot.load(std::memory_order_acquire);
   if (v == 0) {
-    const int n = bn == 256 ? query_active_clusters<256, 2>(ks)
-                            : (bn == 128 ? query_active_clusters<128, 4>(ks)
-                                         : query_active_clusters<64, 6>(ks));
+    constexpr auto T = ptx::MmaKind::TF32;
+    const int n = bn == 256 ? query_active_clusters<T, true, 256, 2>(ks)
+                            : (bn == 128 ? query_active_clusters<T, true, 128, 4>(ks)
+                                         : query_active_clusters<T, true, 64, 6>(ks));
     v = n + 1;
     slot.store(v, std::memory_order_release);
   }
   return v - 1;
+}
+
+// The same for the int8 kernel's single-CTA instantiations.
+int active_clusters_i8(int bn, unsigned ks) {
+  if (ks < 2 || ks > 4 || (bn != 128 && bn != 256)) return 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  static std::atomic<int> cache[64][2][5];
+  std::atomic<int>& slot = cache[dev & 63][bn == 256 ? 0 : 1][ks];
+  int v = slot.load(std::memory_order_acquire);
+  if (v == 0) {
+    constexpr auto I = ptx::MmaKind::I8;
+    const int n = bn == 256 ? query_active_clusters<I, false, 256, 4>(ks)
+                            : query_active_clusters<I, false, 128, 6>(ks);
+    v = n + 1;
+    slot.store(v, std::memory_order_release);
+  }
+  return v - 1;
+}
+
+// Tile shape of the int8 kernel.  What bounds a CTA is filling its stages: with four to six
+// stages of 32-48 KB in flight and ~2 us of load latency an SM takes in about 95 GB/s, so the
+// time of a launch is the bytes one CTA loads over that rate plus fixed costs, and the way to
+// shorten it is to put more SMs on the problem.  With fewer tiles than SMs the K range of a
+// tile is therefore shared by a cluster (reduce-scatter of the int32 partial sums through
+// distributed shared memory, exact in any order).
+struct I8Plan {
+  bool pair;
+  int bn;
+  unsigned cluster_k;
+};
+I8Plan plan_i8(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count, int force_pair) {
+  static const int env_bn = env_int("TFCCB200_I8_BN", 0);
+  static const int env_ks = env_int("TFCCB200_I8_CLUSTER_K", -1);  // -1: planned; 1: off
+  const unsigned num_kb = (K + 127) / 128;
+  I8Plan best = {false, 0, 1};
+  double best_t = 0;
+  for (int pair = 0; pair <= 1; ++pair) {
+    if (force_pair >= 0 && pair != force_pair) continue;
+    for (int bn : {256, 128}) {
+      if (pair && bn != 256) continue;
+      if (env_bn && bn != env_bn && !pair) continue;
+      if (bn > 128 && static_cast<unsigned>(bn) >= 2 * N) continue;
+      const int tile_m = pair ? 256 : 128;
+      const int groups = pair ? sm_count / 2 : sm_count;
+      const unsigned long long tiles = static_cast<unsigned long long>((M + tile_m - 1) / tile_m) *
+                                       ((N + bn - 1) / bn) * batch;
+      if (pair && force_pair < 0 && tiles * 5 < static_cast<unsigned long long>(groups) * 3) continue;
+      for (unsigned ks = 1; ks <= 4; ks *= 2) {
+        if (ks > 1) {
+          if (pair || env_ks == 1) break;
+          if (tiles > static_cast<unsigned long long>(active_clusters_i8(bn, ks))) continue;
+          const unsigned per = (num_kb + ks - 1) / ks;
+          if (per < 4 || (num_kb + per - 1) / per != ks) continue;
+        }
+        if (env_ks > 1 && !pair && ks != static_cast<unsigned>(env_ks)) continue;
+        const double waves = static_cast<double>((tiles * ks + groups - 1) / groups);
+        const double stage_kb = pair ? 32.0 : (bn == 256 ? 48.0 : 32.0);  // KB a CTA loads per k-block
+        const double mma_us = (pair ? 0.42 : (bn == 256 ? 0.42 : 0.21));
+        const double per_kb = std::max(stage_kb / 95.0, mma_us);          // 95 GB/s = 95 KB/us
+        const double kb = static_cast<double>((num_kb + ks - 1) / ks);
+        const double t = waves * (4.5 + kb * per_kb) + (ks > 1 ? 1.0 + 0.5 * ks : 0.0);
+        if (best.bn == 0 || t < best_t) {
+          best_t = t;
+          best = {pair != 0, bn, ks};
+        }
+      }
+    }
+  }
+  if (best.bn == 0) best = {force_pair == 1, force_pair == 1 ? 256 : 128, 1};
+  return best;
 }
 
 // Time model behind the tile choice, in microseconds, fitted to measurements on B200
@@ -243,6 +322,26 @@ int env_int(const char* name, int fallback) {
 void set_test_flag_wait(unsigned long long timeout_ns, unsigned expect_extra) {
   g_flag_timeout_ns.store(timeout_ns, std::memory_order_relaxed);
   g_flag_expect_extra.store(expect_extra, std::memory_order_relaxed);
+}
+
+bool encode_tmap_f32(void* map, const void* base, int rank, const uint64_t* dims,
+                     const uint64_t* strides_bytes, const uint32_t* box, int swizzle_mode) {
+  EncodeFn fn = encode_fn();
+  if (!fn || rank < 1 || rank > 5) return false;
+  cuuint64_t d[5];
+  cuuint64_t st[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (i + 1 < rank) st[i] = strides_bytes[i];
+  }
+  const CUtensorMapSwizzle sw =
+      swizzle_mode == 1 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
+  return fn(static_cast<CUtensorMap*>(map), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, rank,
+            const_cast<void*>(base), d, st, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 int umma_sm_budget(int sm_count, unsigned max_ctas) {
@@ -550,6 +649,10 @@ bool umma_qgemm_supported(const QgemmArgs& a) {
   return true;
 }
 
+bool umma_qgemm_prefers_pair(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count) {
+  return plan_i8(M, N, K, batch, sm_count, -1).pair;
+}
+
 int umma_qgemm(const QgemmArgs& a, bool pair) {
   cudaError_t ce;
   const DeviceInfo* di = current_device_info(&ce);
@@ -559,7 +662,8 @@ int umma_qgemm(const QgemmArgs& a, bool pair) {
 
   const bool a_batched = a.batch > 1 && a.strideA != 0;
   const bool b_batched = a.batch > 1 && a.strideB != 0;
-  const int bn = umma_plan(a.M, a.N, a.K, a.batch, di->sm_count, 1, pair ? 1 : 0, false, false).bn;
+  const I8Plan plan = plan_i8(a.M, a.N, a.K, a.batch, di->sm_count, pair ? 1 : 0);
+  const int bn = plan.bn;
 
   CUtensorMap ta, tb;
   if (!make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.A, a.K, a.M, a_batched ? a.batch : 1,
@@ -582,6 +686,8 @@ int umma_qgemm(const QgemmArgs& a, bool pair) {
   p.kterm = static_cast<int32_t>(static_cast<uint32_t>(a.offA) * static_cast<uint32_t>(a.offB) *
                                  a.K);
   p.q_offsets = a.dev_offsets;
+  // the K split over a cluster stores from registers into one matrix only
+  p.cluster_k = (!pair && a.num_dst <= 1 && !a.mc_dst) ? plan.cluster_k : 1;
   p.strideRsA = a.strideRsA; p.strideRsB = a.strideRsB;
   p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
   p.strideC = a.strideC;

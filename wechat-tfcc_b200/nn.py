@@ -91,3 +91,38 @@ def transpose_last2(a: torch.Tensor) -> torch.Tensor:
         check(lib.tfccb200_transpose_last2_f32(sess.stream_ptr, a.data_ptr(), a.numel() // (r * c),
                                                r, c, out.data_ptr()))
     return out
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int,
+              scale: float | None = None) -> torch.Tensor:
+    """``softmax(scale * Q K^T) V`` per head, in one kernel.
+
+    ``q``, ``k``, ``v`` are ``[batch, seq, heads*dim]`` tensors as the projections produce
+    them; they may be column slices of one packed ``[batch, seq, 3*heads*dim]`` tensor (their
+    last dimension must be contiguous and all three must share the row pitch).  Returns
+    ``[batch, seq, heads*dim]``.  ``scale`` defaults to ``1/sqrt(dim)``.  Shapes outside the
+    fused kernel's range (seq > 128, dim not 32 or 64) raise InvalidArgumentError; compose
+    ``permute_0213`` / ``transpose_last2`` / ``blas.matmul`` / ``softmax`` for those.
+    """
+    for t, nm in ((q, "q"), (k, "k"), (v, "v")):
+        if not isinstance(t, torch.Tensor) or t.dim() != 3 or t.numel() == 0:
+            raise exceptions.InvalidArgumentError(f"invalid tensor {nm}")
+        if t.dtype != torch.float32:
+            raise exceptions.NotImplementedError(f"{nm}: implemented for float32, got {t.dtype}")
+        if not t.is_cuda or t.stride(2) != 1 or t.stride(0) != t.shape[1] * t.stride(1):
+            raise exceptions.InvalidArgumentError(f"{nm}: rows must be contiguous and batches dense")
+    if q.shape != k.shape or q.shape != v.shape or q.shape[2] % heads != 0:
+        raise exceptions.InvalidArgumentError("shape invalid")
+    if not (q.stride(1) == k.stride(1) == v.stride(1)):
+        raise exceptions.InvalidArgumentError("q, k and v must share one row pitch")
+    batch, seq, width = q.shape
+    dim = width // heads
+    if scale is None:
+        scale = 1.0 / float(dim) ** 0.5
+    out = torch.empty((batch, seq, width), dtype=torch.float32, device=q.device)
+    sess = get_session(q.device)
+    with torch.cuda.device(q.device):
+        check(lib.tfccb200_attention_f32(sess.stream_ptr, q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                         out.data_ptr(), batch, seq, heads, dim, q.stride(1), width,
+                                         float(scale), sess.status_ptr))
+    return out
