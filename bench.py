@@ -515,15 +515,42 @@ def extra_measurements(torch, pkg, dev, peaks, probes):
             mm(q4, k4); mm(p4, q4)
             mm(x4, wo, bo); mm(x4, w1, b1); mm(f4, w2, b2)
 
-    launches_before = pkg.launch_count()
-    stack(x4)
-    stack_launches = pkg.launch_count() - launches_before
-    stack_us, _ = time_graph_train(torch, [lambda: stack(x4)])
-    mm_us, _ = time_graph_train(torch, [matmuls_only])
+    # the same stack with the packed Q/K/V projection (one launch) and the one-kernel attention
+    w4p = [nnops.pack_qkv(*l[:6]) + tuple(l[6:]) for l in w4]
+
+    def stack_fused(x):
+        for (wqkv, bqkv, wo, bo, w1, b1, w2, b2) in w4p:
+            qkv = mm(x, wqkv, bqkv)
+            o = nnops.attention(qkv[:, :, :d_model], qkv[:, :, d_model:2 * d_model],
+                                qkv[:, :, 2 * d_model:], heads, scale=0.125)
+            x = nnops.layer_norm(mm(o, wo, bo), gamma4, beta4, 1e-5, residual=x)
+            x = nnops.layer_norm(mm(mm(x, w1, b1, activation="gelu"), w2, b2), gamma4, beta4, 1e-5,
+                                 residual=x)
+        return x
+
+    qkv4 = to(rng.normal(0, 1, (b4, s4, 3 * d_model)).astype(np.float32))
+
+    def attention_only():
+        for _ in range(4):
+            nnops.attention(qkv4[:, :, :d_model], qkv4[:, :, d_model:2 * d_model],
+                            qkv4[:, :, 2 * d_model:], heads, scale=0.125)
+
     flop4 = 4 * 14898167808.0
-    out["cfg4_encoder_stack"] = {"ms": stack_us / 1e3, "matmul_only_ms": mm_us / 1e3,
-                                 "kernels_per_forward": stack_launches,
-                                 "matmul_tflops": flop4 / (mm_us * 1e-6) / 1e12}
+    for name, fn in (("cfg4_encoder_stack_operator_by_operator", stack), ("cfg4_encoder_stack", stack_fused)):
+        launches_before = pkg.launch_count()
+        y = fn(x4)
+        stack_launches = pkg.launch_count() - launches_before
+        stack_us, _ = time_graph_train(torch, [lambda fn=fn: fn(x4)])
+        out[name] = {"ms": stack_us / 1e3, "kernels_per_forward": stack_launches,
+                     "tflops_matmul_flop_over_whole_forward": flop4 / (stack_us * 1e-6) / 1e12}
+    diff = (stack(x4) - stack_fused(x4)).abs().max().item()
+    out["cfg4_encoder_stack"]["max_abs_diff_vs_operator_by_operator"] = diff
+    mm_us, _ = time_graph_train(torch, [matmuls_only])
+    att_us, _ = time_graph_train(torch, [attention_only])
+    out["cfg4_encoder_stack"]["matmul_only_ms_operator_by_operator"] = mm_us / 1e3
+    out["cfg4_encoder_stack"]["matmul_tflops_operator_by_operator"] = flop4 / (mm_us * 1e-6) / 1e12
+    out["cfg4_encoder_stack"]["fused_attention_us_per_layer"] = att_us / 4
+    del w4p
     del w4
     # cfg5 skinny sweep
     w = rng.normal(0, 0.02, (4096, 16384)).astype(np.float32)

@@ -249,7 +249,9 @@ TFCCB200_API int tfccb200_attention_f32(void* stream, const float* q, const floa
 /*
  * dst = (t - mean(t)) / sqrt(var(t) + eps) * gamma + beta with t = x (+ residual when not
  * NULL), row by row, two-pass mean and variance (_mkl_layer_normalize,
- * tfcc/mkl/interfaces/tfcc_mklnormalizationinterface.cpp:29-62).  cols <= 1024.
+ * tfcc/mkl/interfaces/tfcc_mklnormalizationinterface.cpp:29-62).  Rows of up to 1024 columns
+ * are held in registers by one warp; longer rows take one CTA each and three passes (cf.
+ * _cuda_layer_normalize_large, tfcc/cuda/interfaces/tfcc_cudanormalizationinterface.cu:85).
  */
 TFCCB200_API int tfccb200_layer_norm_f32(void* stream, const float* x, const float* residual,
                                          const float* gamma, const float* beta, float eps,

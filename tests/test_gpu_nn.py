@@ -29,7 +29,7 @@ def test_softmax_rows(pkg, orc, shape):
         assert np.allclose(got.sum(-1), 1.0, atol=1e-5)
 
 
-@pytest.mark.parametrize("shape", [(5, 64), (8, 128, 768), (3, 1000), (16, 1024)])
+@pytest.mark.parametrize("shape", [(5, 64), (8, 128, 768), (3, 1000), (16, 1024), (7, 1028), (3, 5000)])
 def test_layer_norm_with_and_without_residual(pkg, orc, shape):
     rng = np.random.default_rng(shape[-1])
     x = rng.normal(0.5, 2, shape).astype(np.float32)

@@ -415,6 +415,22 @@ def encoder_stack_device(pkg, x, weights, gamma, beta):
     return x
 
 
+def encoder_stack_device_fused(pkg, x, weights, gamma, beta):
+    """The same stack with the Q/K/V projections as one launch on a packed weight and the whole
+    attention (head split, Q.K^T, scale, softmax, .V, head merge) as one kernel: 8 or 9 launches
+    per layer instead of 17."""
+    mm, nn = pkg.blas.matmul, pkg.nn
+    heads, w = 12, 768
+    packed = [nn.pack_qkv(*l[:6]) + tuple(l[6:]) for l in weights]  # once, at constant load
+    for (wqkv, bqkv, wo, bo, w1, b1, w2, b2) in packed:
+        qkv = mm(x, wqkv, bqkv)
+        o = nn.attention(qkv[:, :, :w], qkv[:, :, w:2 * w], qkv[:, :, 2 * w:], heads, scale=0.125)
+        x = nn.layer_norm(mm(o, wo, bo), gamma, beta, 1e-5, residual=x)
+        f = mm(x, w1, b1, activation="gelu")
+        x = nn.layer_norm(mm(f, w2, b2), gamma, beta, 1e-5, residual=x)
+    return x
+
+
 def make_encoder_weights(rng):
     shapes = [(768, 768)] * 4 + [(768, 3072), (3072, 768)]
     weights = []
@@ -426,9 +442,11 @@ def make_encoder_weights(rng):
     return weights
 
 
-def test_config4_encoder_stack_on_device(pkg, orc):
+@pytest.mark.parametrize("fused", [False, True])
+def test_config4_encoder_stack_on_device(pkg, orc, fused):
     """Config 4: 4-layer BERT-base-shaped encoder, batch 8, sequence 128, every operator from
-    this library, against the same stack in float64."""
+    this library, against the same stack in float64; operator by operator, and with the packed
+    Q/K/V projection and the one-kernel attention."""
     d = dev_of()
     rng = np.random.default_rng(3)
     x = rng.normal(0, 1, (8, 128, 768)).astype(np.float32)
@@ -436,7 +454,8 @@ def test_config4_encoder_stack_on_device(pkg, orc):
     truth = _encoder_stack_f64(x.astype(np.float64), [[w.astype(np.float64) for w in l] for l in weights])
     tw = [[torch.from_numpy(w).to(d) for w in l] for l in weights]
     gamma, beta = torch.ones(768, device=d), torch.zeros(768, device=d)
-    got = encoder_stack_device(pkg, torch.from_numpy(x).to(d), tw, gamma, beta)
+    run_stack = encoder_stack_device_fused if fused else encoder_stack_device
+    got = run_stack(pkg, torch.from_numpy(x).to(d), tw, gamma, beta)
     pkg.session.get_session(d).sync()
     got = got.cpu().numpy()
     assert orc.normwise_rel_error(got, truth) < 1e-5

@@ -153,6 +153,47 @@ layer_norm_kernel(const float* __restrict__ x, const float* __restrict__ residua
   }
 }
 
+// Rows longer than a warp's registers hold (the reference's _cuda_layer_normalize_large,
+// tfcc/cuda/interfaces/tfcc_cudanormalizationinterface.cu:85): one CTA per row, three passes
+// over the row (mean, variance about the mean, output); the row stays in L1/L2 between them.
+__global__ void __launch_bounds__(256)
+layer_norm_long_rows_kernel(const float* __restrict__ x, const float* __restrict__ residual,
+                            const float* __restrict__ gamma, const float* __restrict__ beta,
+                            float eps, unsigned cols, float* __restrict__ dst) {
+  pdl_release();
+  pdl_wait();
+  __shared__ float red[8];
+  __shared__ float bcast;
+  const size_t off = static_cast<size_t>(blockIdx.x) * cols;
+  const unsigned lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  auto block_sum = [&](float v) {
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = 0.f;
+      for (int i = 0; i < 8; ++i) s += red[i];
+      bcast = s;
+    }
+    __syncthreads();
+    return bcast;
+  };
+  auto value = [&](unsigned c) { return residual ? x[off + c] + residual[off + c] : x[off + c]; };
+  float sum = 0.f;
+  for (unsigned c = threadIdx.x; c < cols; c += 256) sum += value(c);
+  const float mean = block_sum(sum) / static_cast<float>(cols);
+  float var = 0.f;
+  for (unsigned c = threadIdx.x; c < cols; c += 256) {
+    const float d = value(c) - mean;
+    var += d * d;
+  }
+  var = block_sum(var) / static_cast<float>(cols);
+  const float inv = 1.0f / sqrtf(var + eps);
+  for (unsigned c = threadIdx.x; c < cols; c += 256)
+    dst[off + c] = (value(c) - mean) * (inv * gamma[c]) + beta[c];
+}
+
 // Same, for rows that are whole float4 vectors at 16-byte aligned addresses: VPL vectors per
 // lane, all loads of a row issued before the first use.
 template <int VPL>
@@ -325,7 +366,11 @@ int softmax_f32(cudaStream_t stream, const float* src, unsigned rows, unsigned c
 
 int layer_norm_f32(cudaStream_t stream, const float* x, const float* residual, const float* gamma,
                    const float* beta, float eps, unsigned rows, unsigned cols, float* dst) {
-  if (cols > 32u * kMaxPerLane) return TFCCB200_EUNSUPPORTED;
+  if (cols > 32u * kMaxPerLane) {
+    launch_after_previous(layer_norm_long_rows_kernel, dim3(rows), dim3(256), 0, stream, x, residual,
+                          gamma, beta, eps, cols, dst);
+    return done();
+  }
   const unsigned blocks = (rows + 7) / 8;
   auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
   if (cols % 4 == 0 && a16(x) && a16(residual) && a16(gamma) && a16(beta) && a16(dst)) {

@@ -243,12 +243,15 @@ int active_clusters_i8(int bn, unsigned ks) {
   return v - 1;
 }
 
-// Tile shape of the int8 kernel.  What bounds a CTA is filling its stages: with four to six
-// stages of 32-48 KB in flight and ~2 us of load latency an SM takes in about 95 GB/s, so the
-// time of a launch is the bytes one CTA loads over that rate plus fixed costs, and the way to
-// shorten it is to put more SMs on the problem.  With fewer tiles than SMs the K range of a
-// tile is therefore shared by a cluster (reduce-scatter of the int32 partial sums through
-// distributed shared memory, exact in any order).
+// Tile shape of the int8 kernel, from a time model fitted to graph-replayed launches over
+// rotating operands on B200: a launch costs a fixed part (launch, prologue, first loads,
+// epilogue: 8.7 us for 128-wide single-CTA tiles, 12.5 us for 256-wide ones, 8 us for CTA
+// pairs) plus its k-blocks times the time to fill one stage (0.25 us for 32 KB when half the
+// SMs stream, 0.32 us when nearly all do; 0.62 us for the 48 KB of a 256-wide tile; 0.29 us
+// per CTA of a pair).  Filling the stages is what bounds a CTA, so with fewer tiles than SMs the
+// K range of a tile is shared by a cluster (reduce-scatter of the int32 partial sums through
+// distributed shared memory, exact in any order): measured 256x4096x4096 16.8 -> 13.9 us,
+// 128x4096x4096 16.6 -> 12.8 us, 256x1024x8192 24.3 -> 13.0 us.
 struct I8Plan {
   bool pair;
   int bn;
@@ -280,11 +283,11 @@ I8Plan plan_i8(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count,
         }
         if (env_ks > 1 && !pair && ks != static_cast<unsigned>(env_ks)) continue;
         const double waves = static_cast<double>((tiles * ks + groups - 1) / groups);
-        const double stage_kb = pair ? 32.0 : (bn == 256 ? 48.0 : 32.0);  // KB a CTA loads per k-block
-        const double mma_us = (pair ? 0.42 : (bn == 256 ? 0.42 : 0.21));
-        const double per_kb = std::max(stage_kb / 95.0, mma_us);          // 95 GB/s = 95 KB/us
+        const double busy = std::min(1.0, static_cast<double>(tiles * ks) / groups);
+        const double fixed = pair ? 8.0 : (bn == 256 ? 12.5 : 8.7);
+        const double per_kb = pair ? 0.29 : (bn == 256 ? 0.62 : 0.25 + 0.14 * std::max(0.0, busy - 0.5));
         const double kb = static_cast<double>((num_kb + ks - 1) / ks);
-        const double t = waves * (4.5 + kb * per_kb) + (ks > 1 ? 1.0 + 0.5 * ks : 0.0);
+        const double t = waves * (fixed + kb * per_kb) + (ks > 1 ? 0.3 * ks : 0.0);
         if (best.bn == 0 || t < best_t) {
           best_t = t;
           best = {pair != 0, bn, ks};

@@ -126,3 +126,13 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int,
                                          out.data_ptr(), batch, seq, heads, dim, q.stride(1), width,
                                          float(scale), sess.status_ptr))
     return out
+
+
+def pack_qkv(wq, bq, wk, bk, wv, bv):
+    """One ``[K, 3*N]`` weight and one ``[3*N]`` bias from the three projection weights of an
+    attention block: a one-time preparation when the constants are loaded (the reference's
+    Constant preprocess hook, tfcc/core/framework/tfcc_constant.cpp:70-106), after which
+    ``x . Wqkv + bqkv`` is one launch and ``attention`` reads its three slices in place."""
+    for t in (wq, bq, wk, bk, wv, bv):
+        _f32(t, "weight")
+    return torch.cat([wq, wk, wv], dim=1).contiguous(), torch.cat([bq, bk, bv]).contiguous()

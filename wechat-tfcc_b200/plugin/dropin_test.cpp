@@ -4,6 +4,7 @@
 // with m,n,k in [1,100), with and without bias; tfcc/test/quantization.cpp:191-218: raw u8/s8
 // operands, exact int32 result) with a seeded generator and compares against double / int64
 // host loops, using the reference's is_similar predicate for floats.
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -275,6 +276,97 @@ int main() {
               static_cast<float>((hm[r * 33 + c] - mean) / std::sqrt(var + 1e-5) * hg[c] + hb[c]);
       }
       expect(close_enough(ln, ln_want, true), "layer_normalization");
+    }
+
+    // one-kernel attention on a packed Q/K/V tensor against the double-precision formula
+    {
+      const unsigned batch = 2, seq = 77, heads = 3, dim = 64, width = heads * dim;
+      std::uniform_real_distribution<float> u(-1.f, 1.f);
+      std::vector<float> h(static_cast<size_t>(batch) * seq * 3 * width);
+      for (auto& x : h) x = u(rng);
+      tfcc::Variable<float> qkv({batch, seq, 3 * width});
+      tfcc::data::set(qkv, h);
+      std::vector<float> got = tfcc::data::get(tfcc::b200::attention_packed(qkv, heads, 0.125f));
+      std::vector<float> want(static_cast<size_t>(batch) * seq * width);
+      auto at = [&](unsigned b, unsigned s, unsigned which, unsigned hd, unsigned d) {
+        return static_cast<double>(h[(static_cast<size_t>(b) * seq + s) * 3 * width + which * width + hd * dim + d]);
+      };
+      for (unsigned b = 0; b < batch; ++b)
+        for (unsigned hd = 0; hd < heads; ++hd)
+          for (unsigned i = 0; i < seq; ++i) {
+            std::vector<double> p(seq);
+            double mx = -1e300, sum = 0;
+            for (unsigned j = 0; j < seq; ++j) {
+              double sc = 0;
+              for (unsigned d = 0; d < dim; ++d) sc += at(b, i, 0, hd, d) * at(b, j, 1, hd, d);
+              p[j] = sc * 0.125;
+              mx = std::max(mx, p[j]);
+            }
+            for (unsigned j = 0; j < seq; ++j) sum += (p[j] = std::exp(p[j] - mx));
+            for (unsigned d = 0; d < dim; ++d) {
+              double o = 0;
+              for (unsigned j = 0; j < seq; ++j) o += p[j] / sum * at(b, j, 2, hd, d);
+              want[(static_cast<size_t>(b) * seq + i) * width + hd * dim + d] = static_cast<float>(o);
+            }
+          }
+      expect(close_enough(got, want, false), "fused attention on a packed Q/K/V tensor");
+    }
+
+    // derived constants computed once: column sums of an int8 weight, joined projection weights
+    {
+      const unsigned k = 96, n = 80;
+      std::uniform_int_distribution<int> w8(-127, 127);
+      std::vector<int8_t> hw(static_cast<size_t>(k) * n);
+      for (auto& x : hw) x = static_cast<int8_t>(w8(rng));
+      tfcc::Constant<int8_t>::setRuntimeConstantIfNotExist("qweight", tfcc::Shape({k, n}), hw);
+      const tfcc::Constant<int32_t>& sums = tfcc::b200::cached_column_sums("qweight");
+      const tfcc::Constant<int32_t>& again = tfcc::b200::cached_column_sums("qweight");
+      std::vector<int32_t> got = tfcc::data::get(sums);
+      bool ok = got.size() == n && &sums == &again;
+      for (unsigned j = 0; ok && j < n; ++j) {
+        int32_t want = 0;
+        for (unsigned i = 0; i < k; ++i) want += hw[static_cast<size_t>(i) * n + j];
+        ok = got[j] == want;
+      }
+      expect(ok, "cached column sums of an int8 constant");
+
+      std::vector<float> wa(6 * 4), wb(6 * 2);
+      for (size_t i = 0; i < wa.size(); ++i) wa[i] = static_cast<float>(i);
+      for (size_t i = 0; i < wb.size(); ++i) wb[i] = 100.f + static_cast<float>(i);
+      tfcc::Constant<float>::setRuntimeConstantIfNotExist("wa", tfcc::Shape({6, 4}), wa);
+      tfcc::Constant<float>::setRuntimeConstantIfNotExist("wb", tfcc::Shape({6, 2}), wb);
+      const tfcc::Constant<float>& joined = tfcc::b200::cached_concat_columns("wab", {"wa", "wb"});
+      std::vector<float> hj = tfcc::data::get(joined);
+      bool okj = joined.shape().size() == 2 && joined.shape(0) == 6 && joined.shape(1) == 6;
+      for (unsigned r = 0; okj && r < 6; ++r)
+        for (unsigned c = 0; okj && c < 6; ++c)
+          okj = hj[r * 6 + c] == (c < 4 ? wa[r * 4 + c] : wb[r * 2 + (c - 4)]);
+      expect(okj, "projection weights joined along their columns, cached");
+    }
+
+    // the N split over a device group: two members (two GPUs when present, else both on GPU 0)
+    {
+      const unsigned gpus = tfcc::B200Device::getDeviceCount();
+      std::vector<unsigned> members = {0u, gpus >= 2 ? 1u : 0u};
+      tfcc::b200::parallel::NSplitGroup group(members);
+      const unsigned m = 256, n = 272, k = 132;
+      std::uniform_real_distribution<float> u(-1.f, 1.f);
+      float *pa = nullptr, *pb = nullptr, *pc = nullptr;
+      cudaMallocHost(reinterpret_cast<void**>(&pa), sizeof(float) * m * k);
+      cudaMallocHost(reinterpret_cast<void**>(&pb), sizeof(float) * k * n);
+      cudaMallocHost(reinterpret_cast<void**>(&pc), sizeof(float) * m * n);
+      std::vector<float> ha(static_cast<size_t>(m) * k), hb(static_cast<size_t>(k) * n);
+      for (auto& x : ha) x = u(rng);
+      for (auto& x : hb) x = u(rng);
+      std::copy(ha.begin(), ha.end(), pa);
+      std::copy(hb.begin(), hb.end(), pb);
+      group.matmul_host(pa, pb, pc, m, n, k);
+      std::vector<float> got(pc, pc + static_cast<size_t>(m) * n);
+      expect(close_enough(got, host_matmul(ha, hb, nullptr, 1, m, n, k, false, false), false),
+             "N-split product over a device group, host buffers");
+      cudaFreeHost(pa);
+      cudaFreeHost(pb);
+      cudaFreeHost(pc);
     }
 
     // error behaviour comes from the reference's operator layer, unchanged

@@ -539,8 +539,125 @@ void initialize_b200(unsigned deviceID) {
   Device::getThreadDefault()->attach();
 }
 
-// ---------------------------------------------------------------- quantization
+// ---------------------------------------------------------------- attention, constants, groups
 namespace b200 {
+
+namespace {
+
+Variable<float> run_attention(const float* q, const float* k, const float* v, unsigned batch,
+                              unsigned seq, unsigned heads, unsigned width, unsigned ld, float scale) {
+  if (heads == 0 || width % heads != 0) throw InvalidArgumentError("heads does not divide the width");
+  Variable<float> result({batch, seq, width});
+  B200Session* session = current_session();
+  check_status(tfccb200_attention_f32(session->stream(), q, k, v, result.data(), batch, seq, heads,
+                                      width / heads, ld, width, scale, session->deviceStatus()));
+  return result;
+}
+
+}  // namespace
+
+Variable<float> attention(const Tensor<float>& q, const Tensor<float>& k, const Tensor<float>& v,
+                          unsigned heads, float scale) {
+  if (q.shape().size() != 3 || q.size() == 0) throw InvalidArgumentError("invalid tensor q");
+  if (k.shape() != q.shape() || v.shape() != q.shape())
+    throw InvalidArgumentError("q, k and v don't match");
+  return run_attention(q.data(), k.data(), v.data(), q.shape(0), q.shape(1), heads, q.shape(2),
+                       q.shape(2), scale);
+}
+
+Variable<float> attention_packed(const Tensor<float>& qkv, unsigned heads, float scale) {
+  if (qkv.shape().size() != 3 || qkv.size() == 0 || qkv.shape(2) % 3 != 0)
+    throw InvalidArgumentError("invalid packed tensor qkv");
+  const unsigned width = qkv.shape(2) / 3;
+  return run_attention(qkv.data(), qkv.data() + width, qkv.data() + 2 * width, qkv.shape(0),
+                       qkv.shape(1), heads, width, qkv.shape(2), scale);
+}
+
+const Constant<int32_t>& cached_column_sums(const std::string& weightName) {
+  const std::string derived = weightName + "/b200_column_sums";
+  if (Constant<int32_t>* hit = Constant<int32_t>::tryGetRuntimeConstant(derived)) return *hit;
+  const Constant<int8_t>& w = Constant<int8_t>::getConstant(weightName);
+  Variable<int32_t> sums = quantization::reduce_sum(static_cast<const Tensor<int8_t>&>(w), false);
+  std::vector<int32_t> host = data::get(sums);
+  Constant<int32_t>::setRuntimeConstantIfNotExist(derived, sums.shape(), host);
+  return *Constant<int32_t>::tryGetRuntimeConstant(derived);
+}
+
+const Constant<float>& cached_concat_columns(const std::string& packedName,
+                                             const std::vector<std::string>& names) {
+  if (Constant<float>* hit = Constant<float>::tryGetRuntimeConstant(packedName)) return *hit;
+  if (names.empty()) throw InvalidArgumentError("nothing to concatenate");
+  std::vector<std::vector<float>> parts;
+  std::vector<unsigned> widths;
+  unsigned rows = 0, total = 0;
+  bool rank1 = false;
+  for (const std::string& name : names) {
+    const Constant<float>& c = Constant<float>::getConstant(name);
+    if (c.shape().size() != 1 && c.shape().size() != 2)
+      throw InvalidArgumentError("only rank-1 and rank-2 constants can be joined");
+    const unsigned r = c.shape().size() == 2 ? c.shape(0) : 1;
+    const unsigned wcols = c.shape(c.shape().size() - 1);
+    if (parts.empty()) {
+      rows = r;
+      rank1 = c.shape().size() == 1;
+    } else if (r != rows || rank1 != (c.shape().size() == 1)) {
+      throw InvalidArgumentError("constants to join don't match");
+    }
+    parts.push_back(data::get(c));
+    widths.push_back(wcols);
+    total += wcols;
+  }
+  std::vector<float> joined(static_cast<size_t>(rows) * total);
+  for (unsigned r = 0; r < rows; ++r) {
+    size_t at = static_cast<size_t>(r) * total;
+    for (size_t i = 0; i < parts.size(); ++i) {
+      std::copy(parts[i].begin() + static_cast<size_t>(r) * widths[i],
+                parts[i].begin() + static_cast<size_t>(r + 1) * widths[i], joined.begin() + at);
+      at += widths[i];
+    }
+  }
+  Shape shape = rank1 ? Shape({total}) : Shape({rows, total});
+  Constant<float>::setRuntimeConstantIfNotExist(packedName, shape, joined);
+  return *Constant<float>::tryGetRuntimeConstant(packedName);
+}
+
+namespace parallel {
+
+NSplitGroup::NSplitGroup(const std::vector<unsigned>& deviceIDs) : _group(nullptr), _devices(deviceIDs) {
+  std::vector<int> devs(deviceIDs.begin(), deviceIDs.end());
+  tfccb200_group* g = nullptr;
+  check_status(tfccb200_group_create(static_cast<int>(devs.size()), devs.data(), &g));
+  _group = g;
+}
+
+NSplitGroup::~NSplitGroup() {
+  if (_group) tfccb200_group_destroy(static_cast<tfccb200_group*>(_group));
+}
+
+cudaStream_t NSplitGroup::stream(size_t member) const {
+  return static_cast<cudaStream_t>(
+      tfccb200_group_stream(static_cast<tfccb200_group*>(_group), static_cast<int>(member)));
+}
+
+void NSplitGroup::matmul_host(const float* a, const float* b, float* c, unsigned m, unsigned n,
+                              unsigned k) {
+  check_status(tfccb200_group_sgemm_nsplit_host(static_cast<tfccb200_group*>(_group), a, b, c, m, n,
+                                                k, TFCCB200_PRECISION_FP32));
+}
+
+void NSplitGroup::matmul(const std::vector<const float*>& a, const std::vector<const float*>& bShards,
+                         const std::vector<float*>& c, unsigned m, unsigned nShard, unsigned k) {
+  if (a.size() != size() || bShards.size() != size() || c.size() != size())
+    throw InvalidArgumentError("one operand per group member is required");
+  check_status(tfccb200_group_sgemm_nsplit(static_cast<tfccb200_group*>(_group), a.data(),
+                                           bShards.data(), c.data(), nullptr, m, nShard, k,
+                                           TFCCB200_PRECISION_FP32));
+}
+
+void NSplitGroup::sync() { check_status(tfccb200_group_sync(static_cast<tfccb200_group*>(_group))); }
+
+}  // namespace parallel
+
 namespace quantization {
 
 // Argument checks and messages of tfcc::mkl::quantization::matmul

@@ -176,6 +176,56 @@ void initialize_b200();
 void initialize_b200(unsigned deviceID);
 
 namespace b200 {
+
+// softmax(scale * Q K^T) V per head in one kernel (tfccb200_attention_f32).  q, k and v are
+// [batch, seq, heads*dim] tensors, or the three column slices of one packed
+// [batch, seq, 3*heads*dim] tensor given through attention_packed.  Stands for the transposes,
+// batched matmuls, scale and softmax of the reference graph (see include/tfcc_b200.h).
+Variable<float> attention(const Tensor<float>& q, const Tensor<float>& k, const Tensor<float>& v,
+                          unsigned heads, float scale);
+Variable<float> attention_packed(const Tensor<float>& qkv, unsigned heads, float scale);
+
+// Derived constants, computed once per weight and kept as runtime constants of the current
+// scope -- what the reference's Constant preprocess hook is for
+// (tfcc/core/framework/tfcc_constant.cpp:70-106; cache: tfcc_constantmanager.cpp:38-64):
+//   * the int32 column sums of an int8 weight, the reduceSumB argument of the quantized matmul,
+//     so that reduce_sum(B, false) runs when the weight is first used and never again;
+//   * several float weights (or biases) with the same row count joined along their columns, so
+//     that the Q / K / V projections of an attention block become one matmul.
+const Constant<int32_t>& cached_column_sums(const std::string& weightName);
+const Constant<float>& cached_concat_columns(const std::string& packedName,
+                                             const std::vector<std::string>& names);
+
+namespace parallel {
+
+// The N split of one large product over several GPUs driven by this process, one Device per
+// GPU as in tfcc/core/utils/tfcc_initializer.cpp:50-66.  B is column-sharded, every GPU
+// multiplies its shard and stores each finished tile into all GPUs' C over NVLink from the
+// GEMM epilogue; no separate all-gather pass runs (tfccb200_group_*, include/tfcc_b200.h).
+class NSplitGroup {
+  void* _group;
+  std::vector<unsigned> _devices;
+
+ public:
+  explicit NSplitGroup(const std::vector<unsigned>& deviceIDs);
+  ~NSplitGroup();
+  NSplitGroup(const NSplitGroup&) = delete;
+  NSplitGroup& operator=(const NSplitGroup&) = delete;
+
+  size_t size() const { return _devices.size(); }
+  cudaStream_t stream(size_t member) const;
+
+  // c = a . b for row-major host matrices (pinned for overlapped copies); synchronous.
+  void matmul_host(const float* a, const float* b, float* c, unsigned m, unsigned n, unsigned k);
+  // Device-resident operands: a[i] [m,k], bShards[i] [k,nShard] and c[i] [m, size()*nShard]
+  // live on member i's GPU.  Queued on the members' group streams; sync() waits.
+  void matmul(const std::vector<const float*>& a, const std::vector<const float*>& bShards,
+              const std::vector<float*>& c, unsigned m, unsigned nShard, unsigned k);
+  void sync();
+};
+
+}  // namespace parallel
+
 namespace quantization {
 
 std::tuple<Variable<int32_t>, Variable<float>, Variable<float>> matmul(
