@@ -90,6 +90,7 @@ struct UmmaGemmParams {
   unsigned M, N, K, batch;
   unsigned long long strideC;  // elements between batch entries of C
   unsigned a_batched, b_batched;  // 0: operand shared by the whole batch
+  unsigned tma_store;      // 1: the kernel's C tensor map is valid and tiles are stored through it
   unsigned tiles_m, tiles_n;      // tile grid of one batch entry
   unsigned write_head;     // kSplit: 1 = store the truncated head back (independent of how
                            // the tensor core narrows fp32), 0 = feed the raw fp32 as head
@@ -186,7 +187,8 @@ struct UmmaGemmConfig {
   // global stores cover whole 128-byte lines (and peers' memory is written in full lines).
   static constexpr int kEpiStageBytes = 4096;
   static constexpr int kEpiStagingBytes = kNumEpilogueWarps * kEpiStageBytes;
-  static constexpr int kBarrierBytes = 256 + 16 * kMaxSkSegments + 16;  // + segment table
+  static constexpr int kBarrierBytes =
+      256 + 16 * kMaxSkSegments + 16 + 128;  // + segment table, store target
   static constexpr int kSmemBytes =
       kRingBytes + kEpiStagingBytes + kBarrierBytes + 1024;  // +align slack
   static constexpr uint32_t kIdesc =
@@ -306,17 +308,49 @@ __device__ __forceinline__ void epi_stage_chunk(uint32_t* stage, uint32_t lane, 
   *reinterpret_cast<uint4*>(stage + lane * 32 + ((q ^ (lane & 7)) << 2)) = v;
 }
 
+// Where a tile's rows go.  The kernel parameters live in constant memory; read through a
+// reference inside a loop that also stores to global memory they are reloaded after every store
+// (the compiler cannot rule out that the store changed them) at global-load latency each time --
+// measured 0.24 us per store instruction, 4 us per tile.  So thread 0 copies what the store
+// loops need into shared memory once per launch; reloads from there cost a few cycles and no
+// registers are tied up while the running sums fill the register file.
+struct EpiTarget {
+  uint32_t* dst[kMaxDestinations];
+  uint32_t* mc;  // multicast alias or nullptr
+  unsigned long long ldc;
+  unsigned num_dst;
+  unsigned col_offset;
+  unsigned M, N;
+  int activation;
+  const float* bias;
+  unsigned tma_store;  // tiles leave through the C tensor map (single destination)
+};
+
+__device__ __forceinline__ void fill_epi_target(EpiTarget* t, const UmmaGemmParams& p) {
+  for (unsigned d = 0; d < kMaxDestinations; ++d)
+    t->dst[d] = d < p.num_dst ? static_cast<uint32_t*>(p.dst[d]) : nullptr;
+  t->mc = static_cast<uint32_t*>(p.mc_dst);
+  t->ldc = p.ldc;
+  t->num_dst = p.num_dst;
+  t->col_offset = p.col_offset;
+  t->M = p.M;
+  t->N = p.N;
+  t->activation = p.activation;
+  t->bias = p.bias;
+  t->tma_store = p.tma_store;
+}
+
 // After all 8 chunks of every lane are staged: lane l takes column chunk l%8 of rows
 // i*4 + l/8, adds the per-column term, and stores to every destination.  A warp instruction
 // writes 4 rows x 128 contiguous bytes.
 template <bool kIsFloat>
 __device__ __forceinline__ void epi_flush_block(uint32_t* stage, uint32_t lane, unsigned row0,
-                                                unsigned col_blk, const UmmaGemmParams& p,
+                                                unsigned col_blk, const EpiTarget& t,
                                                 unsigned long long batch_off, uint4 col_term) {
   __syncwarp();
   const unsigned cq = lane & 7u;
   const unsigned col = col_blk + cq * 4;
-  const bool col_ok = col < p.N;  // N is a multiple of 4 on this path: a chunk is all in or out
+  const bool col_ok = col < t.N;  // N is a multiple of 4 on this path: a chunk is all in or out
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const unsigned r = i * 4 + (lane >> 3);
@@ -326,27 +360,49 @@ __device__ __forceinline__ void epi_flush_block(uint32_t* stage, uint32_t lane, 
       v.y = __float_as_uint(__uint_as_float(v.y) + __uint_as_float(col_term.y));
       v.z = __float_as_uint(__uint_as_float(v.z) + __uint_as_float(col_term.z));
       v.w = __float_as_uint(__uint_as_float(v.w) + __uint_as_float(col_term.w));
-      if (p.activation != TFCCB200_ACT_NONE) {
-        v.x = __float_as_uint(apply_activation(__uint_as_float(v.x), p.activation));
-        v.y = __float_as_uint(apply_activation(__uint_as_float(v.y), p.activation));
-        v.z = __float_as_uint(apply_activation(__uint_as_float(v.z), p.activation));
-        v.w = __float_as_uint(apply_activation(__uint_as_float(v.w), p.activation));
+      if (t.activation != TFCCB200_ACT_NONE) {
+        v.x = __float_as_uint(apply_activation(__uint_as_float(v.x), t.activation));
+        v.y = __float_as_uint(apply_activation(__uint_as_float(v.y), t.activation));
+        v.z = __float_as_uint(apply_activation(__uint_as_float(v.z), t.activation));
+        v.w = __float_as_uint(apply_activation(__uint_as_float(v.w), t.activation));
       }
     } else {
       v.x += col_term.x; v.y += col_term.y; v.z += col_term.z; v.w += col_term.w;
     }
     const unsigned grow = row0 + r;
-    if (grow < p.M && col_ok) {
+    if (grow < t.M && col_ok) {
       const unsigned long long off =
-          batch_off + static_cast<unsigned long long>(grow) * p.ldc + p.col_offset + col;
-      if (p.mc_dst) {
-        ptx::multimem_st_v4(static_cast<uint32_t*>(p.mc_dst) + off, v);
+          batch_off + static_cast<unsigned long long>(grow) * t.ldc + t.col_offset + col;
+      if (t.mc) {
+        ptx::multimem_st_v4(t.mc + off, v);
       } else {
-        for (unsigned d = 0; d < p.num_dst; ++d)
-          *reinterpret_cast<uint4*>(static_cast<uint32_t*>(p.dst[d]) + off) = v;
+        for (unsigned d = 0; d < t.num_dst; ++d) *reinterpret_cast<uint4*>(t.dst[d] + off) = v;
       }
     }
   }
+  __syncwarp();
+}
+
+// The same 32x32 block leaving through the tensor map of C instead: the staged block (already
+// complete: bias, activation or zero-point terms applied in registers) is handed to the TMA
+// unit by one lane as a [32 rows x 128 bytes] box; the unit clips rows and columns outside C.
+// Plain st.global from the eight epilogue warps of a CTA proved to be latency-bound (about
+// 0.24 us per store instruction per warp, 4 us for a 128-wide tile), which in the
+// latency-bound shapes sits entirely on the critical path of the launch.
+__device__ __forceinline__ void epi_tma_store_block(uint32_t* stage, uint32_t lane,
+                                                    const CUtensorMap* tmap, unsigned col,
+                                                    unsigned row0, unsigned batch) {
+  ptx::fence_proxy_async_smem();  // the staged values -> visible to the async proxy
+  __syncwarp();
+  if (lane == 0) {
+    ptx::tma_store_3d(tmap, ptx::smem_u32(stage), static_cast<int32_t>(col),
+                      static_cast<int32_t>(row0), static_cast<int32_t>(batch));
+    ptx::bulk_commit_group();
+  }
+}
+// Before the stage is written again (and before the CTA leaves).
+__device__ __forceinline__ void epi_tma_stage_free(uint32_t lane) {
+  if (lane == 0) ptx::bulk_wait_read_all();
   __syncwarp();
 }
 
@@ -370,7 +426,7 @@ template <ptx::MmaKind kKind, bool kSplit, int kCtaGroup, int BN, int kStages>
 __global__ void __launch_bounds__(UmmaGemmConfig<kKind, kSplit, kCtaGroup, BN, kStages>::kThreads,
                                   1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
-                 const UmmaGemmParams p) {
+                 const __grid_constant__ CUtensorMap tmapC, const UmmaGemmParams p) {
   using Cfg = UmmaGemmConfig<kKind, kSplit, kCtaGroup, BN, kStages>;
   extern __shared__ uint8_t smem_raw[];
   pdl_release();  // the next kernel in the stream may begin its preamble
@@ -427,6 +483,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   volatile uint32_t* sk_count_gen =
       reinterpret_cast<volatile uint32_t*>(bar_gen + 256 + 16 * kMaxSkSegments);
 
+  // where the tiles go, read from shared memory by the store loops (see EpiTarget)
+  static_assert(sizeof(EpiTarget) <= 128, "store target overruns its area");
+  EpiTarget* tgt_smem = reinterpret_cast<EpiTarget*>(bar_gen + 256 + 16 * kMaxSkSegments + 16);
+
   UmmaCtl ctl{abort_flag, p.status, p.timeout_ns, p.flag_timeout_ns};
 
   if (threadIdx.x == 0) {
@@ -444,6 +504,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     ptx::mbar_init(red_free, (kSplit || ksplit < 2) ? 1 : ksplit - 1);
     ptx::mbar_init(red_ready, ksplit > 1 ? (ksplit - 1) * Cfg::kNumEpilogueWarps * 32 : 1);
     *abort_flag = 0;
+    fill_epi_target(tgt_smem, p);
     unsigned nseg = 0;
     if (kSplit && p.global_k > 1) {
       const unsigned tile = group_id / p.global_k, r = group_id % p.global_k;
@@ -473,6 +534,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmapA);
     ptx::prefetch_tensormap(&tmapB);
+    if (p.tma_store) ptx::prefetch_tensormap(&tmapC);
   }
   if (warp == 1) {
     ptx::tmem_alloc<kCtaGroup>(tmem_slot, Cfg::kTmemCols);
@@ -663,12 +725,29 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       const uint32_t lane_addr = tmem_base + ((q * 32u) << 16) + col_half * Cfg::kEpiCols;
       uint32_t* stage = reinterpret_cast<uint32_t*>(
           epi_stage_gen + (warp - Cfg::kFirstEpilogueWarp) * Cfg::kEpiStageBytes);
-      auto bias_term = [&](unsigned col_blk) {
+      auto bias_term = [&](unsigned col_blk, const float* bias, unsigned n) {
         uint4 t = make_uint4(0u, 0u, 0u, 0u);  // +0.0f
         const unsigned col = col_blk + (lane & 7u) * 4;
-        if (p.bias && col < p.N) t = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+        if (bias && col < n) t = __ldg(reinterpret_cast<const uint4*>(bias + col));
         return t;
       };
+      // The per-column terms of this tile (bias; int8: column sums of B, row sums of A) are
+      // asked for now, while the mainloop runs, so that the loads after the accumulation hit
+      // the cache instead of adding a trip to DRAM to every launch's tail.
+      if (sg.mode != kSegHead) {
+        unsigned pb, ptm, ptn;
+        tile_coords(sg.tile, p.tiles_m, p.tiles_n, pb, ptm, ptn);
+        const unsigned pcol = ptn * BN + lane * 8;  // 32 lanes x 32 bytes cover 256 columns
+        if constexpr (kKind == ptx::MmaKind::I8) {
+          if (pcol < p.N && lane * 8 < BN)
+            ptx::prefetch_l2(p.rsB + static_cast<size_t>(p.strideRsB) * pb + pcol);
+          const unsigned prow = ptm * Cfg::kTileM + cta_rank * Cfg::kBM + q * 32 + (lane & 3u) * 8;
+          if (lane < 4 && prow < p.M)
+            ptx::prefetch_l2(p.rsA + static_cast<size_t>(p.strideRsA) * pb + prow);
+        } else {
+          if (p.bias && pcol < p.N && lane * 8 < BN) ptx::prefetch_l2(p.bias + pcol);
+        }
+      }
 
       if constexpr (kSplit) {
         // ---- promote every chunk's partial sum into registers (round-to-nearest adds) ----
@@ -764,9 +843,38 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           }
         }
         locate_tile();
+        const EpiTarget& tgt = *tgt_smem;
+        const float* const pbias = tgt.bias;
+        if (tgt.tma_store) {
+          const unsigned n_lim = tgt.N;
+          const int act = tgt.activation;
+#pragma unroll
+          for (int c = 0; c < Cfg::kEpiCols / 32; ++c) {
+            if (col0 + c * 32 >= n_lim) break;  // warp-uniform
+            epi_tma_stage_free(lane);
+#pragma unroll
+            for (int qq = 0; qq < 8; ++qq) {
+              const unsigned col = col0 + c * 32 + 4 * qq;
+              float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (pbias && col < n_lim) bv = __ldg(reinterpret_cast<const float4*>(pbias + col));
+              float4 v = make_float4(sum[c * 32 + 4 * qq + 0] + bv.x, sum[c * 32 + 4 * qq + 1] + bv.y,
+                                     sum[c * 32 + 4 * qq + 2] + bv.z, sum[c * 32 + 4 * qq + 3] + bv.w);
+              if (act != TFCCB200_ACT_NONE) {
+                v.x = apply_activation(v.x, act); v.y = apply_activation(v.y, act);
+                v.z = apply_activation(v.z, act); v.w = apply_activation(v.w, act);
+              }
+              epi_stage_chunk(stage, lane, qq,
+                              make_uint4(__float_as_uint(v.x), __float_as_uint(v.y),
+                                         __float_as_uint(v.z), __float_as_uint(v.w)));
+            }
+            epi_tma_store_block(stage, lane, &tmapC, col0 + c * 32, row0, b);
+          }
+          epi_tma_stage_free(lane);
+          continue;
+        }
 #pragma unroll
         for (int c = 0; c < Cfg::kEpiCols / 32; ++c) {
-          if (col0 + c * 32 >= p.N) break;  // warp-uniform
+          if (col0 + c * 32 >= tgt.N) break;  // warp-uniform
 #pragma unroll
           for (int qq = 0; qq < 8; ++qq)
             epi_stage_chunk(stage, lane, qq,
@@ -774,20 +882,71 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                                        __float_as_uint(sum[c * 32 + 4 * qq + 1]),
                                        __float_as_uint(sum[c * 32 + 4 * qq + 2]),
                                        __float_as_uint(sum[c * 32 + 4 * qq + 3])));
-          epi_flush_block<true>(stage, lane, row0, col0 + c * 32, p, batch_off,
-                                bias_term(col0 + c * 32));
+          epi_flush_block<true>(stage, lane, row0, col0 + c * 32, tgt, batch_off,
+                                bias_term(col0 + c * 32, pbias, tgt.N));
         }
       } else {
         const unsigned acc = it & 1u;
         const uint32_t acc_ph = (it >> 1) & 1u;
         ++it;
+        const unsigned pN = tgt_smem->N, pM = tgt_smem->M;
+        const float* const pbias = tgt_smem->bias;
+        // int8: the zero-point scalars of this lane's row, fetched before the accumulator is
+        // waited for so that their latency hides behind the mainloop
+        const int32_t* rsB = nullptr;
+        const unsigned row = row0 + lane;
+        const bool row_ok = row < pM;
+        uint32_t oa = 0, ob = 0, row_term = 0;
+        if constexpr (kKind == ptx::MmaKind::I8) {
+          rsB = p.rsB + static_cast<size_t>(p.strideRsB) * b;
+          oa = static_cast<uint32_t>(p.offA);
+          ob = static_cast<uint32_t>(p.offB);
+          row_term = static_cast<uint32_t>(p.kterm);
+          if (p.q_offsets) {
+            oa = static_cast<uint32_t>(__ldg(p.q_offsets));
+            ob = static_cast<uint32_t>(__ldg(p.q_offsets + 1));
+            row_term = oa * ob * p.K;
+          }
+          if (row_ok)
+            row_term += static_cast<uint32_t>(__ldg(p.rsA + static_cast<size_t>(p.strideRsA) * b + row)) * ob;
+        }
         bounded_wait<false>(tmem_full(acc), acc_ph, TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
         ptx::tc_fence_after_sync();
         const uint32_t taddr = lane_addr + acc * BN;
+        const EpiTarget& tgt = *tgt_smem;
         if constexpr (kKind != ptx::MmaKind::I8) {
+          if (tgt.tma_store) {
+            const int act = tgt.activation;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+              if (col0 + c * 32 >= pN) break;  // warp-uniform
+              uint32_t r[32];
+              ptx::tmem_ld_32x32(taddr + c * 32, r);
+              ptx::tmem_ld_wait();
+              epi_tma_stage_free(lane);
+#pragma unroll
+              for (int qq = 0; qq < 8; ++qq) {
+                const unsigned col = col0 + c * 32 + 4 * qq;
+                float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (pbias && col < pN) bv = __ldg(reinterpret_cast<const float4*>(pbias + col));
+                float4 v = make_float4(__uint_as_float(r[4 * qq]) + bv.x, __uint_as_float(r[4 * qq + 1]) + bv.y,
+                                       __uint_as_float(r[4 * qq + 2]) + bv.z, __uint_as_float(r[4 * qq + 3]) + bv.w);
+                if (act != TFCCB200_ACT_NONE) {
+                  v.x = apply_activation(v.x, act); v.y = apply_activation(v.y, act);
+                  v.z = apply_activation(v.z, act); v.w = apply_activation(v.w, act);
+                }
+                epi_stage_chunk(stage, lane, qq,
+                                make_uint4(__float_as_uint(v.x), __float_as_uint(v.y),
+                                           __float_as_uint(v.z), __float_as_uint(v.w)));
+              }
+              epi_tma_store_block(stage, lane, &tmapC, col0 + c * 32, row0, b);
+            }
+            epi_tma_stage_free(lane);
+          } else {
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
-            if (col0 + c * 32 >= p.N) break;  // warp-uniform
+            if (col0 + c * 32 >= pN) break;  // warp-uniform
+            const uint4 bt = bias_term(col0 + c * 32, pbias, pN);
             uint32_t r[32];
             ptx::tmem_ld_32x32(taddr + c * 32, r);
             ptx::tmem_ld_wait();
@@ -795,25 +954,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             for (int qq = 0; qq < 8; ++qq)
               epi_stage_chunk(stage, lane, qq,
                               make_uint4(r[4 * qq], r[4 * qq + 1], r[4 * qq + 2], r[4 * qq + 3]));
-            epi_flush_block<true>(stage, lane, row0, col0 + c * 32, p, batch_off,
-                                  bias_term(col0 + c * 32));
+            epi_flush_block<true>(stage, lane, row0, col0 + c * 32, tgt, batch_off, bt);
+          }
           }
         } else {
           // zero-point correction.  The int8 mainloop already saturates shared-memory
           // bandwidth (TMA fill + MMA operand reads), so this epilogue stays out of shared
           // memory: every lane stores its own row's columns straight from registers.
-          const int32_t* rsB = p.rsB + static_cast<size_t>(p.strideRsB) * b;
-          const unsigned row = row0 + lane;
-          const bool row_ok = row < p.M;
-          uint32_t oa = static_cast<uint32_t>(p.offA), ob = static_cast<uint32_t>(p.offB);
-          uint32_t row_term = static_cast<uint32_t>(p.kterm);
-          if (p.q_offsets) {
-            oa = static_cast<uint32_t>(__ldg(p.q_offsets));
-            ob = static_cast<uint32_t>(__ldg(p.q_offsets + 1));
-            row_term = oa * ob * p.K;
-          }
-          if (row_ok)
-            row_term += static_cast<uint32_t>(p.rsA[static_cast<size_t>(p.strideRsA) * b + row]) * ob;
           if (ksplit > 1) {
             // ---- K split over the cluster: reduce-scatter of the int32 accumulators.  Rank r
             // owns columns [r, r+1) * BN / ksplit of the tile.  The tmem_full wait above means
@@ -847,10 +994,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             bounded_wait<true>(red_ready, 0u, TFCCB200_DEV_TIMEOUT_EPILOGUE, ctl);
             const uint4* red = reinterpret_cast<const uint4*>(smem_gen);
             const unsigned colbase = col0 + krank * slice;
-            uint32_t* crow = static_cast<uint32_t*>(p.dst[0]) + batch_off +
-                             static_cast<unsigned long long>(row) * p.ldc + p.col_offset + colbase;
+            uint32_t* crow = tgt.dst[0] + batch_off + static_cast<unsigned long long>(row) * tgt.ldc +
+                             tgt.col_offset + colbase;
             for (unsigned c = 0; c < slice / 32; ++c) {
-              if (colbase + c * 32 >= p.N) break;
+              if (colbase + c * 32 >= pN) break;
               uint32_t r[32];
               ptx::tmem_ld_32x32(taddr + krank * slice + c * 32, r);
               ptx::tmem_ld_wait();
@@ -861,11 +1008,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                   r[4 * v] += t.x; r[4 * v + 1] += t.y; r[4 * v + 2] += t.z; r[4 * v + 3] += t.w;
                 }
               }
-              if (row_ok) {
+              if (tgt.tma_store) {
+                epi_tma_stage_free(lane);
+#pragma unroll
+                for (int qq = 0; qq < 8; ++qq) {
+                  const unsigned col = colbase + c * 32 + 4 * qq;
+                  uint4 sb = make_uint4(0u, 0u, 0u, 0u);
+                  if (col < pN) sb = __ldg(reinterpret_cast<const uint4*>(rsB + col));
+                  epi_stage_chunk(stage, lane, qq,
+                                  make_uint4(r[4 * qq] + row_term + sb.x * oa, r[4 * qq + 1] + row_term + sb.y * oa,
+                                             r[4 * qq + 2] + row_term + sb.z * oa, r[4 * qq + 3] + row_term + sb.w * oa));
+                }
+                epi_tma_store_block(stage, lane, &tmapC, colbase + c * 32, row0, b);
+              } else if (row_ok) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
                   const unsigned col = colbase + c * 32 + j;
-                  if (col < p.N) {
+                  if (col < pN) {
                     const uint4 sb = __ldg(reinterpret_cast<const uint4*>(rsB + col));
                     uint4 v;
                     v.x = r[j + 0] + row_term + sb.x * oa;
@@ -877,12 +1036,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                 }
               }
             }
-          } else if (p.num_dst > 1 || p.mc_dst) {
+            if (tgt.tma_store) epi_tma_stage_free(lane);
+          } else if (tgt.num_dst > 1 || tgt.mc) {
             // column shards pushed to several GPUs: go through the transposing stage so that
             // every store instruction covers whole 128-byte lines of the peers' memory
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
-              if (col0 + c * 32 >= p.N) break;
+              if (col0 + c * 32 >= pN) break;
               uint32_t r[32];
               ptx::tmem_ld_32x32(taddr + c * 32, r);
               ptx::tmem_ld_wait();
@@ -893,26 +1053,38 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                                            r[4 * qq + 2] + row_term, r[4 * qq + 3] + row_term));
               uint4 ct = make_uint4(0u, 0u, 0u, 0u);
               const unsigned col = col0 + c * 32 + (lane & 7u) * 4;
-              if (col < p.N) {
+              if (col < pN) {
                 ct = __ldg(reinterpret_cast<const uint4*>(rsB + col));
                 ct.x *= oa; ct.y *= oa; ct.z *= oa; ct.w *= oa;
               }
-              epi_flush_block<false>(stage, lane, row0, col0 + c * 32, p, batch_off, ct);
+              epi_flush_block<false>(stage, lane, row0, col0 + c * 32, tgt, batch_off, ct);
             }
           } else {
-          uint32_t* crow = static_cast<uint32_t*>(p.dst[0]) + batch_off +
-                           static_cast<unsigned long long>(row) * p.ldc + p.col_offset + col0;
+          uint32_t* crow = tgt.dst[0] + batch_off + static_cast<unsigned long long>(row) * tgt.ldc +
+                           tgt.col_offset + col0;
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
-            if (col0 + c * 32 >= p.N) break;
+            if (col0 + c * 32 >= pN) break;
             uint32_t r[32];
             ptx::tmem_ld_32x32(taddr + c * 32, r);
             ptx::tmem_ld_wait();
-            if (row_ok) {
+            if (tgt.tma_store) {
+              epi_tma_stage_free(lane);
+#pragma unroll
+              for (int qq = 0; qq < 8; ++qq) {
+                const unsigned col = col0 + c * 32 + 4 * qq;
+                uint4 sb = make_uint4(0u, 0u, 0u, 0u);
+                if (col < pN) sb = __ldg(reinterpret_cast<const uint4*>(rsB + col));
+                epi_stage_chunk(stage, lane, qq,
+                                make_uint4(r[4 * qq] + row_term + sb.x * oa, r[4 * qq + 1] + row_term + sb.y * oa,
+                                           r[4 * qq + 2] + row_term + sb.z * oa, r[4 * qq + 3] + row_term + sb.w * oa));
+              }
+              epi_tma_store_block(stage, lane, &tmapC, col0 + c * 32, row0, b);
+            } else if (row_ok) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
                 const unsigned col = col0 + c * 32 + j;
-                if (col < p.N) {  // N % 16 == 0 on this path
+                if (col < pN) {  // N % 16 == 0 on this path
                   const uint4 sb = __ldg(reinterpret_cast<const uint4*>(rsB + col));
                   uint4 v;
                   v.x = r[j + 0] + row_term + sb.x * oa;
@@ -924,6 +1096,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
               }
             }
           }
+          if (tgt.tma_store) epi_tma_stage_free(lane);
           }
         }
         release_acc(acc);

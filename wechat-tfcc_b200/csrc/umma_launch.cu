@@ -88,6 +88,20 @@ constexpr size_t kStreamKFlagBytes = 4096;  // one counter per CTA of the grid, 
 template <ptx::MmaKind kKind, bool kSplit, int kCtaGroup, int BN, int kStages>
 int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, UmmaGemmParams p,
            int sm_count) {
+  // Tiles leave through a tensor map of C when there is one destination with the dense
+  // layout the map describes (the multi-GPU push keeps ordinary stores: several destinations,
+  // or a multicast alias).  TFCCB200_TMA_STORE=0 turns it off.
+  static const int env_tma_store = env_int("TFCCB200_TMA_STORE", 1);
+  CUtensorMap tc = {};
+  p.tma_store = 0;
+  if (env_tma_store && p.num_dst == 1 && !p.mc_dst && p.ldc % 4 == 0 && p.strideC % 4 == 0 &&
+      (reinterpret_cast<uintptr_t>(p.dst[0]) & 15u) == 0 && p.col_offset == 0) {
+    const CUtensorMapDataType dt = kKind == ptx::MmaKind::I8 ? CU_TENSOR_MAP_DATA_TYPE_INT32
+                                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    if (make_tmap(&tc, dt, 4, p.dst[0], p.ldc, p.M, p.batch, p.batch > 1 ? p.strideC : 0, 32,
+                  CU_TENSOR_MAP_SWIZZLE_128B))
+      p.tma_store = 1;
+  }
   using Cfg = UmmaGemmConfig<kKind, kSplit, kCtaGroup, BN, kStages>;
   auto kernel = umma_gemm_kernel<kKind, kSplit, kCtaGroup, BN, kStages>;
   // The opt-in shared-memory size is a per-device attribute of the function.
@@ -170,7 +184,7 @@ int launch(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, Um
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
-  e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
+  e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, p);
   if (e != cudaSuccess) return static_cast<int>(e);
   count_launch();
   return TFCCB200_OK;

@@ -8,12 +8,41 @@
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
+#include <map>
+#include <string>
+#include <tuple>
 #include <random>
 #include <vector>
 
 #include "tfcc_b200.h"
 
 namespace {
+
+// Weights served from memory, the way an .npz file would serve them
+// (tfcc/core/dataloaders/tfcc_dataloader.h:24-57): name -> (shape, type tag, raw bytes).
+class MemoryLoader : public tfcc::DataLoader {
+  std::map<std::string, std::tuple<tfcc::Shape, std::string, std::string>> _data;
+
+ public:
+  template <class T>
+  void add(const std::string& name, std::vector<unsigned> shape, const std::vector<T>& values,
+           const char* type) {
+    std::string raw(reinterpret_cast<const char*>(values.data()), values.size() * sizeof(T));
+    _data[name] = std::make_tuple(tfcc::Shape(std::move(shape)), std::string(type), std::move(raw));
+  }
+  const std::tuple<tfcc::Shape, std::string, std::string>& loadData(
+      const std::string& name) const override {
+    auto it = _data.find(name);
+    if (it == _data.end()) throw tfcc::RuntimeError("no such constant: " + name);
+    return it->second;
+  }
+  std::vector<std::tuple<std::string, std::string>> getAllNames() const override {
+    std::vector<std::tuple<std::string, std::string>> names;
+    for (const auto& kv : _data) names.emplace_back(kv.first, std::get<1>(kv.second));
+    return names;
+  }
+  bool hasData(const std::string& name) const override { return _data.count(name) != 0; }
+};
 
 int g_failures = 0;
 int g_cases = 0;
@@ -318,7 +347,9 @@ int main() {
       std::uniform_int_distribution<int> w8(-127, 127);
       std::vector<int8_t> hw(static_cast<size_t>(k) * n);
       for (auto& x : hw) x = static_cast<int8_t>(w8(rng));
-      tfcc::Constant<int8_t>::setRuntimeConstantIfNotExist("qweight", tfcc::Shape({k, n}), hw);
+      MemoryLoader* loader = new MemoryLoader();  // lives as long as the process, like the global it becomes
+      loader->add<int8_t>("qweight", {k, n}, hw, "i1");
+      tfcc::DataLoader::setGlobalDefault(loader);
       const tfcc::Constant<int32_t>& sums = tfcc::b200::cached_column_sums("qweight");
       const tfcc::Constant<int32_t>& again = tfcc::b200::cached_column_sums("qweight");
       std::vector<int32_t> got = tfcc::data::get(sums);
@@ -333,8 +364,8 @@ int main() {
       std::vector<float> wa(6 * 4), wb(6 * 2);
       for (size_t i = 0; i < wa.size(); ++i) wa[i] = static_cast<float>(i);
       for (size_t i = 0; i < wb.size(); ++i) wb[i] = 100.f + static_cast<float>(i);
-      tfcc::Constant<float>::setRuntimeConstantIfNotExist("wa", tfcc::Shape({6, 4}), wa);
-      tfcc::Constant<float>::setRuntimeConstantIfNotExist("wb", tfcc::Shape({6, 2}), wb);
+      loader->add<float>("wa", {6, 4}, wa, "f4");
+      loader->add<float>("wb", {6, 2}, wb, "f4");
       const tfcc::Constant<float>& joined = tfcc::b200::cached_concat_columns("wab", {"wa", "wb"});
       std::vector<float> hj = tfcc::data::get(joined);
       bool okj = joined.shape().size() == 2 && joined.shape(0) == 6 && joined.shape(1) == 6;
