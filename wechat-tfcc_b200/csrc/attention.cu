@@ -33,7 +33,8 @@ namespace tfccb200 {
 
 namespace {
 
-constexpr int kAttThreads = 128;       // four warps: one TMEM lane quarter each, one row per thread
+constexpr int kAttThreads = 256;       // eight warps: warps w and w+4 share TMEM lane quarter w,
+                                       // each taking half of a row's columns
 constexpr int kAttRows = 128;          // query rows = key rows of a tile
 constexpr int kTile = kAttRows * 128;  // bytes of one [128 rows x 32 floats] operand tile
 
@@ -57,7 +58,7 @@ struct AttLayout {
   static constexpr int kVBytes = 4 * kKb * kVChunk; // 128 key rows x DIM floats
   static constexpr int kPBytes = 4 * kTile;         // one copy of P: 4 k-blocks of 32 keys
   static constexpr int kFront = (4 * kQBytes > 2 * kPBytes) ? 4 * kQBytes : 2 * kPBytes;
-  static constexpr int kSmem = kFront + 2 * kVBytes + 64 + 1024;
+  static constexpr int kSmem = kFront + 2 * kVBytes + 64 + 2048 + 1024;  // + row max / sum exchange
 };
 
 __device__ __forceinline__ bool att_wait(uint32_t bar, uint32_t parity, const AttParams& p,
@@ -108,7 +109,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(ctl_gen + 16);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(ctl_gen + 20);
 
-  const unsigned tid = threadIdx.x, warp = tid >> 5;
+  const unsigned tid = threadIdx.x, warp = tid >> 5;  // 8 warps
   const int head = static_cast<int>(blockIdx.x % p.heads);
   const int b = static_cast<int>(blockIdx.x / p.heads);
 
@@ -159,7 +160,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     };
     split(q_raw, q_lo, L::kQBytes);
     split(k_raw, k_lo, L::kQBytes);
-    split(v_raw, v_lo, L::kVBytes);
   }
   ptx::fence_proxy_async_smem();
   ptx::tc_fence_before_sync();
@@ -185,43 +185,64 @@ attention_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     }
     ptx::umma_commit<1>(bar_mma, 0);
   }
+  // V's tails are made while the tensor core works on the scores
+  {
+    const float4* raw = reinterpret_cast<const float4*>(gen + (v_raw - base));
+    float4* lo = reinterpret_cast<float4*>(gen + (v_lo - base));
+    for (int i = tid; i < L::kVBytes / 16; i += kAttThreads) {
+      const float4 x = raw[i];
+      lo[i] = make_float4(tf32_tail(x.x), tf32_tail(x.y), tf32_tail(x.z), tf32_tail(x.w));
+    }
+  }
   att_wait(bar_mma, 0u, p, abort_flag, TFCCB200_DEV_TIMEOUT_MMA);
   ptx::tc_fence_after_sync();
 
-  // ---- softmax of this thread's row, then P (raw and tail) into the K-major operand layout ----
-  const unsigned row = tid;  // TMEM lane = query row
-  const uint32_t lane_addr = tmem_base + ((warp * 32u) << 16);
+  // ---- softmax: a row is shared by two threads (warps w and w+4), 64 columns each; row
+  // maximum and row sum are exchanged through shared memory.  Then P (raw and tail) goes into
+  // the K-major operand layout over the dead Q / K tiles. ----
+  const unsigned row = (warp & 3u) * 32u + (tid & 31u);  // TMEM lane = query row
+  const unsigned half = warp >> 2;                       // which 64 columns of the row
+  const uint32_t lane_addr = tmem_base + (((warp & 3u) * 32u) << 16);
+  float* xch = reinterpret_cast<float*>(ctl_gen + 64);   // [2 halves][128 rows], used twice
   {
-    uint32_t u[128];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32(lane_addr + c * 32, reinterpret_cast<uint32_t(&)[32]>(u[c * 32]));
+    uint32_t u[64];
+    ptx::tmem_ld_32x32(lane_addr + half * 64, reinterpret_cast<uint32_t(&)[32]>(u[0]));
+    ptx::tmem_ld_32x32(lane_addr + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(u[32]));
     ptx::tmem_ld_wait();
     float mx = -3.402823466e+38f;
 #pragma unroll
-    for (int c = 0; c < 128; ++c) {
-      const float v = (static_cast<unsigned>(c) < p.seq) ? __uint_as_float(u[c]) * p.scale
-                                                         : -3.402823466e+38f;
+    for (int c = 0; c < 64; ++c) {
+      const float v = (half * 64 + c < p.seq) ? __uint_as_float(u[c]) * p.scale : -3.402823466e+38f;
       u[c] = __float_as_uint(v);
       mx = fmaxf(mx, v);
     }
+    xch[half * 128 + row] = mx;
+    __syncthreads();
+    mx = fmaxf(mx, xch[(half ^ 1u) * 128 + row]);
+    __syncthreads();
     float sum = 0.f;
 #pragma unroll
-    for (int c = 0; c < 128; ++c) {
-      const float e = (static_cast<unsigned>(c) < p.seq) ? expf(__uint_as_float(u[c]) - mx) : 0.f;
+    for (int c = 0; c < 64; ++c) {
+      const float e = (half * 64 + c < p.seq) ? expf(__uint_as_float(u[c]) - mx) : 0.f;
       u[c] = __float_as_uint(e);
       sum += e;
     }
+    xch[half * 128 + row] = sum;
+    __syncthreads();
+    // the two halves in a fixed order, so that both threads of a row divide by the same sum
+    sum = xch[row] + xch[128 + row];
     uint8_t* p_raw_gen = gen + (p_raw - base);
     uint8_t* p_lo_gen = gen + (p_lo - base);
 #pragma unroll
-    for (int kb = 0; kb < 4; ++kb) {
+    for (int kk = 0; kk < 2; ++kk) {
+      const unsigned kb = half * 2 + kk;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float4 v;
-        v.x = __uint_as_float(u[kb * 32 + j * 4 + 0]) / sum;
-        v.y = __uint_as_float(u[kb * 32 + j * 4 + 1]) / sum;
-        v.z = __uint_as_float(u[kb * 32 + j * 4 + 2]) / sum;
-        v.w = __uint_as_float(u[kb * 32 + j * 4 + 3]) / sum;
+        v.x = __uint_as_float(u[kk * 32 + j * 4 + 0]) / sum;
+        v.y = __uint_as_float(u[kk * 32 + j * 4 + 1]) / sum;
+        v.z = __uint_as_float(u[kk * 32 + j * 4 + 2]) / sum;
+        v.w = __uint_as_float(u[kk * 32 + j * 4 + 3]) / sum;
         const unsigned off = kb * kTile + row * 128 + ((j ^ (row & 7u)) << 4);
         *reinterpret_cast<float4*>(p_raw_gen + off) = v;
         *reinterpret_cast<float4*>(p_lo_gen + off) =
@@ -258,19 +279,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   att_wait(bar_mma, 1u, p, abort_flag, TFCCB200_DEV_TIMEOUT_MMA);
   ptx::tc_fence_after_sync();
 
-  // ---- this thread's output row: DIM contiguous floats of [batch, seq, heads*dim] ----
+  // ---- output: each thread stores its half of the row's DIM floats (DIM = 32: warps 0-3 only) ----
   {
-    float* dst = p.out + (static_cast<unsigned long long>(b) * p.seq + row) * p.ld_out +
-                 static_cast<unsigned long long>(head) * DIM;
-#pragma unroll
-    for (int c = 0; c < L::kKb; ++c) {
+    constexpr int kColsPerThread = DIM / 2 >= 32 ? DIM / 2 : 32;
+    constexpr int kHalves = DIM / kColsPerThread;
+    if (static_cast<int>(half) < kHalves) {
+      float* dst = p.out + (static_cast<unsigned long long>(b) * p.seq + row) * p.ld_out +
+                   static_cast<unsigned long long>(head) * DIM + half * kColsPerThread;
       uint32_t r[32];
-      ptx::tmem_ld_32x32(lane_addr + 128 + c * 32, r);
+      ptx::tmem_ld_32x32(lane_addr + 128 + half * kColsPerThread, r);
       ptx::tmem_ld_wait();
       if (row < p.seq) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<uint4*>(dst + c * 32 + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+          *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
       }
     }
   }

@@ -725,6 +725,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       const uint32_t lane_addr = tmem_base + ((q * 32u) << 16) + col_half * Cfg::kEpiCols;
       uint32_t* stage = reinterpret_cast<uint32_t*>(
           epi_stage_gen + (warp - Cfg::kFirstEpilogueWarp) * Cfg::kEpiStageBytes);
+      uint32_t* const stage_one = stage;
       auto bias_term = [&](unsigned col_blk, const float* bias, unsigned n) {
         uint4 t = make_uint4(0u, 0u, 0u, 0u);  // +0.0f
         const unsigned col = col_blk + (lane & 7u) * 4;
@@ -848,10 +849,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         if (tgt.tma_store) {
           const unsigned n_lim = tgt.N;
           const int act = tgt.activation;
+          // The CTA's last tile: every MMA has retired and every load has been consumed, so
+          // the stage ring is dead and each warp stages ALL its blocks there (its own slot of
+          // the partial-sum area, which only it read), fires the stores back to back and waits
+          // once.  Earlier tiles reuse the warp's 4 KB block, their waits hide behind the next
+          // tile's mainloop.
+          const bool last_tile = si + 1 == num_segments;
+          uint32_t* const wide = reinterpret_cast<uint32_t*>(
+              smem_gen + (warp - Cfg::kFirstEpilogueWarp) * (Cfg::kEpiCols / 32) * Cfg::kEpiStageBytes);
 #pragma unroll
           for (int c = 0; c < Cfg::kEpiCols / 32; ++c) {
             if (col0 + c * 32 >= n_lim) break;  // warp-uniform
-            epi_tma_stage_free(lane);
+            uint32_t* const stage = last_tile ? wide + c * (Cfg::kEpiStageBytes / 4) : stage_one;
+            if (!last_tile) epi_tma_stage_free(lane);
 #pragma unroll
             for (int qq = 0; qq < 8; ++qq) {
               const unsigned col = col0 + c * 32 + 4 * qq;
@@ -1009,7 +1019,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                 }
               }
               if (tgt.tma_store) {
-                epi_tma_stage_free(lane);
+                // the ring is dead (one tile per cluster): all blocks staged side by side in
+                // this warp's own incoming slot, stores fired back to back, one wait at the end
+                uint32_t* const stage = reinterpret_cast<uint32_t*>(smem_gen) +
+                                        (ew * (slice / 32) + c) * (Cfg::kEpiStageBytes / 4);
 #pragma unroll
                 for (int qq = 0; qq < 8; ++qq) {
                   const unsigned col = colbase + c * 32 + 4 * qq;
@@ -1069,7 +1082,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             ptx::tmem_ld_32x32(taddr + c * 32, r);
             ptx::tmem_ld_wait();
             if (tgt.tma_store) {
-              epi_tma_stage_free(lane);
+              const bool last_tile = si + 1 == num_segments;  // ring dead: stage side by side
+              uint32_t* const stage =
+                  last_tile ? reinterpret_cast<uint32_t*>(smem_gen) +
+                                  ((warp - Cfg::kFirstEpilogueWarp) * (BN / 32) + c) * (Cfg::kEpiStageBytes / 4)
+                            : stage_one;
+              if (!last_tile) epi_tma_stage_free(lane);
 #pragma unroll
               for (int qq = 0; qq < 8; ++qq) {
                 const unsigned col = col0 + c * 32 + 4 * qq;
