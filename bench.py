@@ -349,17 +349,23 @@ def profile_case(torch, pkg, dev, name):
         g4, b4 = torch.ones(768, device=dev), torch.zeros(768, device=dev)
         mm, nnops = pkg.blas.matmul, pkg.nn
 
+        w4p = [nnops.pack_qkv(*l[:6]) + tuple(l[6:]) for l in w4]
+
         def fn():
             x = x4
-            split = lambda t: nnops.permute_0213(t.view(8, 128, 12, 64))
-            for (wq, bq, wk, bk, wv, bv, wo, bo, w1, b1, w2, b2) in w4:
-                q, k, v = split(mm(x, wq, bq)), split(mm(x, wk, bk)), split(mm(x, wv, bv))
-                p = nnops.softmax(mm(q, nnops.transpose_last2(k)), scale=0.125)
-                o = nnops.permute_0213(mm(p, v)).view(8, 128, 768)
+            for (wqkv, bqkv, wo, bo, w1, b1, w2, b2) in w4p:
+                qkv = mm(x, wqkv, bqkv)
+                o = nnops.attention(qkv[:, :, :768], qkv[:, :, 768:1536], qkv[:, :, 1536:], 12, scale=0.125)
                 x = nnops.layer_norm(mm(o, wo, bo), g4, b4, 1e-5, residual=x)
                 x = nnops.layer_norm(mm(mm(x, w1, b1, activation="gelu"), w2, b2), g4, b4, 1e-5,
                                      residual=x)
             return x
+    elif name == "attention":
+        qkv = to(rng.normal(0, 1, (8, 128, 2304)).astype(np.float32))
+        fn = lambda: pkg.nn.attention(qkv[:, :, :768], qkv[:, :, 768:1536], qkv[:, :, 1536:], 12, scale=0.125)
+    elif name == "reduce_sum_cols":
+        qb = to(rng.integers(-127, 128, (4096, 4096), dtype=np.int8))
+        fn = lambda: pkg.quantization.reduce_sum(qb, False)
     else:
         raise SystemExit(f"unknown --profile-case {name}")
     for _ in range(5):
@@ -605,15 +611,31 @@ def extra_measurements(torch, pkg, dev, peaks, probes):
                                   "gbs": nbytes / (train_us * 1e-6) / 1e9,
                                   "hbm_frac": nbytes / (train_us * 1e-6) / 1e9 / peaks["hbm_gbs"]}
         if m == 256:
-            qa, qb = ops[0][0], ops[0][1]
-            f1 = lambda: pkg.quantization.reduce_sum(qa, True)
-            f2 = lambda: pkg.quantization.reduce_sum(qb, False)
-            for f, nm, nb in ((f1, "reduce_sum_rows_256x4096", m * 4096),
-                              (f2, "reduce_sum_cols_4096x4096", 4096 * 4096)):
-                for _ in range(3):
+            for nm, nb, row_flag, idx in (("reduce_sum_rows_256x4096", m * 4096, True, 0),
+                                          ("reduce_sum_cols_4096x4096", 4096 * 4096, False, 1)):
+                fs = [(lambda o=o: pkg.quantization.reduce_sum(o[idx], row_flag)) for o in ops]
+                for f in fs[:2]:
                     f()
-                _, med = time_launches(torch, f, 20, fl)
-                out[nm] = {"us": med * 1e3, "gbs": nb / (med * 1e-3) / 1e9}
+                _, med = time_launches(torch, fs[0], 20, fl)
+                tr, _ = time_graph_train(torch, fs * max(1, 16 // len(fs)))
+                out[nm] = {"us": med * 1e3, "train_us": tr, "gbs": nb / (tr * 1e-6) / 1e9,
+                           "hbm_frac": nb / (tr * 1e-6) / 1e9 / peaks["hbm_gbs"]}
+            xs = [torch.randn((m, 4096), device=dev) for _ in range(len(ops))]
+            mn, mx = torch.tensor([-4.0], device=dev), torch.tensor([4.0], device=dev)
+            tr, _ = time_graph_train(torch, [(lambda t=t: pkg.quantization.quantize_with_row_sums(
+                t, torch.uint8, mn, mx)) for t in xs])
+            out["quantize_with_row_sums_256x4096"] = {"train_us": tr}
+            # the whole quantized operator on resident operands: row sums of A + matmul (the
+            # column sums of the weight are a constant, computed once)
+            def whole(o):
+                ra = pkg.quantization.reduce_sum(o[0], True)
+                st = lib.tfccb200_qgemm_u8s8s32(
+                    torch.cuda.current_stream().cuda_stream, o[0].data_ptr(), 0, ra.data_ptr(), 0,
+                    -128, o[1].data_ptr(), 0, o[3].data_ptr(), 0, 0, o[4].data_ptr(), m * 4096, m,
+                    4096, 4096, 1, sess.status_ptr)
+                assert st == 0, st
+            tr, _ = time_graph_train(torch, [(lambda o=o: whole(o)) for o in ops])
+            out["cfg3_operator_rsA_plus_matmul"] = {"train_us": tr}
         del ops, calls
     # int8 at the headline size: u8[8192,8192] x s8[8192,8192] -> s32 (13.8 waves of pair tiles)
     n8 = 8192
@@ -1158,7 +1180,8 @@ def main():
                     help="N > 1: push C tiles to peers from the GEMM epilogue, or NCCL all-gather")
     ap.add_argument("--profile-case", default="",
                     help="run only one small configuration (gemv_M1, int8_M256, int8_M4096, "
-                         "attention_qk, ffn1) a few times and exit: the target of ncu captures")
+                         "attention_qk, ffn1, encoder_stack, attention, reduce_sum_cols) a few "
+                         "times and exit: the target of ncu captures")
     ap.add_argument("--in-flight", type=int, default=0, choices=[0, 1, 2],
                     help="N > 1, fused gather: products in flight (2 = two lanes on half the SMs "
                          "each; 0 = two from four ranks on, else one)")

@@ -748,6 +748,30 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         } else {
           if (p.bias && pcol < p.N && lane * 8 < BN) ptx::prefetch_l2(p.bias + pcol);
         }
+        // The CTA's last tile stages its results in the dead ring (see the store loops), which
+        // leaves this warp's 4 KB block free: the warp's per-column terms go there now, so that
+        // the store phase reads them from shared memory.  (Loaded one by one after the
+        // accumulation they cost about 0.12 us each, a microsecond per 32 columns.)
+        if (si + 1 == num_segments) {
+          constexpr int kWarpCols = kSplit ? Cfg::kEpiCols : BN;
+          const unsigned wcol0 = ptn * BN + col_half * Cfg::kEpiCols;
+          if constexpr (kKind == ptx::MmaKind::I8) {
+            const int32_t* rsb = p.rsB + static_cast<size_t>(p.strideRsB) * pb;
+#pragma unroll
+            for (int i = 0; i < kWarpCols / 32; ++i) {
+              const unsigned col = wcol0 + i * 32 + lane;
+              stage_one[i * 32 + lane] = col < p.N ? static_cast<uint32_t>(__ldg(rsb + col)) : 0u;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < kWarpCols / 32; ++i) {
+              const unsigned col = wcol0 + i * 32 + lane;
+              stage_one[i * 32 + lane] =
+                  (p.bias && col < p.N) ? __float_as_uint(__ldg(p.bias + col)) : 0u;
+            }
+          }
+          __syncwarp();
+        }
       }
 
       if constexpr (kSplit) {
@@ -866,7 +890,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             for (int qq = 0; qq < 8; ++qq) {
               const unsigned col = col0 + c * 32 + 4 * qq;
               float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (pbias && col < n_lim) bv = __ldg(reinterpret_cast<const float4*>(pbias + col));
+              if (last_tile) bv = *reinterpret_cast<const float4*>(stage_one + c * 32 + 4 * qq);
+              else if (pbias && col < n_lim) bv = __ldg(reinterpret_cast<const float4*>(pbias + col));
               float4 v = make_float4(sum[c * 32 + 4 * qq + 0] + bv.x, sum[c * 32 + 4 * qq + 1] + bv.y,
                                      sum[c * 32 + 4 * qq + 2] + bv.z, sum[c * 32 + 4 * qq + 3] + bv.w);
               if (act != TFCCB200_ACT_NONE) {
@@ -1025,9 +1050,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                                         (ew * (slice / 32) + c) * (Cfg::kEpiStageBytes / 4);
 #pragma unroll
                 for (int qq = 0; qq < 8; ++qq) {
-                  const unsigned col = colbase + c * 32 + 4 * qq;
-                  uint4 sb = make_uint4(0u, 0u, 0u, 0u);
-                  if (col < pN) sb = __ldg(reinterpret_cast<const uint4*>(rsB + col));
+                  const uint4 sb = *reinterpret_cast<const uint4*>(stage_one + krank * slice + c * 32 + 4 * qq);
                   epi_stage_chunk(stage, lane, qq,
                                   make_uint4(r[4 * qq] + row_term + sb.x * oa, r[4 * qq + 1] + row_term + sb.y * oa,
                                              r[4 * qq + 2] + row_term + sb.z * oa, r[4 * qq + 3] + row_term + sb.w * oa));
@@ -1092,7 +1115,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
               for (int qq = 0; qq < 8; ++qq) {
                 const unsigned col = col0 + c * 32 + 4 * qq;
                 uint4 sb = make_uint4(0u, 0u, 0u, 0u);
-                if (col < pN) sb = __ldg(reinterpret_cast<const uint4*>(rsB + col));
+                if (last_tile) sb = *reinterpret_cast<const uint4*>(stage_one + c * 32 + 4 * qq);
+                else if (col < pN) sb = __ldg(reinterpret_cast<const uint4*>(rsB + col));
                 epi_stage_chunk(stage, lane, qq,
                                 make_uint4(r[4 * qq] + row_term + sb.x * oa, r[4 * qq + 1] + row_term + sb.y * oa,
                                            r[4 * qq + 2] + row_term + sb.z * oa, r[4 * qq + 3] + row_term + sb.w * oa));
