@@ -117,6 +117,9 @@ def workload_config():
             "flop_per_step": FLOP_PER_STEP, "seed": 4}
 
 
+_PANEL_CACHE = {}
+
+
 def cpu_sgemm_panel(orc, threads, seconds_target=12.0):
     """The CPU arm's fp32 GEMM (torch's MKL sgemm on `threads` threads, set here and not
     inherited from the environment) on a bounded sample of the 8192^3 problem: a row panel
@@ -124,7 +127,10 @@ def cpu_sgemm_panel(orc, threads, seconds_target=12.0):
     shorter than that.  Returns (TFLOP/s, threads, text)."""
     threads = orc.set_cpu_threads(threads)
     rng = np.random.default_rng(4)
-    b = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    if _PANEL_CACHE.get("shape") != (K, N):
+        _PANEL_CACHE["shape"] = (K, N)
+        _PANEL_CACHE["b"] = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    b = _PANEL_CACHE["b"]
     rows = 64
     a = rng.uniform(-1, 1, (rows, K)).astype(np.float32)
     orc.blas_matmul_mkl(a, b)  # warm the thread pool

@@ -84,9 +84,23 @@ int nsplit_host_upload(const NsplitHostRank& r) {
   const unsigned rows = r.M / r.num_ranks;
   float* my_rows = r.A_ranks[r.rank] + static_cast<size_t>(r.rank) * rows * r.K;
   cudaError_t e;
-  // A rows first: the peers wait for them; B follows while the rows cross NVLink
+  // A rows first: the peers wait for them.  B follows on the copy stream (when there is one),
+  // so that it crosses PCIe while the rows cross NVLink.
   if ((e = cudaMemcpyAsync(my_rows, r.hA_rows, static_cast<size_t>(rows) * r.K * 4,
                            cudaMemcpyHostToDevice, r.stream)) != cudaSuccess)
+    return static_cast<int>(e);
+  cudaStream_t b_stream = r.stream;
+  if (r.copy_stream && r.copy_event) {
+    // the copy stream starts behind the A upload (one PCIe direction: no point in racing it)
+    if ((e = cudaEventRecord(r.copy_event, r.stream)) != cudaSuccess) return static_cast<int>(e);
+    if ((e = cudaStreamWaitEvent(r.copy_stream, r.copy_event, 0)) != cudaSuccess)
+      return static_cast<int>(e);
+    b_stream = r.copy_stream;
+  }
+  if ((e = cudaMemcpy2DAsync(r.B_shard_dev, static_cast<size_t>(r.N_shard) * 4, r.hB_shard,
+                             static_cast<size_t>(r.ldb_host) * 4,
+                             static_cast<size_t>(r.N_shard) * 4, r.K, cudaMemcpyHostToDevice,
+                             b_stream)) != cudaSuccess)
     return static_cast<int>(e);
   void* dst[8];
   unsigned n = 0;
@@ -96,11 +110,11 @@ int nsplit_host_upload(const NsplitHostRank& r) {
   void* mc = r.A_multicast ? r.A_multicast + static_cast<size_t>(r.rank) * rows * r.K : nullptr;
   int st = broadcast_bytes(r.stream, my_rows, dst, n, mc, static_cast<size_t>(rows) * r.K * 4);
   if (st != TFCCB200_OK) return st;
-  if ((e = cudaMemcpy2DAsync(r.B_shard_dev, static_cast<size_t>(r.N_shard) * 4, r.hB_shard,
-                             static_cast<size_t>(r.ldb_host) * 4,
-                             static_cast<size_t>(r.N_shard) * 4, r.K, cudaMemcpyHostToDevice,
-                             r.stream)) != cudaSuccess)
-    return static_cast<int>(e);
+  if (b_stream != r.stream) {  // the product needs B: rejoin
+    if ((e = cudaEventRecord(r.copy_event, b_stream)) != cudaSuccess) return static_cast<int>(e);
+    if ((e = cudaStreamWaitEvent(r.stream, r.copy_event, 0)) != cudaSuccess)
+      return static_cast<int>(e);
+  }
   return TFCCB200_OK;
 }
 
@@ -141,6 +155,8 @@ struct tfccb200_group {
   int dev[8] = {};
   cudaStream_t stream[8] = {};
   cudaEvent_t done[8] = {};      // "everything queued on stream[i] so far"
+  cudaStream_t copy_stream[8] = {};  // second stream per member for the B upload of the host path
+  cudaEvent_t copy_event[8] = {};
   int* status[8] = {};           // device status words
   void* workspace[8] = {};
   size_t workspace_bytes[8] = {};
@@ -242,6 +258,10 @@ int tfccb200_group_create(int ndev, const int* devices, tfccb200_group** out) {
       return fail(static_cast<int>(e));
     if ((e = cudaEventCreateWithFlags(&g->done[i], cudaEventDisableTiming)) != cudaSuccess)
       return fail(static_cast<int>(e));
+    if ((e = cudaStreamCreateWithFlags(&g->copy_stream[i], cudaStreamNonBlocking)) != cudaSuccess)
+      return fail(static_cast<int>(e));
+    if ((e = cudaEventCreateWithFlags(&g->copy_event[i], cudaEventDisableTiming)) != cudaSuccess)
+      return fail(static_cast<int>(e));
     if ((e = cudaMalloc(reinterpret_cast<void**>(&g->status[i]), sizeof(int))) != cudaSuccess)
       return fail(static_cast<int>(e));
     if ((e = cudaMemset(g->status[i], 0, sizeof(int))) != cudaSuccess)
@@ -269,6 +289,11 @@ int tfccb200_group_destroy(tfccb200_group* g) {
     if (g->workspace[i]) cudaFree(g->workspace[i]);
     if (g->status[i]) cudaFree(g->status[i]);
     if (g->done[i]) cudaEventDestroy(g->done[i]);
+    if (g->copy_event[i]) cudaEventDestroy(g->copy_event[i]);
+    if (g->copy_stream[i]) {
+      cudaStreamSynchronize(g->copy_stream[i]);
+      cudaStreamDestroy(g->copy_stream[i]);
+    }
     if (g->stream[i]) cudaStreamDestroy(g->stream[i]);
   }
   delete g;
@@ -364,6 +389,8 @@ int tfccb200_group_sgemm_nsplit_host(tfccb200_group* g, const float* hA, const f
   for (unsigned i = 0; i < G; ++i) {
     r[i] = {};
     r[i].stream = g->stream[i];
+    r[i].copy_stream = g->copy_stream[i];
+    r[i].copy_event = g->copy_event[i];
     r[i].hA_rows = hA + static_cast<size_t>(i) * rows * K;
     r[i].hB_shard = hB + static_cast<size_t>(i) * ns;
     r[i].ldb_host = N;
@@ -422,6 +449,20 @@ int tfccb200_sgemm_nsplit_host(void* stream, const float* hA_rows, const float* 
   int st = nsplit_host_check(r);
   if (st != TFCCB200_OK) return st;
   if (num_ranks > 1 && !barrier) return TFCCB200_EINVAL;
+  struct Side {  // second stream for the B upload; destroyed after everything has been waited for
+    cudaStream_t s = nullptr;
+    cudaEvent_t e = nullptr;
+    ~Side() {
+      if (s) cudaStreamSynchronize(s);  // nothing may still read the caller's host buffer
+      if (e) cudaEventDestroy(e);
+      if (s) cudaStreamDestroy(s);
+    }
+  } side;
+  if (cudaStreamCreateWithFlags(&side.s, cudaStreamNonBlocking) == cudaSuccess &&
+      cudaEventCreateWithFlags(&side.e, cudaEventDisableTiming) == cudaSuccess) {
+    r.copy_stream = side.s;
+    r.copy_event = side.e;
+  }
   auto sync_ranks = [&]() { return num_ranks > 1 ? barrier(barrier_ctx, stream) : 0; };
   // an early return must not leave copies from / into the caller's host buffers in flight
   struct Join {

@@ -118,6 +118,8 @@ int reduce_sum(cudaStream_t stream, const T* src, unsigned batch, unsigned rows,
 // One rank's view of an N-split product whose operands start in host memory.
 struct NsplitHostRank {
   cudaStream_t stream;
+  cudaStream_t copy_stream;  // optional: the B upload runs here, beside the exchange of A rows
+  cudaEvent_t copy_event;    // with copy_stream: event used to fork and rejoin
   const float* hA_rows;    // host: this rank's M / num_ranks rows of A
   const float* hB_shard;   // host: first element of this rank's column shard of B
   unsigned ldb_host;       // row pitch of hB_shard in elements

@@ -386,7 +386,7 @@ reduce_cols_cluster_kernel(const T* __restrict__ src, unsigned rows, unsigned co
 #pragma unroll
   for (unsigned v = 0; v < V; ++v) acc[v] = 0;
   if (active) {
-    constexpr unsigned U = 8;
+    constexpr unsigned U = 16;  // one round of memory latency for 512 rows per CTA
     unsigned r = r0 + rlane;
     for (; r + (U - 1) * 32 < r1; r += U * 32) {
       uint4 w[U];
