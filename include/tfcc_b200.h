@@ -68,7 +68,7 @@ extern "C" {
 /* ---- kernel paths (for tests and benchmarks; AUTO is what TFCC uses) ----- */
 #define TFCCB200_PATH_AUTO 0
 #define TFCCB200_PATH_SIMT 1    /* CUDA-core tiled kernel, any shape / alignment          */
-#define TFCCB200_PATH_SKINNY 2  /* M <= 8 streaming kernel, HBM-bound                      */
+#define TFCCB200_PATH_SKINNY 2  /* streaming kernel for few rows (M <= 32; AUTO: M <= 16)   */
 #define TFCCB200_PATH_UMMA 3    /* tcgen05 + TMEM + TMA, one CTA per tile                  */
 #define TFCCB200_PATH_UMMA2 4   /* tcgen05 cta_group::2, a pair of CTAs per 256-row tile    */
 
@@ -116,8 +116,8 @@ TFCCB200_API int tfccb200_sgemm_ex(void* stream, const float* A, unsigned stride
                       unsigned N, unsigned K, unsigned batch, int precision_mode, int path,
                       void* workspace, size_t workspace_bytes, int* device_status);
 
-/* Scratch bytes tfccb200_sgemm wants for this problem on the current device.  The M <= 8
- * streaming kernel and the bf16 mode cannot run without theirs; the fp32 tensor-core kernel
+/* Scratch bytes tfccb200_sgemm wants for this problem on the current device.  The few-row
+ * streaming kernel (M <= 16) and the bf16 mode cannot run without theirs; the fp32 tensor-core kernel
  * runs without but uses its share (partial tiles of a ragged last wave) when given. */
 TFCCB200_API size_t tfccb200_sgemm_workspace(unsigned M, unsigned N, unsigned K, unsigned batch,
                                 int precision_mode);

@@ -102,7 +102,7 @@ def test_config2_attention_batches(pkg, orc):
     assert orc.normwise_rel_error(o, orc.blas_matmul(p, v)) < TOL_FP32
 
 
-@pytest.mark.parametrize("m", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 8, 12, 16, 27, 32])
 def test_skinny_decode_shapes(pkg, orc, m):
     rng = np.random.default_rng(50 + m)
     w = rng.normal(0, 0.02, (4096, 16384)).astype(np.float32)
@@ -112,6 +112,19 @@ def test_skinny_decode_shapes(pkg, orc, m):
     for path in ("skinny", "auto"):
         got = run(pkg, x, w, bias, path=path)
         assert orc.normwise_rel_error(got, truth) < TOL_FP32
+
+
+def test_streaming_kernel_takes_config1(pkg, orc):
+    """Config 1 (32 x 512 x 2048) through the streaming kernel, which can serve up to 32 rows
+    (the planner sends more than 16 rows to the tensor cores): fp32 FMA in k order, within the
+    fp32 tolerance like every other path."""
+    rng = np.random.default_rng(0)
+    a = rng.uniform(-1, 1, (32, 512)).astype(np.float32)
+    b = rng.normal(0, 0.02, (512, 2048)).astype(np.float32)
+    bias = rng.normal(0, 1, 2048).astype(np.float32)
+    for path in ("skinny", "auto"):
+        got = run(pkg, a, b, bias, path=path)
+        assert orc.normwise_rel_error(got, orc.blas_matmul(a, b, bias)) < TOL_FP32
 
 
 def test_skinny_ragged_and_batched(pkg, orc):

@@ -141,7 +141,10 @@ simt_gemm_kernel(const TA* __restrict__ A, const TB* __restrict__ B, TAcc* __res
 // --------------------------------------------------------------------------
 constexpr int kSkinnyThreads = 256;
 constexpr int kSkinnyCols = kSkinnyThreads * 4;
-constexpr int kSkinnyMaxSlice = 512;  // rows of W per CTA (bounds the x slice in smem)
+// rows of W per CTA: bounds the x slice in shared memory to 32 KB
+__host__ __device__ constexpr int skinny_max_slice(int mp) { return mp <= 16 ? 512 : 256; }
+// weight rows in flight per thread (two batches of U 128-bit loads live at once)
+__host__ __device__ constexpr int skinny_unroll(int mp) { return mp <= 16 ? 8 : 4; }
 
 // acc[m] (4 columns as two packed pairs) += x[m] * w, with the packed fp32x2 FMA of sm_100.
 template <int MP>
@@ -170,7 +173,7 @@ __device__ __forceinline__ void skinny_row_fma(float2 (&acc)[MP][2], const float
 }
 
 // CTAs of the kernel that fit one SM (register-bound); the grid is planned as one full wave.
-constexpr int skinny_resident(int mp) { return mp == 1 ? 3 : 2; }
+constexpr int skinny_resident(int mp) { return mp == 1 ? 3 : (mp <= 8 ? 2 : 1); }
 
 template <int MP>
 __global__ void __launch_bounds__(kSkinnyThreads, skinny_resident(MP))
@@ -178,7 +181,7 @@ skinny_partial_kernel(const float* __restrict__ X, const float* __restrict__ W,
                       float* __restrict__ part, unsigned M, unsigned N, unsigned K,
                       unsigned slice_rows, unsigned long long strideX, unsigned long long strideW,
                       unsigned kslices) {
-  __shared__ __align__(16) float xs[kSkinnyMaxSlice * MP];
+  __shared__ __align__(16) float xs[skinny_max_slice(MP) * MP];
   pdl_wait();  // launched to overlap the previous kernel's tail: no global access before this
   const unsigned b = blockIdx.z;
   X += strideX * b;
@@ -191,7 +194,7 @@ skinny_partial_kernel(const float* __restrict__ X, const float* __restrict__ W,
   const float4* wp =
       reinterpret_cast<const float4*>(W + static_cast<size_t>(k_begin) * N + (active ? col : 0));
   const size_t pitch = N / 4;
-  constexpr int U = 8;
+  constexpr int U = skinny_unroll(MP);
 
   // first batch of weight rows is requested before the x slice is staged
   float4 w[U];
@@ -281,14 +284,17 @@ skinny_reduce_kernel(const float* __restrict__ part, const float* __restrict__ b
 void skinny_plan(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count,
                  unsigned* kslices, unsigned* slice_rows) {
   const unsigned col_blocks = (N + kSkinnyCols - 1) / kSkinnyCols;
-  const int mp = M == 1 ? 1 : (M == 2 ? 2 : (M <= 4 ? 4 : 8));
+  const int mp = M == 1 ? 1 : (M == 2 ? 2 : (M <= 4 ? 4 : (M <= 8 ? 8 : (M <= 16 ? 16 : 32))));
   const unsigned long long want = static_cast<unsigned long long>(skinny_resident(mp)) * sm_count;
   unsigned long long ks = want / (static_cast<unsigned long long>(col_blocks) * batch);
+  // beyond 8 rows the partial sums (one M x N slab per slice, written and read once) would
+  // outweigh the weights themselves unless the slices stay at least 2 M rows long
+  if (M > 8 && ks > K / (2ull * M)) ks = K / (2ull * M);
   if (ks < 1) ks = 1;
   if (ks > K) ks = K;
   unsigned rows = static_cast<unsigned>((K + ks - 1) / ks);
   rows = (rows + 7) / 8 * 8;  // whole batches of 8 rows, no ragged tail inside a slice
-  if (rows > kSkinnyMaxSlice) rows = kSkinnyMaxSlice;
+  if (rows > static_cast<unsigned>(skinny_max_slice(mp))) rows = skinny_max_slice(mp);
   *slice_rows = rows;
   *kslices = (K + rows - 1) / rows;
 }
@@ -521,7 +527,7 @@ int simt_qgemm(const QgemmArgs& a) {
 }
 
 bool skinny_sgemm_supported(const SgemmArgs& a) {
-  if (a.M > 8 || a.N % 4 != 0) return false;
+  if (a.M > 32 || a.N % 4 != 0) return false;
   if ((reinterpret_cast<uintptr_t>(a.B) & 15u) || (reinterpret_cast<uintptr_t>(a.C) & 15u))
     return false;
   if (a.bias && (reinterpret_cast<uintptr_t>(a.bias) & 15u)) return false;
@@ -556,7 +562,9 @@ int skinny_sgemm(const SgemmArgs& a) {
   if (a.M == 1) TFCCB200_SKINNY(1);
   else if (a.M == 2) TFCCB200_SKINNY(2);
   else if (a.M <= 4) TFCCB200_SKINNY(4);
-  else TFCCB200_SKINNY(8);
+  else if (a.M <= 8) TFCCB200_SKINNY(8);
+  else if (a.M <= 16) TFCCB200_SKINNY(16);
+  else TFCCB200_SKINNY(32);
 #undef TFCCB200_SKINNY
   cudaError_t e = launch_status();
   if (e != cudaSuccess) return static_cast<int>(e);
