@@ -209,7 +209,7 @@ def test_host_buffer_entry_point(pkg, orc):
 
 @pytest.mark.parametrize("m", [2049, 2056, 2057, 3000])
 def test_host_buffer_pipelined_path_ragged_rows(pkg, orc, m):
-    """Large single products go up in 1024-row blocks while earlier blocks are multiplied and
+    """Large single products go up in row blocks (512 rows) while earlier blocks are multiplied and
     downloaded.  A row count that leaves eight rows or fewer for the last block must not send
     that block to the M <= 8 kernel (which would need scratch of another size): it is merged
     into the block before it.  Sampled rows, including the very last ones, against float64."""

@@ -664,7 +664,7 @@ int tfccb200_sgemm_host(void* stream, const float* hA, unsigned strideA, const f
   // B goes up first; A then goes up in row blocks on a copy stream while the block before it
   // is multiplied on the caller's stream and the block before that comes down on a third
   // stream.  (Pinned host buffers are needed for the copies to really overlap.)
-  constexpr unsigned kRowBlock = 1024;
+  constexpr unsigned kRowBlock = 512;  // short last block: little is left to do after the last upload
   static const bool pipeline = [] {
     const char* v = std::getenv("TFCCB200_HOST_PIPELINE");
     return !(v && v[0] == '0');
