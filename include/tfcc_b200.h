@@ -431,18 +431,25 @@ typedef int (*tfccb200_barrier_fn)(void* ctx, void* stream);
  * returns to host memory -- the data::set -> matmul -> data::get round trip
  * (tfcc/cuda/interfaces/tfcc_cudadatainterface.cu:62-90) spread over num_ranks GPUs so that the
  * job's host traffic crosses num_ranks PCIe links once instead of every link carrying all of it:
- *   1. rank r uploads rows [r*M/G, (r+1)*M/G) of A (hA_rows) into its own A buffer and stores
- *      them on into the same rows of every peer's A buffer over NVLink, and uploads its column
- *      shard of B (hB_shard, row pitch ldb_host elements) into B_shard_dev;
+ *   1. rank r uploads rows [r*M/G, (r+1)*M/G) of A (hA_rows) into its own A staging and stores
+ *      them on into every peer's A staging over NVLink, and uploads its column shard of B
+ *      (hB_shard, row pitch ldb_host elements) into B_shard_dev;
  *   2. barrier; tfccb200_sgemm_nsplit_push; barrier;
  *   3. rank r downloads rows [r*M/G, (r+1)*M/G) of the assembled C into hC_rows
  *      ([M/G, num_ranks*N_shard]).
+ * The three run as a pipeline over row blocks of about 512 rows per rank (at most 16 blocks;
+ * TFCCB200_HOST_BLOCKS in the environment overrides the count): step p multiplies block p of
+ * every rank while later blocks are still being uploaded and exchanged and earlier ones are
+ * being downloaded, on three side streams that the calling thread keeps per device; `barrier`
+ * is called blocks + 1 times, always on `stream`.
  * Per rank 4 (M K / G + K N_shard) bytes go up and 4 M N / G come down.  A_ranks / C_ranks are
- * every rank's device buffers mapped into this process ([M,K] and [M, num_ranks*N_shard]);
- * A_multicast / C_multicast their NVLink multicast aliases or NULL.  M % num_ranks == 0,
- * K % 4 == 0, N_shard % 4 == 0.  Host buffers should be pinned.  Synchronises `stream` before
- * returning; *device_status is left for the caller to read.  `barrier` may be NULL when
- * num_ranks == 1.  No counterpart in the reference.
+ * every rank's device staging buffers mapped into this process ([M,K] and
+ * [M, num_ranks*N_shard] floats; the call orders rows inside them block by block, so their
+ * content afterwards is not the row-major A or C); A_multicast / C_multicast their NVLink
+ * multicast aliases or NULL.  M % num_ranks == 0, K % 4 == 0, N_shard % 4 == 0.  Host buffers
+ * should be pinned.  Every rank must make the call with the same shapes.  Synchronises `stream`
+ * and the side streams before returning, also on an error; *device_status is left for the
+ * caller to read.  `barrier` may be NULL when num_ranks == 1.  No counterpart in the reference.
  */
 TFCCB200_API int tfccb200_sgemm_nsplit_host(void* stream, const float* hA_rows,
                                             const float* hB_shard, unsigned ldb_host,

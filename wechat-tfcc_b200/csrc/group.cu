@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -80,58 +81,159 @@ int broadcast_bytes(cudaStream_t stream, const void* src, void* const* dst, unsi
 }  // namespace
 
 // ---- one rank's share of an N-split product whose operands start in host memory ----------
-int nsplit_host_upload(const NsplitHostRank& r) {
-  const unsigned rows = r.M / r.num_ranks;
-  float* my_rows = r.A_ranks[r.rank] + static_cast<size_t>(r.rank) * rows * r.K;
+//
+// The rank's M/G rows are cut into `blocks` row blocks of Rb rows.  Step p multiplies row block p
+// of EVERY rank, so the staging buffers are laid out step by step: block p of rank q lives at
+// staging rows [p*G*Rb + q*Rb, +Rb) of A and of C, which makes the operand of step p one
+// contiguous [G*Rb, K] matrix and this rank's result rows of step p one contiguous piece.  Four
+// streams per rank:
+//   up:    A block 0, the B shard, A blocks 1.. from host memory
+//   xch:   block p stored on into every peer's staging once it has arrived
+//   main:  barrier, product of step p (tiles pushed into every rank's C staging), barrier, ...
+//   down:  this rank's rows of step p to host memory once the barrier after the product says
+//          that every rank's tiles have landed
+// so that the uploads of later blocks and the downloads of earlier ones run under the products.
+cudaError_t HostLanes::create() {
   cudaError_t e;
-  // A rows first: the peers wait for them.  B follows on the copy stream (when there is one),
-  // so that it crosses PCIe while the rows cross NVLink.
-  if ((e = cudaMemcpyAsync(my_rows, r.hA_rows, static_cast<size_t>(rows) * r.K * 4,
-                           cudaMemcpyHostToDevice, r.stream)) != cudaSuccess)
-    return static_cast<int>(e);
-  cudaStream_t b_stream = r.stream;
-  if (r.copy_stream && r.copy_event) {
-    // the copy stream starts behind the A upload (one PCIe direction: no point in racing it)
-    if ((e = cudaEventRecord(r.copy_event, r.stream)) != cudaSuccess) return static_cast<int>(e);
-    if ((e = cudaStreamWaitEvent(r.copy_stream, r.copy_event, 0)) != cudaSuccess)
-      return static_cast<int>(e);
-    b_stream = r.copy_stream;
+  for (cudaStream_t* s : {&up, &xch, &down})
+    if ((e = cudaStreamCreateWithFlags(s, cudaStreamNonBlocking)) != cudaSuccess) return e;
+  for (cudaEvent_t* ev : {&start, &b_up, &tail})
+    if ((e = cudaEventCreateWithFlags(ev, cudaEventDisableTiming)) != cudaSuccess) return e;
+  for (unsigned p = 0; p < kMaxHostBlocks; ++p)
+    for (cudaEvent_t* ev : {&a_up[p], &a_sent[p], &c_whole[p]})
+      if ((e = cudaEventCreateWithFlags(ev, cudaEventDisableTiming)) != cudaSuccess) return e;
+  return cudaSuccess;
+}
+
+void HostLanes::join() {
+  for (cudaStream_t s : {up, xch, down})
+    if (s) cudaStreamSynchronize(s);
+}
+
+void HostLanes::destroy() {
+  join();
+  for (cudaEvent_t* ev : {&start, &b_up, &tail})
+    if (*ev) cudaEventDestroy(*ev), *ev = nullptr;
+  for (unsigned p = 0; p < kMaxHostBlocks; ++p)
+    for (cudaEvent_t* ev : {&a_up[p], &a_sent[p], &c_whole[p]})
+      if (*ev) cudaEventDestroy(*ev), *ev = nullptr;
+  for (cudaStream_t* s : {&up, &xch, &down})
+    if (*s) cudaStreamDestroy(*s), *s = nullptr;
+}
+
+namespace {
+
+#define HOST_TRY(expr)                                        \
+  do {                                                        \
+    cudaError_t e_ = (expr);                                  \
+    if (e_ != cudaSuccess) return static_cast<int>(e_);       \
+  } while (0)
+
+struct HostBlocks {
+  unsigned G, rows, rb, step_rows;
+  size_t n_total;
+};
+
+HostBlocks host_blocks(const NsplitHostRank& r, unsigned blocks) {
+  HostBlocks h;
+  h.G = r.num_ranks;
+  h.rows = r.M / r.num_ranks;
+  h.rb = h.rows / blocks;
+  h.step_rows = h.rb * h.G;
+  h.n_total = static_cast<size_t>(r.N_shard) * r.num_ranks;
+  return h;
+}
+
+int host_download(const NsplitHostRank& r, const HostBlocks& h, unsigned p) {
+  HostLanes& L = *r.lanes;
+  HOST_TRY(cudaEventRecord(L.c_whole[p], r.stream));
+  HOST_TRY(cudaStreamWaitEvent(L.down, L.c_whole[p], 0));
+  const float* src = r.C_ranks[r.rank] +
+                     (static_cast<size_t>(p) * h.step_rows + static_cast<size_t>(r.rank) * h.rb) * h.n_total;
+  HOST_TRY(cudaMemcpyAsync(r.hC_rows + static_cast<size_t>(p) * h.rb * h.n_total, src,
+                           static_cast<size_t>(h.rb) * h.n_total * 4, cudaMemcpyDeviceToHost, L.down));
+  return TFCCB200_OK;
+}
+
+}  // namespace
+
+// Row blocks of about 512 rows per rank (a step of G*512 rows by N/G columns fills the chip
+// once); at most kMaxHostBlocks, and a count that divides the rank's rows.
+unsigned nsplit_host_blocks(const NsplitHostRank& r) {
+  const unsigned rows = r.M / r.num_ranks;
+  unsigned want = std::min(kMaxHostBlocks, std::max(1u, rows / 512));
+  if (const char* env = std::getenv("TFCCB200_HOST_BLOCKS")) {
+    const int v = std::atoi(env);
+    if (v >= 1) want = std::min<unsigned>(kMaxHostBlocks, static_cast<unsigned>(v));
   }
-  if ((e = cudaMemcpy2DAsync(r.B_shard_dev, static_cast<size_t>(r.N_shard) * 4, r.hB_shard,
-                             static_cast<size_t>(r.ldb_host) * 4,
-                             static_cast<size_t>(r.N_shard) * 4, r.K, cudaMemcpyHostToDevice,
-                             b_stream)) != cudaSuccess)
-    return static_cast<int>(e);
-  void* dst[8];
-  unsigned n = 0;
-  for (unsigned d = 0; d < r.num_ranks; ++d)
-    if (d != r.rank && r.A_ranks[d])
-      dst[n++] = r.A_ranks[d] + static_cast<size_t>(r.rank) * rows * r.K;
-  void* mc = r.A_multicast ? r.A_multicast + static_cast<size_t>(r.rank) * rows * r.K : nullptr;
-  int st = broadcast_bytes(r.stream, my_rows, dst, n, mc, static_cast<size_t>(rows) * r.K * 4);
-  if (st != TFCCB200_OK) return st;
-  if (b_stream != r.stream) {  // the product needs B: rejoin
-    if ((e = cudaEventRecord(r.copy_event, b_stream)) != cudaSuccess) return static_cast<int>(e);
-    if ((e = cudaStreamWaitEvent(r.stream, r.copy_event, 0)) != cudaSuccess)
-      return static_cast<int>(e);
+  while (want > 1 && rows % want != 0) --want;
+  return want;
+}
+
+int nsplit_host_start(const NsplitHostRank& r, unsigned blocks) {
+  const HostBlocks h = host_blocks(r, blocks);
+  HostLanes& L = *r.lanes;
+  // the side streams begin behind whatever the caller queued on the product stream
+  HOST_TRY(cudaEventRecord(L.start, r.stream));
+  for (cudaStream_t s : {L.up, L.xch, L.down}) HOST_TRY(cudaStreamWaitEvent(s, L.start, 0));
+  const size_t block_elems = static_cast<size_t>(h.rb) * r.K;
+  for (unsigned p = 0; p < blocks; ++p) {
+    const size_t at = (static_cast<size_t>(p) * h.step_rows + static_cast<size_t>(r.rank) * h.rb) * r.K;
+    float* mine = r.A_ranks[r.rank] + at;
+    HOST_TRY(cudaMemcpyAsync(mine, r.hA_rows + static_cast<size_t>(p) * block_elems, block_elems * 4,
+                             cudaMemcpyHostToDevice, L.up));
+    HOST_TRY(cudaEventRecord(L.a_up[p], L.up));
+    if (p == 0) {  // B behind the first block: the first exchange runs while it crosses PCIe
+      HOST_TRY(cudaMemcpy2DAsync(r.B_shard_dev, static_cast<size_t>(r.N_shard) * 4, r.hB_shard,
+                                 static_cast<size_t>(r.ldb_host) * 4,
+                                 static_cast<size_t>(r.N_shard) * 4, r.K, cudaMemcpyHostToDevice,
+                                 L.up));
+      HOST_TRY(cudaEventRecord(L.b_up, L.up));
+    }
+    HOST_TRY(cudaStreamWaitEvent(L.xch, L.a_up[p], 0));
+    void* dst[8];
+    unsigned n = 0;
+    for (unsigned d = 0; d < r.num_ranks; ++d)
+      if (d != r.rank && r.A_ranks[d]) dst[n++] = r.A_ranks[d] + at;
+    void* mc = r.A_multicast ? r.A_multicast + at : nullptr;
+    int st = broadcast_bytes(L.xch, mine, dst, n, mc, block_elems * 4);
+    if (st != TFCCB200_OK) return st;
+    HOST_TRY(cudaEventRecord(L.a_sent[p], L.xch));
   }
   return TFCCB200_OK;
 }
 
-int nsplit_host_multiply(const NsplitHostRank& r) {
-  return tfccb200_sgemm_nsplit_push(r.stream, r.A_ranks[r.rank], r.B_shard_dev, r.C_ranks,
-                                    r.num_ranks, r.rank, nullptr, r.M, r.N_shard, r.K,
-                                    r.precision, r.C_multicast, r.workspace, r.workspace_bytes,
-                                    r.status);
+// Before barrier p (p < blocks): this rank's block p must have reached every peer.
+int nsplit_host_before_barrier(const NsplitHostRank& r, unsigned blocks, unsigned p) {
+  if (p >= blocks) return TFCCB200_OK;
+  HOST_TRY(cudaStreamWaitEvent(r.stream, r.lanes->a_sent[p], 0));
+  return TFCCB200_OK;
 }
 
-int nsplit_host_download(const NsplitHostRank& r) {
-  const unsigned rows = r.M / r.num_ranks;
-  const size_t n_total = static_cast<size_t>(r.N_shard) * r.num_ranks;
-  const float* my_rows = r.C_ranks[r.rank] + static_cast<size_t>(r.rank) * rows * n_total;
-  cudaError_t e = cudaMemcpyAsync(r.hC_rows, my_rows, static_cast<size_t>(rows) * n_total * 4,
-                                  cudaMemcpyDeviceToHost, r.stream);
-  return e == cudaSuccess ? TFCCB200_OK : static_cast<int>(e);
+// Behind barrier p: every rank's tiles of step p-1 have landed (download them) and every
+// rank's A block p has arrived (multiply it).  Barrier 0 also says that the peers have finished
+// reading the C staging of their previous call.  p == blocks closes the call.
+int nsplit_host_after_barrier(const NsplitHostRank& r, unsigned blocks, unsigned p) {
+  const HostBlocks h = host_blocks(r, blocks);
+  HostLanes& L = *r.lanes;
+  if (p > 0) {
+    int st = host_download(r, h, p - 1);
+    if (st != TFCCB200_OK) return st;
+  }
+  if (p == blocks) {
+    HOST_TRY(cudaEventRecord(L.tail, L.down));
+    HOST_TRY(cudaStreamWaitEvent(r.stream, L.tail, 0));
+    return TFCCB200_OK;
+  }
+  if (p == 0) HOST_TRY(cudaStreamWaitEvent(r.stream, L.b_up, 0));
+  const size_t a_at = static_cast<size_t>(p) * h.step_rows * r.K;
+  const size_t c_at = static_cast<size_t>(p) * h.step_rows * h.n_total;
+  float* c_step[8];
+  for (unsigned d = 0; d < r.num_ranks; ++d) c_step[d] = r.C_ranks[d] ? r.C_ranks[d] + c_at : nullptr;
+  return tfccb200_sgemm_nsplit_push(r.stream, r.A_ranks[r.rank] + a_at, r.B_shard_dev, c_step,
+                                    r.num_ranks, r.rank, nullptr, h.step_rows, r.N_shard, r.K,
+                                    r.precision, r.C_multicast ? r.C_multicast + c_at : nullptr,
+                                    r.workspace, r.workspace_bytes, r.status);
 }
 
 int nsplit_host_check(const NsplitHostRank& r) {
@@ -155,8 +257,7 @@ struct tfccb200_group {
   int dev[8] = {};
   cudaStream_t stream[8] = {};
   cudaEvent_t done[8] = {};      // "everything queued on stream[i] so far"
-  cudaStream_t copy_stream[8] = {};  // second stream per member for the B upload of the host path
-  cudaEvent_t copy_event[8] = {};
+  HostLanes lanes[8];            // side streams of the host-buffer path
   int* status[8] = {};           // device status words
   void* workspace[8] = {};
   size_t workspace_bytes[8] = {};
@@ -218,6 +319,38 @@ int group_finish(tfccb200_group* g) {
   return result;
 }
 
+// The calling thread's side streams on the current device, made on first use and kept until
+// the thread ends (a per-call set would cost more than a small product).
+constexpr int kLaneDevices = 16;
+HostLanes* thread_lanes(cudaError_t* err) {
+  struct PerThread {
+    HostLanes lanes[kLaneDevices];
+    bool made[kLaneDevices] = {};
+    ~PerThread() {
+      int saved = -1;
+      if (cudaGetDevice(&saved) != cudaSuccess) return;  // the runtime is already gone
+      for (int d = 0; d < kLaneDevices; ++d)
+        if (made[d] && cudaSetDevice(d) == cudaSuccess) lanes[d].destroy();
+      cudaSetDevice(saved);
+    }
+  };
+  static thread_local PerThread t;
+  int dev = -1;
+  if ((*err = cudaGetDevice(&dev)) != cudaSuccess) return nullptr;
+  if (dev < 0 || dev >= kLaneDevices) {
+    *err = cudaErrorInvalidDevice;
+    return nullptr;
+  }
+  if (!t.made[dev]) {
+    if ((*err = t.lanes[dev].create()) != cudaSuccess) {
+      t.lanes[dev].destroy();
+      return nullptr;
+    }
+    t.made[dev] = true;
+  }
+  return &t.lanes[dev];
+}
+
 }  // namespace
 
 extern "C" {
@@ -258,10 +391,7 @@ int tfccb200_group_create(int ndev, const int* devices, tfccb200_group** out) {
       return fail(static_cast<int>(e));
     if ((e = cudaEventCreateWithFlags(&g->done[i], cudaEventDisableTiming)) != cudaSuccess)
       return fail(static_cast<int>(e));
-    if ((e = cudaStreamCreateWithFlags(&g->copy_stream[i], cudaStreamNonBlocking)) != cudaSuccess)
-      return fail(static_cast<int>(e));
-    if ((e = cudaEventCreateWithFlags(&g->copy_event[i], cudaEventDisableTiming)) != cudaSuccess)
-      return fail(static_cast<int>(e));
+    if ((e = g->lanes[i].create()) != cudaSuccess) return fail(static_cast<int>(e));
     if ((e = cudaMalloc(reinterpret_cast<void**>(&g->status[i]), sizeof(int))) != cudaSuccess)
       return fail(static_cast<int>(e));
     if ((e = cudaMemset(g->status[i], 0, sizeof(int))) != cudaSuccess)
@@ -289,11 +419,7 @@ int tfccb200_group_destroy(tfccb200_group* g) {
     if (g->workspace[i]) cudaFree(g->workspace[i]);
     if (g->status[i]) cudaFree(g->status[i]);
     if (g->done[i]) cudaEventDestroy(g->done[i]);
-    if (g->copy_event[i]) cudaEventDestroy(g->copy_event[i]);
-    if (g->copy_stream[i]) {
-      cudaStreamSynchronize(g->copy_stream[i]);
-      cudaStreamDestroy(g->copy_stream[i]);
-    }
+    g->lanes[i].destroy();
     if (g->stream[i]) cudaStreamDestroy(g->stream[i]);
   }
   delete g;
@@ -389,8 +515,7 @@ int tfccb200_group_sgemm_nsplit_host(tfccb200_group* g, const float* hA, const f
   for (unsigned i = 0; i < G; ++i) {
     r[i] = {};
     r[i].stream = g->stream[i];
-    r[i].copy_stream = g->copy_stream[i];
-    r[i].copy_event = g->copy_event[i];
+    r[i].lanes = &g->lanes[i];
     r[i].hA_rows = hA + static_cast<size_t>(i) * rows * K;
     r[i].hB_shard = hB + static_cast<size_t>(i) * ns;
     r[i].ldb_host = N;
@@ -407,22 +532,34 @@ int tfccb200_group_sgemm_nsplit_host(tfccb200_group* g, const float* hA, const f
     int st = nsplit_host_check(r[i]);
     if (st != TFCCB200_OK) return st;
   }
-  if ((e = group_barrier(g)) != cudaSuccess) return static_cast<int>(e);
-  for (unsigned i = 0; i < G; ++i) {
-    if ((e = cudaSetDevice(g->dev[i])) != cudaSuccess) return static_cast<int>(e);
-    int st = nsplit_host_upload(r[i]);
+  // whatever happens, no copy from / into the caller's host buffers outlives the call
+  struct JoinAll {
+    tfccb200_group* g;
+    ~JoinAll() {
+      for (int i = 0; i < g->ndev; ++i) {
+        if (cudaSetDevice(g->dev[i]) != cudaSuccess) continue;
+        g->lanes[i].join();
+        cudaStreamSynchronize(g->stream[i]);
+      }
+    }
+  } join_all{g};
+  const unsigned blocks = nsplit_host_blocks(r[0]);
+  auto each = [&](auto&& phase) -> int {
+    for (unsigned i = 0; i < G; ++i) {
+      cudaError_t ce = cudaSetDevice(g->dev[i]);
+      if (ce != cudaSuccess) return static_cast<int>(ce);
+      int st = phase(r[i]);
+      if (st != TFCCB200_OK) return st;
+    }
+    return TFCCB200_OK;
+  };
+  int st = each([&](const NsplitHostRank& x) { return nsplit_host_start(x, blocks); });
+  if (st != TFCCB200_OK) return st;
+  for (unsigned p = 0; p <= blocks; ++p) {
+    st = each([&](const NsplitHostRank& x) { return nsplit_host_before_barrier(x, blocks, p); });
     if (st != TFCCB200_OK) return st;
-  }
-  if ((e = group_barrier(g)) != cudaSuccess) return static_cast<int>(e);  // every A is whole
-  for (unsigned i = 0; i < G; ++i) {
-    if ((e = cudaSetDevice(g->dev[i])) != cudaSuccess) return static_cast<int>(e);
-    int st = nsplit_host_multiply(r[i]);
-    if (st != TFCCB200_OK) return st;
-  }
-  if ((e = group_barrier(g)) != cudaSuccess) return static_cast<int>(e);  // every C is whole
-  for (unsigned i = 0; i < G; ++i) {
-    if ((e = cudaSetDevice(g->dev[i])) != cudaSuccess) return static_cast<int>(e);
-    int st = nsplit_host_download(r[i]);
+    if ((e = group_barrier(g)) != cudaSuccess) return static_cast<int>(e);
+    st = each([&](const NsplitHostRank& x) { return nsplit_host_after_barrier(x, blocks, p); });
     if (st != TFCCB200_OK) return st;
   }
   return group_finish(g);
@@ -446,36 +583,30 @@ int tfccb200_sgemm_nsplit_host(void* stream, const float* hA_rows, const float* 
   r.precision = precision_mode;
   r.workspace = workspace; r.workspace_bytes = workspace ? workspace_bytes : 0;
   r.status = device_status;
+  if (num_ranks > 1 && !barrier) return TFCCB200_EINVAL;
   int st = nsplit_host_check(r);
   if (st != TFCCB200_OK) return st;
-  if (num_ranks > 1 && !barrier) return TFCCB200_EINVAL;
-  struct Side {  // second stream for the B upload; destroyed after everything has been waited for
-    cudaStream_t s = nullptr;
-    cudaEvent_t e = nullptr;
-    ~Side() {
-      if (s) cudaStreamSynchronize(s);  // nothing may still read the caller's host buffer
-      if (e) cudaEventDestroy(e);
-      if (s) cudaStreamDestroy(s);
-    }
-  } side;
-  if (cudaStreamCreateWithFlags(&side.s, cudaStreamNonBlocking) == cudaSuccess &&
-      cudaEventCreateWithFlags(&side.e, cudaEventDisableTiming) == cudaSuccess) {
-    r.copy_stream = side.s;
-    r.copy_event = side.e;
-  }
-  auto sync_ranks = [&]() { return num_ranks > 1 ? barrier(barrier_ctx, stream) : 0; };
+  cudaError_t e;
+  HostLanes* lanes = thread_lanes(&e);
+  if (!lanes) return static_cast<int>(e);
+  r.lanes = lanes;
   // an early return must not leave copies from / into the caller's host buffers in flight
   struct Join {
+    HostLanes* l;
     cudaStream_t s;
-    ~Join() { cudaStreamSynchronize(s); }
-  } join{r.stream};
-  if ((st = sync_ranks()) != 0) return st;  // the peers have finished with the previous A and C
-  if ((st = nsplit_host_upload(r)) != TFCCB200_OK) return st;
-  if ((st = sync_ranks()) != 0) return st;  // every rank's A is whole
-  if ((st = nsplit_host_multiply(r)) != TFCCB200_OK) return st;
-  if ((st = sync_ranks()) != 0) return st;  // every rank's C is whole
-  if ((st = nsplit_host_download(r)) != TFCCB200_OK) return st;
-  cudaError_t e = cudaStreamSynchronize(r.stream);
+    ~Join() {
+      l->join();
+      cudaStreamSynchronize(s);
+    }
+  } join{lanes, r.stream};
+  const unsigned blocks = nsplit_host_blocks(r);
+  if ((st = nsplit_host_start(r, blocks)) != TFCCB200_OK) return st;
+  for (unsigned p = 0; p <= blocks; ++p) {
+    if ((st = nsplit_host_before_barrier(r, blocks, p)) != TFCCB200_OK) return st;
+    if (num_ranks > 1 && (st = barrier(barrier_ctx, stream)) != 0) return st;
+    if ((st = nsplit_host_after_barrier(r, blocks, p)) != TFCCB200_OK) return st;
+  }
+  e = cudaStreamSynchronize(r.stream);
   return e == cudaSuccess ? TFCCB200_OK : static_cast<int>(e);
 }
 

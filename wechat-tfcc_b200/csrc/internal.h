@@ -116,18 +116,33 @@ int reduce_sum(cudaStream_t stream, const T* src, unsigned batch, unsigned rows,
 
 // ---- multi-GPU shim (group.cu) ----
 // One rank's view of an N-split product whose operands start in host memory.
+// Side streams and events of one rank of the host-buffer N split: uploads, the exchange of A rows
+// and downloads each run on a stream of their own beside the stream of the products.
+constexpr unsigned kMaxHostBlocks = 16;
+struct HostLanes {
+  cudaStream_t up = nullptr, xch = nullptr, down = nullptr;
+  cudaEvent_t start = nullptr;  // everything queued on the product stream before the call
+  cudaEvent_t b_up = nullptr;   // the B shard is on the device
+  cudaEvent_t tail = nullptr;   // the last download has finished
+  cudaEvent_t a_up[kMaxHostBlocks] = {};     // row block p of A is on this device
+  cudaEvent_t a_sent[kMaxHostBlocks] = {};   // ... and stored into every peer
+  cudaEvent_t c_whole[kMaxHostBlocks] = {};  // row block p of C is whole on this device
+  cudaError_t create();  // on the current device
+  void join();           // waits for the three streams
+  void destroy();
+};
+
 struct NsplitHostRank {
   cudaStream_t stream;
-  cudaStream_t copy_stream;  // optional: the B upload runs here, beside the exchange of A rows
-  cudaEvent_t copy_event;    // with copy_stream: event used to fork and rejoin
+  HostLanes* lanes;
   const float* hA_rows;    // host: this rank's M / num_ranks rows of A
   const float* hB_shard;   // host: first element of this rank's column shard of B
   unsigned ldb_host;       // row pitch of hB_shard in elements
   float* hC_rows;          // host: this rank's M / num_ranks rows of the full-width C
-  float* const* A_ranks;   // device: every rank's [M,K] buffer (peers may be NULL = not written)
+  float* const* A_ranks;   // device: every rank's [M,K] staging (peers may be NULL = not written)
   float* A_multicast;      // NVLink multicast alias of the A buffers, or nullptr
   float* B_shard_dev;      // device: [K, N_shard]
-  float* const* C_ranks;   // device: every rank's [M, N_shard * num_ranks]
+  float* const* C_ranks;   // device: every rank's [M, N_shard * num_ranks] staging
   float* C_multicast;
   unsigned num_ranks, rank;
   unsigned M, N_shard, K;
@@ -136,10 +151,15 @@ struct NsplitHostRank {
   size_t workspace_bytes;
   int* status;
 };
+// The call runs in nsplit_host_blocks() row blocks; a caller drives all its ranks through
+//   start(r);  for p in 0..blocks: { if p < blocks: before_barrier(r, p);  BARRIER;
+//   after_barrier(r, p); }  finish(r)
+// where BARRIER orders the ranks' product streams.
 int nsplit_host_check(const NsplitHostRank& r);
-int nsplit_host_upload(const NsplitHostRank& r);    // rows of A up and on to the peers, B shard up
-int nsplit_host_multiply(const NsplitHostRank& r);  // product, tiles stored into every rank's C
-int nsplit_host_download(const NsplitHostRank& r);  // this rank's rows of C down
+unsigned nsplit_host_blocks(const NsplitHostRank& r);
+int nsplit_host_start(const NsplitHostRank& r, unsigned blocks);
+int nsplit_host_before_barrier(const NsplitHostRank& r, unsigned blocks, unsigned p);
+int nsplit_host_after_barrier(const NsplitHostRank& r, unsigned blocks, unsigned p);
 
 // ---- fused attention (attention.cu) ----
 struct AttentionArgs {
