@@ -1058,11 +1058,20 @@ def run_ours(args):
         h2d = 4 * (rows * K + K * ns)
         d2h = 4 * rows * N
         # the rows this rank brought down, against the float64 product of the host operands
+        # (every column: this rank's own shard and the tiles the peers stored over NVLink)
         idx = np.random.default_rng(rank).choice(rows, size=8, replace=False)
-        bfull_cols = hb.numpy().astype(np.float64)
-        truth_shard = ha.numpy()[idx].astype(np.float64) @ bfull_cols
-        got_shard = hc.numpy()[idx][:, rank * ns:(rank + 1) * ns].astype(np.float64)
-        e2e_err = float(np.linalg.norm(got_shard - truth_shard) / np.linalg.norm(truth_shard))
+        if world > 1:
+            shards = [torch.empty_like(b) for _ in range(world)]
+            dist.all_gather(shards, b)
+            bfull_cols = torch.cat(shards, dim=1).cpu().numpy().astype(np.float64)
+            del shards
+            got_rows = hc.numpy()[idx].astype(np.float64)
+        else:
+            bfull_cols = hb.numpy().astype(np.float64)
+            got_rows = hc.numpy()[idx][:, rank * ns:(rank + 1) * ns].astype(np.float64)
+        truth_rows = ha.numpy()[idx].astype(np.float64) @ bfull_cols
+        e2e_err = float(np.linalg.norm(got_rows - truth_rows) / np.linalg.norm(truth_rows))
+        del bfull_cols
     else:
         h2d = 4 * (M * K + K * ns)
         d2h = 4 * M * N

@@ -127,6 +127,46 @@ def test_streaming_kernel_takes_config1(pkg, orc):
         assert orc.normwise_rel_error(got, orc.blas_matmul(a, b, bias)) < TOL_FP32
 
 
+@pytest.mark.parametrize("m,k,n", [(32, 512, 2048), (1, 64, 4), (7, 100, 260), (32, 2048, 512),
+                                   (17, 2044, 300), (8, 8, 8), (25, 33, 1028), (9, 777, 1024)])
+def test_cluster_kernel_for_few_rows_and_small_b(pkg, orc, m, k, n):
+    """One launch on CUDA cores, K cut into ways and cluster slices that are added through
+    distributed shared memory (config 1 is the first shape): fp32 FMA, fp32 tolerance, with and
+    without bias, with the GELU epilogue, and the same bits on every run (fixed order of the
+    slices)."""
+    rng = np.random.default_rng(m * 31 + k + n)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.normal(0, 0.05, (k, n)).astype(np.float32)
+    bias = rng.normal(0, 1, n).astype(np.float32)
+    got = run(pkg, a, b, path="cluster_simt")
+    assert orc.normwise_rel_error(got, orc.blas_matmul(a, b)) < TOL_FP32
+    got_b = run(pkg, a, b, bias, path="cluster_simt")
+    assert orc.normwise_rel_error(got_b, orc.blas_matmul(a, b, bias)) < TOL_FP32
+    assert np.array_equal(got_b, run(pkg, a, b, bias, path="cluster_simt"))
+    got_g = run(pkg, a, b, bias, path="cluster_simt", activation="gelu")
+    want_g = orc.gelu_accurate(orc.blas_matmul(a, b, bias).astype(np.float32))
+    assert orc.normwise_rel_error(got_g, want_g) < TOL_FP32
+
+
+def test_cluster_kernel_batched_and_planner(pkg, orc):
+    rng = np.random.default_rng(77)
+    x = rng.normal(0, 1, (3, 5, 333)).astype(np.float32)
+    w = rng.normal(0, 1, (3, 333, 1100)).astype(np.float32)
+    got = run(pkg, x, w, path="cluster_simt")
+    assert orc.normwise_rel_error(got, orc.blas_matmul(x, w)) < TOL_FP32
+    # rank-3 A against one B: the batch becomes rows (here 4 x 6 = 24 rows)
+    x2 = rng.normal(0, 1, (4, 6, 256)).astype(np.float32)
+    w2 = rng.normal(0, 1, (256, 512)).astype(np.float32)
+    assert orc.normwise_rel_error(run(pkg, x2, w2, path="cluster_simt"), orc.blas_matmul(x2, w2)) < TOL_FP32
+    # config 1 goes there by itself; a long K or a large B does not
+    assert pkg.lib.tfccb200_sgemm_path(32, 2048, 512, 1, 0, 0, 0) == 5
+    assert pkg.lib.tfccb200_sgemm_path(32, 2048, 4096, 1, 0, 0, 0) != 5
+    assert pkg.lib.tfccb200_sgemm_path(8, 16384, 1024, 1, 0, 0, 0) != 5
+    with pytest.raises(pkg.exceptions.TFCCError):
+        run(pkg, rng.normal(0, 1, (4, 4096)).astype(np.float32),
+            rng.normal(0, 1, (4096, 64)).astype(np.float32), path="cluster_simt")
+
+
 def test_skinny_ragged_and_batched(pkg, orc):
     rng = np.random.default_rng(9)
     x = rng.normal(0, 1, (3, 5, 333)).astype(np.float32)

@@ -59,6 +59,8 @@ def test_path_choice_is_host_only(pkg):
     lib = pkg.lib
     assert lib.tfccb200_sgemm_path(1, 16384, 4096, 1, 0, 0, 0) == 2      # skinny
     assert lib.tfccb200_sgemm_path(8192, 8192, 8192, 1, 0, 0, 0) == 4   # CTA pairs
+    assert lib.tfccb200_sgemm_path(32, 2048, 512, 1, 0, 0, 0) == 5       # config 1: few rows, small B
+    assert lib.tfccb200_sgemm_path(16, 16384, 4096, 1, 0, 0, 0) == 2     # few rows, large B: streaming
     assert lib.tfccb200_sgemm_path(37, 41, 53, 1, 0, 0, 0) == 1         # ragged -> CUDA cores
     assert lib.tfccb200_sgemm_path(0, 4, 4, 1, 0, 0, 0) == -1
     # rank-3 x rank-2 folds the batch into rows: [8,128,768] x [768,3072]

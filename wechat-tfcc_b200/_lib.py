@@ -120,7 +120,7 @@ EXPORTED_SYMBOLS = (
     "tfccb200_interleave_panels_f32", "tfccb200_sgemm_host", "tfccb200_qgemm_u8s8s32_host",
 )
 
-PATHS = {"auto": 0, "simt": 1, "skinny": 2, "umma": 3, "umma2": 4}
+PATHS = {"auto": 0, "simt": 1, "skinny": 2, "umma": 3, "umma2": 4, "cluster_simt": 5}
 PRECISIONS = {"fp32": 0, "tf32": 1, "bf16": 2}
 ACTIVATIONS = {None: 0, "none": 0, "gelu": 1}
 

@@ -23,7 +23,7 @@ INCLUDE = HERE.parent / "include"
 LIB = HERE / "libtfcc_b200.so"
 OBJ_DIR = HERE / "build"
 SOURCES = ["capi.cu", "umma_launch.cu", "simt_kernels.cu", "quantize_kernels.cu",
-           "nn_kernels.cu", "group.cu", "attention.cu"]
+           "nn_kernels.cu", "group.cu", "attention.cu", "cluster_simt.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

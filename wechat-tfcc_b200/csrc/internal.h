@@ -100,6 +100,8 @@ int simt_sgemm(const SgemmArgs& a);
 bool skinny_sgemm_supported(const SgemmArgs& a);
 size_t skinny_sgemm_workspace(unsigned M, unsigned N, unsigned K, unsigned batch, int sm_count);
 int skinny_sgemm(const SgemmArgs& a);
+bool cluster_simt_sgemm_supported(const SgemmArgs& a);  // cluster_simt.cu: M <= 32, K <= 2048
+int cluster_simt_sgemm(const SgemmArgs& a);
 int skinny_sgemm_static(cudaStream_t stream, const float* A, const float* B, float* C,
                         const float* bias, unsigned M, unsigned N, unsigned K);
 size_t skinny_sgemm_static_capacity();
