@@ -139,21 +139,33 @@ cluster_simt_kernel(const float* __restrict__ X, const float* __restrict__ W,
                 : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   cluster.sync();
+  float4 sum[kItems];
 #pragma unroll
   for (int j = 0; j < kItems; ++j) {
     const unsigned i = crank * share + t + j * kLanes * kWays;
-    if (i >= (crank + 1) * share) break;
+    sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < (crank + 1) * share) {
+      float4 v[kMaxCluster];
+#pragma unroll
+      for (int p = 0; p < kMaxCluster; ++p)
+        if (static_cast<unsigned>(p) < ks) v[p] = cluster.map_shared_rank(mine, p)[i];
+#pragma unroll
+      for (int p = 0; p < kMaxCluster; ++p)
+        if (static_cast<unsigned>(p) < ks) {
+          sum[j].x += v[p].x; sum[j].y += v[p].y; sum[j].z += v[p].z; sum[j].w += v[p].w;
+        }
+    }
+  }
+  // this CTA has finished reading its peers' partial sums: say so now, store, and leave once
+  // every peer has said the same (nobody exits while its shared memory may still be read)
+  cluster.barrier_arrive();
+#pragma unroll
+  for (int j = 0; j < kItems; ++j) {
+    const unsigned i = crank * share + t + j * kLanes * kWays;
     const unsigned m = i / kLanes, l = i % kLanes;
-    float4 v[kMaxCluster];
-#pragma unroll
-    for (int p = 0; p < kMaxCluster; ++p)
-      if (static_cast<unsigned>(p) < ks) v[p] = cluster.map_shared_rank(mine, p)[i];
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int p = 0; p < kMaxCluster; ++p)
-      if (static_cast<unsigned>(p) < ks) { s.x += v[p].x; s.y += v[p].y; s.z += v[p].z; s.w += v[p].w; }
     const unsigned c = blockIdx.x * kCols + l * 4;
-    if (m0 + m < M && c < N) {
+    if (i < (crank + 1) * share && m0 + m < M && c < N) {
+      float4 s = sum[j];
       s.x += bv[j].x; s.y += bv[j].y; s.z += bv[j].z; s.w += bv[j].w;
       if (activation != TFCCB200_ACT_NONE) {
         s.x = apply_activation(s.x, activation); s.y = apply_activation(s.y, activation);
@@ -162,7 +174,7 @@ cluster_simt_kernel(const float* __restrict__ X, const float* __restrict__ W,
       *reinterpret_cast<float4*>(Y + static_cast<size_t>(m0 + m) * N + c) = s;
     }
   }
-  cluster.sync();  // nobody leaves while a peer may still read its partial sums
+  cluster.barrier_wait();
 }
 
 struct Plan {
