@@ -97,8 +97,8 @@ TFCCB200_API int tfccb200_version(void);
  * Non-finite inputs: NaN propagates as NaN on every path.  On the tensor-core paths an
  * infinite element makes its whole output row (column) NaN where IEEE arithmetic would give
  * +-inf, because the fp32 product is rebuilt from head and tail parts and inf has no tail
- * (inf - inf); the CUDA-core paths (M <= 8, unaligned shapes) follow IEEE.  The reference's
- * own tests feed finite values only.
+ * (inf - inf); the CUDA-core paths (few rows: M <= 16, or M <= 32 against a small B; unaligned
+ * shapes) follow IEEE.  The reference's own tests feed finite values only.
  *
  * workspace / workspace_bytes: scratch in device memory of at least
  * tfccb200_sgemm_workspace() bytes (may be NULL when that returns 0).
