@@ -819,7 +819,7 @@ def nsplit_breakdown(torch, dist, pkg, dev, fused, a, b, world, rank, steps=20):
     of `steps` launches, maximum over ranks: the product of this rank's shard alone; the same
     kernel storing its tiles into every rank's C but with no barrier; the barrier alone; the
     kernel storing only into its own C followed by the barrier; and the step as timed, one
-    product at a time and (when planned) two in flight."""
+    product at a time and (when planned) several in flight."""
     out = {}
 
     def slowest(ms):
@@ -874,7 +874,8 @@ def nsplit_breakdown(torch, dist, pkg, dev, fused, a, b, world, rank, steps=20):
     out["step_one_at_a_time_us"] = train(lambda: one.matmul(a, b))
     if fused.get("two") is not None:
         two = fused["two"]
-        out["step_two_in_flight_us"] = train(lambda: two.matmul(a, b, wait=False), finish=two.join)
+        out["lanes"] = two.in_flight
+        out["step_lanes_in_flight_us"] = train(lambda: two.matmul(a, b, wait=False), finish=two.join)
         out["half_chip_product_us"] = train(lambda: push(own_only, None, two._max_ctas))
     out["local_product_again_us"] = train(lambda: pkg.blas.matmul(a, b))
     out["exposed_us"] = out["step_one_at_a_time_us"] - out["local_product_us"]
@@ -912,16 +913,17 @@ def run_ours(args):
     if world > 1:
         del b_full
     staging = c_out = None
-    fused = {}   # "one": one product at a time; "two": two in flight on half the SMs each
+    fused = {}   # "one": one product at a time; "two": 2..4 in flight on half the SMs each
     mode = "single GPU"
     in_flight = 1
     if world > 1:
         if args.gather == "fused":
             try:
                 fused["one"] = pkg.parallel.FusedNSplit(M, N, dev)
-                if args.in_flight == 2 or (args.in_flight == 0 and world >= 4):
-                    fused["two"] = pkg.parallel.FusedNSplit(M, N, dev, in_flight=2)
-                    in_flight = 2
+                want = args.in_flight if args.in_flight else (2 if world >= 4 else 1)
+                if want >= 2:
+                    fused["two"] = pkg.parallel.FusedNSplit(M, N, dev, in_flight=want)
+                    in_flight = want
             except Exception as exc:  # peer mapping unavailable: NCCL gather of our local product
                 print(f"[bench] fused N-split unavailable ({exc!r}); using NCCL all-gather",
                       file=sys.stderr)
@@ -934,14 +936,14 @@ def run_ours(args):
         if fused:
             mode = (f"N-split x{world}: B column shards; C tiles pushed to every rank from the "
                     f"GEMM epilogue over NVLink ({fused['one'].how}) + barrier"
-                    + ("; two steps in flight, each on half of the SMs, so that the last tiles of "
-                       "one step cross NVLink while the next step multiplies" if in_flight == 2 else ""))
+                    + (f"; {in_flight} steps in flight, each on half of the SMs, so that the last tiles "
+                       "of one step cross NVLink while the next step multiplies" if in_flight >= 2 else ""))
         else:
             staging = torch.empty((world, M, ns), dtype=torch.float32, device=dev)
             c_out = torch.empty((M, N), dtype=torch.float32, device=dev)
             mode = f"N-split x{world}: B column shards, NCCL all-gather of C + interleave kernel"
     sess = pkg.session.get_session(dev)
-    timed = fused.get("two") if in_flight == 2 else fused.get("one")
+    timed = fused.get("two") if in_flight >= 2 else fused.get("one")
 
     def step():
         if world == 1:
@@ -951,7 +953,7 @@ def run_ours(args):
         return pkg.parallel.nsplit_matmul(a, b, staging=staging, out=c_out)
 
     def finish():
-        if in_flight == 2:
+        if in_flight >= 2:
             timed.join()
 
     def barrier():
@@ -1197,9 +1199,9 @@ def main():
                     help="run only one small configuration (gemv_M1, int8_M256, int8_M4096, "
                          "attention_qk, ffn1, encoder_stack, attention, reduce_sum_cols) a few "
                          "times and exit: the target of ncu captures")
-    ap.add_argument("--in-flight", type=int, default=0, choices=[0, 1, 2],
-                    help="N > 1, fused gather: products in flight (2 = two lanes on half the SMs "
-                         "each; 0 = two from four ranks on, else one)")
+    ap.add_argument("--in-flight", type=int, default=0, choices=[0, 1, 2, 3, 4],
+                    help="N > 1, fused gather: products in flight (2..4 lanes on half the SMs each; "
+                         "0 = two from four ranks on, else one)")
     ap.add_argument("--no-probe", action="store_true",
                     help="skip the library probes of the tensor-core peaks")
     ap.add_argument("--size", type=int, default=8192,

@@ -438,7 +438,7 @@ typedef int (*tfccb200_barrier_fn)(void* ctx, void* stream);
  *   2. barrier; tfccb200_sgemm_nsplit_push; barrier;
  *   3. rank r downloads rows [r*M/G, (r+1)*M/G) of the assembled C into hC_rows
  *      ([M/G, num_ranks*N_shard]).
- * The three run as a pipeline over row blocks of about 512 rows per rank (at most 16 blocks;
+ * The three run as a pipeline over row blocks of about 256 rows per rank (at most 16 blocks;
  * TFCCB200_HOST_BLOCKS in the environment overrides the count): step p multiplies block p of
  * every rank while later blocks are still being uploaded and exchanged and earlier ones are
  * being downloaded, on three side streams that the calling thread keeps per device; `barrier`

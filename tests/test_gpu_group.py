@@ -90,12 +90,12 @@ def test_group_int8_nsplit_bit_exact(pkg, orc, devices):
     grp.close()
 
 
-@pytest.mark.parametrize("rows", [128, 1100, 1536])
+@pytest.mark.parametrize("rows", [128, 550, 1536])
 @pytest.mark.parametrize("devices", _members())
 def test_group_host_buffers_round_trip(pkg, orc, devices, rows):
     """Host buffers in, host buffer out.  ``rows`` per member: one row block (128), two blocks of
-    550 and three of 512 -- with several blocks the uploads, the exchange of A rows, the products
-    and the downloads of different blocks overlap on four streams per member."""
+    275 (550) and six of 256 (1536) -- with several blocks the uploads, the exchange of A rows,
+    the products and the downloads of different blocks overlap on four streams per member."""
     g = len(devices)
     rng = np.random.default_rng(33 + rows)
     m, k, n = rows * g, 260, 136 * g
