@@ -108,7 +108,7 @@ class FusedNSplit:
     SMs.  The last tiles of one product are then pushed while the other product is still
     multiplying, which hides the burst of NVLink traffic at the end of a product (every GPU
     finishes its last tiles at the same moment and every GPU receives from all the others).
-    ``in_flight=3`` (or 4) adds lanes without making the products narrower: two products
+    ``in_flight=3`` and more add lanes without making the products narrower: two products
     multiply side by side and the CTAs of a third take over the SMs of whichever finishes,
     while that one's last tiles cross NVLink and its barrier runs -- no half of the chip waits
     for a barrier.
@@ -123,8 +123,8 @@ class FusedNSplit:
         self.device = torch.device(device)
         if n_total % self.world != 0:
             raise exceptions.InvalidArgumentError("N must divide evenly over the ranks")
-        if in_flight not in (1, 2, 3, 4):
-            raise exceptions.InvalidArgumentError("in_flight is 1 to 4")
+        if in_flight not in range(1, 9):
+            raise exceptions.InvalidArgumentError("in_flight is 1 to 8")
         if dtype not in (torch.float32, torch.int32):
             raise exceptions.InvalidArgumentError("C is float32 (matmul) or int32 (qmatmul)")
         self.m, self.n_total, self.ns = m, n_total, n_total // self.world
