@@ -111,7 +111,8 @@ class FusedNSplit:
     ``in_flight=3`` and more add lanes without making the products narrower: two products
     multiply side by side and the CTAs of a third take over the SMs of whichever finishes,
     while that one's last tiles cross NVLink and its barrier runs -- no half of the chip waits
-    for a barrier.
+    for a barrier.  Measured on eight GPUs (8192^3): 1358 / 1533 / 1674 / 1757 TFLOP/s with one
+    to four lanes, 1440 with six.
     Use ``matmul(..., wait=False)`` and ``join()`` to get the overlap.
     """
 
