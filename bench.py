@@ -920,7 +920,7 @@ def run_ours(args):
         if args.gather == "fused":
             try:
                 fused["one"] = pkg.parallel.FusedNSplit(M, N, dev)
-                want = args.in_flight if args.in_flight else (4 if world >= 8 else (2 if world >= 4 else 1))
+                want = args.in_flight if args.in_flight else (4 if world >= 8 else 2)
                 if want >= 2:
                     fused["two"] = pkg.parallel.FusedNSplit(M, N, dev, in_flight=want)
                     in_flight = want
@@ -1201,7 +1201,7 @@ def main():
                          "times and exit: the target of ncu captures")
     ap.add_argument("--in-flight", type=int, default=0, choices=list(range(9)),
                     help="N > 1, fused gather: products in flight (2..8 lanes on half the SMs each; "
-                         "0 = four on eight ranks, two on four, else one)")
+                         "0 = four on eight ranks, else two)")
     ap.add_argument("--no-probe", action="store_true",
                     help="skip the library probes of the tensor-core peaks")
     ap.add_argument("--size", type=int, default=8192,
