@@ -338,6 +338,10 @@ def profile_case(torch, pkg, dev, name):
         ra, rb = pkg.quantization.reduce_sum(qa, True), pkg.quantization.reduce_sum(qb, False)
         f = lambda v: torch.tensor([v], dtype=torch.float32)
         fn = lambda: pkg.quantization.matmul(qa, ra, f(-128.0), f(127.0), qb, rb, f(-128.0), f(127.0))
+    elif name == "cfg1":
+        x = to(rng.uniform(-1, 1, (32, 512)).astype(np.float32))
+        w = to(rng.normal(0, 0.02, (512, 2048)).astype(np.float32))
+        fn = lambda: pkg.blas.matmul(x, w)
     elif name == "attention_qk":
         q = to(rng.normal(0, 1, (96, 128, 64)).astype(np.float32))
         kt = to(rng.normal(0, 1, (96, 64, 128)).astype(np.float32))
@@ -1196,7 +1200,7 @@ def main():
     ap.add_argument("--gather", choices=["fused", "nccl"], default="fused",
                     help="N > 1: push C tiles to peers from the GEMM epilogue, or NCCL all-gather")
     ap.add_argument("--profile-case", default="",
-                    help="run only one small configuration (gemv_M1, int8_M256, int8_M4096, "
+                    help="run only one small configuration (cfg1, gemv_M1, int8_M256, int8_M4096, "
                          "attention_qk, ffn1, encoder_stack, attention, reduce_sum_cols) a few "
                          "times and exit: the target of ncu captures")
     ap.add_argument("--in-flight", type=int, default=0, choices=list(range(9)),
