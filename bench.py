@@ -566,6 +566,17 @@ def extra_measurements(torch, pkg, dev, peaks, probes):
     out["cfg4_encoder_stack"]["matmul_only_ms_operator_by_operator"] = mm_us / 1e3
     out["cfg4_encoder_stack"]["matmul_tflops_operator_by_operator"] = flop4 / (mm_us * 1e-6) / 1e12
     out["cfg4_encoder_stack"]["fused_attention_us_per_layer"] = att_us / 4
+
+    # the sixteen dense layers of the fused form alone (packed Q/K/V, output projection, FFN1
+    # with GELU, FFN2), on operands of the shapes they see in the stack
+    def dense_only():
+        for (wqkv, bqkv, wo, bo, w1, b1, w2, b2) in w4p:
+            mm(x4, wqkv, bqkv); mm(x4, wo, bo); mm(x4, w1, b1, activation="gelu"); mm(f4, w2, b2)
+
+    dense_us, _ = time_graph_train(torch, [dense_only])
+    dense_flop = 4 * 2.0 * (b4 * s4) * d_model * (3 * d_model + d_model + 3072 + 3072)
+    out["cfg4_encoder_stack"]["dense_layers_only_ms"] = dense_us / 1e3
+    out["cfg4_encoder_stack"]["dense_layers_only_tflops"] = dense_flop / (dense_us * 1e-6) / 1e12
     del w4p
     del w4
     # cfg5 skinny sweep
