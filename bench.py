@@ -782,6 +782,41 @@ def multi_gpu_extras(torch, dist, pkg, dev, world, rank, peaks):
             "us_per_step": ms * 1e3, "tops_whole_job": ops / (ms * 1e-3) / 1e12,
             "vs_ungathered_product": ms / (out["int8_4096_column_shards"]["us_per_step"] * 1e-3),
             "how": fused_q.how}
+        # the other kind of store (plain peer stores are the default for the int32 result)
+        fused_qm = None
+        try:
+            fused_qm = pkg.parallel.FusedNSplit(m, n, dev, dtype=torch.int32, multicast=True)
+        except Exception:
+            pass
+        okm = torch.tensor([1.0 if (fused_qm is not None and fused_qm.buffers[0][0][2] is not None)
+                            else 0.0], device=dev)
+        dist.all_reduce(okm, op=dist.ReduceOp.MIN)
+        if float(okm.item()) == 1.0:
+            msm = timed(lambda: fused_qm.qmatmul(qa, ra, -128, qb, rb, 0), iters=40)
+            out["int8_4096_column_shards_fused_gather"]["multicast_stores_us_per_step"] = msm * 1e3
+        del fused_qm
+        # two products in flight: the stores of one cross NVLink while the next multiplies
+        fused_q2 = None
+        try:
+            fused_q2 = pkg.parallel.FusedNSplit(m, n, dev, dtype=torch.int32, in_flight=2)
+        except Exception:
+            pass
+        ok2 = torch.tensor([1.0 if fused_q2 is not None else 0.0], device=dev)
+        dist.all_reduce(ok2, op=dist.ReduceOp.MIN)
+        if float(ok2.item()) == 1.0:
+            def train2():
+                for _ in range(8):
+                    fused_q2.qmatmul(qa, ra, -128, qb, rb, 0, wait=False)
+                fused_q2.join()
+            ms2 = timed(train2, iters=5) / 8
+            cq2 = fused_q2.qmatmul(qa, ra, -128, qb, rb, 0)
+            dist.barrier()
+            torch.cuda.synchronize()
+            out["int8_4096_column_shards_fused_gather"]["two_in_flight_us_per_step"] = ms2 * 1e3
+            out["int8_4096_column_shards_fused_gather"]["two_in_flight_equals_one"] = bool(
+                torch.equal(cq2, fused_q.qmatmul(qa, ra, -128, qb, rb, 0)))
+            dist.barrier()
+            torch.cuda.synchronize()
     # exactness of the assembled matrices against the int64 product, on sampled rows
     gathered()
     torch.cuda.synchronize()
