@@ -641,6 +641,16 @@ def extra_measurements(torch, pkg, dev, peaks, probes):
                 tr, _ = time_graph_train(torch, fs * max(1, 16 // len(fs)))
                 out[nm] = {"us": med * 1e3, "train_us": tr, "gbs": nb / (tr * 1e-6) / 1e9,
                            "hbm_frac": nb / (tr * 1e-6) / 1e9 / peaks["hbm_gbs"]}
+            # the same two kernels on an operand large enough for bandwidth to be the bound
+            # (256 MiB, twice the L2): what they reach once launch and latency are amortised
+            big = torch.randint(-127, 128, (16384, 16384), dtype=torch.int8, device=dev)
+            for nm, row_flag in (("reduce_sum_rows_16384x16384", True), ("reduce_sum_cols_16384x16384", False)):
+                f = lambda: pkg.quantization.reduce_sum(big, row_flag)
+                f()
+                tr, _ = time_graph_train(torch, [f] * 8)
+                out[nm] = {"train_us": tr, "gbs": big.numel() / (tr * 1e-6) / 1e9,
+                           "hbm_frac": big.numel() / (tr * 1e-6) / 1e9 / peaks["hbm_gbs"]}
+            del big
             xs = [torch.randn((m, 4096), device=dev) for _ in range(len(ops))]
             mn, mx = torch.tensor([-4.0], device=dev), torch.tensor([4.0], device=dev)
             tr, _ = time_graph_train(torch, [(lambda t=t: pkg.quantization.quantize_with_row_sums(

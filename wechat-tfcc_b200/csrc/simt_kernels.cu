@@ -392,17 +392,32 @@ reduce_cols_cluster_kernel(const T* __restrict__ src, unsigned rows, unsigned co
 #pragma unroll
   for (unsigned v = 0; v < V; ++v) acc[v] = 0;
   if (active) {
-    constexpr unsigned U = 16;  // one round of memory latency for 512 rows per CTA
+    constexpr unsigned U = 8;  // two batches in flight: one round of latency for 512 rows per CTA
     unsigned r = r0 + rlane;
-    for (; r + (U - 1) * 32 < r1; r += U * 32) {
+    // full batches of U rows per thread, the next batch requested before this one is added
+    // (a slab of more than 512 rows would otherwise pay one round of latency per batch)
+    if (r + (U - 1) * 32 < r1) {
       uint4 w[U];
 #pragma unroll
       for (unsigned u = 0; u < U; ++u) w[u] = __ldcs(p + static_cast<size_t>(r + u * 32) * pitch);
+      for (;;) {
+        const unsigned rn = r + U * 32;
+        const bool more = rn + (U - 1) * 32 < r1;
+        uint4 nx[U];
+        if (more) {
 #pragma unroll
-      for (unsigned u = 0; u < U; ++u) {
-        const T* e = reinterpret_cast<const T*>(&w[u]);
+          for (unsigned u = 0; u < U; ++u) nx[u] = __ldcs(p + static_cast<size_t>(rn + u * 32) * pitch);
+        }
 #pragma unroll
-        for (unsigned v = 0; v < V; ++v) acc[v] += static_cast<int32_t>(e[v]);
+        for (unsigned u = 0; u < U; ++u) {
+          const T* e = reinterpret_cast<const T*>(&w[u]);
+#pragma unroll
+          for (unsigned v = 0; v < V; ++v) acc[v] += static_cast<int32_t>(e[v]);
+        }
+        r = rn;
+        if (!more) break;
+#pragma unroll
+        for (unsigned u = 0; u < U; ++u) w[u] = nx[u];
       }
     }
     for (; r < r1; r += 32) {
