@@ -167,7 +167,8 @@ def test_reduce_sum_all_types(pkg, orc, dtype):
     info = np.iinfo(dtype)
     d = dev_of()
     for shape in ((257, 515), (3, 64, 4096), (2, 2, 33, 17), (1, 1), (4096, 4096), (256, 4096),
-                  (5, 1000, 48), (70, 16400), (3, 9, 2064), (1037, 640)):
+                  (5, 1000, 48), (70, 16400), (3, 9, 2064), (1037, 640), (600, 10240),
+                  (2, 300, 5120)):
         a = rng.integers(info.min, info.max + 1, shape).astype(dtype)
         t = torch.from_numpy(a).to(d)
         for row in (True, False):

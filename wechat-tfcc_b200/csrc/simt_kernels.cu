@@ -365,13 +365,17 @@ reduce_rows_kernel(const T* __restrict__ src, unsigned total_rows, unsigned cols
 // which adds them and writes the sums.  Needs cols % V == 0 and a 16-byte aligned base.
 constexpr int kColsCluster = 8;
 
-template <class T>
+// LANES threads share a row segment of LANES x 16 bytes: 8 (a 128-byte line; most CTAs for a
+// small operand) or 32 (512 contiguous bytes per row, kinder to DRAM pages, when the operand is
+// wide enough to still fill the chip).
+template <class T, int LANES>
 __global__ void __launch_bounds__(256)
 reduce_cols_cluster_kernel(const T* __restrict__ src, unsigned rows, unsigned cols,
                            int32_t* __restrict__ dst) {
   constexpr unsigned V = 16 / sizeof(T);
-  constexpr unsigned CW = 8 * V;  // columns per CTA
-  __shared__ int32_t part[32][CW + 4];
+  constexpr unsigned CW = LANES * V;  // columns per CTA
+  constexpr unsigned RL = 256 / LANES;  // rows per pass
+  __shared__ int32_t part[RL][CW + 4];
   __shared__ int32_t gather[kColsCluster][CW];
   uint32_t rank;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
@@ -379,7 +383,7 @@ reduce_cols_cluster_kernel(const T* __restrict__ src, unsigned rows, unsigned co
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   pdl_wait();
   const unsigned b = blockIdx.z;
-  const unsigned lane8 = threadIdx.x & 7u, rlane = threadIdx.x >> 3;
+  const unsigned lane8 = threadIdx.x % LANES, rlane = threadIdx.x / LANES;
   const unsigned col = blockIdx.y * CW + lane8 * V;
   const bool active = col < cols;
   const unsigned slab = (rows + kColsCluster - 1) / kColsCluster;
@@ -396,17 +400,17 @@ reduce_cols_cluster_kernel(const T* __restrict__ src, unsigned rows, unsigned co
     unsigned r = r0 + rlane;
     // full batches of U rows per thread, the next batch requested before this one is added
     // (a slab of more than 512 rows would otherwise pay one round of latency per batch)
-    if (r + (U - 1) * 32 < r1) {
+    if (r + (U - 1) * RL < r1) {
       uint4 w[U];
 #pragma unroll
-      for (unsigned u = 0; u < U; ++u) w[u] = __ldcs(p + static_cast<size_t>(r + u * 32) * pitch);
+      for (unsigned u = 0; u < U; ++u) w[u] = __ldcs(p + static_cast<size_t>(r + u * RL) * pitch);
       for (;;) {
-        const unsigned rn = r + U * 32;
-        const bool more = rn + (U - 1) * 32 < r1;
+        const unsigned rn = r + U * RL;
+        const bool more = rn + (U - 1) * RL < r1;
         uint4 nx[U];
         if (more) {
 #pragma unroll
-          for (unsigned u = 0; u < U; ++u) nx[u] = __ldcs(p + static_cast<size_t>(rn + u * 32) * pitch);
+          for (unsigned u = 0; u < U; ++u) nx[u] = __ldcs(p + static_cast<size_t>(rn + u * RL) * pitch);
         }
 #pragma unroll
         for (unsigned u = 0; u < U; ++u) {
@@ -420,7 +424,7 @@ reduce_cols_cluster_kernel(const T* __restrict__ src, unsigned rows, unsigned co
         for (unsigned u = 0; u < U; ++u) w[u] = nx[u];
       }
     }
-    for (; r < r1; r += 32) {
+    for (; r < r1; r += RL) {
       const uint4 w = __ldcs(p + static_cast<size_t>(r) * pitch);
       const T* e = reinterpret_cast<const T*>(&w);
 #pragma unroll
@@ -430,27 +434,41 @@ reduce_cols_cluster_kernel(const T* __restrict__ src, unsigned rows, unsigned co
 #pragma unroll
   for (unsigned v = 0; v < V; ++v) part[rlane][lane8 * V + v] = acc[v];
   __syncthreads();
-  int32_t s = 0;
-  if (threadIdx.x < CW) {
+  constexpr unsigned kPer = (CW + 255) / 256;  // columns per thread in the tree
+  int32_t s[kPer];
+#pragma unroll
+  for (unsigned j = 0; j < kPer; ++j) {
+    const unsigned c = threadIdx.x + j * 256;
+    s[j] = 0;
+    if (c < CW) {
 #pragma unroll 8
-    for (unsigned r = 0; r < 32; ++r) s += part[r][threadIdx.x];
+      for (unsigned r = 0; r < RL; ++r) s[j] += part[r][c];
+    }
   }
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-  if (threadIdx.x < CW) {
-    const uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(&gather[rank][threadIdx.x]));
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0u));
-    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(s) : "memory");
+#pragma unroll
+  for (unsigned j = 0; j < kPer; ++j) {
+    const unsigned c = threadIdx.x + j * 256;
+    if (c < CW) {
+      const uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(&gather[rank][c]));
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0u));
+      asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(s[j]) : "memory");
+    }
   }
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-  if (rank == 0 && threadIdx.x < CW) {
-    const unsigned c = blockIdx.y * CW + threadIdx.x;
-    if (c < cols) {
-      int32_t total = 0;
+  if (rank == 0) {
 #pragma unroll
-      for (int k = 0; k < kColsCluster; ++k) total += gather[k][threadIdx.x];
-      dst[static_cast<size_t>(b) * cols + c] = total;
+    for (unsigned j = 0; j < kPer; ++j) {
+      const unsigned cc = threadIdx.x + j * 256;
+      const unsigned c = blockIdx.y * CW + cc;
+      if (cc < CW && c < cols) {
+        int32_t total = 0;
+#pragma unroll
+        for (int k = 0; k < kColsCluster; ++k) total += gather[k][cc];
+        dst[static_cast<size_t>(b) * cols + c] = total;
+      }
     }
   }
 }
@@ -729,8 +747,15 @@ int reduce_sum(cudaStream_t stream, const T* src, unsigned batch, unsigned rows,
   if (batch > 65535) return TFCCB200_EOVERFLOW;
   if (cols % V == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0 &&
       (cols + 8 * V - 1) / (8 * V) <= 65535) {
+    cudaError_t ce;
+    const DeviceInfo* di = current_device_info(&ce);
+    if (!di) return static_cast<int>(ce);
+    // 512-byte row segments when that still leaves a CTA for every SM
+    const unsigned wide_blocks = (cols + 32 * V - 1) / (32 * V);
+    const bool wide = static_cast<unsigned long long>(wide_blocks) * kColsCluster * batch >=
+                      static_cast<unsigned long long>(di->sm_count);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(kColsCluster, (cols + 8 * V - 1) / (8 * V), batch);
+    cfg.gridDim = dim3(kColsCluster, wide ? wide_blocks : (cols + 8 * V - 1) / (8 * V), batch);
     cfg.blockDim = dim3(256, 1, 1);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -742,7 +767,8 @@ int reduce_sum(cudaStream_t stream, const T* src, unsigned batch, unsigned rows,
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, reduce_cols_cluster_kernel<T>, src, rows, cols, dst);
+    cudaError_t e = wide ? cudaLaunchKernelEx(&cfg, reduce_cols_cluster_kernel<T, 32>, src, rows, cols, dst)
+                         : cudaLaunchKernelEx(&cfg, reduce_cols_cluster_kernel<T, 8>, src, rows, cols, dst);
     if (e != cudaSuccess) return static_cast<int>(e);
     count_launch();
     return TFCCB200_OK;
