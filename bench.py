@@ -656,6 +656,38 @@ def extra_measurements(torch, pkg, dev, peaks, probes):
             tr, _ = time_graph_train(torch, [(lambda t=t: pkg.quantization.quantize_with_row_sums(
                 t, torch.uint8, mn, mx)) for t in xs])
             out["quantize_with_row_sums_256x4096"] = {"train_us": tr}
+            # the element-wise and row-wise kernels either side of the matmuls on operands of
+            # 64 Mi elements (256 MiB of float32, twice the L2): bytes that must move / time
+            n_big = 64 << 20
+            xb = torch.randn((16384, 4096), device=dev)
+            qb8 = torch.randint(0, 256, (16384, 4096), dtype=torch.uint8, device=dev)
+            qb32 = torch.randint(-(1 << 20), 1 << 20, (16384, 4096), dtype=torch.int32, device=dev)
+            xr = xb.view(65536, 1024)
+            res = torch.randn((65536, 1024), device=dev)
+            gam, bet = torch.ones(1024, device=dev), torch.zeros(1024, device=dev)
+            big_cases = (
+                ("minmax_f32", 4 * n_big, lambda: lib.tfccb200_minmax_f32(
+                    torch.cuda.current_stream().cuda_stream, xb.data_ptr(), n_big, mn_mx.data_ptr())),
+                ("quantize_f32_to_u8", 5 * n_big, lambda: pkg.quantization.quantize(xb, torch.uint8, mn, mx)),
+                ("quantize_with_row_sums_f32_to_u8", 5 * n_big,
+                 lambda: pkg.quantization.quantize_with_row_sums(xb, torch.uint8, mn, mx)),
+                ("dequantize_u8_to_f32", 5 * n_big, lambda: pkg.quantization.dequantize(qb8, mn, mx)),
+                ("requantize_s32_to_u8", 5 * n_big,
+                 lambda: pkg.quantization.requantize(qb32, mn, mx, mn, mx, torch.uint8)),
+                ("gelu_f32", 8 * n_big, lambda: pkg.nn.gelu(xb)),
+                ("softmax_65536x1024", 8 * n_big, lambda: pkg.nn.softmax(xr, 0.125)),
+                ("layer_norm_residual_65536x1024", 12 * n_big,
+                 lambda: pkg.nn.layer_norm(xr, gam, bet, 1e-5, residual=res)),
+            )
+            mn_mx = torch.empty(2, dtype=torch.float32, device=dev)
+            glue = {}
+            for nm, nbytes_moved, f in big_cases:
+                f()
+                tr, _ = time_graph_train(torch, [f] * 4)
+                glue[nm] = {"us": tr, "gbs": nbytes_moved / (tr * 1e-6) / 1e9,
+                            "hbm_frac": nbytes_moved / (tr * 1e-6) / 1e9 / peaks["hbm_gbs"]}
+            out["glue_kernels_on_64Mi_elements"] = glue
+            del xb, qb8, qb32, xr, res
             # the whole quantized operator on resident operands: row sums of A + matmul (the
             # column sums of the weight are a constant, computed once)
             def whole(o):

@@ -68,6 +68,52 @@ softmax_rows_kernel(const float* __restrict__ src, unsigned rows, unsigned cols,
   }
 }
 
+// The same with 128-bit loads and stores, for rows whose length is a multiple of 4 and whose
+// base is 16-byte aligned: a quarter of the memory instructions, and the division by the row
+// sum stays a division (the reference divides).
+template <int VECS>
+__global__ void __launch_bounds__(256)
+softmax_rows_vec_kernel(const float4* __restrict__ src, unsigned rows, unsigned vecs, float scale,
+                        float4* __restrict__ dst) {
+  pdl_release();
+  pdl_wait();
+  const unsigned row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const unsigned lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float4* p = src + static_cast<size_t>(row) * vecs;
+  constexpr float kLowest = -3.402823466e+38f;
+  float4 v[VECS];
+  float mx = kLowest;
+#pragma unroll
+  for (int i = 0; i < VECS; ++i) {
+    const unsigned c = lane + 32 * i;
+    if (c < vecs) {
+      const float4 t = __ldcs(p + c);
+      v[i] = make_float4(t.x * scale, t.y * scale, t.z * scale, t.w * scale);
+    } else {
+      v[i] = make_float4(kLowest, kLowest, kLowest, kLowest);
+    }
+    mx = fmaxf(fmaxf(mx, v[i].x), fmaxf(v[i].y, fmaxf(v[i].z, v[i].w)));
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < VECS; ++i) {
+    const unsigned c = lane + 32 * i;
+    if (c < vecs) {
+      v[i] = make_float4(expf(v[i].x - mx), expf(v[i].y - mx), expf(v[i].z - mx), expf(v[i].w - mx));
+      sum += v[i].x; sum += v[i].y; sum += v[i].z; sum += v[i].w;
+    }
+  }
+  sum = warp_sum(sum);
+  float4* q = dst + static_cast<size_t>(row) * vecs;
+#pragma unroll
+  for (int i = 0; i < VECS; ++i) {
+    const unsigned c = lane + 32 * i;
+    if (c < vecs) q[c] = make_float4(v[i].x / sum, v[i].y / sum, v[i].z / sum, v[i].w / sum);
+  }
+}
+
 // Any row length: one CTA per row, three passes over the row (it stays in L1/L2).
 __global__ void __launch_bounds__(256)
 softmax_long_rows_kernel(const float* __restrict__ src, unsigned cols, float scale,
@@ -349,6 +395,20 @@ unsigned flat_grid(size_t n, int sm_count) {
 int softmax_f32(cudaStream_t stream, const float* src, unsigned rows, unsigned cols, float scale,
                 float* dst) {
   const unsigned blocks = (rows + 7) / 8;
+  if (cols % 4 == 0 && cols >= 128 && cols <= 1024 &&
+      ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0) {
+    const unsigned vecs = cols / 4;
+#define TFCCB200_SOFTMAXV(V)                                                                  \
+  launch_after_previous(softmax_rows_vec_kernel<V>, dim3(blocks), dim3(256), 0, stream,       \
+                        reinterpret_cast<const float4*>(src), rows, vecs, scale,              \
+                        reinterpret_cast<float4*>(dst))
+    if (vecs <= 32) TFCCB200_SOFTMAXV(1);
+    else if (vecs <= 64) TFCCB200_SOFTMAXV(2);
+    else if (vecs <= 128) TFCCB200_SOFTMAXV(4);
+    else TFCCB200_SOFTMAXV(8);
+#undef TFCCB200_SOFTMAXV
+    return done();
+  }
 #define TFCCB200_SOFTMAX(P)                                                                   \
   launch_after_previous(softmax_rows_kernel<P>, dim3(blocks), dim3(256), 0, stream, src, rows, cols,  \
                         scale, dst)

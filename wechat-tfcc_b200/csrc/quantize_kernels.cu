@@ -65,6 +65,55 @@ __device__ __forceinline__ float key_float(unsigned k) {
   return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
 }
 
+// ---- element-wise skeleton -----------------------------------------------------------------
+// dst[i] = f(src[i]) for n elements.  These passes are bound by memory bandwidth, so the bulk
+// moves in the widest words both sides allow: a thread takes E = 16 / max(sizeof) adjacent
+// elements per step -- one 128-bit word on the wider side, 32 to 128 bits on the narrower --
+// consecutive threads take consecutive words (every warp instruction reads or writes one
+// contiguous run), and four steps' loads are requested before the first is used.  Pointers that
+// are not aligned to those words, and the ragged end, go element by element.
+template <int BYTES> struct WordOf;
+template <> struct WordOf<4> { using type = uint32_t; };
+template <> struct WordOf<8> { using type = uint2; };
+template <> struct WordOf<16> { using type = uint4; };
+
+template <class TI, class TO, class F>
+__device__ __forceinline__ void map_elements(const TI* __restrict__ src, TO* __restrict__ dst,
+                                             size_t n, F f) {
+  constexpr int kWide = sizeof(TI) > sizeof(TO) ? sizeof(TI) : sizeof(TO);
+  constexpr int E = 16 / kWide;
+  using WI = typename WordOf<E * sizeof(TI)>::type;
+  using WO = typename WordOf<E * sizeof(TO)>::type;
+  constexpr int U = 4;
+  const size_t tid = blockIdx.x * 256ull + threadIdx.x, stride = gridDim.x * 256ull;
+  size_t done = 0;
+  if ((reinterpret_cast<uintptr_t>(src) & (sizeof(WI) - 1)) == 0 &&
+      (reinterpret_cast<uintptr_t>(dst) & (sizeof(WO) - 1)) == 0) {
+    const size_t steps = n / E;
+    const WI* in = reinterpret_cast<const WI*>(src);
+    WO* out = reinterpret_cast<WO*>(dst);
+    auto convert = [&](const WI& w) {
+      WO o;
+      const TI* e = reinterpret_cast<const TI*>(&w);
+      TO* q = reinterpret_cast<TO*>(&o);
+#pragma unroll
+      for (int v = 0; v < E; ++v) q[v] = f(e[v]);
+      return o;
+    };
+    size_t i = tid;
+    for (; i + (U - 1) * stride < steps; i += U * stride) {
+      WI w[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) w[u] = __ldcs(in + i + u * stride);
+#pragma unroll
+      for (int u = 0; u < U; ++u) out[i + u * stride] = convert(w[u]);
+    }
+    for (; i < steps; i += stride) out[i] = convert(__ldcs(in + i));
+    done = steps * E;
+  }
+  for (size_t i = done + tid; i < n; i += stride) dst[i] = f(src[i]);
+}
+
 __global__ void minmax_init_kernel(unsigned* out) {
   out[0] = 0xffffffffu;  // larger than every key
   out[1] = 0u;
@@ -73,7 +122,27 @@ __global__ void minmax_init_kernel(unsigned* out) {
 __global__ void __launch_bounds__(256)
 minmax_reduce_kernel(const float* __restrict__ src, size_t n, unsigned* out) {
   float lo = 3.402823466e+38f, hi = -3.402823466e+38f;  // std::numeric_limits<float>::max / lowest
-  for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull) {
+  const size_t tid = blockIdx.x * 256ull + threadIdx.x, stride = gridDim.x * 256ull;
+  size_t done = 0;
+  if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {  // 128-bit loads, four in flight
+    const size_t steps = n / 4;
+    const float4* in = reinterpret_cast<const float4*>(src);
+    auto take = [&](const float4& v) {
+      lo = fminf(fminf(lo, v.x), fminf(v.y, fminf(v.z, v.w)));
+      hi = fmaxf(fmaxf(hi, v.x), fmaxf(v.y, fmaxf(v.z, v.w)));
+    };
+    size_t i = tid;
+    for (; i + 3 * stride < steps; i += 4 * stride) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = __ldcs(in + i + u * stride);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) take(v[u]);
+    }
+    for (; i < steps; i += stride) take(__ldcs(in + i));
+    done = steps * 4;
+  }
+  for (size_t i = done + tid; i < n; i += stride) {
     const float v = src[i];
     lo = fminf(lo, v);
     hi = fmaxf(hi, v);
@@ -139,9 +208,10 @@ quantize_kernel(const float* __restrict__ src, size_t n, const float* __restrict
   double scale = 0;
   long long offset = 0;
   if (!degenerate) quantized_scale_info<T>(mn, mx, &scale, &offset);
-  for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull)
-    dst[i] = degenerate ? static_cast<T>(Limits<T>::lo)
-                        : quantize_value<T>(static_cast<double>(src[i]), scale, offset);
+  map_elements(src, dst, n, [&](float v) {
+    return degenerate ? static_cast<T>(Limits<T>::lo)
+                      : quantize_value<T>(static_cast<double>(v), scale, offset);
+  });
 }
 
 // quantize with the row sums of the quantized values produced in the same pass: the
@@ -213,11 +283,11 @@ dequantize_kernel(const T* __restrict__ src, size_t n, const float* __restrict__
   const bool degenerate = mn >= mx;
   double scale = 0, min_rounded = 0;
   if (!degenerate) dequantized_scale_info<T>(mn, mx, &scale, &min_rounded);
-  for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull) {
-    const double off = static_cast<double>(src[i]) - static_cast<double>(Limits<T>::lo);
+  map_elements(src, dst, n, [&](T q) {
+    const double off = static_cast<double>(q) - static_cast<double>(Limits<T>::lo);
     // separate multiply and add, each rounded: the reference's expression is not fused
-    dst[i] = degenerate ? mn : static_cast<float>(__dadd_rn(min_rounded, __dmul_rn(off, scale)));
-  }
+    return degenerate ? mn : static_cast<float>(__dadd_rn(min_rounded, __dmul_rn(off, scale)));
+  });
 }
 
 template <class TI, class TO>
@@ -228,8 +298,7 @@ requantize_kernel(const TI* __restrict__ src, size_t n, const float* __restrict_
   const float min_in = *pmin_in, max_in = *pmax_in, min_out = *pmin_out, max_out = *pmax_out;
   // the three cases of _requantize_helper (tfcc/mkl/interfaces/tfcc_mklquantizationinterface.cpp:114-140)
   if (min_out >= max_out) {
-    for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull)
-      dst[i] = static_cast<TO>(Limits<TO>::lo);
+    map_elements(src, dst, n, [](TI) { return static_cast<TO>(Limits<TO>::lo); });
     return;
   }
   double in_scale, in_min, out_scale;
@@ -238,13 +307,13 @@ requantize_kernel(const TI* __restrict__ src, size_t n, const float* __restrict_
   quantized_scale_info<TO>(min_out, max_out, &out_scale, &out_offset);
   if (min_in >= max_in) {
     const TO q = quantize_value<TO>(static_cast<double>(min_in), out_scale, out_offset);
-    for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull) dst[i] = q;
+    map_elements(src, dst, n, [q](TI) { return q; });
     return;
   }
-  for (size_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += gridDim.x * 256ull) {
-    const double off = static_cast<double>(src[i]) - static_cast<double>(Limits<TI>::lo);
-    dst[i] = quantize_value<TO>(__dadd_rn(in_min, __dmul_rn(off, in_scale)), out_scale, out_offset);
-  }
+  map_elements(src, dst, n, [&](TI v) {
+    const double off = static_cast<double>(v) - static_cast<double>(Limits<TI>::lo);
+    return quantize_value<TO>(__dadd_rn(in_min, __dmul_rn(off, in_scale)), out_scale, out_offset);
+  });
 }
 
 unsigned grid_for(size_t n, int sm_count) {
