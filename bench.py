@@ -663,6 +663,8 @@ def extra_measurements(torch, pkg, dev, peaks, probes):
             qb8 = torch.randint(0, 256, (16384, 4096), dtype=torch.uint8, device=dev)
             qb32 = torch.randint(-(1 << 20), 1 << 20, (16384, 4096), dtype=torch.int32, device=dev)
             xr = xb.view(65536, 1024)
+            x4d, x3d = xb.view(64, 128, 128, 64), xb.view(1024, 256, 256)
+            xpan, xout = xb.view(8, 8192, 1024), torch.empty((8192, 8192), device=dev)
             res = torch.randn((65536, 1024), device=dev)
             gam, bet = torch.ones(1024, device=dev), torch.zeros(1024, device=dev)
             big_cases = (
@@ -674,6 +676,10 @@ def extra_measurements(torch, pkg, dev, peaks, probes):
                 ("dequantize_u8_to_f32", 5 * n_big, lambda: pkg.quantization.dequantize(qb8, mn, mx)),
                 ("requantize_s32_to_u8", 5 * n_big,
                  lambda: pkg.quantization.requantize(qb32, mn, mx, mn, mx, torch.uint8)),
+                ("permute_0213_64x128x128x64", 8 * n_big, lambda: pkg.nn.permute_0213(x4d)),
+                ("transpose_last2_1024x256x256", 8 * n_big, lambda: pkg.nn.transpose_last2(x3d)),
+                ("interleave_panels_8x8192x1024", 8 * n_big,
+                 lambda: pkg.parallel.interleave_panels(xpan, xout)),
                 ("gelu_f32", 8 * n_big, lambda: pkg.nn.gelu(xb)),
                 ("softmax_65536x1024", 8 * n_big, lambda: pkg.nn.softmax(xr, 0.125)),
                 ("layer_norm_residual_65536x1024", 12 * n_big,
@@ -687,7 +693,7 @@ def extra_measurements(torch, pkg, dev, peaks, probes):
                 glue[nm] = {"us": tr, "gbs": nbytes_moved / (tr * 1e-6) / 1e9,
                             "hbm_frac": nbytes_moved / (tr * 1e-6) / 1e9 / peaks["hbm_gbs"]}
             out["glue_kernels_on_64Mi_elements"] = glue
-            del xb, qb8, qb32, xr, res
+            del xb, qb8, qb32, xr, res, x4d, x3d, xpan, xout
             # the whole quantized operator on resident operands: row sums of A + matmul (the
             # column sums of the weight are a constant, computed once)
             def whole(o):
