@@ -50,6 +50,47 @@ def test_quantize_dequantize_all_types_match_oracle(pkg, orc, np_t):
     assert np.array_equal(back, orc.dequantize(want, wmn, wmx))
 
 
+@pytest.mark.parametrize("np_t", [np.int8, np.uint8, np.int16, np.uint16])
+@pytest.mark.parametrize("mn,mx", [(-1.0, 1.0), (-128.0, 127.0), (0.0, 255.0), (-3.7, 9.25), (0.001, 0.0625),
+                                   (-32768.0, 32767.0), (-1e-3, 1e6)])
+def test_quantize_at_and_around_rounding_ties(pkg, orc, np_t, mn, mx):
+    """round(real * scale) is half away from zero on the double-precision product.  Inputs placed
+    on the half-integers of the scaled axis and one to three float steps either side of them, the
+    integers themselves, zeros, denormals and values far outside the range (clamped): every
+    result must be the oracle's."""
+    bits = np.dtype(np_t).itemsize * 8
+    scale, _ = orc.quantized_scale_info(mn, mx, bits=bits)
+    lo_k, hi_k = int(np.floor(mn * scale)) - 3, int(np.ceil(mx * scale)) + 3
+    rng = np.random.default_rng(bits + int(abs(mn) * 10))
+    ks = np.unique(np.concatenate([np.arange(lo_k, min(hi_k, lo_k + 600)),
+                                   rng.integers(lo_k, hi_k + 1, 3000),
+                                   np.arange(max(lo_k, hi_k - 600), hi_k + 1)])).astype(np.float64)
+    base = ((ks + 0.5) / scale).astype(np.float32)
+    vals = [base]
+    up, down = base.copy(), base.copy()
+    for _ in range(3):
+        up = np.nextafter(up, np.float32(np.inf)).astype(np.float32)
+        down = np.nextafter(down, np.float32(-np.inf)).astype(np.float32)
+        vals += [up.copy(), down.copy()]
+    vals.append((ks / scale).astype(np.float32))  # the integers themselves
+    # (products beyond the 64-bit integers are left out: the reference's conversion of those is
+    # undefined behaviour)
+    far = np.array([0.0, -0.0, 1e-45, -1e-45, 1e-30, 1e9, -1e9, 12345.678, 4194303.9, -4194304.5,
+                    8388607.5], dtype=np.float32)
+    vals.append(far[np.abs(far.astype(np.float64) * scale) < 2.0 ** 60])
+    a = np.concatenate(vals).astype(np.float32)
+    a = np.concatenate([a, rng.uniform(mn - 1, mx + 1, (-a.size) % 64 + 640).astype(np.float32)])
+    a = a.reshape(-1, 64)
+    ta = torch.from_numpy(a).to(dev())
+    want = orc.quantize(a, np_t, mn, mx)[0]
+    got = pkg.quantization.quantize(ta, NP2T[np_t], s1(mn), s1(mx))
+    assert np.array_equal(got.cpu().numpy().view(np_t), want)
+    if np_t in (np.int8, np.uint8, np.int16):
+        q, sums = pkg.quantization.quantize_with_row_sums(ta, NP2T[np_t], s1(mn), s1(mx))
+        assert np.array_equal(q.cpu().numpy().view(np_t), want)
+        assert np.array_equal(sums.cpu().numpy(), want.astype(np.int64).sum(-1).astype(np.int32))
+
+
 def test_dequantize_requantize_known_answers(pkg, orc):
     a = torch.from_numpy(DEQUANT_IN).to(dev())
     got = pkg.quantization.dequantize(a, s1(-2.5), s1(3.4)).cpu().numpy()
