@@ -241,33 +241,56 @@ skinny_partial_kernel(const float* __restrict__ X, const float* __restrict__ W,
   }
 }
 
-// Adds the K slices in a fixed order (slice 0 first), then the bias.  Launched with
-// programmatic stream serialisation: it may start while the partial kernel drains, and
-// waits for that kernel's memory to be visible before it reads the partial sums.
+// Adds the K slices in a fixed order, then the bias.  Eight lanes share an output quad: lane j
+// adds slices j, j + 8, j + 16, ... (all its loads in flight together, two batches at most for
+// the slice counts the planner makes), then the eight sums meet in a shuffle tree -- always the
+// same order, so a result does not depend on the run.  (One thread per quad walking all the
+// slices paid one round of L2 latency per batch of 8 slices: ten rounds for a 4096 x 4096
+// weight.)  Launched with programmatic stream serialisation: it may start while the partial
+// kernel drains, and waits for that kernel's memory to be visible before it reads the sums.
+// LANES = 1 when there are outputs enough to fill the chip with one thread per quad.
+template <int LANES>
 __global__ void __launch_bounds__(128)
 skinny_reduce_kernel(const float* __restrict__ part, const float* __restrict__ bias,
                      float* __restrict__ Y, unsigned MN, unsigned N, unsigned kslices,
                      unsigned long long strideY, int activation) {
   const unsigned b = blockIdx.y;
-  const unsigned i = (blockIdx.x * 128 + threadIdx.x) * 4;
+  const unsigned lane = threadIdx.x % LANES;
+  const unsigned i = ((blockIdx.x * 128 + threadIdx.x) / LANES) * 4;
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (i >= MN) return;
-  const float* pp = part + static_cast<size_t>(b) * kslices * MN + i;
+  const bool live = i < MN;  // whole groups of eight lanes share i, and every lane shuffles
+  const float* pp = part + static_cast<size_t>(b) * kslices * MN + (live ? i : 0);
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
   constexpr unsigned U = 8;
-  unsigned k = 0;
-  for (; k + U <= kslices; k += U) {  // U independent loads in flight, summed in slice order
-    float4 v[U];
+  unsigned k = lane;
+  if (live) {
+    for (; k + (U - 1) * LANES < kslices; k += U * LANES) {
+      float4 v[U];
 #pragma unroll
-    for (unsigned u = 0; u < U; ++u)
-      v[u] = __ldcg(reinterpret_cast<const float4*>(pp + static_cast<size_t>(k + u) * MN));
+      for (unsigned u = 0; u < U; ++u)
+        v[u] = __ldcg(reinterpret_cast<const float4*>(pp + static_cast<size_t>(k + u * LANES) * MN));
 #pragma unroll
-    for (unsigned u = 0; u < U; ++u) { s.x += v[u].x; s.y += v[u].y; s.z += v[u].z; s.w += v[u].w; }
+      for (unsigned u = 0; u < U; ++u) { s.x += v[u].x; s.y += v[u].y; s.z += v[u].z; s.w += v[u].w; }
+    }
+    {
+      float4 v[U];
+#pragma unroll
+      for (unsigned u = 0; u < U; ++u)
+        v[u] = (k + u * LANES < kslices)
+                   ? __ldcg(reinterpret_cast<const float4*>(pp + static_cast<size_t>(k + u * LANES) * MN))
+                   : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (unsigned u = 0; u < U; ++u) { s.x += v[u].x; s.y += v[u].y; s.z += v[u].z; s.w += v[u].w; }
+    }
   }
-  for (; k < kslices; ++k) {
-    const float4 v = __ldcg(reinterpret_cast<const float4*>(pp + static_cast<size_t>(k) * MN));
-    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) {
+    s.x += __shfl_xor_sync(0xffffffffu, s.x, o);
+    s.y += __shfl_xor_sync(0xffffffffu, s.y, o);
+    s.z += __shfl_xor_sync(0xffffffffu, s.z, o);
+    s.w += __shfl_xor_sync(0xffffffffu, s.w, o);
   }
+  if (!live || lane != 0) return;
   if (bias) {
     const float4 bv = *reinterpret_cast<const float4*>(bias + (i % N));
     s.x += bv.x; s.y += bv.y; s.z += bv.z; s.w += bv.w;
@@ -603,7 +626,9 @@ int skinny_sgemm(const SgemmArgs& a) {
   if (e != cudaSuccess) return static_cast<int>(e);
   const unsigned MN = a.M * a.N;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((MN / 4 + 127) / 128, a.batch, 1);
+  // eight lanes per output quad unless one thread per quad already fills the chip
+  const bool wide = MN / 4 < 16384u;
+  cfg.gridDim = dim3(wide ? (MN / 4 + 15) / 16 : (MN / 4 + 127) / 128, a.batch, 1);
   cfg.blockDim = dim3(128, 1, 1);
   cfg.stream = a.stream;
   cudaLaunchAttribute attr[1];
@@ -617,8 +642,10 @@ int skinny_sgemm(const SgemmArgs& a) {
   unsigned n_c = a.N;
   unsigned long long stride_c = a.strideC;
   int act_c = a.activation;
-  e = cudaLaunchKernelEx(&cfg, skinny_reduce_kernel, part_c, bias_c, out_c, MN, n_c, ks, stride_c,
-                         act_c);
+  e = wide ? cudaLaunchKernelEx(&cfg, skinny_reduce_kernel<8>, part_c, bias_c, out_c, MN, n_c, ks,
+                                stride_c, act_c)
+           : cudaLaunchKernelEx(&cfg, skinny_reduce_kernel<1>, part_c, bias_c, out_c, MN, n_c, ks,
+                                stride_c, act_c);
   if (e != cudaSuccess) return static_cast<int>(e);
   count_launch(2);
   return TFCCB200_OK;
