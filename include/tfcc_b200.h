@@ -68,10 +68,10 @@ extern "C" {
 /* ---- kernel paths (for tests and benchmarks; AUTO is what TFCC uses) ----- */
 #define TFCCB200_PATH_AUTO 0
 #define TFCCB200_PATH_SIMT 1    /* CUDA-core tiled kernel, any shape / alignment          */
-#define TFCCB200_PATH_SKINNY 2  /* streaming kernel for few rows (M <= 32; AUTO: M <= 16)   */
+#define TFCCB200_PATH_SKINNY 2  /* streaming kernel for few rows (M <= 32; AUTO: M <= 16 and a B too large for path 5) */
 #define TFCCB200_PATH_UMMA 3    /* tcgen05 + TMEM + TMA, one CTA per tile                  */
 #define TFCCB200_PATH_UMMA2 4   /* tcgen05 cta_group::2, a pair of CTAs per 256-row tile    */
-#define TFCCB200_PATH_CLUSTER_SIMT 5 /* M <= 32, K <= 2048: CUDA cores, K split over a cluster */
+#define TFCCB200_PATH_CLUSTER_SIMT 5 /* M <= 32, K <= 2048: CUDA cores, one launch, K split over a cluster (AUTO: B up to 16 MB) */
 
 /* Bits a kernel ORs into *device_status when it abandons a bounded wait.     */
 #define TFCCB200_DEV_TIMEOUT_TMA 0x1
