@@ -246,15 +246,24 @@ quantize_rows_kernel(const float* __restrict__ src, unsigned rows, unsigned cols
     const bool vec = cols % 4 == 0 && (reinterpret_cast<uintptr_t>(p) & 15u) == 0 &&
                      (reinterpret_cast<uintptr_t>(q) & (4 * sizeof(T) - 1)) == 0;
     if (vec) {
-      for (unsigned i = t; i < cols / 4; i += TPR) {
-        const float4 v = __ldcs(reinterpret_cast<const float4*>(p) + i);
+      auto put = [&](unsigned i, const float4& v) {
         T r[4] = {one(v.x), one(v.y), one(v.z), one(v.w)};
         if constexpr (sizeof(T) == 1) {
           reinterpret_cast<uint32_t*>(q)[i] = *reinterpret_cast<const uint32_t*>(r);
         } else {
           reinterpret_cast<uint2*>(q)[i] = *reinterpret_cast<const uint2*>(r);
         }
+      };
+      const unsigned vecs = cols / 4;
+      unsigned i = t;
+      for (; i + 3 * TPR < vecs; i += 4 * TPR) {  // four loads requested before the first is used
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = __ldcs(reinterpret_cast<const float4*>(p) + i + u * TPR);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) put(i + u * TPR, v[u]);
       }
+      for (; i < vecs; i += TPR) put(i, __ldcs(reinterpret_cast<const float4*>(p) + i));
     } else {
       for (unsigned i = t; i < cols; i += TPR) q[i] = one(p[i]);
     }
