@@ -426,6 +426,7 @@ def library_probes(torch, dev, sustained_seconds=1.5):
         e1.record()
         torch.cuda.synchronize()
         out["tf32_tflops_sustained"] = flop * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12
+        out["tf32_sustained_loop_ms"] = e0.elapsed_time(e1)
         torch.backends.cuda.matmul.allow_tf32 = False
         t = burst(f, reps=5)
         out["cublas_fp32_8192"] = {"ms": t, "tflops": flop / (t * 1e-3) / 1e12,
@@ -1177,7 +1178,10 @@ def run_ours(args):
         d2h = 4 * M * N
         e2e_err = None
 
-    probes = library_probes(torch, dev) if not args.no_probe else {}
+    # the sustained probe runs as long as the timed region did (0.25 s at least), so that both
+    # have settled equally far under the power cap
+    probe_seconds = min(2.0, max(0.25, ms_total * 1e-3))
+    probes = library_probes(torch, dev, probe_seconds) if not args.no_probe else {}
 
     # ---- max over ranks
     t = torch.tensor([ms_total, e2e_s * 1e3, float(launches), e2e_err or 0.0],
