@@ -116,8 +116,9 @@ def test_skinny_decode_shapes(pkg, orc, m):
 
 def test_streaming_kernel_takes_config1(pkg, orc):
     """Config 1 (32 x 512 x 2048) through the streaming kernel, which can serve up to 32 rows
-    (the planner sends more than 16 rows to the tensor cores): fp32 FMA in k order, within the
-    fp32 tolerance like every other path."""
+    (left to itself the planner uses it up to 16 rows against a large B, and the one-launch
+    cluster kernel for this shape): fp32 FMA in k order, within the fp32 tolerance like every
+    other path."""
     rng = np.random.default_rng(0)
     a = rng.uniform(-1, 1, (32, 512)).astype(np.float32)
     b = rng.normal(0, 0.02, (512, 2048)).astype(np.float32)
