@@ -514,7 +514,7 @@ int tfccb200_group_sgemm_nsplit_host(tfccb200_group* g, const float* hA, const f
     g->b_elems = std::max(g->b_elems, need_b);
     g->c_elems = std::max(g->c_elems, need_c);
   }
-  NsplitHostRank r[8];
+  NsplitHostRank r[8] = {};
   for (unsigned i = 0; i < G; ++i) {
     r[i] = {};
     r[i].stream = g->stream[i];
