@@ -706,6 +706,13 @@ def extra_measurements(torch, pkg, dev, peaks, probes):
                 assert st == 0, st
             tr, _ = time_graph_train(torch, [(lambda o=o: whole(o)) for o in ops])
             out["cfg3_operator_rsA_plus_matmul"] = {"train_us": tr}
+            # the operator as the plugin runs it: the (min, max) ranges are tensors in device
+            # memory, the offsets and the result range are derived on the device in front of the
+            # product (tfccb200_qgemm_u8s8s32_dev)
+            fmin, fmax = torch.tensor([-128.0], device=dev), torch.tensor([127.0], device=dev)
+            tr, _ = time_graph_train(torch, [(lambda o=o: pkg.quantization.matmul(
+                o[0], o[2], fmin, fmax, o[1], o[3], fmin, fmax)) for o in ops])
+            out["cfg3_int8_M256_device_ranges"] = {"train_us": tr}
         del ops, calls
     # int8 at the headline size: u8[8192,8192] x s8[8192,8192] -> s32 (13.8 waves of pair tiles)
     n8 = 8192

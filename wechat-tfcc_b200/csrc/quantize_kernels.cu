@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 
 #include "internal.h"
+#include "pdl.cuh"
 
 namespace tfccb200 {
 
@@ -185,6 +186,10 @@ __global__ void qmatmul_params_kernel(const float* __restrict__ minA, const floa
                                       const float* __restrict__ minB, const float* __restrict__ maxB,
                                       int32_t* __restrict__ offsets, float* __restrict__ minC,
                                       float* __restrict__ maxC) {
+  // one thread in front of the product: it is launched to overlap the tail of the kernel before
+  // it, and lets the product's own preamble (barriers, tensor memory) run beside it
+  pdl_release();
+  pdl_wait();
   double scale;
   long long off;
   quantized_scale_info<uint8_t>(*minA, *maxA, &scale, &off);
@@ -381,7 +386,9 @@ int quantize_f32(cudaStream_t stream, const float* src, size_t n, const float* p
 int quantized_matmul_params_dev(cudaStream_t stream, const float* minA, const float* maxA,
                                 const float* minB, const float* maxB, int32_t* offsets,
                                 float* minC, float* maxC) {
-  qmatmul_params_kernel<<<1, 1, 0, stream>>>(minA, maxA, minB, maxB, offsets, minC, maxC);
+  cudaError_t e = launch_after_previous(qmatmul_params_kernel, dim3(1), dim3(1), 0, stream, minA, maxA,
+                                        minB, maxB, offsets, minC, maxC);
+  if (e != cudaSuccess) return static_cast<int>(e);
   return finish(1);
 }
 

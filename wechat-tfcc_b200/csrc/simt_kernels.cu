@@ -343,6 +343,7 @@ reduce_rows_kernel(const T* __restrict__ src, unsigned total_rows, unsigned cols
   constexpr unsigned V = 16 / sizeof(T);
   constexpr int kRowsPerCta = 256 / TPR;
   __shared__ int32_t warp_sums[8];
+  pdl_release();  // the product that follows may run its preamble beside this
   pdl_wait();
   const unsigned row = blockIdx.x * kRowsPerCta + threadIdx.x / TPR;
   const unsigned t = threadIdx.x % TPR;
@@ -404,6 +405,7 @@ reduce_cols_cluster_kernel(const T* __restrict__ src, unsigned rows, unsigned co
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
   // every CTA of the cluster is running before anyone writes into a peer's shared memory
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  pdl_release();
   pdl_wait();
   const unsigned b = blockIdx.z;
   const unsigned lane8 = threadIdx.x % LANES, rlane = threadIdx.x / LANES;
